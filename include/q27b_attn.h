@@ -1,0 +1,144 @@
+/* q27b_attn: B200 (sm_100a) attention hot path for qwen27-engine, C ABI.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle (passed as
+ * void*, it is a cudaStream_t / CUstream). Work is enqueued on that stream on the device that
+ * is current at call time; nothing synchronises with the host. All entry points return a
+ * status code (0 = ok); q27b_last_error() gives the text of the last failure on the calling
+ * thread. No exception crosses this boundary.
+ *
+ * Each declaration names the interface of the reference engine that it replaces
+ * (file:line in avallavall/qwen27-engine).
+ *
+ * Fixed model constants (reference src/attn.cu:22-28): head dim 256, 6 query heads per KV
+ * head, at most 4 query tokens per decode call.
+ *
+ * Memory: the caller owns every buffer that it passes. The library keeps one lazily allocated
+ * workspace per device (split partials, a status word), grown only when a call needs more than
+ * any earlier call on that device did; run every shape class once before capturing a CUDA
+ * graph (the reference's Decoder::warmup does the same, src/model.cu:910-931).
+ * Threading: one caller thread per device at a time (as the reference, src/attn.cu:869-879).
+ */
+#ifndef Q27B_ATTN_H_
+#define Q27B_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define Q27B_OK 0
+#define Q27B_BAD_SHAPE 1      /* the reference throws "bad shape" here (src/attn.cu:906,929) */
+#define Q27B_CUDA_ERROR 2     /* a CUDA runtime / driver call failed (the reference's CK(), src/common.cuh:12-13) */
+#define Q27B_UNSUPPORTED 3
+#define Q27B_DEVICE_STATUS 4  /* a kernel recorded a bounded wait that ran out */
+
+#define Q27B_HEAD_DIM 256
+#define Q27B_GQA 6
+#define Q27B_MAX_T 4
+#define Q27B_PART_ROW 258 /* floats of one partial row: max, sum, unnormalised O[256] (src/attn.cu:26) */
+#define Q27B_PAGE 256     /* positions per page of the paged cache */
+
+/* Text of the last error on this thread ("" if none). */
+const char* q27b_last_error(void);
+
+/* Reads (and clears) the device status word of the current device. Synchronises the device:
+ * call it after your own synchronisation point. 0 = no kernel reported a problem. */
+int q27b_device_status(int* status_out);
+
+/* Bytes of the K (or V) cache of one layer. q8_0 (q8 != 0): int8 values [nkvh][n_ctx][256]
+ * followed by f16 scales [nkvh][n_ctx][8]; else f16 [nkvh][n_ctx][256].
+ * Replaces q27::kv_cache_bytes (src/ops.h:53, src/attn.cu:890-892). */
+uint64_t q27b_kv_cache_bytes(int nkvh, int n_ctx, int q8);
+
+/* Position chunks per KV head used by the decode kernel on the current device.
+ * Replaces q27::attn_chunks (src/ops.h:77, src/attn.cu:883-888). */
+int q27b_attn_chunks(int nkvh);
+
+/* Append T tokens' K and V rows (k, v: f32 [T][nkvh][256]) at cache rows *pos0 + t, quantised
+ * to q8_0 (d = amax/127 per 32 values, q = round(x/d), f16 scale) or rounded to f16.
+ * pos0 is read on the device. Replaces the cache-write tail of q27::attn_prep
+ * (src/ops.h:59-62, attn_prep_kernel src/ops.cu:628-652). */
+int q27b_kv_append(const float* k, const float* v, void* kcache, void* vcache, const int* pos0, int T, int nkvh,
+                   int n_ctx, int q8, void* stream);
+
+/* Full q27::attn_prep (src/ops.h:54-62, src/ops.cu:587-654,798-803): per-head RMSNorm of q and
+ * k, NeoX RoPE on the first 64 dims (IMRoPE sections), q -> qn [T][nqh][256], K and V -> cache
+ * rows *pos0 + t. rope3 / rdelta may be null. The reference's pf / pf_bytes L2-prefetch hint
+ * has no counterpart (the shim ignores it). */
+int q27b_attn_prep(const float* qg, const float* k, const float* v, const float* q_norm, const float* k_norm,
+                   float* qn, void* kcache, void* vcache, const int* pos0, int T, float eps, float theta_scale,
+                   int nqh, int nkvh, int n_ctx, int q8, void* stream, const int* rope3, const int* rdelta);
+
+/* Decode attention of T = 1..4 query tokens at positions *pos0 + t over cache rows
+ * 0 .. *pos0 + t (causal inside the block), GQA 6:1, then o *= sigmoid(gate).
+ * qn [T][nqh][256], qg [T][nqh][512] (gate in the second half of each 512), o [T][nqh][256] f32.
+ * With xq != null the result goes to q8_1 (xq int8 [T*nqh*256], xd f32 [T*nqh*8]) instead of o.
+ * Replaces q27::attn_decode (src/ops.h:63-67, src/attn.cu:894-918). */
+int q27b_attn_decode(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o, int8_t* xq,
+                     float* xd, const int* pos0, int T, float kq_scale, int nqh, int nkvh, int n_ctx, int q8,
+                     void* stream);
+
+/* Same attention, restricted to the cache rows that this GPU holds when one sequence is split
+ * by KV length across GPUs: local cache row i is global position base_pos + i, rows
+ * 0 .. n_local-1 are attended (a row is visible to token t iff its global position is
+ * <= *pos0 + t). Output is not normalised: part [T][nqh][258] = (max, sum, O[256]) per row,
+ * ready for q27b_lse_merge. Extends the per-chunk partials of attn_mma_kernel
+ * (src/attn.cu:115-120,286-289) to a per-GPU partial; the reference has no multi-GPU split. */
+int q27b_attn_decode_partial(const float* qn, const void* kcache, const void* vcache, float* part, const int* pos0,
+                             int T, float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos, int n_local,
+                             void* stream);
+
+/* Log-sum-exp merge of nparts partials of `rows` rows (partial c, row r at
+ * part + c*part_stride + r*258 floats): M = max m, L = sum l e^(m-M), A = sum O e^(m-M),
+ * y = A/L * sigmoid(gate) with the gate of row r at qg + r*512 + 256 (qg null: no gate).
+ * Output f32 o [rows][256], or q8_1 (xq, xd) when xq != null.
+ * Replaces attn_combine_kernel (src/attn.cu:294-316) and attn_pf_combine_kernel
+ * (src/attn.cu:803-822). */
+int q27b_lse_merge(const float* part, int nparts, int64_t part_stride, int64_t rows, const float* qg, float* o,
+                   int8_t* xq, float* xd, void* stream);
+
+/* Batched decode over a paged q8_0 cache: B sequences, T query tokens each at positions
+ * seq_len[b] - T + t (seq_len counts the T new tokens, whose K/V are already in the cache).
+ * Pool layout (K and V each): int8 values [n_pages][nkvh][256][256] followed by f16 scales
+ * [n_pages][nkvh][256][8]; page_table [B][max_pages] int32 (page j of sequence b holds its
+ * positions 256*j .. 256*j+255); seq_len int32 [B] on the device.
+ * qn [B][T][nqh][256], qg [B][T][nqh][512], o [B][T][nqh][256].
+ * The reference is single-sequence with one contiguous cache (src/model.cu:462-472); this is
+ * the same operator (src/ops.h:63-67) applied per sequence through a page table. */
+int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, const void* vpool,
+                           const int* page_table, const int* seq_len, float* o, int B, int T, float kq_scale, int nqh,
+                           int nkvh, int n_pages, int max_pages, int max_seq_len, void* stream);
+
+/* Measurement hook, no counterpart in the reference: while `event` (a cudaEvent_t) is set, every
+ * q27b_attn_decode / q27b_attn_decode_partial call on the current device records it on the
+ * caller's stream between its split-K kernel and its merge kernel, so that a benchmark can time
+ * the dominant kernel alone with CUDA events. NULL switches it off. */
+int q27b_debug_split_event(void* event);
+
+/* Bytes of the K (or V) page pool of q27b_attn_decode_paged. */
+uint64_t q27b_kv_pool_bytes(int nkvh, int n_pages);
+
+/* Prefill attention: M query tokens at positions *pos0 .. *pos0+M-1 (their K/V already in the
+ * cache), causal, o [M][nqh][256] f32 with the gate applied. q8_0 cache: Q K^T on the int8
+ * tensor path (Q rounded to int8 with an f32 scale per 32 dims, K = the cache bytes, one int32
+ * dot product per 32-dim block, scaled and summed in f32), P V in f16 with f32 accumulation.
+ * depth_hint: host copy of *pos0 or -1. Replaces q27::attn_prefill (src/ops.h:68-72,
+ * src/attn.cu:920-974; kernel attn_prefill_i8_kernel src/attn.cu:557-801). */
+int q27b_attn_prefill(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
+                      const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, int q8, void* stream,
+                      int depth_hint);
+
+/* Test hook of the prefill kernel's integer stage: quantises `rows` (<= 128) query rows
+ * (x [rows][256] f32, already the rows of one head) as the prefill kernel does and multiplies
+ * them on the int8 tensor path with npos (<= 64) K rows taken from a q8_0 cache (head kh,
+ * first row p0). Outputs: q_i8 [rows][256], q_scale [rows][8] f32, acc [rows][npos][8] int32
+ * (the per-32-block accumulators of src/attn.cu:690-691, which must be bit-exact). */
+int q27b_prefill_qk_debug(const float* x, int rows, float kq_scale, const void* kcache, int nkvh, int n_ctx, int kh,
+                          int p0, int npos, int8_t* q_i8, float* q_scale, int32_t* acc, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q27B_ATTN_H_ */

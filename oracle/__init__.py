@@ -1,0 +1,152 @@
+"""ctypes bindings of the CPU oracle (oracle/attn_oracle.cpp) on numpy arrays.
+
+Test infrastructure only: imported by tests/, the smoke check and the cpu_baseline leg of the
+benchmark. The shipped package never imports this module.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+from . import build as _build
+
+AD = 256
+GQA = 6
+PROW = AD + 2
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = _build.ORACLE_SO
+        if not os.path.exists(path):
+            path = _build.build_oracle()
+        _lib = ctypes.CDLL(path)
+        _lib.orc_kv_cache_bytes.restype = ctypes.c_uint64
+    return _lib
+
+
+def _p(a):
+    return ctypes.c_void_p(a.ctypes.data) if a is not None else ctypes.c_void_p(0)
+
+
+def _c(a, dt):
+    a = np.ascontiguousarray(a, dtype=dt)
+    return a
+
+
+def num_threads():
+    return int(lib().orc_num_threads())
+
+
+def kv_cache_bytes(nkvh, n_ctx, q8=True):
+    return int(lib().orc_kv_cache_bytes(nkvh, n_ctx, int(q8)))
+
+
+def quant_q8_0(x):
+    """x [..., 256] f32 -> (int8 [..., 256], f16-bit scales uint16 [..., 8])."""
+    x = _c(x, np.float32)
+    rows = x.size // AD
+    q = np.empty(x.shape, np.int8)
+    d = np.empty(x.shape[:-1] + (8,), np.uint16)
+    lib().orc_quant_q8_0(_p(x), ctypes.c_int64(rows), _p(q), _p(d))
+    return q, d
+
+
+def new_cache(nkvh, n_ctx, q8=True, fill=0):
+    return np.full(kv_cache_bytes(nkvh, n_ctx, q8), fill, np.uint8)
+
+
+def kv_append(k, v, kcache, vcache, pos0, nkvh, n_ctx, q8=True):
+    """k, v [T][nkvh][256] f32 written in place at cache rows pos0 + t."""
+    k = _c(k, np.float32)
+    v = _c(v, np.float32)
+    T = k.shape[0]
+    assert pos0 >= 0 and pos0 + T <= n_ctx
+    lib().orc_kv_append(_p(k), _p(v), _p(kcache), _p(vcache), int(pos0), int(T), int(nkvh), int(n_ctx), int(q8))
+
+
+def fill_cache(kf, vf, n_ctx, q8=True):
+    """kf, vf [nkvh][n][256] f32 -> (kcache, vcache) byte arrays with rows 0..n-1 filled."""
+    nkvh, n = kf.shape[0], kf.shape[1]
+    kc, vc = new_cache(nkvh, n_ctx, q8), new_cache(nkvh, n_ctx, q8)
+    for src, c in ((kf, kc), (vf, vc)):
+        if q8:
+            q, d = quant_q8_0(src)
+            c[: nkvh * n_ctx * AD].reshape(nkvh, n_ctx, AD)[:, :n] = q.view(np.uint8)
+            c[nkvh * n_ctx * AD:].view(np.uint16).reshape(nkvh, n_ctx, 8)[:, :n] = d
+        else:
+            c.view(np.float16).reshape(nkvh, n_ctx, AD)[:, :n] = src.astype(np.float16)
+    return kc, vc
+
+
+def q8_1(y):
+    y = _c(y, np.float32)
+    xq = np.empty(y.shape, np.int8)
+    xd = np.empty(y.size // 32, np.float32)
+    lib().orc_q8_1(_p(y), ctypes.c_int64(y.size), _p(xq), _p(xd))
+    return xq, xd
+
+
+def attn_ref(qn, qg, kcache, vcache, pos0, kq_scale, nkvh, n_ctx, q8=True):
+    """qn [T][nqh][256], qg [T][nqh][512] -> o [T][nqh][256] (decode numerics)."""
+    qn = _c(qn, np.float32)
+    qg = _c(qg, np.float32)
+    T, nqh = qn.shape[0], qn.shape[1]
+    assert nqh == nkvh * GQA and pos0 + T <= n_ctx
+    o = np.empty((T, nqh, AD), np.float32)
+    lib().orc_attn_ref(_p(qn), _p(qg), _p(kcache), _p(vcache), _p(o), int(pos0), int(T), ctypes.c_float(kq_scale),
+                       int(nqh), int(nkvh), int(n_ctx), int(q8))
+    return o
+
+
+def attn_partial(qn, kcache, vcache, pos0, kq_scale, nkvh, n_ctx, p_lo, p_hi, q8=True):
+    """(m, l, O) partial [T][nqh][258] over positions [p_lo, p_hi)."""
+    qn = _c(qn, np.float32)
+    T, nqh = qn.shape[0], qn.shape[1]
+    part = np.zeros((T, nqh, PROW), np.float32)
+    lib().orc_attn_partial(_p(qn), _p(kcache), _p(vcache), _p(part), int(pos0), int(T), ctypes.c_float(kq_scale),
+                           int(nqh), int(nkvh), int(n_ctx), int(q8), int(p_lo), int(p_hi))
+    return part
+
+
+def lse_merge(parts, qg=None):
+    """parts [nparts][rows...][258]; qg [rows...][512] or None -> o [rows...][256]."""
+    parts = _c(parts, np.float32)
+    nparts = parts.shape[0]
+    rows = parts[0].size // PROW
+    o = np.empty(parts.shape[1:-1] + (AD,), np.float32)
+    g = _c(qg, np.float32) if qg is not None else None
+    lib().orc_lse_merge(_p(parts), int(nparts), ctypes.c_int64(rows * PROW), ctypes.c_int64(rows), _p(g), _p(o))
+    return o
+
+
+def quant_q_i8(x, kq_scale):
+    x = _c(x, np.float32)
+    q = np.empty(x.shape, np.int8)
+    d = np.empty(x.shape[:-1] + (8,), np.float32)
+    lib().orc_quant_q_i8(_p(x), ctypes.c_int64(x.size // AD), ctypes.c_float(kq_scale), _p(q), _p(d))
+    return q, d
+
+
+def qk_i32(q, k):
+    """q [rows][256] int8, k [npos][256] int8 -> int32 [rows][npos][8] block dot products."""
+    q = _c(q, np.int8)
+    k = _c(k, np.int8)
+    out = np.empty((q.shape[0], k.shape[0], 8), np.int32)
+    lib().orc_qk_i32(_p(q), _p(k), int(q.shape[0]), int(k.shape[0]), _p(out))
+    return out
+
+
+def attn_prefill_i8(qn, qg, kcache, vcache, pos0, kq_scale, nkvh, n_ctx, t_lo=0, t_hi=None):
+    """qn [M][nqh][256], qg [M][nqh][512] -> o [M][nqh][256]; only tokens [t_lo, t_hi) are filled."""
+    qn = _c(qn, np.float32)
+    qg = _c(qg, np.float32)
+    M, nqh = qn.shape[0], qn.shape[1]
+    t_hi = M if t_hi is None else t_hi
+    o = np.zeros((M, nqh, AD), np.float32)
+    lib().orc_attn_prefill_i8(_p(qn), _p(qg), _p(kcache), _p(vcache), _p(o), int(pos0), int(M),
+                              ctypes.c_float(kq_scale), int(nqh), int(nkvh), int(n_ctx), int(t_lo), int(t_hi))
+    return o

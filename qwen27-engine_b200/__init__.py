@@ -1,0 +1,171 @@
+"""Host-side mirror of the reference's attention operators over the q27b_attn C ABI.
+
+The functions carry the names, argument order and error behaviour of the reference's operator
+layer (namespace q27, src/ops.h:50-77: kv_cache_bytes, attn_prep, attn_decode, attn_prefill,
+attn_chunks), so that a test written against the reference reads the same here. Arguments are
+torch CUDA tensors (torch is used for device memory and streams only); every call forwards the
+raw device pointers to libq27b_attn.so and raises RuntimeError where the reference throws
+std::runtime_error. There is no CPU path: if the library cannot be loaded the import fails.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libq27b_attn.so")
+
+HEAD_DIM = 256
+GQA = 6
+MAX_T = 4
+PART_ROW = 258
+PAGE = 256
+
+OK, BAD_SHAPE, CUDA_ERROR, UNSUPPORTED, DEVICE_STATUS = 0, 1, 2, 3, 4
+
+# Every symbol that include/q27b_attn.h declares.
+SYMBOLS = [
+    "q27b_last_error", "q27b_device_status", "q27b_kv_cache_bytes", "q27b_attn_chunks", "q27b_kv_append",
+    "q27b_attn_prep", "q27b_attn_decode", "q27b_attn_decode_partial", "q27b_lse_merge", "q27b_attn_decode_paged",
+    "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event",
+]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "libq27b_attn.so is not built (run `python qwen27-engine_b200/build.py`); there is no fallback path")
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.q27b_last_error.restype = ctypes.c_char_p
+    lib.q27b_kv_cache_bytes.restype = ctypes.c_uint64
+    lib.q27b_kv_pool_bytes.restype = ctypes.c_uint64
+    return lib
+
+
+_lib = _load()
+
+
+class Q27Error(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("q27b_attn error %d: %s" % (code, msg))
+        self.code = code
+
+
+def _check(rc):
+    if rc != 0:
+        raise Q27Error(rc, _lib.q27b_last_error().decode())
+
+
+def _ptr(t, dtype=None, optional=False):
+    if t is None:
+        if not optional:
+            raise Q27Error(BAD_SHAPE, "null tensor")
+        return ctypes.c_void_p(0)
+    if not t.is_cuda or not t.is_contiguous():
+        raise Q27Error(BAD_SHAPE, "tensors must be contiguous CUDA tensors")
+    if dtype is not None and t.dtype != dtype:
+        raise Q27Error(BAD_SHAPE, "expected dtype %s, got %s" % (dtype, t.dtype))
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _f(x):
+    return ctypes.c_float(x)
+
+
+def kv_cache_bytes(nkvh, n_ctx, q8=True):
+    """q27::kv_cache_bytes (src/ops.h:53)."""
+    return int(_lib.q27b_kv_cache_bytes(int(nkvh), int(n_ctx), int(bool(q8))))
+
+
+def kv_pool_bytes(nkvh, n_pages):
+    return int(_lib.q27b_kv_pool_bytes(int(nkvh), int(n_pages)))
+
+
+def attn_chunks(nkvh):
+    """q27::attn_chunks (src/ops.h:77)."""
+    return int(_lib.q27b_attn_chunks(int(nkvh)))
+
+
+def device_status():
+    """Synchronises the device; returns the status word (0 = fine) and clears it."""
+    st = ctypes.c_int(0)
+    rc = _lib.q27b_device_status(ctypes.byref(st))
+    if rc not in (OK, DEVICE_STATUS):
+        _check(rc)
+    return st.value
+
+
+def debug_split_event(event):
+    """event: a recorded-at-least-once torch.cuda.Event (timing enabled) or None."""
+    _check(_lib.q27b_debug_split_event(ctypes.c_void_p(event.cuda_event if event is not None else 0)))
+
+
+def new_cache(nkvh, n_ctx, q8=True, device="cuda", fill=0):
+    """Zero-filled K (or V) cache of one layer, as the reference allocates it (src/model.cu:441-446)."""
+    return torch.full((kv_cache_bytes(nkvh, n_ctx, q8),), fill, dtype=torch.uint8, device=device)
+
+
+def kv_append(k, v, kcache, vcache, pos0, T, nkvh, n_ctx, q8=True):
+    """K/V rows [T][nkvh][256] f32 -> cache rows *pos0 + t (the cache-write tail of q27::attn_prep)."""
+    _check(_lib.q27b_kv_append(_ptr(k, torch.float32), _ptr(v, torch.float32), _ptr(kcache), _ptr(vcache),
+                               _ptr(pos0, torch.int32), int(T), int(nkvh), int(n_ctx), int(bool(q8)), _stream()))
+
+
+def attn_prep(qg, k, v, q_norm, k_norm, qn, kcache, vcache, pos0, T, eps, theta_scale, nqh, nkvh, n_ctx, q8=True,
+              rope3=None, rdelta=None):
+    """q27::attn_prep (src/ops.h:59-62)."""
+    _check(_lib.q27b_attn_prep(_ptr(qg, torch.float32), _ptr(k, torch.float32), _ptr(v, torch.float32),
+                               _ptr(q_norm, torch.float32), _ptr(k_norm, torch.float32), _ptr(qn, torch.float32),
+                               _ptr(kcache), _ptr(vcache), _ptr(pos0, torch.int32), int(T), _f(eps), _f(theta_scale),
+                               int(nqh), int(nkvh), int(n_ctx), int(bool(q8)), _stream(),
+                               _ptr(rope3, torch.int32, True), _ptr(rdelta, torch.int32, True)))
+
+
+def attn_decode(qn, qg, kcache, vcache, o, xq, xd, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8=True):
+    """q27::attn_decode (src/ops.h:66-67). With xq given the result goes to q8_1 (xq, xd) instead of o."""
+    _check(_lib.q27b_attn_decode(_ptr(qn, torch.float32), _ptr(qg, torch.float32), _ptr(kcache), _ptr(vcache),
+                                 _ptr(o, torch.float32, True), _ptr(xq, torch.int8, True),
+                                 _ptr(xd, torch.float32, True), _ptr(pos0, torch.int32), int(T), _f(kq_scale),
+                                 int(nqh), int(nkvh), int(n_ctx), int(bool(q8)), _stream()))
+
+
+def attn_decode_partial(qn, kcache, vcache, part, pos0, T, kq_scale, nqh, nkvh, n_ctx, base_pos, n_local, q8=True):
+    """Unnormalised (m, l, O) [T][nqh][258] over the local cache rows of a KV-length shard."""
+    _check(_lib.q27b_attn_decode_partial(_ptr(qn, torch.float32), _ptr(kcache), _ptr(vcache),
+                                         _ptr(part, torch.float32), _ptr(pos0, torch.int32), int(T), _f(kq_scale),
+                                         int(nqh), int(nkvh), int(n_ctx), int(bool(q8)), int(base_pos), int(n_local),
+                                         _stream()))
+
+
+def lse_merge(part, nparts, part_stride, rows, qg, o, xq=None, xd=None):
+    """Log-sum-exp merge of partials (attn_combine_kernel / attn_pf_combine_kernel of the reference)."""
+    _check(_lib.q27b_lse_merge(_ptr(part, torch.float32), int(nparts), ctypes.c_int64(part_stride),
+                               ctypes.c_int64(rows), _ptr(qg, torch.float32, True), _ptr(o, torch.float32, True),
+                               _ptr(xq, torch.int8, True), _ptr(xd, torch.float32, True), _stream()))
+
+
+def attn_decode_paged(qn, qg, kpool, vpool, page_table, seq_len, o, B, T, kq_scale, nqh, nkvh, n_pages, max_pages,
+                      max_seq_len):
+    """Batched decode over a paged q8_0 cache (256-position pages)."""
+    _check(_lib.q27b_attn_decode_paged(_ptr(qn, torch.float32), _ptr(qg, torch.float32), _ptr(kpool), _ptr(vpool),
+                                       _ptr(page_table, torch.int32), _ptr(seq_len, torch.int32),
+                                       _ptr(o, torch.float32), int(B), int(T), _f(kq_scale), int(nqh), int(nkvh),
+                                       int(n_pages), int(max_pages), int(max_seq_len), _stream()))
+
+
+def attn_prefill(qn, qg, kcache, vcache, o, pos0, M, kq_scale, nqh, nkvh, n_ctx, q8=True, depth_hint=-1):
+    """q27::attn_prefill (src/ops.h:71-72)."""
+    _check(_lib.q27b_attn_prefill(_ptr(qn, torch.float32), _ptr(qg, torch.float32), _ptr(kcache), _ptr(vcache),
+                                  _ptr(o, torch.float32), _ptr(pos0, torch.int32), int(M), _f(kq_scale), int(nqh),
+                                  int(nkvh), int(n_ctx), int(bool(q8)), _stream(), int(depth_hint)))
+
+
+def prefill_qk_debug(x, rows, kq_scale, kcache, nkvh, n_ctx, kh, p0, npos, q_i8, q_scale, acc):
+    """Integer stage of the prefill kernel on one tile (test hook)."""
+    _check(_lib.q27b_prefill_qk_debug(_ptr(x, torch.float32), int(rows), _f(kq_scale), _ptr(kcache), int(nkvh),
+                                      int(n_ctx), int(kh), int(p0), int(npos), _ptr(q_i8, torch.int8),
+                                      _ptr(q_scale, torch.float32), _ptr(acc, torch.int32), _stream()))

@@ -1,0 +1,121 @@
+// Log-sum-exp merge of split partials (m, l, O[256]) -> normalised, gated output.
+//
+// Replaces attn_combine_kernel (src/attn.cu:294-316) and attn_pf_combine_kernel
+// (src/attn.cu:803-822) of the reference: M = max m_c, L = sum l_c e^(m_c - M),
+// A = sum O_c e^(m_c - M), y = (A / L) * sigmoid(gate); partials are added in index order, so
+// the result does not depend on scheduling. One CTA per output row, one thread per dim; the
+// factors e^(m_c - M) are computed once per CTA into shared memory, then every thread streams
+// its column of the partials with independent loads. Built without fast-math: the q8_1 epilogue
+// (q8_store, src/common.cuh:72-81) is specified in IEEE operations.
+#include "combine.h"
+
+#include "common.cuh"
+
+namespace q27b {
+namespace {
+
+constexpr int MAX_PARTS = 1024;
+
+// Where row `row` finds its partials and its gate.
+struct RowMap {
+  const float* first;  // partial 0 of this row
+  size_t stride;       // floats between partials
+  const float* gate;   // 256 gate values, or null
+};
+
+__device__ __forceinline__ RowMap map_generic(const MergeParams& p, int64_t row) {
+  return {p.part + row * PROW, (size_t)p.part_stride, p.qg ? p.qg + row * 512 + 256 : nullptr};
+}
+// Decode layout: part [seq][kvh][chunk][24][258], output row = (seq, t, h), partial row = t*6 + h%6.
+__device__ __forceinline__ RowMap map_decode(const MergeParams& p, int64_t row) {
+  const int h = (int)(row % p.nqh), t = (int)((row / p.nqh) % p.T);
+  const int64_t seq = row / ((int64_t)p.nqh * p.T);
+  const int kh = h / GQA, r = t * GQA + h % GQA, nkvh = p.nqh / GQA;
+  const float* first = p.part + (((seq * nkvh + kh) * p.nparts) * MAXR + r) * (size_t)PROW;
+  return {first, (size_t)MAXR * PROW, p.qg ? p.qg + row * 512 + 256 : nullptr};
+}
+
+template <bool DECODE_LAYOUT>
+__global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float sf[MAX_PARTS];
+  __shared__ float sred[2][8];
+  const int64_t row = blockIdx.x;
+  const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
+  const RowMap rm = DECODE_LAYOUT ? map_decode(p, row) : map_generic(p, row);
+  int np = p.nparts;
+  if (DECODE_LAYOUT && p.seq_len) {
+    const int64_t seq = row / ((int64_t)p.nqh * p.T);
+    np = min(np, max(1, (p.seq_len[seq] + p.chunk_len - 1) / p.chunk_len));
+  }
+
+  // M and the factors
+  float mx = M_INIT;
+  for (int c = d; c < np; c += AD) mx = fmaxf(mx, rm.first[c * rm.stride]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) sred[0][warp] = mx;
+  __syncthreads();
+  float M = sred[0][0];
+#pragma unroll
+  for (int i = 1; i < 8; i++) M = fmaxf(M, sred[0][i]);
+  for (int c = d; c < np; c += AD) sf[c] = expf(rm.first[c * rm.stride] - M);
+  __syncthreads();
+
+  float L = 0.f, A = 0.f;
+  const float* col = rm.first + 2 + d;
+#pragma unroll 8
+  for (int c = 0; c < np; c++) {
+    const float f = sf[c];
+    L += rm.first[c * rm.stride + 1] * f;
+    A += col[c * rm.stride] * f;
+  }
+
+  const size_t oi = (size_t)row * AD + d;
+  if (p.part_out) {  // merged but not normalised: (M, L, A) for a later merge
+    float* po = p.part_out + (size_t)row * PROW;
+    po[2 + d] = A;
+    if (d == 0) {
+      po[0] = M;
+      po[1] = L;
+    }
+    return;
+  }
+  float y = A / L;
+  if (rm.gate) y *= 1.0f / (1.0f + expf(-rm.gate[d]));
+  if (!p.xq) {
+    p.o[oi] = y;
+    return;
+  }
+  float amax = fabsf(y);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float dd = __fdiv_rn(amax, 127.0f);
+  p.xq[oi] = amax == 0.0f ? (int8_t)0 : (int8_t)roundf(__fdiv_rn(y, dd));
+  if (lane == 0) p.xd[oi / 32] = __half2float(__float2half_rn(dd));
+}
+
+}  // namespace
+
+int launch_merge(const MergeParams& p, bool decode_layout, cudaStream_t s) {
+  if (p.nparts < 1 || p.nparts > MAX_PARTS) return fail(Q27B_BAD_SHAPE, "lse_merge: 1..1024 partials");
+  if (p.rows < 1) return Q27B_OK;
+  if (decode_layout) merge_kernel<true><<<(unsigned)p.rows, AD, 0, s>>>(p);
+  else merge_kernel<false><<<(unsigned)p.rows, AD, 0, s>>>(p);
+  Q27B_CK(cudaGetLastError());
+  return Q27B_OK;
+}
+
+}  // namespace q27b
+
+using namespace q27b;
+
+extern "C" int q27b_lse_merge(const float* part, int nparts, int64_t part_stride, int64_t rows, const float* qg, float* o,
+                              int8_t* xq, float* xd, void* stream) {
+  if (!part || (!o && !xq) || (xq && !xd)) return fail(Q27B_BAD_SHAPE, "lse_merge: null pointer");
+  if (rows < 0 || rows > 0x7fffffff || part_stride < 0) return fail(Q27B_BAD_SHAPE, "lse_merge: bad shape");
+  MergeParams p = {};
+  p.part = part; p.nparts = nparts; p.part_stride = part_stride; p.rows = rows; p.qg = qg; p.o = o; p.xq = xq; p.xd = xd;
+  return launch_merge(p, false, (cudaStream_t)stream);
+}

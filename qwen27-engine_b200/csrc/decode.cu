@@ -1,0 +1,609 @@
+// Split-K flash-decode over a q8_0 (or f16) KV cache for 1..4 speculative-verify query tokens.
+//
+// Replaces attn_mma_kernel + the host wrapper attn_decode of the reference (src/attn.cu:95-292,
+// 894-918). Same decomposition of the work (one CTA per (position chunk, KV head), all 6*T query
+// rows of the KV head in the CTA, so each K/V byte leaves HBM once; per-chunk partials (m, l, O)
+// merged by the log-sum-exp kernel) and the same roundings (Q*scale -> f16, K/V -> f16(int8 * f16
+// scale), P -> f16, f32 accumulation, row sums from the f32 P; src/attn.cu:10-11). The kernel
+// itself is built for B200:
+//
+//  * 64-position tiles (K and V values as two 128-byte-swizzled 64x128 B boxes each, plus the
+//    two 64x16 B scale boxes) are streamed by TMA into a 6-stage mbarrier ring. A stage is
+//    refilled by one elected lane right after the group barrier that proves all four warps are
+//    done with it, so there is no producer warp and no "empty" barrier: ~140 KB stay in flight
+//    per SM, which is what HBM3e needs to stay busy.
+//  * Eight consumer warps in two groups of four; the groups take alternate tiles and keep their
+//    own running (m, l, O), merged once at the end. Within a group, warp w computes
+//    S^T = K Q^T for tile rows 16w..16w+15 (positions on the MMA M axis, the 6*T query rows on
+//    N = 8/16/24: no padding waste), then O^T += V^T P^T for head dims 64w..64w+63 over all 64
+//    positions. P (64 x 24 f16) is the only thing exchanged between warps.
+//  * K and V go from shared memory straight into mma.sync fragments: each lane loads 16 (K) or
+//    8 (V) consecutive int8 of a row, and the byte -> f16 conversion (0x64xx magic, minus 1152,
+//    times the block scale: one rounding) happens in registers. The contraction index of an MMA
+//    may be permuted freely, so the k-slots are chosen to match what a coalesced 16-byte load
+//    delivers; Q is pre-permuted to match, once, into registers. With the 128-byte swizzle and a
+//    bit-reversed row order inside each 16-row slab every shared-memory load is conflict-free.
+#include "combine.h"
+#include "common.cuh"
+
+#include <algorithm>
+
+namespace q27b {
+namespace {
+
+constexpr int TILE = 64;                       // positions per tile
+constexpr int NSTAGE = 6;
+constexpr int VAL_BYTES = TILE * AD;           // int8 values of one operand: two [64][128 B] halves
+constexpr int SC_BYTES = TILE * 16;            // f16 scales [64][8]
+constexpr int STAGE_BYTES = 2 * VAL_BYTES + 2 * SC_BYTES;  // 34816
+constexpr int OFF_KV = 0, OFF_VV = VAL_BYTES, OFF_KS = 2 * VAL_BYTES, OFF_VS = 2 * VAL_BYTES + SC_BYTES;
+constexpr int P_STRIDE = 36;                   // words per P row (32 position pairs + 4 padding: no bank conflicts)
+constexpr int P_WORDS = MAXR * P_STRIDE;
+constexpr int OFF_P = NSTAGE * STAGE_BYTES;                 // [2 groups][2 buffers][24][36] words
+constexpr int OFF_MAX = OFF_P + 2 * 2 * P_WORDS * 4;        // [2 groups][2 buffers][4 warps][24] floats
+constexpr int OFF_L = OFF_MAX + 2 * 2 * 4 * MAXR * 4;       // [2 groups][4 warps][24] floats
+constexpr int OFF_M1 = OFF_L + 2 * 4 * MAXR * 4;            // [24] floats: running max of group 1
+constexpr int OFF_BAR = OFF_M1 + MAXR * 4;                  // full[NSTAGE]
+constexpr int OFF_FLAG = OFF_BAR + NSTAGE * 8;
+constexpr int SMEM_USED = OFF_FLAG + 16;
+constexpr int SMEM_BYTES = SMEM_USED + 1024;               // slack for the 1024-byte alignment of the ring
+constexpr int O_STRIDE = AD + 4;                            // floats per row of the end-of-kernel O exchange
+static_assert(MAXR * O_STRIDE * 4 <= NSTAGE * STAGE_BYTES, "O exchange must fit in the ring");
+static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+
+constexpr int N_THREADS = 256;
+
+struct DecodeParams {
+  const float* qn;   // [T][nqh][256]
+  float* part;       // [nkvh][nch][24][258]
+  const int* pos0;
+  int* status;
+  int T, nqh, nkvh, n_ctx, nch;
+  float kq_scale;
+  int base_pos;      // global position of local cache row 0
+  int n_local;       // local rows to attend; < 0: all rows up to *pos0 + T
+  // paged / batched variant: grid (chunks, nkvh, B), fixed chunk length, rows through the page table
+  const int* page_table;  // [B][max_pages]
+  const int* seq_len;     // [B], counts the T new tokens
+  int max_pages, n_pages, chunk_len;
+};
+
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldsu16(uint32_t a) {
+  uint32_t v;
+  asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v)); }
+__device__ __forceinline__ void stsf(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v)); }
+__device__ __forceinline__ float ldsf(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) { return __byte_perm(a, b, sel); }
+
+// Row of a 16-row slab that MMA row slot s (0..15) stands for: 8 * (s >> 3) + bitrev3(s & 7).
+__device__ __forceinline__ int slot_row(int s) { return (s & 8) | ((s & 1) << 2) | (s & 2) | ((s & 4) >> 2); }
+
+// NT = 8-row groups of query rows (ceil(6 T / 8)). PAGED: batched decode over 256-position pages.
+template <int NT, bool PAGED>
+__global__ void __launch_bounds__(N_THREADS, 1)
+decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_ks,
+                 const __grid_constant__ CUtensorMap tm_vv, const __grid_constant__ CUtensorMap tm_vs,
+                 const DecodeParams p) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  uint64_t* full = (uint64_t*)(sgen + OFF_BAR);
+  volatile int* abort_flag = (volatile int*)(sgen + OFF_FLAG);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ch = blockIdx.x, kh = blockIdx.y;
+  const int T = p.T, R = GQA * T;
+  const int seq = PAGED ? blockIdx.z : 0;
+  const int pos0 = PAGED ? p.seq_len[seq] - T : *p.pos0;
+  const float* qn = p.qn + (size_t)seq * T * p.nqh * AD;
+
+  // Local rows to attend, and this CTA's chunk [c0, c1) of them (multiples of TILE).
+  int n = pos0 + T - p.base_pos;
+  if (p.n_local >= 0) n = min(n, p.n_local);
+  n = max(0, min(n, p.n_ctx));
+  int chunk;
+  if (PAGED) {
+    chunk = p.chunk_len;
+  } else {
+    chunk = (n + p.nch - 1) / p.nch;
+    chunk = max(TILE, (chunk + TILE - 1) / TILE * TILE);
+  }
+  const int c0 = min(n, ch * chunk), c1 = min(n, c0 + chunk);
+  float* out = p.part + (((size_t)seq * p.nkvh + kh) * p.nch + ch) * MAXR * PROW;
+
+  if (c0 >= c1) {
+    // Empty chunk: neutral partial (src/attn.cu:117-120). The paged merge reads only the chunks
+    // that a sequence has, so there nothing is written.
+    if (!PAGED)
+      for (int i = tid; i < R * PROW; i += N_THREADS) out[i] = (i % PROW == 0) ? M_INIT : 0.f;
+    return;
+  }
+  const int ntiles = (c1 - c0 + TILE - 1) / TILE;
+
+  if (tid == 0) {
+    for (int s = 0; s < NSTAGE; s++) mbar_init(&full[s], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  {
+    // TMA of tile `it` into stage it % NSTAGE (one thread).
+    const int row0 = kh * p.n_ctx + c0;
+    auto issue_tile = [&](int it) {
+      const int s = it % NSTAGE;
+      uint8_t* st = sgen + (size_t)s * STAGE_BYTES;
+      mbar_expect_tx(&full[s], STAGE_BYTES);
+      int row = row0 + it * TILE;
+      if (PAGED) {  // a tile never straddles a page (64 | 256)
+        const int pp = c0 + it * TILE;
+        int pg = p.page_table[(size_t)seq * p.max_pages + pp / Q27B_PAGE];
+        if (pg < 0 || pg >= p.n_pages) {  // never read outside the pool: flag it and read page 0
+          atomicOr(p.status, ST_BAD_PAGE);
+          pg = 0;
+        }
+        row = (pg * p.nkvh + kh) * Q27B_PAGE + pp % Q27B_PAGE;
+      }
+      tma_load_2d(st + OFF_KV, &tm_kv, 0, row, &full[s]);
+      tma_load_2d(st + OFF_KV + VAL_BYTES / 2, &tm_kv, 128, row, &full[s]);
+      tma_load_2d(st + OFF_VV, &tm_vv, 0, row, &full[s]);
+      tma_load_2d(st + OFF_VV + VAL_BYTES / 2, &tm_vv, 128, row, &full[s]);
+      tma_load_2d(st + OFF_KS, &tm_ks, 0, row, &full[s]);
+      tma_load_2d(st + OFF_VS, &tm_vs, 0, row, &full[s]);
+    };
+    const int g = lane >> 2, tg = lane & 3;
+    const int grp = warp >> 2, wq = warp & 3;
+    const bool loader = wq == 0 && lane == 0;  // refills this group's stages
+    if (loader)
+      for (int it = grp; it < min(ntiles, NSTAGE); it += 2) issue_tile(it);
+    const int ra = 16 * wq + slot_row(g), rb = ra + 8;  // tile rows of MMA row slots g and g + 8 (S^T)
+
+    // Q fragments (B operand of S^T = K Q^T), permuted to the k-slot order of the K loads:
+    // k-step ks = 8h + 4j + s covers dims 128h + 64j + 16tg + 4s .. +3 of query row 8nt + g.
+    uint32_t qf[16][NT][2];
+#pragma unroll
+    for (int ks = 0; ks < 16; ks++) {
+      const int dim0 = 128 * (ks >> 3) + 64 * ((ks >> 2) & 1) + 16 * tg + 4 * (ks & 3);
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) {
+        const int r = 8 * nt + g;
+        uint32_t b0 = 0, b1 = 0;
+        if (r < R) {
+          const float4 q = *(const float4*)(qn + ((size_t)(r / GQA) * p.nqh + kh * GQA + r % GQA) * AD + dim0);
+          b0 = pack_h2(q.x * p.kq_scale, q.y * p.kq_scale);
+          b1 = pack_h2(q.z * p.kq_scale, q.w * p.kq_scale);
+        }
+        qf[ks][nt][0] = b0;
+        qf[ks][nt][1] = b1;
+      }
+    }
+
+    // Visible end (local row index, exclusive) of this lane's query rows 8nt + 2tg + e.
+    int lim[NT][2];
+    int lim_min = c1;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const int r = 8 * nt + 2 * tg + e;
+        lim[nt][e] = min(c1, pos0 + min(r / GQA, T - 1) + 1 - p.base_pos);
+      }
+    lim_min = min(c1, pos0 + 1 - p.base_pos);
+
+    float o[4][NT][4];
+#pragma unroll
+    for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) o[mt][nt][0] = o[mt][nt][1] = o[mt][nt][2] = o[mt][nt][3] = 0.f;
+    float m[NT][2], l[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      m[nt][0] = m[nt][1] = M_INIT;
+      l[nt][0] = l[nt][1] = 0.f;
+    }
+
+    const uint32_t sP = sbase + OFF_P + grp * 2 * P_WORDS * 4;
+    const uint32_t sMax = sbase + OFF_MAX + grp * 2 * 4 * MAXR * 4;
+    const uint32_t sel_sc = (tg & 2) ? 0x3232u : 0x1010u;  // which f16 of a scale word this lane's K blocks use
+    const uint32_t MAGIC = 0x64646464u;
+
+    int jt = 0;
+    for (int it = grp; it < ntiles; it += 2, jt++) {
+      const int s = it % NSTAGE;
+      mbar_wait(&full[s], (it / NSTAGE) & 1, abort_flag, p.status);
+      const uint32_t st = sbase + s * STAGE_BYTES;
+      const int tile_p0 = c0 + it * TILE;
+      const bool edge = tile_p0 + TILE > lim_min;  // some row of the tile is masked for some query row
+
+      // ---- S^T = K Q^T for tile rows ra, rb
+      float sacc[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+      {
+        const uint4 sca = lds128(st + OFF_KS + ra * 16), scb = lds128(st + OFF_KS + rb * 16);
+        const uint32_t scaw[4] = {sca.x, sca.y, sca.z, sca.w}, scbw[4] = {scb.x, scb.y, scb.z, scb.w};
+#pragma unroll
+        for (int hj = 0; hj < 4; hj++) {
+          const int h = hj >> 1, j = hj & 1;
+          const uint4 xa = lds128(st + OFF_KV + h * (VAL_BYTES / 2) + swz128(ra, 4 * j + tg));
+          const uint4 xb = lds128(st + OFF_KV + h * (VAL_BYTES / 2) + swz128(rb, 4 * j + tg));
+          const __half2 da = u32_as_h2(prmt(scaw[hj], scaw[hj], sel_sc));
+          const __half2 db = u32_as_h2(prmt(scbw[hj], scbw[hj], sel_sc));
+          const uint32_t xaw[4] = {xa.x, xa.y, xa.z, xa.w}, xbw[4] = {xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+          for (int s2 = 0; s2 < 4; s2++) {
+            const uint32_t wa = xaw[s2] ^ 0x80808080u, wb = xbw[s2] ^ 0x80808080u;
+            const uint32_t a0 = dq_pair(prmt(wa, MAGIC, 0x4140), da), a2 = dq_pair(prmt(wa, MAGIC, 0x4342), da);
+            const uint32_t a1 = dq_pair(prmt(wb, MAGIC, 0x4140), db), a3 = dq_pair(prmt(wb, MAGIC, 0x4342), db);
+            const int ks = 4 * hj + s2;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) mma16816(sacc[nt], a0, a1, a2, a3, qf[ks][nt][0], qf[ks][nt][1]);
+          }
+        }
+      }
+      if (edge) {
+        const int pa = tile_p0 + ra, pb = tile_p0 + rb;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            if (pa >= lim[nt][e]) sacc[nt][e] = -INFINITY;
+            if (pb >= lim[nt][e]) sacc[nt][2 + e] = -INFINITY;
+          }
+      }
+
+      // ---- tile maximum per query row: over this warp's 16 positions, then over the 4 warps
+      const int buf = jt & 1;
+      {
+        float mx[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            float v = fmaxf(sacc[nt][e], sacc[nt][2 + e]);
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+            mx[nt][e] = v;
+          }
+        if (g == 0) {
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) stsf(sMax + ((buf * 4 + wq) * MAXR + 8 * nt + 2 * tg + e) * 4, mx[nt][e]);
+        }
+      }
+      bar_sync(1 + grp, 128);
+      // All four warps are past the previous tile of this group: its stage can be refilled.
+      if (loader && jt >= 1 && it - 2 + NSTAGE < ntiles) issue_tile(it - 2 + NSTAGE);
+
+      float sc[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          const int r = 8 * nt + 2 * tg + e;
+          float tm = ldsf(sMax + ((buf * 4 + 0) * MAXR + r) * 4);
+#pragma unroll
+          for (int w = 1; w < 4; w++) tm = fmaxf(tm, ldsf(sMax + ((buf * 4 + w) * MAXR + r) * 4));
+          const float mn = fmaxf(m[nt][e], tm);
+          sc[nt][e] = ex2((m[nt][e] - mn) * LOG2E);
+          m[nt][e] = mn;
+          const float mb = mn * LOG2E;
+          const float pa = ex2(fmaf(sacc[nt][e], LOG2E, -mb)), pb = ex2(fmaf(sacc[nt][2 + e], LOG2E, -mb));
+          l[nt][e] = fmaf(l[nt][e], sc[nt][e], pa + pb);
+          // position pair (slot g, slot g + 8) of warp wq = P^T k-slot pair 8wq + g
+          sts32(sP + (buf * P_WORDS + r * P_STRIDE + 8 * wq + g) * 4, pack_h2(pa, pb));
+        }
+#pragma unroll
+      for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          o[mt][nt][0] *= sc[nt][0];
+          o[mt][nt][1] *= sc[nt][1];
+          o[mt][nt][2] *= sc[nt][0];
+          o[mt][nt][3] *= sc[nt][1];
+        }
+      bar_sync(1 + grp, 128);
+
+      // ---- O^T += V^T P^T for head dims 64wq + 8g .. +7 (8 bytes of each V row per lane)
+      {
+        const uint32_t vbase = st + OFF_VV + (wq >> 1) * (VAL_BYTES / 2) + (g & 1) * 8;
+        const uint32_t cb = (wq & 1) * 4 + (g >> 1);
+        const uint32_t vsc = st + OFF_VS + (2 * wq + (g >> 2)) * 2;
+        const uint32_t pP = sP + (buf * P_WORDS + g * P_STRIDE + tg) * 4;
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+          const int pa = 16 * ks + slot_row(tg), pb = pa + 8, pc = pa + 1, pd = pa + 9;
+          const uint2 xa = lds64(vbase + swz128(pa, cb)), xb = lds64(vbase + swz128(pb, cb));
+          const uint2 xc = lds64(vbase + swz128(pc, cb)), xd = lds64(vbase + swz128(pd, cb));
+          uint32_t sa = ldsu16(vsc + pa * 16), sb = ldsu16(vsc + pb * 16);
+          uint32_t scc = ldsu16(vsc + pc * 16), sd = ldsu16(vsc + pd * 16);
+          if (edge) {  // rows past the end of the sequence may hold anything: make them exact zeros
+            if (tile_p0 + pa >= c1) sa = 0;
+            if (tile_p0 + pb >= c1) sb = 0;
+            if (tile_p0 + pc >= c1) scc = 0;
+            if (tile_p0 + pd >= c1) sd = 0;
+          }
+          const __half2 sab = u32_as_h2(sa | (sb << 16)), scd = u32_as_h2(scc | (sd << 16));
+          uint32_t b0[NT], b1[NT];
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) {
+            b0[nt] = lds32(pP + (8 * nt * P_STRIDE + 8 * ks) * 4);
+            b1[nt] = lds32(pP + (8 * nt * P_STRIDE + 8 * ks + 4) * 4);
+          }
+          const uint32_t xaw[2] = {xa.x, xa.y}, xbw[2] = {xb.x, xb.y}, xcw[2] = {xc.x, xc.y}, xdw[2] = {xd.x, xd.y};
+#pragma unroll
+          for (int wi = 0; wi < 2; wi++) {
+            const uint32_t ua = xaw[wi] ^ 0x80808080u, ub = xbw[wi] ^ 0x80808080u;
+            const uint32_t uc = xcw[wi] ^ 0x80808080u, ud = xdw[wi] ^ 0x80808080u;
+            const uint32_t t1 = prmt(ua, ub, 0x5140), t2 = prmt(ua, ub, 0x7362);
+            const uint32_t t3 = prmt(uc, ud, 0x5140), t4 = prmt(uc, ud, 0x7362);
+            {
+              const uint32_t a0 = dq_pair(prmt(t1, MAGIC, 0x4140), sab), a1 = dq_pair(prmt(t1, MAGIC, 0x4342), sab);
+              const uint32_t a2 = dq_pair(prmt(t3, MAGIC, 0x4140), scd), a3 = dq_pair(prmt(t3, MAGIC, 0x4342), scd);
+#pragma unroll
+              for (int nt = 0; nt < NT; nt++) mma16816(o[2 * wi][nt], a0, a1, a2, a3, b0[nt], b1[nt]);
+            }
+            {
+              const uint32_t a0 = dq_pair(prmt(t2, MAGIC, 0x4140), sab), a1 = dq_pair(prmt(t2, MAGIC, 0x4342), sab);
+              const uint32_t a2 = dq_pair(prmt(t4, MAGIC, 0x4140), scd), a3 = dq_pair(prmt(t4, MAGIC, 0x4342), scd);
+#pragma unroll
+              for (int nt = 0; nt < NT; nt++) mma16816(o[2 * wi + 1][nt], a0, a1, a2, a3, b0[nt], b1[nt]);
+            }
+          }
+        }
+      }
+    }
+
+    // ---- row sums over this warp's positions
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        float v = l[nt][e];
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        l[nt][e] = v;
+        if (g == 0) stsf(sbase + OFF_L + ((grp * 4 + wq) * MAXR + 8 * nt + 2 * tg + e) * 4, v);
+      }
+    bar_sync(3, N_THREADS);  // every tile consumed: the ring is free for the O exchange
+
+    // ---- merge the two groups (log-sum-exp) and write the chunk partial
+    const uint32_t sO = sbase;
+    if (grp == 1) {
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          const int r = 8 * nt + 2 * tg + e;
+          if (wq == 0 && g == 0) stsf(sbase + OFF_M1 + r * 4, m[nt][e]);
+#pragma unroll
+          for (int mt = 0; mt < 4; mt++) {
+            const int d = 64 * wq + 8 * g + 2 * mt;
+            stsf(sO + (r * O_STRIDE + d) * 4, o[mt][nt][e]);
+            stsf(sO + (r * O_STRIDE + d + 1) * 4, o[mt][nt][2 + e]);
+          }
+        }
+    }
+    bar_sync(3, N_THREADS);
+    if (grp == 0) {
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          const int r = 8 * nt + 2 * tg + e;
+          if (r >= R) continue;
+          const float m0 = m[nt][e], m1 = ldsf(sbase + OFF_M1 + r * 4);
+          const float M = fmaxf(m0, m1);
+          const float f0 = ex2((m0 - M) * LOG2E), f1 = ex2((m1 - M) * LOG2E);
+          float* po = out + (size_t)r * PROW;
+#pragma unroll
+          for (int mt = 0; mt < 4; mt++) {
+            const int d = 64 * wq + 8 * g + 2 * mt;
+            const float v0 = o[mt][nt][e] * f0 + ldsf(sO + (r * O_STRIDE + d) * 4) * f1;
+            const float v1 = o[mt][nt][2 + e] * f0 + ldsf(sO + (r * O_STRIDE + d + 1) * 4) * f1;
+            *(float2*)(po + 2 + d) = make_float2(v0, v1);
+          }
+          if (wq == 0 && g == 0) {
+            float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+              l0 += ldsf(sbase + OFF_L + ((0 * 4 + w) * MAXR + r) * 4);
+              l1 += ldsf(sbase + OFF_L + ((1 * 4 + w) * MAXR + r) * 4);
+            }
+            po[0] = M;
+            po[1] = l0 * f0 + l1 * f1;
+          }
+        }
+    }
+  }
+}
+
+struct TmapKey {
+  const void* base;
+  int nkvh, n_ctx;
+  CUtensorMap vals, scales;
+};
+// Small cache of tensor maps per (cache pointer, shape): the reference's caches never move
+// (src/model.cu:464-472), so a decode step re-encodes nothing.
+constexpr int TMAP_CACHE = 64;
+TmapKey g_tmaps[TMAP_CACHE];
+int g_tmap_next = 0;
+
+int get_tmaps(const void* cache, int nkvh, int n_ctx, const CUtensorMap** vals, const CUtensorMap** scales) {
+  for (int i = 0; i < TMAP_CACHE; i++)
+    if (g_tmaps[i].base == cache && g_tmaps[i].nkvh == nkvh && g_tmaps[i].n_ctx == n_ctx) {
+      *vals = &g_tmaps[i].vals;
+      *scales = &g_tmaps[i].scales;
+      return Q27B_OK;
+    }
+  TmapKey& k = g_tmaps[g_tmap_next];
+  g_tmap_next = (g_tmap_next + 1) % TMAP_CACHE;
+  k.base = nullptr;
+  const uint64_t rows = (uint64_t)nkvh * n_ctx;
+  if (int rc = make_tmap_2d(&k.vals, cache, rows, AD, AD, 128, TILE, true)) return rc;
+  if (int rc = make_tmap_2d(&k.scales, (const uint8_t*)cache + rows * AD, rows, 16, 16, 16, TILE, false)) return rc;
+  k.base = cache;
+  k.nkvh = nkvh;
+  k.n_ctx = n_ctx;
+  *vals = &k.vals;
+  *scales = &k.scales;
+  return Q27B_OK;
+}
+
+template <int NT, bool PAGED>
+int launch_decode(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
+                  const DecodeParams& p, int nseq, cudaStream_t s) {
+  static bool attr[64] = {};
+  int dev;
+  Q27B_CK(cudaGetDevice(&dev));
+  if (!attr[dev]) {
+    Q27B_CK(cudaFuncSetAttribute(decode_q8_kernel<NT, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr[dev] = true;
+  }
+  decode_q8_kernel<NT, PAGED><<<dim3(p.nch, p.nkvh, nseq), N_THREADS, SMEM_BYTES, s>>>(*kv, *ks, *vv, *vs, p);
+  Q27B_CK(cudaGetLastError());
+  return Q27B_OK;
+}
+template <bool PAGED>
+int launch_decode_t(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
+                    const DecodeParams& p, int nseq, cudaStream_t s) {
+  const int nt = (GQA * p.T + 7) / 8;
+  if (nt == 1) return launch_decode<1, PAGED>(kv, ks, vv, vs, p, nseq, s);
+  if (nt == 2) return launch_decode<2, PAGED>(kv, ks, vv, vs, p, nseq, s);
+  return launch_decode<3, PAGED>(kv, ks, vv, vs, p, nseq, s);
+}
+
+// Split-K pass of one sequence into ctx->part [nkvh][nch][24][258].
+int decode_split(DeviceCtx* ctx, const float* qn, const void* kcache, const void* vcache, const int* pos0, int T,
+                 float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos, int n_local, int* nch_out,
+                 cudaStream_t s) {
+  if (!q8) return fail(Q27B_UNSUPPORTED, "attn_decode: f16 KV cache is not built yet");
+  const int nch = std::max(1, ctx->n_sm / nkvh);
+  if (int rc = ensure_part(ctx, (size_t)nkvh * nch * MAXR * PROW)) return rc;
+  const CUtensorMap *kv, *ks, *vv, *vs;
+  if (int rc = get_tmaps(kcache, nkvh, n_ctx, &kv, &ks)) return rc;
+  if (int rc = get_tmaps(vcache, nkvh, n_ctx, &vv, &vs)) return rc;
+  DecodeParams p = {};
+  p.qn = qn; p.part = ctx->part; p.pos0 = pos0; p.status = ctx->status;
+  p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nch = nch; p.kq_scale = kq_scale;
+  p.base_pos = base_pos; p.n_local = n_local;
+  *nch_out = nch;
+  if (int rc = launch_decode_t<false>(kv, ks, vv, vs, p, 1, s)) return rc;
+  if (ctx->split_event) Q27B_CK(cudaEventRecord(ctx->split_event, s));
+  return Q27B_OK;
+}
+
+}  // namespace
+}  // namespace q27b
+
+using namespace q27b;
+
+extern "C" {
+
+int q27b_attn_decode(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o, int8_t* xq,
+                     float* xd, const int* pos0, int T, float kq_scale, int nqh, int nkvh, int n_ctx, int q8,
+                     void* stream) {
+  if (T < 1 || T > Q27B_MAX_T || nkvh < 1 || nqh != nkvh * GQA || n_ctx < 1)
+    return fail(Q27B_BAD_SHAPE, "attn_decode: bad shape");
+  if (!qn || !qg || !kcache || !vcache || !pos0 || (!o && !xq) || (xq && !xd))
+    return fail(Q27B_BAD_SHAPE, "attn_decode: null pointer");
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  int nch;
+  if (int rc = decode_split(ctx, qn, kcache, vcache, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8, 0, -1, &nch,
+                            (cudaStream_t)stream))
+    return rc;
+  MergeParams mp = {};
+  mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.qg = qg; mp.o = o; mp.xq = xq; mp.xd = xd;
+  mp.T = T; mp.nqh = nqh;
+  return launch_merge(mp, true, (cudaStream_t)stream);
+}
+
+int q27b_attn_decode_partial(const float* qn, const void* kcache, const void* vcache, float* part, const int* pos0,
+                             int T, float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos, int n_local,
+                             void* stream) {
+  if (T < 1 || T > Q27B_MAX_T || nkvh < 1 || nqh != nkvh * GQA || n_ctx < 1 || base_pos < 0 || n_local < 0 ||
+      n_local > n_ctx)
+    return fail(Q27B_BAD_SHAPE, "attn_decode_partial: bad shape");
+  if (!qn || !kcache || !vcache || !pos0 || !part) return fail(Q27B_BAD_SHAPE, "attn_decode_partial: null pointer");
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  int nch;
+  if (int rc = decode_split(ctx, qn, kcache, vcache, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8, base_pos, n_local, &nch,
+                            (cudaStream_t)stream))
+    return rc;
+  MergeParams mp = {};
+  mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.part_out = part; mp.T = T; mp.nqh = nqh;
+  return launch_merge(mp, true, (cudaStream_t)stream);
+}
+
+int q27b_debug_split_event(void* event) {
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  ctx->split_event = (cudaEvent_t)event;
+  return Q27B_OK;
+}
+
+int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, const void* vpool,
+                           const int* page_table, const int* seq_len, float* o, int B, int T, float kq_scale, int nqh,
+                           int nkvh, int n_pages, int max_pages, int max_seq_len, void* stream) {
+  if (B < 1 || T < 1 || T > Q27B_MAX_T || nkvh < 1 || nqh != nkvh * GQA || n_pages < 1 || max_pages < 1 ||
+      max_seq_len < T || max_seq_len > max_pages * Q27B_PAGE || B > 65535)
+    return fail(Q27B_BAD_SHAPE, "attn_decode_paged: bad shape");
+  if (!qn || !qg || !kpool || !vpool || !page_table || !seq_len || !o)
+    return fail(Q27B_BAD_SHAPE, "attn_decode_paged: null pointer");
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  // Fixed chunk length (a multiple of the page): about 8 chunks per SM over the whole batch at
+  // the longest length, between 1024 and 8192 positions.
+  const int64_t total = (int64_t)B * nkvh * max_seq_len;
+  int chunk = (int)std::min<int64_t>(8192, std::max<int64_t>(1024, total / (8 * (int64_t)ctx->n_sm)));
+  chunk = (chunk + Q27B_PAGE - 1) / Q27B_PAGE * Q27B_PAGE;
+  const int nch = (max_seq_len + chunk - 1) / chunk;
+  if (int rc = ensure_part(ctx, (size_t)B * nkvh * nch * MAXR * PROW)) return rc;
+  // One pool = n_pages * nkvh pages of 256 rows: the same row tensor as a cache of that many rows.
+  const int pool_rows_per_head = n_pages * Q27B_PAGE;
+  const CUtensorMap *kv, *ks, *vv, *vs;
+  if (int rc = get_tmaps(kpool, nkvh, pool_rows_per_head, &kv, &ks)) return rc;
+  if (int rc = get_tmaps(vpool, nkvh, pool_rows_per_head, &vv, &vs)) return rc;
+  DecodeParams p = {};
+  p.qn = qn; p.part = ctx->part; p.status = ctx->status;
+  p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = max_pages * Q27B_PAGE; p.nch = nch; p.kq_scale = kq_scale;
+  p.base_pos = 0; p.n_local = -1;
+  p.page_table = page_table; p.seq_len = seq_len; p.max_pages = max_pages; p.n_pages = n_pages; p.chunk_len = chunk;
+  if (int rc = launch_decode_t<true>(kv, ks, vv, vs, p, B, (cudaStream_t)stream)) return rc;
+  MergeParams mp = {};
+  mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)B * T * nqh; mp.qg = qg; mp.o = o; mp.T = T; mp.nqh = nqh;
+  mp.seq_len = seq_len; mp.chunk_len = chunk;
+  return launch_merge(mp, true, (cudaStream_t)stream);
+}
+
+}  // extern "C"

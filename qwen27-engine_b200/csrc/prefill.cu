@@ -1,0 +1,661 @@
+// Causal flash-attention prefill over a q8_0 KV cache with int8 Q K^T on the 5th-generation
+// tensor cores (tcgen05.mma kind::i8 into TMEM) and P V on kind::f16.
+//
+// Replaces attn_prefill_i8_kernel + the host wrapper attn_prefill of the reference
+// (src/attn.cu:557-801, 920-974) with the same arithmetic definition: Q * kq_scale rounded to
+// int8 with one f32 scale per 32 dims, K = the cache bytes as stored, one exact int32 dot product
+// per 32-dim block, s = sum_b (dq[b] * dk[p][b]) * float(I_b) in block order, online softmax,
+// P -> f16, V -> f16(int8 * f16 scale). Unlike the reference, O accumulates in f32 (in TMEM), so
+// no max offset is needed; the running reference max is only moved when the true max has grown
+// by more than TAU, which keeps P <= e^TAU and makes the O rescale rare.
+//
+// One CTA = 128 query tokens of one query head (TMEM lane = token) x one split of the positions,
+// walking 64-position tiles. Roles:
+//   warps 0-3  softmax: each thread owns one query row; reads the per-block int32 accumulators
+//              from TMEM, applies the block scales, keeps (m, l), writes P (f16) into shared
+//              memory in the tensor core's K-major 128B-swizzled layout, rescales O when needed,
+//              and writes the output.
+//   warps 4-7  converter: V tile int8 -> f16 into the MN-major 128B-swizzled layout that the P V
+//              MMA reads directly (no transpose), and the K scales f16 -> f32 table.
+//   warp 8     TMA producer (one lane): K and V tiles, double buffered.
+//   warp 9     MMA issuer (one lane): per tile 8 x (128x64x32 int8) into a 4-slot ring of TMEM
+//              accumulators, then 4 x (128x256x16 f16) into the O accumulator; owns TMEM.
+// TMEM: columns 0-255 O (f32), 256-511 four S slots of 64 columns (s32).
+#include "combine.h"
+#include "common.cuh"
+
+#include <algorithm>
+
+namespace q27b {
+namespace {
+
+constexpr int QT = 128;          // query tokens per CTA
+constexpr int PT = 64;           // positions per tile
+constexpr float TAU = 5.0f;      // the reference max moves only when the true max exceeds it by this much
+
+// shared memory map (offsets from a 1024-byte aligned base)
+constexpr int SQ_BYTES = 2 * QT * 128;              // int8 Q: two K-halves of [128][128 B]
+constexpr int KST_BYTES = 2 * PT * 128 + PT * 16;   // one K (or V) stage: values + scales
+constexpr int VF_BYTES = 4 * PT * 128;              // f16 V: [4 dim chunks][64 positions][128 B]
+constexpr int P_BYTES = QT * 128;                   // f16 P: [128][64 positions]
+constexpr int DKF_BYTES = 8 * PT * 4;               // f32 K scales [8 blocks][64]
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + SQ_BYTES;             // 2 stages (each padded to 18432 = 18 KB)
+constexpr int KST_PAD = 18432;
+constexpr int OFF_V = OFF_K + 2 * KST_PAD;
+constexpr int OFF_VF = OFF_V + 2 * KST_PAD;
+constexpr int OFF_P = OFF_VF + 2 * VF_BYTES;
+constexpr int OFF_DKF = OFF_P + 2 * P_BYTES;
+constexpr int OFF_BAR = OFF_DKF + 2 * DKF_BYTES;
+constexpr int NBAR = 32;
+constexpr int OFF_MISC = OFF_BAR + NBAR * 8;        // tmem base address, abort flag
+constexpr int PF_SMEM_USED = OFF_MISC + 16;
+constexpr int PF_SMEM_BYTES = PF_SMEM_USED + 1024;
+static_assert(KST_BYTES <= KST_PAD && KST_PAD % 1024 == 0, "stage padding");
+static_assert(OFF_VF % 1024 == 0 && OFF_P % 1024 == 0 && OFF_K % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+static_assert(PF_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+
+// mbarrier indices
+enum {
+  B_QFULL = 0,
+  B_KFULL = 1,    // [2]
+  B_KEMPTY = 3,   // [2]
+  B_VFULL = 5,    // [2]
+  B_VEMPTY = 7,   // [2]
+  B_VFFULL = 9,   // [2]
+  B_VFEMPTY = 11, // [2]
+  B_DKEMPTY = 13, // [2]
+  B_SFULL = 15,   // [4]
+  B_SEMPTY = 19,  // [4]
+  B_PFULL = 23,   // [2]
+  B_PEMPTY = 25,  // [2]
+  B_ODONE = 27,
+};
+
+constexpr int PF_THREADS = 320;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TM_O = 0, TM_S = 256;
+constexpr uint32_t IDESC_QK = umma_idesc(2, 1, 1, 0, 0, QT, PT);    // s32 += s8 * s8, both K-major, M128 N64
+constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, QT, AD);    // f32 += f16 * f16, B MN-major, M128 N256
+
+struct PrefillParams {
+  const float* qn;   // [M][nqh][256]
+  const float* qg;   // [M][nqh][512]
+  float* o;          // [M][nqh][256]
+  float* part;       // [nsplit][M][nqh][258] when nsplit > 1
+  const int* pos0;
+  int* status;
+  int M, nqh, nkvh, n_ctx, nsplit;
+  float kq_scale;
+};
+
+__device__ __forceinline__ float i2f_exact(int v) { return __int_as_float(v + 0x4B400000) - 12582912.0f; }  // |v| < 2^22
+
+// Quantises one query row (256 floats at src, or zeros when src is null) to int8 with an f32
+// scale per 32 dims (src/attn.cu:587-606: v = q * kq_scale, d = amax / 127, id = 127 / amax,
+// q8 = rint(v * id)) and stores it as row r of the Q tile in the K-major 128B-swizzled layout.
+__device__ __forceinline__ void quantise_q_row(const float* src, float kq_scale, uint8_t* sQ, int r, float (&dq)[8]) {
+#pragma unroll
+  for (int b = 0; b < 8; b++) {
+    uint32_t w[8];
+    float d = 0.f;
+    if (src) {
+      float v[32];
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 f = *(const float4*)(src + b * 32 + j);
+        v[j] = __fmul_rn(f.x, kq_scale);
+        v[j + 1] = __fmul_rn(f.y, kq_scale);
+        v[j + 2] = __fmul_rn(f.z, kq_scale);
+        v[j + 3] = __fmul_rn(f.w, kq_scale);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[j]), fabsf(v[j + 1])), fmaxf(fabsf(v[j + 2]), fabsf(v[j + 3]))));
+      }
+      d = __fdiv_rn(amax, 127.f);
+      const float id = amax > 0.f ? __fdiv_rn(127.f, amax) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int q0 = __float2int_rn(__fmul_rn(v[4 * j], id)), q1 = __float2int_rn(__fmul_rn(v[4 * j + 1], id));
+        const int q2 = __float2int_rn(__fmul_rn(v[4 * j + 2], id)), q3 = __float2int_rn(__fmul_rn(v[4 * j + 3], id));
+        w[j] = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
+               ((uint32_t)(q3 & 0xFF) << 24);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; j++) w[j] = 0;
+    }
+    dq[b] = d;
+    uint8_t* half = sQ + (b >> 2) * (QT * 128);
+    const uint32_t c = 2 * (b & 3);
+    *(uint4*)(half + swz128(r, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+    *(uint4*)(half + swz128(r, c + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
+// Descriptors of the 32-byte k-block b of a K-major 128B-swizzled int8 tile made of two halves
+// of `rows` rows x 128 B.
+__device__ __forceinline__ uint64_t desc_kblock(uint32_t tile_addr, int rows, int b) {
+  return umma_desc_sw128(tile_addr + (b >> 2) * (rows * 128) + (b & 3) * 32, 16, 1024);
+}
+
+__global__ void __launch_bounds__(PF_THREADS, 1)
+prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_ks,
+                  const __grid_constant__ CUtensorMap tm_vv, const __grid_constant__ CUtensorMap tm_vs,
+                  const PrefillParams p) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  uint64_t* bar = (uint64_t*)(sgen + OFF_BAR);
+  uint32_t* tmem_slot = (uint32_t*)(sgen + OFF_MISC);
+  volatile int* abort_flag = (volatile int*)(sgen + OFF_MISC + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.y, kh = h / GQA;
+  const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * QT;  // long tiles first (src/attn.cu:567)
+  const int z = blockIdx.z, nsplit = p.nsplit;
+  const int pos0 = *p.pos0;
+  const int n_end = min(pos0 + min(t0 + QT, p.M), p.n_ctx);
+  const int ntot = (n_end + PT - 1) / PT;
+  const int per = (ntot + nsplit - 1) / nsplit;
+  const int it0 = min(ntot, z * per), it1 = min(ntot, it0 + per);
+  const int nt = it1 - it0;
+
+  if (nt <= 0) {  // nothing in this split: neutral partials
+    if (nsplit > 1 && tid < QT && t0 + tid < p.M) {
+      float* po = p.part + (((size_t)z * p.M + t0 + tid) * p.nqh + h) * PROW;
+      po[0] = M_INIT;
+      po[1] = 0.f;
+      for (int d = 0; d < AD; d++) po[2 + d] = 0.f;
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    mbar_init(&bar[B_QFULL], 4);
+    for (int s = 0; s < 2; s++) {
+      mbar_init(&bar[B_KFULL + s], 1);
+      mbar_init(&bar[B_KEMPTY + s], 5);
+      mbar_init(&bar[B_VFULL + s], 1);
+      mbar_init(&bar[B_VEMPTY + s], 4);
+      mbar_init(&bar[B_VFFULL + s], 4);
+      mbar_init(&bar[B_VFEMPTY + s], 1);
+      mbar_init(&bar[B_DKEMPTY + s], 4);
+      mbar_init(&bar[B_PFULL + s], 4);
+      mbar_init(&bar[B_PEMPTY + s], 1);
+    }
+    for (int s = 0; s < 4; s++) {
+      mbar_init(&bar[B_SFULL + s], 1);
+      mbar_init(&bar[B_SEMPTY + s], 4);
+    }
+    mbar_init(&bar[B_ODONE], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp < 4) {
+    // ================================================================ softmax warps
+    const int r = tid;                 // query row = TMEM lane
+    const int t = t0 + r;
+    const bool live = t < p.M;
+    float dq[8];
+    quantise_q_row(live ? p.qn + ((size_t)t * p.nqh + h) * AD : nullptr, p.kq_scale, sgen + OFF_Q, r, dq);
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bar[B_QFULL]);
+
+    const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
+    const int limit = pos0 + t + 1;    // positions < limit are visible
+    float m_run = M_INIT, m_ref = M_INIT, l = 0.f;
+
+    for (int j = 0; j < nt; j++) {
+      const int pb = j & 1, ph = (j >> 1) & 1;
+      const int p_tile = (it0 + j) * PT;
+      mbar_wait(&bar[B_VFFULL + pb], ph, abort_flag, p.status);  // K scale table of this tile is ready
+      const uint32_t dkf = sbase + OFF_DKF + pb * DKF_BYTES;
+      float s[PT];
+#pragma unroll
+      for (int i = 0; i < PT; i++) s[i] = 0.f;
+#pragma unroll
+      for (int b = 0; b < 8; b++) {
+        const int slot = b & 3;
+        mbar_wait(&bar[B_SFULL + slot], (b >> 2) & 1, abort_flag, p.status);
+        tc_fence_after();
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+          uint32_t v[32];
+          tmem_ld32(tlane + TM_S + slot * PT + hf * 32, v);
+          tc_wait_ld();
+          if (hf == 1) {  // both halves are in registers: the slot can be overwritten
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar[B_SEMPTY + slot]);
+          }
+#pragma unroll
+          for (int i4 = 0; i4 < 8; i4++) {
+            float4 dk;
+            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                         : "=f"(dk.x), "=f"(dk.y), "=f"(dk.z), "=f"(dk.w)
+                         : "r"(dkf + (b * PT + hf * 32 + i4 * 4) * 4));
+            const int i = hf * 32 + i4 * 4;
+            s[i] = fmaf(dq[b] * dk.x, i2f_exact((int)v[i4 * 4]), s[i]);
+            s[i + 1] = fmaf(dq[b] * dk.y, i2f_exact((int)v[i4 * 4 + 1]), s[i + 1]);
+            s[i + 2] = fmaf(dq[b] * dk.z, i2f_exact((int)v[i4 * 4 + 2]), s[i + 2]);
+            s[i + 3] = fmaf(dq[b] * dk.w, i2f_exact((int)v[i4 * 4 + 3]), s[i + 3]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[B_DKEMPTY + pb]);
+
+      // causal mask (only tiles that reach past the first row's limit need it) and the tile max
+      float mt = -INFINITY;
+      if (p_tile + PT > pos0 + t0 + 1) {
+#pragma unroll
+        for (int i = 0; i < PT; i++) {
+          if (p_tile + i >= limit) s[i] = -INFINITY;
+          mt = fmaxf(mt, s[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < PT; i++) mt = fmaxf(mt, s[i]);
+      }
+      m_run = fmaxf(m_run, mt);
+
+      // Move the reference max when the true max has run away from it (or on the first tile).
+      const bool want = m_run > m_ref + TAU;
+      if (__any_sync(0xffffffffu, want)) {
+        const float f = ex2((m_ref - m_run) * LOG2E);  // 0 on the first move (m_ref = -1e30)
+        m_ref = m_run;
+        l *= f;
+        if (j > 0) {
+          // O holds the sum of tiles < j once the P V of tile j-1 has completed.
+          mbar_wait(&bar[B_PEMPTY + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag, p.status);
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < AD / 32; c++) {
+            uint32_t v[32];
+            tmem_ld32(tlane + TM_O + c * 32, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+            tmem_st32(tlane + TM_O + c * 32, v);
+          }
+          tc_wait_st();
+          tc_fence_before();
+        }
+      }
+
+      // P = exp(s - m_ref): f32 row sum, f16 tile for the P V MMA
+      mbar_wait(&bar[B_PEMPTY + pb], ph ^ 1, abort_flag, p.status);
+      uint8_t* sP = sgen + OFF_P + pb * P_BYTES;
+      const float mb = m_ref * LOG2E;
+#pragma unroll
+      for (int c = 0; c < 8; c++) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          const float e0 = ex2(fmaf(s[c * 8 + 2 * k], LOG2E, -mb)), e1 = ex2(fmaf(s[c * 8 + 2 * k + 1], LOG2E, -mb));
+          l += e0 + e1;
+          w[k] = pack_h2(e0, e1);
+        }
+        *(uint4*)(sP + swz128(r, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[B_PFULL + pb]);
+    }
+
+    // ---- epilogue: O / l * sigmoid(gate), or the unnormalised partial of this split
+    mbar_wait(&bar[B_ODONE], 0, abort_flag, p.status);
+    tc_fence_after();
+    const float inv_l = 1.0f / l;
+    float* po = nsplit > 1 ? p.part + (((size_t)z * p.M + t) * p.nqh + h) * PROW : nullptr;
+    if (live && po) {
+      po[0] = m_ref;
+      po[1] = l;
+    }
+#pragma unroll 1
+    for (int c = 0; c < AD / 32; c++) {
+      uint32_t v[32];
+      tmem_ld32(tlane + TM_O + c * 32, v);
+      tc_wait_ld();
+      if (!live) continue;
+      if (po) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          *(float2*)(po + 2 + c * 32 + i) = make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+      } else {
+        const float* gt = p.qg + ((size_t)t * p.nqh + h) * 512 + 256 + c * 32;
+        float* dst = p.o + ((size_t)t * p.nqh + h) * AD + c * 32;
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 gg = *(const float4*)(gt + i);
+          float4 y;
+          y.x = (__uint_as_float(v[i]) * inv_l) * (1.0f / (1.0f + __expf(-gg.x)));
+          y.y = (__uint_as_float(v[i + 1]) * inv_l) * (1.0f / (1.0f + __expf(-gg.y)));
+          y.z = (__uint_as_float(v[i + 2]) * inv_l) * (1.0f / (1.0f + __expf(-gg.z)));
+          y.w = (__uint_as_float(v[i + 3]) * inv_l) * (1.0f / (1.0f + __expf(-gg.w)));
+          *(float4*)(dst + i) = y;
+        }
+      }
+    }
+    tc_fence_before();
+  } else if (warp < 8) {
+    // ================================================================ converter warps
+    const int ct = tid - 128;
+    for (int j = 0; j < nt; j++) {
+      const int pb = j & 1, ph = (j >> 1) & 1;
+      mbar_wait(&bar[B_VFULL + pb], ph, abort_flag, p.status);
+      mbar_wait(&bar[B_KFULL + pb], ph, abort_flag, p.status);
+      mbar_wait(&bar[B_VFEMPTY + pb], ph ^ 1, abort_flag, p.status);
+      mbar_wait(&bar[B_DKEMPTY + pb], ph ^ 1, abort_flag, p.status);
+      const uint8_t* vst = sgen + OFF_V + pb * KST_PAD;
+      const uint8_t* kst = sgen + OFF_K + pb * KST_PAD;
+      uint8_t* vf = sgen + OFF_VF + pb * VF_BYTES;
+      // V: 64 rows x 16 chunks of 16 int8 -> 16 f16 (one rounding of q * d, as src/attn.cu:59-76)
+#pragma unroll 2
+      for (int k = 0; k < 8; k++) {
+        const int q = ct + 128 * k, row = q >> 4, c16 = q & 15;
+        const uint4 x = *(const uint4*)(vst + (c16 >> 3) * (PT * 128) + swz128(row, c16 & 7));
+        const __half d = *(const __half*)(vst + 2 * PT * 128 + row * 16 + (c16 >> 1) * 2);
+        const __half2 dd = __half2half2(d);
+        const uint32_t xw[4] = {x.x ^ 0x80808080u, x.y ^ 0x80808080u, x.z ^ 0x80808080u, x.w ^ 0x80808080u};
+        uint32_t o[8];
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+          o[2 * w] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4140), dd);
+          o[2 * w + 1] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4342), dd);
+        }
+        uint8_t* dst = vf + (c16 >> 2) * (PT * 128);
+        const uint32_t cc = 2 * (c16 & 3);
+        *(uint4*)(dst + swz128(row, cc)) = make_uint4(o[0], o[1], o[2], o[3]);
+        *(uint4*)(dst + swz128(row, cc + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+      // K scales f16 [64][8] -> f32 [8][64]
+      {
+        float* dkf = (float*)(sgen + OFF_DKF + pb * DKF_BYTES);
+        const int row = ct >> 1, b0 = (ct & 1) * 4;
+        const uint2 sc = *(const uint2*)(kst + 2 * PT * 128 + row * 16 + b0 * 2);
+        const __half2 s01 = u32_as_h2(sc.x), s23 = u32_as_h2(sc.y);
+        dkf[(b0 + 0) * PT + row] = __low2float(s01);
+        dkf[(b0 + 1) * PT + row] = __high2float(s01);
+        dkf[(b0 + 2) * PT + row] = __low2float(s23);
+        dkf[(b0 + 3) * PT + row] = __high2float(s23);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bar[B_VFFULL + pb]);
+        mbar_arrive(&bar[B_VEMPTY + pb]);
+        mbar_arrive(&bar[B_KEMPTY + pb]);
+      }
+    }
+  } else if (warp == 8) {
+    // ================================================================ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_kv);
+      tma_prefetch_desc(&tm_ks);
+      tma_prefetch_desc(&tm_vv);
+      tma_prefetch_desc(&tm_vs);
+      for (int j = 0; j < nt; j++) {
+        const int pb = j & 1, ph = (j >> 1) & 1;
+        const int row = kh * p.n_ctx + (it0 + j) * PT;
+        uint8_t* kst = sgen + OFF_K + pb * KST_PAD;
+        uint8_t* vst = sgen + OFF_V + pb * KST_PAD;
+        mbar_wait(&bar[B_KEMPTY + pb], ph ^ 1, abort_flag, p.status);
+        mbar_expect_tx(&bar[B_KFULL + pb], KST_BYTES);
+        tma_load_2d(kst, &tm_kv, 0, row, &bar[B_KFULL + pb]);
+        tma_load_2d(kst + PT * 128, &tm_kv, 128, row, &bar[B_KFULL + pb]);
+        tma_load_2d(kst + 2 * PT * 128, &tm_ks, 0, row, &bar[B_KFULL + pb]);
+        mbar_wait(&bar[B_VEMPTY + pb], ph ^ 1, abort_flag, p.status);
+        mbar_expect_tx(&bar[B_VFULL + pb], KST_BYTES);
+        tma_load_2d(vst, &tm_vv, 0, row, &bar[B_VFULL + pb]);
+        tma_load_2d(vst + PT * 128, &tm_vv, 128, row, &bar[B_VFULL + pb]);
+        tma_load_2d(vst + 2 * PT * 128, &tm_vs, 0, row, &bar[B_VFULL + pb]);
+      }
+    }
+  } else {
+    // ================================================================ MMA issuer
+    if (lane == 0) {
+      mbar_wait(&bar[B_QFULL], 0, abort_flag, p.status);
+      tc_fence_after();
+      auto issue_pv = [&](int jj) {
+        const int pb = jj & 1, ph = (jj >> 1) & 1;
+        mbar_wait(&bar[B_PFULL + pb], ph, abort_flag, p.status);
+        mbar_wait(&bar[B_VFFULL + pb], ph, abort_flag, p.status);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < PT / 16; kk++) {
+          const uint64_t da = umma_desc_sw128(sbase + OFF_P + pb * P_BYTES + kk * 32, 16, 1024);
+          const uint64_t db = umma_desc_sw128(sbase + OFF_VF + pb * VF_BYTES + kk * 2048, PT * 128, 1024);
+          tc_mma_f16(tmem + TM_O, da, db, IDESC_PV, (jj > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&bar[B_PEMPTY + pb]);
+        tc_commit(&bar[B_VFEMPTY + pb]);
+      };
+      for (int j = 0; j < nt; j++) {
+        const int pb = j & 1, ph = (j >> 1) & 1;
+        mbar_wait(&bar[B_KFULL + pb], ph, abort_flag, p.status);
+        tc_fence_after();
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+          const int slot = b & 3;
+          mbar_wait(&bar[B_SEMPTY + slot], ((b >> 2) & 1) ^ 1, abort_flag, p.status);
+          tc_fence_after();
+          tc_mma_i8(tmem + TM_S + slot * PT, desc_kblock(sbase + OFF_Q, QT, b),
+                    desc_kblock(sbase + OFF_K + pb * KST_PAD, PT, b), IDESC_QK, 0u);
+          tc_commit(&bar[B_SFULL + slot]);
+        }
+        tc_commit(&bar[B_KEMPTY + pb]);
+        if (j >= 1) issue_pv(j - 1);
+      }
+      issue_pv(nt - 1);
+      tc_commit(&bar[B_ODONE]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- integer-stage test hook
+// 128 threads: quantise up to 128 rows, load one 64-row K tile by TMA, run the 8 block MMAs into
+// 8 x 64 TMEM columns, dump everything.
+struct QkDebugParams {
+  const float* x;
+  int rows;
+  float kq_scale;
+  int row0;   // first row of the K tile in the cache's row space
+  int npos;
+  int8_t* q_i8;
+  float* q_scale;
+  int32_t* acc;
+  int* status;
+};
+constexpr int DBG_OFF_K = SQ_BYTES;
+constexpr int DBG_OFF_BAR = DBG_OFF_K + 2 * PT * 128;
+constexpr int DBG_SMEM = DBG_OFF_BAR + 64 + 1024;
+
+__global__ void __launch_bounds__(128, 1)
+prefill_qk_debug_kernel(const __grid_constant__ CUtensorMap tm_kv, const QkDebugParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  uint64_t* bar = (uint64_t*)(sgen + DBG_OFF_BAR);
+  uint32_t* tmem_slot = (uint32_t*)(sgen + DBG_OFF_BAR + 32);
+  volatile int* abort_flag = (volatile int*)(sgen + DBG_OFF_BAR + 36);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  float dq[8];
+  quantise_q_row(tid < p.rows ? p.x + (size_t)tid * AD : nullptr, p.kq_scale, sgen, tid, dq);
+  if (tid < p.rows) {
+    for (int b = 0; b < 8; b++) p.q_scale[tid * 8 + b] = dq[b];
+    for (int b = 0; b < 8; b++)
+      for (int c = 0; c < 2; c++) {
+        const uint4 w = *(const uint4*)(sgen + (b >> 2) * (QT * 128) + swz128(tid, 2 * (b & 3) + c));
+        *(uint4*)(p.q_i8 + (size_t)tid * AD + b * 32 + c * 16) = w;
+      }
+  }
+  fence_proxy_async();
+  __syncthreads();
+  if (tid == 0) {
+    mbar_expect_tx(&bar[0], 2 * PT * 128);
+    tma_load_2d(sgen + DBG_OFF_K, &tm_kv, 0, p.row0, &bar[0]);
+    tma_load_2d(sgen + DBG_OFF_K + PT * 128, &tm_kv, 128, p.row0, &bar[0]);
+    mbar_wait(&bar[0], 0, abort_flag, p.status);
+    tc_fence_after();
+    for (int b = 0; b < 8; b++)
+      tc_mma_i8(tmem + b * PT, desc_kblock(sbase, QT, b), desc_kblock(sbase + DBG_OFF_K, PT, b), IDESC_QK, 0u);
+    tc_commit(&bar[1]);
+  }
+  mbar_wait(&bar[1], 0, abort_flag, p.status);
+  tc_fence_after();
+  const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
+  for (int b = 0; b < 8; b++)
+    for (int hf = 0; hf < 2; hf++) {
+      uint32_t v[32];
+      tmem_ld32(tlane + b * PT + hf * 32, v);
+      tc_wait_ld();
+      if (tid < p.rows)
+        for (int i = 0; i < 32; i++) {
+          const int pp = hf * 32 + i;
+          if (pp < p.npos) p.acc[((size_t)tid * p.npos + pp) * 8 + b] = (int32_t)v[i];
+        }
+    }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+struct TmapPair {
+  const void* base;
+  int nkvh, n_ctx;
+  CUtensorMap vals, scales;
+};
+constexpr int TMAP_CACHE = 64;
+TmapPair g_tmaps[TMAP_CACHE];
+int g_tmap_next = 0;
+
+int get_tmaps(const void* cache, int nkvh, int n_ctx, const CUtensorMap** vals, const CUtensorMap** scales) {
+  for (int i = 0; i < TMAP_CACHE; i++)
+    if (g_tmaps[i].base == cache && g_tmaps[i].nkvh == nkvh && g_tmaps[i].n_ctx == n_ctx) {
+      *vals = &g_tmaps[i].vals;
+      *scales = &g_tmaps[i].scales;
+      return Q27B_OK;
+    }
+  TmapPair& k = g_tmaps[g_tmap_next];
+  g_tmap_next = (g_tmap_next + 1) % TMAP_CACHE;
+  k.base = nullptr;
+  const uint64_t rows = (uint64_t)nkvh * n_ctx;
+  if (int rc = make_tmap_2d(&k.vals, cache, rows, AD, AD, 128, PT, true)) return rc;
+  if (int rc = make_tmap_2d(&k.scales, (const uint8_t*)cache + rows * AD, rows, 16, 16, 16, PT, false)) return rc;
+  k.base = cache;
+  k.nkvh = nkvh;
+  k.n_ctx = n_ctx;
+  *vals = &k.vals;
+  *scales = &k.scales;
+  return Q27B_OK;
+}
+
+}  // namespace
+}  // namespace q27b
+
+using namespace q27b;
+
+extern "C" {
+
+int q27b_attn_prefill(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
+                      const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, int q8, void* stream,
+                      int depth_hint) {
+  if (nkvh < 1 || nqh != nkvh * GQA || M < 1 || n_ctx < 1) return fail(Q27B_BAD_SHAPE, "attn_prefill: bad shape");
+  if (!qn || !qg || !kcache || !vcache || !o || !pos0) return fail(Q27B_BAD_SHAPE, "attn_prefill: null pointer");
+  if (!q8) return fail(Q27B_UNSUPPORTED, "attn_prefill: only the q8_0 cache (int8 Q K^T path) is built");
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (!ctx->prefill_attr) {
+    Q27B_CK(cudaFuncSetAttribute(prefill_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_BYTES));
+    Q27B_CK(cudaFuncSetAttribute(prefill_qk_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DBG_SMEM));
+    ctx->prefill_attr = true;
+  }
+  const int tiles = (M + QT - 1) / QT;
+  const int ctas = tiles * nqh;
+  // Splits over the positions: enough CTAs for every SM, at least 2048 positions per split
+  // (the reference's rule, src/attn.cu:945-951, with this kernel's CTA count).
+  int nsplit = 1;
+  if (depth_hint >= 0) nsplit = std::max(1, std::min({8, (2 * ctx->n_sm + ctas - 1) / ctas, (depth_hint + M) / 2048}));
+  if (const char* e = getenv("Q27_ATTN_SPLIT")) {  // same switch as the reference (src/attn.cu:952)
+    const int f = atoi(e);
+    if (f > 0) nsplit = std::min(f, 64);
+  }
+  if (nsplit > 1)
+    if (int rc = ensure_part(ctx, (size_t)nsplit * M * nqh * PROW)) return rc;
+  const CUtensorMap *kv, *ks, *vv, *vs;
+  if (int rc = get_tmaps(kcache, nkvh, n_ctx, &kv, &ks)) return rc;
+  if (int rc = get_tmaps(vcache, nkvh, n_ctx, &vv, &vs)) return rc;
+  PrefillParams p = {};
+  p.qn = qn; p.qg = qg; p.o = o; p.part = nsplit > 1 ? ctx->part : nullptr; p.pos0 = pos0; p.status = ctx->status;
+  p.M = M; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nsplit = nsplit; p.kq_scale = kq_scale;
+  prefill_i8_kernel<<<dim3(tiles, nqh, nsplit), PF_THREADS, PF_SMEM_BYTES, s>>>(*kv, *ks, *vv, *vs, p);
+  Q27B_CK(cudaGetLastError());
+  if (nsplit > 1) {
+    MergeParams mp = {};
+    mp.part = ctx->part; mp.nparts = nsplit; mp.part_stride = (int64_t)M * nqh * PROW; mp.rows = (int64_t)M * nqh;
+    mp.qg = qg; mp.o = o;
+    return launch_merge(mp, false, s);
+  }
+  return Q27B_OK;
+}
+
+int q27b_prefill_qk_debug(const float* x, int rows, float kq_scale, const void* kcache, int nkvh, int n_ctx, int kh,
+                          int p0, int npos, int8_t* q_i8, float* q_scale, int32_t* acc, void* stream) {
+  if (rows < 1 || rows > QT || npos < 1 || npos > PT || kh < 0 || kh >= nkvh || p0 < 0 || p0 + npos > n_ctx)
+    return fail(Q27B_BAD_SHAPE, "prefill_qk_debug: bad shape");
+  if (!x || !kcache || !q_i8 || !q_scale || !acc) return fail(Q27B_BAD_SHAPE, "prefill_qk_debug: null pointer");
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  if (!ctx->prefill_attr) {
+    Q27B_CK(cudaFuncSetAttribute(prefill_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_BYTES));
+    Q27B_CK(cudaFuncSetAttribute(prefill_qk_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DBG_SMEM));
+    ctx->prefill_attr = true;
+  }
+  const CUtensorMap *kv, *ks;
+  if (int rc = get_tmaps(kcache, nkvh, n_ctx, &kv, &ks)) return rc;
+  QkDebugParams p = {x, rows, kq_scale, kh * n_ctx + p0, npos, q_i8, q_scale, acc, ctx->status};
+  prefill_qk_debug_kernel<<<1, 128, DBG_SMEM, (cudaStream_t)stream>>>(*kv, p);
+  Q27B_CK(cudaGetLastError());
+  return Q27B_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,93 @@
+"""Partitioning of the attention path over the GPUs of one box, one process per GPU.
+
+The reference shards attention by KV head only (2 KV heads + their 12 query heads per card,
+src/model.cu:161-164) and never exchanges anything inside attention. The same split is used here
+up to 4 GPUs; beyond that one sequence is also split by KV length, and the only exchange of the
+path appears: each rank's (m, l, O) partial of 6*T rows (24.8 KB at T = 4) is all-gathered among
+the ranks that share a head group and merged by the log-sum-exp kernel. Batched decode shards whole
+sequences, with no exchange. The collective is torch.distributed (NCCL on GPUs, gloo in CPU tests).
+"""
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+TILE = 64
+
+
+@dataclass
+class SeqShard:
+    rank: int
+    world: int
+    kv_head0: int     # first KV head of this rank
+    n_kv_heads: int   # KV heads of this rank
+    z: int            # index of this rank's KV-length slice
+    nz: int           # KV-length slices per head group
+    peers: tuple      # ranks holding the other slices of the same heads (including this rank), by z
+
+
+def plan_single_sequence(rank, world, nkvh=4):
+    """KV-head groups first, then KV-length slices once there are more ranks than KV heads."""
+    if world < 1 or rank < 0 or rank >= world:
+        raise ValueError("bad rank/world")
+    if world <= nkvh:
+        if nkvh % world:
+            raise ValueError("world must divide the KV heads")
+        per = nkvh // world
+        return SeqShard(rank, world, rank * per, per, 0, 1, (rank,))
+    if world % nkvh:
+        raise ValueError("world must be a multiple of the KV heads")
+    nz = world // nkvh
+    hg, z = rank // nz, rank % nz
+    return SeqShard(rank, world, hg, 1, z, nz, tuple(hg * nz + i for i in range(nz)))
+
+
+def kv_slice(n, z, nz):
+    """Positions [lo, hi) of KV-length slice z of nz; boundaries are multiples of the 64-position tile."""
+    per = -(-n // nz)
+    per = -(-per // TILE) * TILE
+    lo = min(n, z * per)
+    return lo, min(n, lo + per)
+
+
+def shard_sequences(lengths, world):
+    """Greedy longest-first assignment of sequences to ranks, balanced by KV length.
+    Returns a list of index lists, one per rank."""
+    order = sorted(range(len(lengths)), key=lambda i: (-int(lengths[i]), i))
+    load = [0] * world
+    out = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda j: (load[j], j))
+        out[r].append(i)
+        load[r] += int(lengths[i])
+    return [sorted(x) for x in out]
+
+
+_groups = {}
+
+
+def peer_group(shard):
+    """Process group of the ranks that share this rank's KV heads. Every rank must call this
+    (new_group is collective over the default group)."""
+    if shard.nz == 1:
+        return None
+    key = (shard.world, shard.nz)
+    if key not in _groups:
+        nkvh_groups = shard.world // shard.nz
+        gs = [dist.new_group([g * shard.nz + i for i in range(shard.nz)]) for g in range(nkvh_groups)]
+        _groups[key] = gs
+    return _groups[key][shard.rank // shard.nz]
+
+
+def gather_partials(part, shard, group=None):
+    """part [rows][258] of this rank -> [nz][rows][258] holding every KV-length slice of the head
+    group, in slice order. The result lives in this rank's own memory before anything reads it."""
+    if shard.nz == 1:
+        return part.unsqueeze(0)
+    out = torch.empty((shard.nz,) + tuple(part.shape), dtype=part.dtype, device=part.device)
+    if part.is_cuda:
+        dist.all_gather_into_tensor(out, part.contiguous(), group=group)
+    else:
+        lst = [out[i] for i in range(shard.nz)]
+        dist.all_gather(lst, part.contiguous(), group=group)
+    return out

@@ -1,0 +1,50 @@
+"""The seeded cases of tests/golden/ref_b200.npz, shared by the script that makes the fixture (on
+a B200, from the reference's own kernels) and the tests that read it."""
+import numpy as np
+
+AD = 256
+
+CASES = {
+    # attn_prep: RMSNorm + RoPE + cache write. The V rows pin the q8_0 quantiser (V is written raw).
+    "prep_q8": dict(kind="prep", T=4, nqh=12, nkvh=2, n_ctx=64, pos0=20, q8=True, eps=1e-6,
+                    theta_scale=float(10000000.0 ** (-2.0 / 64))),
+    "prep_f16": dict(kind="prep", T=2, nqh=6, nkvh=1, n_ctx=16, pos0=3, q8=False, eps=1e-6,
+                     theta_scale=float(10000000.0 ** (-2.0 / 64))),
+    "prep_q8_many": dict(kind="prep", T=256, nqh=6, nkvh=1, n_ctx=256, pos0=0, q8=True, eps=1e-6,
+                         theta_scale=float(10000000.0 ** (-2.0 / 64))),
+    # decode: the reference's slow kernel (attn_decode_ref) and its fast kernel (attn_decode)
+    "decode_cfg1": dict(kind="decode", T=1, nkvh=4, n=1024, n_ctx=1024, q8=True, scale=1 / 16),
+    "decode_t4": dict(kind="decode", T=4, nkvh=2, n=2500, n_ctx=2504, q8=True, scale=1 / 16, q8_1=True),
+    "decode_f16": dict(kind="decode", T=4, nkvh=1, n=700, n_ctx=704, q8=False, scale=1 / 16),
+    # prefill: the reference's int8 Q K^T kernel, and its slow f16-Q kernel on the same rows
+    "prefill_a": dict(kind="prefill", M=40, nkvh=1, pos0=300, n_ctx=344, scale=1 / 16),
+    "prefill_b": dict(kind="prefill", M=37, nkvh=1, pos0=0, n_ctx=40, scale=1 / 16),
+}
+
+
+def case_inputs(name):
+    from qwen27_engine_b200 import synth
+    c = CASES[name]
+    tag = (sorted(CASES).index(name) + 1) << 26  # disjoint slices of the streams per case
+    if c["kind"] == "prep":
+        T, nqh, nkvh = c["T"], c["nqh"], c["nkvh"]
+        return dict(qg=synth.normal(synth.SEED_Q, (T, nqh, 512), start=tag),
+                    k=synth.normal(synth.SEED_K, (T, nkvh, AD), start=tag),
+                    v=synth.normal(synth.SEED_V, (T, nkvh, AD), start=tag) * np.float32(1.7),
+                    q_norm=(1 + 0.1 * synth.normal(synth.SEED_GATE, (AD,), start=tag)).astype(np.float32),
+                    k_norm=(1 + 0.1 * synth.normal(synth.SEED_GATE, (AD,), start=tag + 4096)).astype(np.float32))
+    if c["kind"] == "decode":
+        T, nkvh, n = c["T"], c["nkvh"], c["n"]
+        nqh = nkvh * 6
+        qn = synth.normal(synth.SEED_Q, (T, nqh, AD), start=tag)
+        qg = np.zeros((T, nqh, 512), np.float32)
+        qg[..., 256:] = synth.normal(synth.SEED_GATE, (T, nqh, AD), start=tag)
+        return dict(qn=qn, qg=qg, k=synth.normal(synth.SEED_K, (nkvh, n, AD), start=tag),
+                    v=synth.normal(synth.SEED_V, (nkvh, n, AD), start=tag))
+    M, nkvh, n = c["M"], c["nkvh"], c["pos0"] + c["M"]
+    nqh = nkvh * 6
+    qn = synth.normal(synth.SEED_Q, (M, nqh, AD), start=tag)
+    qg = np.zeros((M, nqh, 512), np.float32)
+    qg[..., 256:] = synth.normal(synth.SEED_GATE, (M, nqh, AD), start=tag)
+    return dict(qn=qn, qg=qg, k=synth.normal(synth.SEED_K, (nkvh, n, AD), start=tag),
+                v=synth.normal(synth.SEED_V, (nkvh, n, AD), start=tag))

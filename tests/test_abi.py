@@ -1,0 +1,73 @@
+"""The C-ABI library loads without a GPU, exports every symbol that include/q27b_attn.h declares,
+and rejects bad shapes on the host with the reference's error behaviour (src/attn.cu:906,929)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "q27b_attn.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(q27b_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_exports_every_declared_symbol(q27):
+    lib = ctypes.CDLL(q27.LIB_PATH)
+    names = declared_symbols()
+    assert len(names) >= 14
+    for n in names:
+        assert hasattr(lib, n), "missing export " + n
+    assert sorted(q27.SYMBOLS) == names
+
+
+def test_cache_sizes(q27):
+    assert q27.kv_cache_bytes(4, 150008, True) == 4 * 150008 * 272
+    assert q27.kv_cache_bytes(2, 1000, False) == 2 * 1000 * 512
+    assert q27.kv_pool_bytes(4, 10) == 10 * 4 * 256 * 272
+
+
+def test_bad_shapes_are_rejected_on_the_host(q27):
+    lib = ctypes.CDLL(q27.LIB_PATH)
+    lib.q27b_last_error.restype = ctypes.c_char_p
+    null = ctypes.c_void_p(0)
+    one = ctypes.c_void_p(16)  # never dereferenced: the shape check comes first
+    f = ctypes.c_float(0.0625)
+    # T out of range, and nqh != 6 * nkvh
+    for T, nqh, nkvh in [(0, 24, 4), (5, 24, 4), (4, 20, 4)]:
+        rc = lib.q27b_attn_decode(one, one, one, one, one, null, null, one, T, f, nqh, nkvh, 1024, 1, null)
+        assert rc == q27.BAD_SHAPE
+        assert b"attn_decode: bad shape" in lib.q27b_last_error()
+    rc = lib.q27b_attn_prefill(one, one, one, one, one, one, 0, f, 24, 4, 1024, 1, null, -1)
+    assert rc == q27.BAD_SHAPE and b"attn_prefill: bad shape" in lib.q27b_last_error()
+    rc = lib.q27b_attn_prefill(one, one, one, one, one, one, 16, f, 25, 4, 1024, 1, null, -1)
+    assert rc == q27.BAD_SHAPE
+    rc = lib.q27b_attn_decode(null, one, one, one, one, null, null, one, 4, f, 24, 4, 1024, 1, null)
+    assert rc == q27.BAD_SHAPE and b"null pointer" in lib.q27b_last_error()
+    rc = lib.q27b_kv_append(one, one, one, one, one, 0, 4, 1024, 1, null)
+    assert rc == q27.BAD_SHAPE
+    rc = lib.q27b_lse_merge(null, 2, ctypes.c_int64(0), ctypes.c_int64(1), null, one, null, null, null)
+    assert rc == q27.BAD_SHAPE
+
+
+def test_python_mirror_raises(q27):
+    with pytest.raises(RuntimeError):
+        q27.kv_append(None, None, None, None, None, 1, 4, 16)
+
+
+def test_shim_header_compiles():
+    """The C++ shim with the reference's signatures compiles against the C ABI (host only)."""
+    import subprocess
+    import tempfile
+    src = '#include "ops_attn.h"\nint main() { return (int)q27::kv_cache_bytes(4, 16, true) == 4 * 16 * 272 ? 0 : 1; }\n'
+    with tempfile.TemporaryDirectory() as d:
+        p = os.path.join(d, "t.cpp")
+        open(p, "w").write(src)
+        pkg = os.path.join(ROOT, "qwen27-engine_b200")
+        exe = os.path.join(d, "t")
+        subprocess.check_call(["g++", "-std=c++17", "-I", os.path.join(pkg, "shim"), "-I", "/usr/local/cuda/include", p,
+                               "-L", pkg, "-lq27b_attn", "-Wl,-rpath," + pkg, "-o", exe])
+        assert subprocess.call([exe]) == 0

@@ -1,0 +1,172 @@
+"""Decode attention on the GPU through the C ABI against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close
+from helpers_gpu import dev, pos_tensor, poisoned_cache
+
+pytestmark = pytest.mark.gpu
+AD, GQA = 256, 6
+SCALE = 1.0 / 16.0
+
+
+def run_decode(q27, orc, T, nkvh, n, n_ctx=None, seed_shift=0, check=True, q8_1=False):
+    from qwen27_engine_b200 import synth
+    nqh = nkvh * GQA
+    n_ctx = n_ctx or n + 11
+    qn, qg, kf, vf = synth.decode_inputs(T, nqh, nkvh, n, start_kv=seed_shift)
+    kc_ref, vc_ref = orc.fill_cache(kf, vf, n_ctx)
+    kc = poisoned_cache(q27, kc_ref, nkvh, n_ctx, n)
+    vc = poisoned_cache(q27, vc_ref, nkvh, n_ctx, n)
+    o = torch.full((T, nqh, AD), float("nan"), device="cuda")
+    q27.attn_decode(dev(qn), dev(qg), kc, vc, o, None, None, pos_tensor(n - T), T, SCALE, nqh, nkvh, n_ctx)
+    torch.cuda.synchronize()
+    out = o.cpu().numpy()
+    if check:
+        ref = orc.attn_ref(qn, qg, kc_ref, vc_ref, n - T, SCALE, nkvh, n_ctx)
+        assert_close(out, ref, "decode T=%d nkvh=%d n=%d" % (T, nkvh, n))
+    return out, (qn, qg, kc, vc, kc_ref, vc_ref)
+
+
+def test_config1_cpu_checkable(q27, orc):
+    """1 query token, 24 Q / 4 KV heads, KV length 1024."""
+    run_decode(q27, orc, 1, 4, 1024)
+    assert q27.device_status() == 0
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 4])
+@pytest.mark.parametrize("n", [4, 5, 7, 33, 63, 64, 65, 100, 127, 128, 129, 1000, 4096, 4100, 9472, 9473, 20011])
+def test_decode_depths(q27, orc, T, n):
+    if n < T:
+        pytest.skip("fewer positions than query tokens")
+    run_decode(q27, orc, T, 2, n)
+
+
+@pytest.mark.parametrize("nkvh", [1, 2, 4])
+def test_decode_head_counts(q27, orc, nkvh):
+    run_decode(q27, orc, 4, nkvh, 3000)
+    assert q27.device_status() == 0
+
+
+def test_config2_spec_verify_32k(q27, orc):
+    """4 query tokens (causal inside the block), 24 Q / 4 KV heads, q8_0 KV length 32,768."""
+    run_decode(q27, orc, 4, 4, 32768)
+
+
+def test_config3_long_context(q27, orc):
+    for n in (30000, 100000, 150000):
+        run_decode(q27, orc, 4, 4, n, n_ctx=n + 8)
+    assert q27.device_status() == 0
+
+
+def test_causal_inside_the_block(q27, orc):
+    """Token t must not see the K/V of tokens t+1..: changing them leaves its output unchanged."""
+    T, nkvh, n = 4, 1, 500
+    out, (qn, qg, kc, vc, kc_ref, vc_ref) = run_decode(q27, orc, T, nkvh, n)
+    kc2, vc2 = kc.clone(), vc.clone()
+    n_ctx = n + 11
+    # overwrite the last row (position n-1, visible to the last token only)
+    kc2[: n_ctx * AD].view(n_ctx, AD)[n - 1] = 77
+    vc2[: n_ctx * AD].view(n_ctx, AD)[n - 1] = 99
+    o2 = torch.empty((T, nkvh * GQA, AD), device="cuda")
+    q27.attn_decode(dev(qn), dev(qg), kc2, vc2, o2, None, None, pos_tensor(n - T), T, SCALE, nkvh * GQA, nkvh, n_ctx)
+    torch.cuda.synchronize()
+    o2 = o2.cpu().numpy()
+    assert np.array_equal(o2[:3], out[:3]) and not np.array_equal(o2[3], out[3])
+
+
+def test_run_twice_bitwise(q27, orc):
+    a, _ = run_decode(q27, orc, 4, 4, 12345, check=False)
+    b, _ = run_decode(q27, orc, 4, 4, 12345, check=False)
+    assert np.array_equal(a, b)
+
+
+def test_q8_1_epilogue(q27, orc):
+    """With xq the result leaves as q8_1: exactly the oracle's q8_1 of the kernel's own f32 result."""
+    T, nkvh, n = 4, 2, 2000
+    nqh = nkvh * GQA
+    out, (qn, qg, kc, vc, _, _) = run_decode(q27, orc, T, nkvh, n)
+    xq = torch.zeros((T, nqh, AD), dtype=torch.int8, device="cuda")
+    xd = torch.zeros((T * nqh * 8,), dtype=torch.float32, device="cuda")
+    q27.attn_decode(dev(qn), dev(qg), kc, vc, None, xq, xd, pos_tensor(n - T), T, SCALE, nqh, nkvh, n + 11)
+    torch.cuda.synchronize()
+    rq, rd = orc.q8_1(out.reshape(-1))
+    assert np.array_equal(xq.cpu().numpy().reshape(-1), rq) and np.array_equal(xd.cpu().numpy(), rd)
+
+
+@pytest.mark.parametrize("n,cuts", [(1000, [0, 512, 1000]), (5000, [0, 1280, 2560, 3840, 5000]), (300, [0, 64, 300])])
+def test_kv_length_partials_merge(q27, orc, n, cuts):
+    """One sequence split by KV length (each slice a cache of its own, as on separate GPUs):
+    per-slice partials + the log-sum-exp merge = the whole."""
+    from qwen27_engine_b200 import synth
+    T, nkvh = 4, 2
+    nqh = nkvh * GQA
+    qn, qg, kf, vf = synth.decode_inputs(T, nqh, nkvh, n)
+    parts, refs = [], []
+    full_k, full_v = orc.fill_cache(kf, vf, n)
+    for lo, hi in zip(cuts, cuts[1:]):
+        n_ctx = hi - lo + 3
+        kc_ref, vc_ref = orc.fill_cache(kf[:, lo:hi], vf[:, lo:hi], n_ctx)
+        kc = poisoned_cache(q27, kc_ref, nkvh, n_ctx, hi - lo)
+        vc = poisoned_cache(q27, vc_ref, nkvh, n_ctx, hi - lo)
+        part = torch.full((T, nqh, 258), float("nan"), device="cuda")
+        q27.attn_decode_partial(dev(qn), kc, vc, part, pos_tensor(n - T), T, SCALE, nqh, nkvh, n_ctx, lo, hi - lo)
+        parts.append(part)
+        refs.append(orc.attn_partial(qn, full_k, full_v, n - T, SCALE, nkvh, n, lo, hi))
+    allp = torch.stack(parts).contiguous()
+    o = torch.empty((T, nqh, AD), device="cuda")
+    q27.lse_merge(allp, len(parts), T * nqh * 258, T * nqh, dev(qg), o)
+    torch.cuda.synchronize()
+    whole = orc.attn_ref(qn, qg, full_k, full_v, n - T, SCALE, nkvh, n)
+    assert_close(o.cpu().numpy(), whole, "merged slices")
+    # each partial, normalised on its own, against the oracle's partial
+    for part, ref in zip(parts, refs):
+        a = part.cpu().numpy()
+        live = ref[..., 1] > 0
+        assert np.array_equal(a[..., 1] > 0, live)
+        ya = a[..., 2:][live] / a[..., 1:2][live]
+        yr = ref[..., 2:][live] / ref[..., 1:2][live]
+        assert_close(ya, yr, "slice partial")
+        lse_a = a[..., 0][live] + np.log(a[..., 1][live])
+        lse_r = ref[..., 0][live] + np.log(ref[..., 1][live])
+        assert np.abs(lse_a - lse_r).max() < 2e-3
+    assert q27.device_status() == 0
+
+
+def test_lse_merge_generic(q27, orc):
+    rng = np.random.default_rng(5)
+    nparts, rows = 7, 50
+    parts = rng.standard_normal((nparts, rows, 258)).astype(np.float32)
+    parts[..., 1] = np.abs(parts[..., 1]) + 0.1
+    parts[3, :, 0] = -1e30   # an empty partial is neutral
+    parts[3, :, 1:] = 0
+    qg = rng.standard_normal((rows, 512)).astype(np.float32)
+    ref = orc.lse_merge(parts, qg)
+    o = torch.empty((rows, AD), device="cuda")
+    q27.lse_merge(dev(parts), nparts, rows * 258, rows, dev(qg), o)
+    torch.cuda.synchronize()
+    assert np.abs(o.cpu().numpy() - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())
+    ref2 = orc.lse_merge(parts, None)
+    q27.lse_merge(dev(parts), nparts, rows * 258, rows, None, o)
+    torch.cuda.synchronize()
+    assert np.abs(o.cpu().numpy() - ref2).max() <= 1e-5 * max(1.0, np.abs(ref2).max())
+
+
+def test_f16_cache_is_reported_unsupported_or_correct(q27, orc):
+    """The f16 KV variant: either built (then it must match the oracle) or refused loudly."""
+    from qwen27_engine_b200 import synth
+    T, nkvh, n = 4, 2, 777
+    nqh = nkvh * GQA
+    qn, qg, kf, vf = synth.decode_inputs(T, nqh, nkvh, n)
+    kc_ref, vc_ref = orc.fill_cache(kf, vf, n + 5, q8=False)
+    o = torch.empty((T, nqh, AD), device="cuda")
+    try:
+        q27.attn_decode(dev(qn), dev(qg), poisoned_cache(q27, kc_ref, nkvh, n + 5, n, False),
+                        poisoned_cache(q27, vc_ref, nkvh, n + 5, n, False), o, None, None, pos_tensor(n - T), T, SCALE,
+                        nqh, nkvh, n + 5, q8=False)
+    except q27.Q27Error as e:
+        assert e.code == q27.UNSUPPORTED
+        pytest.skip("f16 KV decode not built: " + str(e))
+    torch.cuda.synchronize()
+    assert_close(o.cpu().numpy(), orc.attn_ref(qn, qg, kc_ref, vc_ref, n - T, SCALE, nkvh, n + 5, q8=False), "f16 KV")

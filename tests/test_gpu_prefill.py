@@ -1,0 +1,111 @@
+"""Prefill attention (int8 Q K^T on tcgen05) on the GPU through the C ABI against the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close
+from helpers_gpu import dev, pos_tensor, poisoned_cache
+
+pytestmark = pytest.mark.gpu
+AD, GQA = 256, 6
+SCALE = 1.0 / 16.0
+
+
+def make_case(orc, M, pos0, nkvh, n_ctx=None):
+    from qwen27_engine_b200 import synth
+    nqh = nkvh * GQA
+    n = pos0 + M
+    n_ctx = n_ctx or n + 9
+    qn = synth.normal(synth.SEED_Q, (M, nqh, AD))
+    qg = np.zeros((M, nqh, 512), np.float32)
+    qg[..., 256:] = synth.normal(synth.SEED_GATE, (M, nqh, AD))
+    kf = synth.normal(synth.SEED_K, (nkvh, n, AD))
+    vf = synth.normal(synth.SEED_V, (nkvh, n, AD))
+    kc, vc = orc.fill_cache(kf, vf, n_ctx)
+    return qn, qg, kc, vc, n, n_ctx
+
+
+@pytest.mark.parametrize("rows,npos,p0", [(128, 64, 0), (37, 64, 100), (128, 17, 5), (1, 1, 63)])
+def test_integer_stage_bit_exact(q27, orc, rows, npos, p0):
+    """int8 Q bytes, f32 Q scales and the per-32-block int32 Q K^T accumulators: bit-exact."""
+    from qwen27_engine_b200 import synth
+    nkvh, kh, n_ctx = 2, 1, 300
+    x = synth.normal(synth.SEED_Q, (rows, AD), start=12345)
+    x[0, :32] = 0
+    kf = synth.normal(synth.SEED_K, (nkvh, n_ctx, AD))
+    kc, _ = orc.fill_cache(kf, kf, n_ctx)
+    q_i8 = torch.zeros((rows, AD), dtype=torch.int8, device="cuda")
+    q_sc = torch.zeros((rows, 8), dtype=torch.float32, device="cuda")
+    acc = torch.zeros((rows, npos, 8), dtype=torch.int32, device="cuda")
+    q27.prefill_qk_debug(dev(x), rows, SCALE, dev(kc), nkvh, n_ctx, kh, p0, npos, q_i8, q_sc, acc)
+    torch.cuda.synchronize()
+    rq, rd = orc.quant_q_i8(x, SCALE)
+    assert np.array_equal(q_i8.cpu().numpy(), rq)
+    assert np.array_equal(q_sc.cpu().numpy(), rd)
+    kq = kc[: nkvh * n_ctx * AD].view(np.int8).reshape(nkvh, n_ctx, AD)[kh, p0:p0 + npos]
+    assert np.array_equal(acc.cpu().numpy(), orc.qk_i32(rq, kq))
+    assert q27.device_status() == 0
+
+
+# {pos0, M} of the reference's own check (tools/bench_attn.cu:77), at sizes the oracle finishes quickly
+@pytest.mark.parametrize("pos0,M", [(0, 37), (0, 128), (1000, 64), (5000, 128), (0, 1), (63, 2), (300, 200), (129, 257)])
+@pytest.mark.parametrize("nkvh", [1, 2])
+def test_prefill_matches_oracle(q27, orc, pos0, M, nkvh):
+    if nkvh == 2 and M > 130:
+        pytest.skip("covered with one KV head")
+    qn, qg, kc_ref, vc_ref, n, n_ctx = make_case(orc, M, pos0, nkvh)
+    nqh = nkvh * GQA
+    o = torch.full((M, nqh, AD), float("nan"), device="cuda")
+    q27.attn_prefill(dev(qn), dev(qg), poisoned_cache(q27, kc_ref, nkvh, n_ctx, n),
+                     poisoned_cache(q27, vc_ref, nkvh, n_ctx, n), o, pos_tensor(pos0), M, SCALE, nqh, nkvh, n_ctx)
+    torch.cuda.synchronize()
+    ref = orc.attn_prefill_i8(qn, qg, kc_ref, vc_ref, pos0, SCALE, nkvh, n_ctx)
+    assert_close(o.cpu().numpy(), ref, "prefill pos0=%d M=%d" % (pos0, M))
+    assert q27.device_status() == 0
+
+
+@pytest.mark.parametrize("depth_hint", [8000, -1])
+def test_prefill_split_kv(q27, orc, depth_hint):
+    """With a depth hint the positions are split over CTAs and merged by log-sum-exp."""
+    pos0, M, nkvh = 8000, 70, 1
+    qn, qg, kc_ref, vc_ref, n, n_ctx = make_case(orc, M, pos0, nkvh)
+    o = torch.full((M, 6, AD), float("nan"), device="cuda")
+    q27.attn_prefill(dev(qn), dev(qg), dev(kc_ref), dev(vc_ref), o, pos_tensor(pos0), M, SCALE, 6, nkvh, n_ctx,
+                     depth_hint=depth_hint)
+    torch.cuda.synchronize()
+    ref = orc.attn_prefill_i8(qn, qg, kc_ref, vc_ref, pos0, SCALE, nkvh, n_ctx)
+    assert_close(o.cpu().numpy(), ref, "prefill split hint=%d" % depth_hint)
+
+
+def test_prefill_chunk_2048_rows_sampled(q27, orc):
+    """Config: 2048 new tokens on a 32,768-token prefix, 24 Q / 4 KV heads. The oracle checks the
+    first, a middle and the last 4 tokens of the chunk (all heads)."""
+    pos0, M, nkvh = 32768, 2048, 4
+    qn, qg, kc_ref, vc_ref, n, n_ctx = make_case(orc, M, pos0, nkvh, n_ctx=pos0 + M)
+    nqh = nkvh * GQA
+    o = torch.full((M, nqh, AD), float("nan"), device="cuda")
+    q27.attn_prefill(dev(qn), dev(qg), dev(kc_ref), dev(vc_ref), o, pos_tensor(pos0), M, SCALE, nqh, nkvh, n_ctx,
+                     depth_hint=pos0)
+    torch.cuda.synchronize()
+    out = o.cpu().numpy()
+    assert np.isfinite(out).all()
+    for lo in (0, 1022, 2044):
+        ref = orc.attn_prefill_i8(qn, qg, kc_ref, vc_ref, pos0, SCALE, nkvh, n_ctx, lo, lo + 4)
+        assert_close(out[lo:lo + 4], ref[lo:lo + 4], "tokens %d..%d" % (lo, lo + 3))
+    assert q27.device_status() == 0
+
+
+def test_prefill_agrees_with_decode(q27, orc):
+    """The last 4 tokens of a prefill chunk and a 4-token decode over the same cache differ only by
+    the int8 rounding of Q (bounded well inside the path's tolerance)."""
+    pos0, M, nkvh = 700, 64, 1
+    qn, qg, kc_ref, vc_ref, n, n_ctx = make_case(orc, M, pos0, nkvh)
+    kc, vc = dev(kc_ref), dev(vc_ref)
+    o = torch.empty((M, 6, AD), device="cuda")
+    q27.attn_prefill(dev(qn), dev(qg), kc, vc, o, pos_tensor(pos0), M, SCALE, 6, nkvh, n_ctx)
+    o4 = torch.empty((4, 6, AD), device="cuda")
+    q27.attn_decode(dev(qn[-4:]), dev(qg[-4:]), kc, vc, o4, None, None, pos_tensor(n - 4), 4, SCALE, 6, nkvh, n_ctx)
+    torch.cuda.synchronize()
+    assert_close(o[-4:].cpu().numpy(), o4.cpu().numpy(), "prefill vs decode", abs_tol=5e-3, rel_tol=5e-2)
