@@ -1,0 +1,461 @@
+"""Benchmark of the attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extras]
+
+One step = one decode-attention call (split-K kernel + log-sum-exp merge kernel) for a
+4-token speculative-verify block, 24 Q / 4 KV heads, head dim 256, over a q8_0 KV cache of
+150,000 positions. Metric: algorithmic KV bytes streamed per second,
+2 * nkvh * n * 272 B / step time, the reference's own accounting (tools/bench_attn.cu:148).
+Inputs are resident in HBM for `value`; `e2e` goes through the C ABI with host buffers (query,
+gate, the new K/V rows in pinned host memory -> device, KV append, decode, result -> host).
+With N > 1 (torchrun, one rank per GPU) every rank decodes its own sequence (batched decode
+sharded by sequence, no exchange): value is the aggregate. The same run also reports, as extra
+keys, one sequence sharded over the ranks by KV-head group and then KV length with the NCCL
+gather + log-sum-exp merge ("strong"), the other context depths, the prefill TOPS and the
+reference's own kernels on the same GPU.
+
+--impl reference runs the reference's kernels (oracle/_ref/libq27ref.so: its src/attn.cu compiled
+for sm_100a, called through its own q27::attn_decode) on the same workload; the reference has no
+CPU implementation of this path. If that library is missing, the CPU oracle is timed instead.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+import __graft_entry__ as ge  # noqa: E402
+
+AD, GQA, T, NKVH, NQH = 256, 6, 4, 4, 24
+N_POS = 150000
+N_CTX = 150056
+SCALE = 1.0 / 16.0
+NBUF = 3  # rotating caches: the reuse distance (3 x 326 MB) is far beyond the 126 MB L2
+
+
+def env_int(name, default):
+    return int(os.environ.get(name, default))
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def fill_caches(q, nkvh, n, n_ctx, seed):
+    """K and V caches of n positions, quantised by the library's own append kernel from N(0,1) rows."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    kc, vc = q.new_cache(nkvh, n_ctx), q.new_cache(nkvh, n_ctx)
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    step = 8192
+    for p0 in range(0, n, step):
+        m = min(step, n - p0)
+        k = torch.randn((m, nkvh, AD), generator=g, device="cuda")
+        v = torch.randn((m, nkvh, AD), generator=g, device="cuda")
+        pos.fill_(p0)
+        q.kv_append(k, v, kc, vc, pos, m, nkvh, n_ctx)
+    torch.cuda.synchronize()
+    return kc, vc
+
+
+def kv_bytes(nkvh, n):
+    return 2.0 * nkvh * n * 272
+
+
+def time_steps(fn, steps, warmup, dist=None):
+    """W untimed calls, then K calls between two events; barrier + synchronize on both sides;
+    returns ms per step (max over ranks)."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        ms = float(t.item())
+    return ms
+
+
+class RefLib:
+    """The reference's kernels (oracle/_ref/libq27ref.so) behind its own operator API."""
+
+    def __init__(self):
+        path = os.path.join(ROOT, "oracle", "_ref", "libq27ref.so")
+        self.lib = ctypes.CDLL(path)
+        self.lib.ref_last_error.restype = ctypes.c_char_p
+
+    @staticmethod
+    def _p(t):
+        return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+    def _ck(self, rc):
+        if rc:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+
+    def decode(self, qn, qg, kc, vc, o, pos, T_, nqh, nkvh, n_ctx):
+        s = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        self._ck(self.lib.ref_attn_decode(self._p(qn), self._p(qg), self._p(kc), self._p(vc), self._p(o), None, None,
+                                          self._p(pos), T_, ctypes.c_float(SCALE), nqh, nkvh, n_ctx, 1, s))
+
+    def prefill(self, qn, qg, kc, vc, o, pos, M, nqh, nkvh, n_ctx, hint):
+        s = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        self._ck(self.lib.ref_attn_prefill(self._p(qn), self._p(qg), self._p(kc), self._p(vc), self._p(o), self._p(pos), M,
+                                           ctypes.c_float(SCALE), nqh, nkvh, n_ctx, 1, s, hint))
+
+
+def cpu_baseline(n=N_POS):
+    """The CPU oracle (C++/OpenMP restatement of the reference numerics) on the full decode workload."""
+    import oracle
+    rng = np.random.default_rng(7)
+    nkvh, nqh = NKVH, NQH
+    kc = oracle.new_cache(nkvh, n)
+    vc = oracle.new_cache(nkvh, n)
+    for c in (kc, vc):  # random int8 values and scales around 1/127: the cost does not depend on the values
+        c[: nkvh * n * AD] = rng.integers(0, 256, nkvh * n * AD, dtype=np.uint8)
+        c[nkvh * n * AD:].view(np.float16)[:] = (rng.random(nkvh * n * 8) * 0.02 + 0.005).astype(np.float16)
+    qn = rng.standard_normal((T, nqh, AD)).astype(np.float32)
+    qg = rng.standard_normal((T, nqh, 512)).astype(np.float32)
+    oracle.attn_ref(qn, qg, kc, vc, n - T, SCALE, nkvh, n)  # warm
+    reps, t0 = 0, time.perf_counter()
+    while reps < 3 or (time.perf_counter() - t0 < 8 and reps < 20):
+        oracle.attn_ref(qn, qg, kc, vc, n - T, SCALE, nkvh, n)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": kv_bytes(nkvh, n) / dt / 1e9, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": "%d full calls of the same workload (T=4, 24q/4kv, n=%d) on the host cores" % (reps, n),
+            "ms_per_step": dt * 1e3}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return json.load(open(path)), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--ref-cpu", action="store_true", help="reference arm: time the CPU oracle instead of the reference's GPU kernels")
+    ap.add_argument("--n", type=int, default=N_POS)
+    args = ap.parse_args()
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    world = env_int("WORLD_SIZE", 1)
+    rank = env_int("RANK", 0)
+    local = env_int("LOCAL_RANK", 0)
+    n = args.n
+    n_ctx = max(N_CTX, n + 2048 + 8)
+
+    if args.impl == "reference" and rank != 0:
+        return  # the reference arm is a single-GPU program: rank 0 alone runs it
+    dist = None
+    if world > 1 and args.impl != "reference":
+        import torch.distributed as dist_
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist_.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_
+    else:
+        torch.cuda.set_device(local)
+
+    q = ge.load_package()
+    line = {
+        "metric": "q8_0 decode-attn HBM GB/s @150k ctx (4-token verify block, 24q/4kv heads, head dim 256)",
+        "unit": "GB/s", "n_gpus": world if args.impl != "reference" else 1, "steps": steps, "warmup": warmup,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "verify-decode T=4, 24 Q / 4 KV heads, head_dim 256, q8_0 KV length %d" % n,
+                   "per_gpu": "one sequence per GPU (batched decode sharded by sequence, no exchange)",
+                   "bytes_per_step_per_gpu": kv_bytes(NKVH, n),
+                   "l2": "%.0f MB of KV per step, %d caches in rotation: inputs larger than L2" % (kv_bytes(NKVH, n) / 1e6, NBUF)},
+    }
+
+    # ---- inputs resident in HBM
+    caches = [fill_caches(q, NKVH, n, n_ctx, 1002 + 10 * rank + i) for i in range(NBUF)]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1001 + rank)
+    qn = torch.randn((T, NQH, AD), generator=g, device="cuda")
+    qg = torch.randn((T, NQH, 512), generator=g, device="cuda")
+    o = torch.empty((T, NQH, AD), device="cuda")
+    pos = torch.tensor([n - T], dtype=torch.int32, device="cuda")
+
+    if args.impl == "reference":
+        run_reference(args, line, q, caches, qn, qg, o, pos, n, n_ctx, steps, warmup)
+        return
+
+    def step(i):
+        kc, vc = caches[i % NBUF]
+        q.attn_decode(qn, qg, kc, vc, o, None, None, pos, T, SCALE, NQH, NKVH, n_ctx)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = time_steps(step, steps, warmup, dist)
+    clocks = sampler.stop()
+    assert q.device_status() == 0, "a kernel reported a device-side problem"
+    line["value"] = world * kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9
+    line["ms_per_step"] = ms
+    line["us_per_step"] = ms * 1e3
+    line["gpu_launches"] = 2 * steps
+    line["clocks"] = clocks
+
+    # ---- the dominant kernel alone (split-K decode kernel), CUDA events on the launching stream
+    ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ev1 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for e in ev1:
+        e.record()
+    torch.cuda.synchronize()
+    for i in range(steps):
+        q.debug_split_event(ev1[i])
+        ev0[i].record()
+        step(i)
+    q.debug_split_event(None)
+    torch.cuda.synchronize()
+    kms = statistics.mean(a.elapsed_time(b) for a, b in zip(ev0, ev1))
+    pk, pk_kind = peaks()
+    ach = kv_bytes(NKVH, n) / (kms * 1e-3) / 1e9
+    line["roofline"] = {"bound": "hbm", "kernel": "decode_q8_kernel<3,false>", "achieved": ach, "peak": pk["hbm_gbs"],
+                        "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "peak_kind": pk_kind + " copy bandwidth (burst)",
+                        "frac_of_8TBs_nominal": ach / 8000.0, "kernel_us": kms * 1e3,
+                        "traffic": env_float("Q27B_NCU_TRAFFIC_BYTES")}
+
+    # ---- end to end through the C ABI with host buffers
+    line["e2e"] = e2e(q, caches, n, n_ctx, steps, warmup, dist, world)
+
+    if rank == 0 and world == 1:
+        line["cpu_baseline"] = cpu_baseline(n)
+    if world > 1:
+        line["strong"] = strong_scaling(q, dist, rank, world, n, steps, warmup)
+    if rank == 0 and world == 1 and not args.no_extras:
+        line["extras"] = extras(q, caches, qn, qg, o, n_ctx)
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def env_float(name):
+    v = os.environ.get(name)
+    return float(v) if v else NCU_TRAFFIC_BYTES
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel at the bench
+# workload, from the ncu capture summarised under profiles/ (None until a capture exists).
+NCU_TRAFFIC_BYTES = None
+
+
+def e2e(q, caches, n, n_ctx, steps, warmup, dist, world):
+    """Host buffers in, host buffer out, every step: query + gate + the 4 new K/V rows from pinned
+    memory, KV append at the tail of the cache, decode, result back to pinned memory."""
+    h_qn = torch.randn((T, NQH, AD)).pin_memory()
+    h_qg = torch.randn((T, NQH, 512)).pin_memory()
+    h_k = torch.randn((T, NKVH, AD)).pin_memory()
+    h_v = torch.randn((T, NKVH, AD)).pin_memory()
+    h_o = torch.empty((T, NQH, AD)).pin_memory()
+    d_qn, d_qg = torch.empty_like(h_qn, device="cuda"), torch.empty_like(h_qg, device="cuda")
+    d_k, d_v = torch.empty_like(h_k, device="cuda"), torch.empty_like(h_v, device="cuda")
+    d_o = torch.empty((T, NQH, AD), device="cuda")
+    pos = torch.tensor([n - T], dtype=torch.int32, device="cuda")
+
+    def step(i):
+        kc, vc = caches[i % NBUF]
+        d_qn.copy_(h_qn, non_blocking=True)
+        d_qg.copy_(h_qg, non_blocking=True)
+        d_k.copy_(h_k, non_blocking=True)
+        d_v.copy_(h_v, non_blocking=True)
+        q.kv_append(d_k, d_v, kc, vc, pos, T, NKVH, n_ctx)
+        q.attn_decode(d_qn, d_qg, kc, vc, d_o, None, None, pos, T, SCALE, NQH, NKVH, n_ctx)
+        h_o.copy_(d_o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result before the next step
+
+    ms = time_steps(step, steps, warmup, dist)
+    h2d = (h_qn.numel() + h_qg.numel() + h_k.numel() + h_v.numel()) * 4
+    return {"value": world * kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": h_o.numel() * 4,
+            "what": "pinned host q/gate/new K,V rows -> device, kv_append, attn_decode, result -> pinned host, sync"}
+
+
+def strong_scaling(q, dist, rank, world, n, steps, warmup):
+    """One sequence over all ranks: KV-head groups up to 4 ranks, then KV length with the NCCL
+    gather of (m, l, O) partials and the log-sum-exp merge on every rank."""
+    from qwen27_engine_b200 import shard
+    sh = shard.plan_single_sequence(rank, world, NKVH)
+    group = shard.peer_group(sh)
+    lo, hi = shard.kv_slice(n, sh.z, sh.nz)
+    nk, nq = sh.n_kv_heads, sh.n_kv_heads * GQA
+    n_ctx = hi - lo + 64
+    caches = [fill_caches(q, nk, hi - lo, n_ctx, 5000 + 10 * rank + i) for i in range(NBUF)]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(77 + sh.kv_head0)
+    qn = torch.randn((T, nq, AD), generator=g, device="cuda")
+    qg = torch.randn((T, nq, 512), generator=g, device="cuda")
+    o = torch.empty((T, nq, AD), device="cuda")
+    pos = torch.tensor([n - T], dtype=torch.int32, device="cuda")
+    part = torch.empty((T * nq, 258), device="cuda")
+
+    def step(i):
+        kc, vc = caches[i % NBUF]
+        if sh.nz == 1:
+            q.attn_decode(qn, qg, kc, vc, o, None, None, pos, T, SCALE, nq, nk, n_ctx)
+        else:
+            q.attn_decode_partial(qn, kc, vc, part, pos, T, SCALE, nq, nk, n_ctx, lo, hi - lo)
+            allp = shard.gather_partials(part, sh, group)
+            q.lse_merge(allp, sh.nz, T * nq * 258, T * nq, qg, o)
+
+    ms = time_steps(step, steps, warmup, dist)
+    return {"what": "one 150k sequence sharded over %d GPUs: %d KV head(s) per GPU x %d KV-length slice(s)%s" % (
+                world, nk, sh.nz, ", NCCL all-gather of partials + LSE merge" if sh.nz > 1 else ", no exchange"),
+            "us_per_step": ms * 1e3, "value": kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong"}
+
+
+def extras(q, caches, qn, qg, o, n_ctx):
+    """Other depths of the metric, the prefill TOPS, the batched paged decode and the reference's kernels."""
+    out = {"decode_us": {}, "prefill": {}}
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for depth in (1024, 30000, 100000, 150000):
+        pos.fill_(depth - T)
+
+        def step(i):
+            kc, vc = caches[i % NBUF]
+            q.attn_decode(qn, qg, kc, vc, o, None, None, pos, T, SCALE, NQH, NKVH, n_ctx)
+        ms = time_steps(step, 200, 10)
+        out["decode_us"][str(depth)] = {"us": ms * 1e3, "gbs": kv_bytes(NKVH, depth) / (ms * 1e-3) / 1e9}
+    # prefill chunk: 2048 new tokens on a prefix of P tokens (int8 Q K^T, f16 P V); ops as the reference counts them
+    M = 2048
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    pqn = torch.randn((M, NQH, AD), generator=g, device="cuda")
+    pqg = torch.randn((M, NQH, 512), generator=g, device="cuda")
+    po = torch.empty((M, NQH, AD), device="cuda")
+    kc, vc = caches[0]
+    for P in (0, 32768, 148000):
+        pos.fill_(P)
+        ops = NQH * 1024.0 * (M * P + M * (M + 1) / 2)
+        try:
+            ms = time_steps(lambda i: q.attn_prefill(pqn, pqg, kc, vc, po, pos, M, SCALE, NQH, NKVH, n_ctx, True, P), 3, 3)
+            out["prefill"][str(P)] = {"ms": ms, "tops": ops / (ms * 1e-3) / 1e12}
+        except Exception as e:  # report, do not hide
+            out["prefill"][str(P)] = {"error": str(e)}
+    out["device_status"] = q.device_status()
+    try:
+        ref = RefLib()
+        pos.fill_(N_POS - T)
+        ms = time_steps(lambda i: ref.decode(qn, qg, caches[i % NBUF][0], caches[i % NBUF][1], o, pos, T, NQH, NKVH, n_ctx), 100, 5)
+        out["reference_kernels_same_gpu"] = {"decode_150k_us": ms * 1e3, "decode_150k_gbs": kv_bytes(NKVH, N_POS) / (ms * 1e-3) / 1e9}
+        for P in (32768,):
+            pos.fill_(P)
+            ops = NQH * 1024.0 * (M * P + M * (M + 1) / 2)
+            ms = time_steps(lambda i: ref.prefill(pqn, pqg, kc, vc, po, pos, M, NQH, NKVH, n_ctx, P), 2, 3)
+            out["reference_kernels_same_gpu"]["prefill_%d_tops" % P] = ops / (ms * 1e-3) / 1e12
+    except Exception as e:
+        out["reference_kernels_same_gpu"] = {"unavailable": str(e)}
+    return out
+
+
+def run_reference(args, line, q, caches, qn, qg, o, pos, n, n_ctx, steps, warmup):
+    line["impl"] = "reference"
+    use_cpu = args.ref_cpu
+    ref = None
+    if not use_cpu:
+        try:
+            ref = RefLib()
+        except OSError:
+            use_cpu = True
+    if use_cpu:
+        cb = cpu_baseline(n)
+        line.update({"value": cb["value"], "ms_per_step": cb["ms_per_step"], "cpu_baseline": cb,
+                     "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                     "reference_arm": "CPU oracle (C++/OpenMP port of the reference numerics)"})
+        print(json.dumps(line))
+        return
+
+    def step(i):
+        kc, vc = caches[i % NBUF]
+        ref.decode(qn, qg, kc, vc, o, pos, T, NQH, NKVH, n_ctx)
+
+    sampler = ClockSampler(env_int("LOCAL_RANK", 0))
+    sampler.start()
+    ms = time_steps(step, steps, warmup)
+    line["clocks"] = sampler.stop()
+    v = kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9
+    line.update({"value": v, "ms_per_step": ms, "us_per_step": ms * 1e3, "gpu_launches": 2 * steps,
+                 "reference_arm": "the reference's own CUDA kernels (src/attn.cu, mma.sync + cp.async) compiled for "
+                                  "sm_100a and called through q27::attn_decode on the same GPU; the reference has no "
+                                  "CPU implementation of this path",
+                 "cpu_baseline": {"value": v, "unit": "GB/s", "cores": 0, "kind": "reference",
+                                  "sample": "%d full steps on the GPU (not host cores)" % steps},
+                 "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

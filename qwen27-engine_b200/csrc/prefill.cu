@@ -376,6 +376,10 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
           o[2 * w] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4140), dd);
           o[2 * w + 1] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4342), dd);
         }
+        if ((it0 + j) * PT + row >= n_end) {  // rows past the end may hold anything: P is 0 there, V must be too
+#pragma unroll
+          for (int w = 0; w < 8; w++) o[w] = 0;
+        }
         uint8_t* dst = vf + (c16 >> 2) * (PT * 128);
         const uint32_t cc = 2 * (c16 & 3);
         *(uint4*)(dst + swz128(row, cc)) = make_uint4(o[0], o[1], o[2], o[3]);

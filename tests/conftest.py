@@ -44,7 +44,8 @@ def err_stats(a, ref):
 
 
 def assert_close(a, ref, what="", abs_tol=ABS_TOL, rel_tol=REL_TOL):
-    assert np.isfinite(np.asarray(a)).all(), "%s: non-finite values" % what
+    finite = bool(np.isfinite(np.asarray(a)).all())
+    assert finite, "%s: non-finite values" % what
     mx, rms, l2 = err_stats(a, ref)
     assert mx <= abs_tol and mx <= rel_tol * rms and l2 <= rel_tol, \
         "%s: max err %.3e, ref rms %.3e, rel L2 %.3e" % (what, mx, rms, l2)

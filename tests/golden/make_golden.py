@@ -54,11 +54,13 @@ def main():
             kc = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
             vc = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
             pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
-            ck(ref.ref_attn_prep(p(d(x["qg"])), p(d(x["k"])), p(d(x["v"])), p(d(x["q_norm"])), p(d(x["k_norm"])), p(qn),
+            keep = [d(x[k]) for k in ("qg", "k", "v", "q_norm", "k_norm")]  # stay alive until the kernel has run
+            ck(ref.ref_attn_prep(p(keep[0]), p(keep[1]), p(keep[2]), p(keep[3]), p(keep[4]), p(qn),
                                  p(kc), p(vc), p(pos), T, f(c["eps"]), f(c["theta_scale"]), nqh, nkvh, n_ctx, int(q8),
                                  None, None, None))
             torch.cuda.synchronize()
-            out[name + "/qn"] = qn.cpu().numpy()
+            if T <= 8:
+                out[name + "/qn"] = qn.cpu().numpy()
             out[name + "/kcache"] = kc.cpu().numpy()
             out[name + "/vcache"] = vc.cpu().numpy()
         elif kind == "decode":
@@ -90,12 +92,13 @@ def main():
             kc, vc = oracle.fill_cache(x["k"], x["v"], n_ctx, True)
             pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
             o = torch.zeros((M, nqh, AD), device="cuda")
-            ck(ref.ref_attn_prefill(p(d(x["qn"])), p(d(x["qg"])), p(d(kc)), p(d(vc)), p(o), p(pos), M, f(c["scale"]), nqh,
+            qn, qg, kcd, vcd = d(x["qn"]), d(x["qg"]), d(kc), d(vc)
+            ck(ref.ref_attn_prefill(p(qn), p(qg), p(kcd), p(vcd), p(o), p(pos), M, f(c["scale"]), nqh,
                                     nkvh, n_ctx, 1, None, -1))
             torch.cuda.synchronize()
             out[name + "/i8"] = o.cpu().numpy()
             o2 = torch.zeros((M, nqh, AD), device="cuda")
-            ck(ref.ref_attn_decode_ref(p(d(x["qn"])), p(d(x["qg"])), p(d(kc)), p(d(vc)), p(o2), p(pos), M, f(c["scale"]),
+            ck(ref.ref_attn_decode_ref(p(qn), p(qg), p(kcd), p(vcd), p(o2), p(pos), M, f(c["scale"]),
                                        nqh, nkvh, n_ctx, 1, None))
             torch.cuda.synchronize()
             out[name + "/slow_f16q"] = o2.cpu().numpy()

@@ -1,0 +1,126 @@
+"""The CPU oracle against tests/golden/ref_b200.npz: outputs of the reference's own kernels
+(compiled for sm_100a, run on a B200 by tests/golden/make_golden.py) on the same seeded inputs.
+This is what pins the oracle; the GPU tests then compare the new kernels with the oracle, and the
+last test here compares them with the fixture directly."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, assert_close, err_stats
+from golden_cases import CASES, case_inputs
+
+AD = 256
+PATH = os.path.join(ROOT, "tests", "golden", "ref_b200.npz")
+
+
+@pytest.fixture(scope="module")
+def gold(q27):
+    assert os.path.exists(PATH), "golden fixture missing: run tests/golden/make_golden.py on a B200"
+    return np.load(PATH)
+
+
+def split_q8(cache, nkvh, n_ctx):
+    vals = cache[: nkvh * n_ctx * AD].view(np.int8).reshape(nkvh, n_ctx, AD)
+    sc = cache[nkvh * n_ctx * AD:].view(np.float16).reshape(nkvh, n_ctx, 8)
+    return vals, sc
+
+
+def test_q8_0_quantiser_against_reference_bytes(gold, orc):
+    """V rows are written raw by the reference's attn_prep: its bytes are the q8_0 quantiser's
+    output. The reference is built with fast-math (approximate division), the oracle is IEEE: a
+    value that sits on a rounding boundary may differ by one step; everything else is identical."""
+    total = bad = 0
+    for name in ("prep_q8", "prep_q8_many"):
+        c = CASES[name]
+        x = case_inputs(name)
+        T, nkvh, n_ctx, pos0 = c["T"], c["nkvh"], c["n_ctx"], c["pos0"]
+        kc, vc = orc.new_cache(nkvh, n_ctx), orc.new_cache(nkvh, n_ctx)
+        orc.kv_append(x["k"], x["v"], kc, vc, pos0, nkvh, n_ctx)
+        rv, rs = split_q8(gold[name + "/vcache"], nkvh, n_ctx)
+        ov, os_ = split_q8(vc, nkvh, n_ctx)
+        d = np.abs(rv.astype(np.int32) - ov.astype(np.int32))
+        assert d.max() <= 1
+        total += d.size
+        bad += int((d != 0).sum())
+        sd = np.abs(rs.astype(np.float32) - os_.astype(np.float32))
+        assert (sd <= np.abs(os_.astype(np.float32)) * 2.0 ** -10).all()  # at most one f16 ulp
+        untouched = np.ones(n_ctx, bool)
+        untouched[pos0:pos0 + T] = False
+        assert (rv[:, untouched] == 0).all()
+    assert bad <= 1e-4 * total, "%d of %d values differ" % (bad, total)
+
+
+def test_f16_cache_rows(gold, orc):
+    c = CASES["prep_f16"]
+    x = case_inputs("prep_f16")
+    kc, vc = orc.new_cache(c["nkvh"], c["n_ctx"], False), orc.new_cache(c["nkvh"], c["n_ctx"], False)
+    orc.kv_append(x["k"], x["v"], kc, vc, c["pos0"], c["nkvh"], c["n_ctx"], False)
+    assert np.array_equal(gold["prep_f16/vcache"], vc)
+
+
+@pytest.mark.parametrize("name", ["decode_cfg1", "decode_t4", "decode_f16"])
+def test_decode_oracle_against_reference_kernels(gold, orc, name):
+    c = CASES[name]
+    x = case_inputs(name)
+    kc, vc = orc.fill_cache(x["k"], x["v"], c["n_ctx"], c["q8"])
+    o = orc.attn_ref(x["qn"], x["qg"], kc, vc, c["n"] - c["T"], c["scale"], c["nkvh"], c["n_ctx"], c["q8"])
+    # the reference's slow kernel is the definition: agreement far inside the path's tolerance
+    assert_close(o, gold[name + "/slow"], name + " vs attn_decode_ref", abs_tol=5e-5, rel_tol=1e-3)
+    # its fast kernel (online softmax, mma.sync) within the tolerance of the path
+    assert_close(o, gold[name + "/fast"], name + " vs attn_decode")
+
+
+def test_q8_1_epilogue_against_reference(gold, orc):
+    """The reference's fused q8_1 output equals the oracle's q8_1 of the reference's own f32 output,
+    except where fast-math division moves a value across a rounding boundary."""
+    xq, xd = orc.q8_1(gold["decode_t4/fast"].reshape(-1))
+    d = np.abs(xq.astype(np.int32) - gold["decode_t4/xq"].reshape(-1).astype(np.int32))
+    assert d.max() <= 1 and (d != 0).mean() <= 2e-3
+    assert np.abs(xd - gold["decode_t4/xd"]).max() <= np.abs(xd).max() * 2.0 ** -10
+
+
+@pytest.mark.parametrize("name", ["prefill_a", "prefill_b"])
+def test_prefill_oracle_against_reference_kernel(gold, orc, name):
+    c = CASES[name]
+    x = case_inputs(name)
+    kc, vc = orc.fill_cache(x["k"], x["v"], c["n_ctx"], True)
+    o = orc.attn_prefill_i8(x["qn"], x["qg"], kc, vc, c["pos0"], c["scale"], c["nkvh"], c["n_ctx"])
+    # the reference kernel accumulates O in f16 (its own source of error): tolerance of the path
+    assert_close(o, gold[name + "/i8"], name + " vs attn_prefill (int8)")
+    # and the int8 rounding of Q stays close to the f16-Q definition
+    mx, rms, l2 = err_stats(o, gold[name + "/slow_f16q"])
+    assert l2 <= 2e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["decode_cfg1", "decode_t4"])
+def test_new_decode_kernel_against_reference_outputs(gold, q27, orc, name):
+    import torch
+    from helpers_gpu import dev, pos_tensor
+    c = CASES[name]
+    x = case_inputs(name)
+    nqh = c["nkvh"] * 6
+    kc, vc = orc.fill_cache(x["k"], x["v"], c["n_ctx"], True)
+    o = torch.empty((c["T"], nqh, AD), device="cuda")
+    q27.attn_decode(dev(x["qn"]), dev(x["qg"]), dev(kc), dev(vc), o, None, None, pos_tensor(c["n"] - c["T"]), c["T"],
+                    c["scale"], nqh, c["nkvh"], c["n_ctx"])
+    torch.cuda.synchronize()
+    assert_close(o.cpu().numpy(), gold[name + "/slow"], name + ": new kernel vs the reference's slow kernel")
+    assert_close(o.cpu().numpy(), gold[name + "/fast"], name + ": new kernel vs the reference's fast kernel")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["prefill_a", "prefill_b"])
+def test_new_prefill_kernel_against_reference_outputs(gold, q27, orc, name):
+    import torch
+    from helpers_gpu import dev, pos_tensor
+    c = CASES[name]
+    x = case_inputs(name)
+    nqh = c["nkvh"] * 6
+    kc, vc = orc.fill_cache(x["k"], x["v"], c["n_ctx"], True)
+    o = torch.empty((c["M"], nqh, AD), device="cuda")
+    q27.attn_prefill(dev(x["qn"]), dev(x["qg"]), dev(kc), dev(vc), o, pos_tensor(c["pos0"]), c["M"], c["scale"], nqh,
+                     c["nkvh"], c["n_ctx"])
+    torch.cuda.synchronize()
+    assert_close(o.cpu().numpy(), gold[name + "/i8"], name + ": new kernel vs the reference's int8 kernel")
