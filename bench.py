@@ -208,6 +208,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--ref-cpu", action="store_true", help="reference arm: time the CPU oracle instead of the reference's GPU kernels")
     ap.add_argument("--n", type=int, default=N_POS)
+    ap.add_argument("--mode", default="decode", help="decode (the headline) or prefill (second half of the metric)")
+    ap.add_argument("--prefix", type=int, default=32768, help="prefill mode: tokens already in the cache")
     args = ap.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     world = env_int("WORLD_SIZE", 1)
@@ -229,6 +231,9 @@ def main():
         torch.cuda.set_device(local)
 
     q = ge.load_package()
+    if args.mode == "prefill":
+        prefill_mode(q, args, steps, warmup)
+        return
     line = {
         "metric": "q8_0 decode-attn HBM GB/s @150k ctx (4-token verify block, 24q/4kv heads, head dim 256)",
         "unit": "GB/s", "n_gpus": world if args.impl != "reference" else 1, "steps": steps, "warmup": warmup,
@@ -419,6 +424,53 @@ def extras(q, caches, qn, qg, o, n_ctx):
     except Exception as e:
         out["reference_kernels_same_gpu"] = {"unavailable": str(e)}
     return out
+
+
+def prefill_mode(q, args, steps, warmup):
+    """Second half of the metric: one 2048-token prefill chunk on a q8_0 prefix of --prefix tokens
+    (int8 Q K^T, f16 P V). One step = one attn_prefill call; ops as the reference counts them
+    (tools/bench_attn.cu:104): nqh * 1024 * (M * P + M (M + 1) / 2)."""
+    M, P = 2048, args.prefix
+    n_ctx = P + M + 8
+    kc, vc = fill_caches(q, NKVH, P + M, n_ctx, 1002)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    qn = torch.randn((M, NQH, AD), generator=g, device="cuda")
+    qg = torch.randn((M, NQH, 512), generator=g, device="cuda")
+    o = torch.empty((M, NQH, AD), device="cuda")
+    pos = torch.tensor([P], dtype=torch.int32, device="cuda")
+    use_ref = args.impl == "reference"
+    ref = RefLib() if use_ref else None
+
+    def step(i):
+        if use_ref:
+            ref.prefill(qn, qg, kc, vc, o, pos, M, NQH, NKVH, n_ctx, P)
+        else:
+            q.attn_prefill(qn, qg, kc, vc, o, pos, M, SCALE, NQH, NKVH, n_ctx, True, P)
+
+    sampler = ClockSampler(env_int("LOCAL_RANK", 0))
+    sampler.start()
+    ms = time_steps(step, steps, warmup)
+    clocks = sampler.stop()
+    ops = NQH * 1024.0 * (M * P + M * (M + 1) / 2)
+    tops = ops / (ms * 1e-3) / 1e12
+    pk, pk_kind = peaks()
+    f16 = pk["bf16_tflops_sustained"]
+    # half of the ops run on the int8 pipe (taken as twice the measured 16-bit rate), half on the f16 pipe
+    t_min_ms = (ops / 2 / (2 * f16 * 1e12) + ops / 2 / (f16 * 1e12)) * 1e3
+    line = {"metric": "int8 prefill-attn TOPS (2048-token chunk, 24q/4kv heads, head dim 256, q8_0 prefix)",
+            "value": tops, "unit": "TOPS", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8 x s8 -> s32 (QK), f16 -> f32 (PV)",
+            "data": "synthetic", "config": {"workload": "prefill chunk M=2048 on a q8_0 prefix of %d tokens" % P},
+            "gpu_launches": steps, "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": tops, "peak": 2 * f16, "unit": "TOP/s",
+                         "frac": tops / (2 * f16), "peak_kind": "2 x %s bf16 GEMM rate (sustained) as the int8 peak" % pk_kind,
+                         "frac_of_mixed_int8_f16_bound": t_min_ms / ms, "traffic": None}}
+    if use_ref:
+        line["impl"] = "reference"
+    if not use_ref:
+        assert q.device_status() == 0
+    print(json.dumps(line))
 
 
 def run_reference(args, line, q, caches, qn, qg, o, pos, n, n_ctx, steps, warmup):

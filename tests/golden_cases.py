@@ -17,8 +17,8 @@ CASES = {
     "decode_t4": dict(kind="decode", T=4, nkvh=2, n=2500, n_ctx=2504, q8=True, scale=1 / 16, q8_1=True),
     "decode_f16": dict(kind="decode", T=4, nkvh=1, n=700, n_ctx=704, q8=False, scale=1 / 16),
     # prefill: the reference's int8 Q K^T kernel, and its slow f16-Q kernel on the same rows
-    "prefill_a": dict(kind="prefill", M=40, nkvh=1, pos0=300, n_ctx=344, scale=1 / 16),
-    "prefill_b": dict(kind="prefill", M=37, nkvh=1, pos0=0, n_ctx=40, scale=1 / 16),
+    "prefill_a": dict(kind="prefill", M=24, nkvh=1, pos0=300, n_ctx=328, scale=1 / 16),
+    "prefill_b": dict(kind="prefill", M=17, nkvh=1, pos0=0, n_ctx=20, scale=1 / 16),
 }
 
 
