@@ -80,6 +80,30 @@ int q27b_attn_decode(const float* qn, const float* qg, const void* kcache, const
                      float* xd, const int* pos0, int T, float kq_scale, int nqh, int nkvh, int n_ctx, int q8,
                      void* stream);
 
+/* q27b_attn_decode for callers that must not allocate device memory. It has no counterpart in
+ * the reference, whose attn_decode allocates its partial buffer on first use
+ * (src/attn.cu:898-900). Same arguments, same result as q27b_attn_decode (q8_0 cache only).
+ *
+ * Who needs it: a host that runs under a fixed device-memory budget fixed at start-up, or that
+ * drives several GPUs in lock step - there a cudaMalloc in the middle of a batch synchronises the
+ * whole device while its peer is waiting for it (the situation the reference describes at
+ * src/attn.cu:954-956) - or an embedding runtime that owns the allocator and forbids the library
+ * to touch it. This entry point calls no cudaMalloc / cudaFree and no allocating library routine:
+ * the split partials live in an array that is part of the library image (3.96 MB of every GPU
+ * that loads the library, held until the process exits), and the result goes to the caller's
+ * own buffers.
+ *
+ * Limit: nkvh * q27b_attn_chunks(nkvh) <= 160 chunk partials, i.e. any KV-head count on GPUs of up
+ * to 160 SMs; beyond that the call returns Q27B_BAD_SHAPE and says so.
+ * The first call on a device looks up the array's device address and opts the kernels into their
+ * shared-memory size; make that first call before any stream capture starts.
+ * Every call on a device uses the same array and leaves its partials there; nothing in it has to
+ * start at zero (each call rewrites every partial it later reads). Two calls that can overlap on
+ * the GPU (different streams) race on it: keep calls of one device in one stream order. */
+int q27b_attn_decode_noalloc(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
+                             int8_t* xq, float* xd, const int* pos0, int T, float kq_scale, int nqh, int nkvh,
+                             int n_ctx, int q8, void* stream);
+
 /* Same attention, restricted to the cache rows that this GPU holds when one sequence is split
  * by KV length across GPUs: local cache row i is global position base_pos + i, rows
  * 0 .. n_local-1 are attended (a row is visible to token t iff its global position is

@@ -28,6 +28,7 @@ SYMBOLS = [
     "q27b_last_error", "q27b_device_status", "q27b_kv_cache_bytes", "q27b_attn_chunks", "q27b_kv_append",
     "q27b_attn_prep", "q27b_attn_decode", "q27b_attn_decode_partial", "q27b_lse_merge", "q27b_attn_decode_paged",
     "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event",
+    "q27b_attn_decode_noalloc",
 ]
 
 
@@ -131,6 +132,18 @@ def attn_decode(qn, qg, kcache, vcache, o, xq, xd, pos0, T, kq_scale, nqh, nkvh,
                                  _ptr(o, torch.float32, True), _ptr(xq, torch.int8, True),
                                  _ptr(xd, torch.float32, True), _ptr(pos0, torch.int32), int(T), _f(kq_scale),
                                  int(nqh), int(nkvh), int(n_ctx), int(bool(q8)), _stream()))
+
+
+def attn_decode_noalloc(qn, qg, kcache, vcache, o, xq, xd, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8=True):
+    """attn_decode for hosts that may not allocate device memory (fixed memory budgets, several GPUs
+    driven in lock step, runtimes that own the allocator): the split partials live in a 3.96 MB array
+    inside the library image instead of a cudaMalloc'ed workspace. Same arguments and result as
+    attn_decode; at most 160 chunk partials (nkvh * attn_chunks(nkvh)); calls of one device must not
+    overlap on the GPU, and the first one should come before any stream capture."""
+    _check(_lib.q27b_attn_decode_noalloc(_ptr(qn, torch.float32), _ptr(qg, torch.float32), _ptr(kcache),
+                                         _ptr(vcache), _ptr(o, torch.float32, True), _ptr(xq, torch.int8, True),
+                                         _ptr(xd, torch.float32, True), _ptr(pos0, torch.int32), int(T),
+                                         _f(kq_scale), int(nqh), int(nkvh), int(n_ctx), int(bool(q8)), _stream()))
 
 
 def attn_decode_partial(qn, kcache, vcache, part, pos0, T, kq_scale, nqh, nkvh, n_ctx, base_pos, n_local, q8=True):

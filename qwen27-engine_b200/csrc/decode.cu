@@ -521,6 +521,36 @@ int decode_split(DeviceCtx* ctx, const float* qn, const void* kcache, const void
   return Q27B_OK;
 }
 
+// ---------------------------------------------------------------- decode without any allocation
+// Scratch of q27b_attn_decode_noalloc: the split partials [chunk slots][24 rows][258 floats] and a
+// status word, reserved in the library image itself. NOALLOC_SLOTS chunk slots = nkvh * chunks per
+// KV head, which on a GPU with up to 160 SMs is at most 160 (3.96 MB). Every GPU that loads the
+// library carries this array until the process exits.
+constexpr int NOALLOC_SLOTS = 160;
+static __device__ __align__(256) float g_noalloc_part[(size_t)NOALLOC_SLOTS * MAXR * PROW];
+static __device__ __align__(256) int g_noalloc_status[64];
+
+// Device addresses of the two arrays, per device. In host code `g_noalloc_part` is only a
+// handle for the runtime, not an address a kernel could use: the address has to be asked for, on
+// the device in question, with cudaGetSymbolAddress.
+float* g_noalloc_part_ptr[64] = {};
+int* g_noalloc_status_ptr[64] = {};
+
+int noalloc_setup(int dev) {
+  if (g_noalloc_part_ptr[dev]) return Q27B_OK;
+  float* part = nullptr;
+  int* status = nullptr;
+  Q27B_CK(cudaGetSymbolAddress((void**)&part, g_noalloc_part));
+  Q27B_CK(cudaGetSymbolAddress((void**)&status, g_noalloc_status));
+  // the kernels' shared-memory opt-in, done here so that later calls only launch
+  Q27B_CK(cudaFuncSetAttribute(decode_q8_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  Q27B_CK(cudaFuncSetAttribute(decode_q8_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  Q27B_CK(cudaFuncSetAttribute(decode_q8_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  g_noalloc_status_ptr[dev] = status;
+  g_noalloc_part_ptr[dev] = part;
+  return Q27B_OK;
+}
+
 }  // namespace
 }  // namespace q27b
 
@@ -562,6 +592,38 @@ int q27b_attn_decode_partial(const float* qn, const void* kcache, const void* vc
     return rc;
   MergeParams mp = {};
   mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.part_out = part; mp.T = T; mp.nqh = nqh;
+  return launch_merge(mp, true, (cudaStream_t)stream);
+}
+
+int q27b_attn_decode_noalloc(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
+                             int8_t* xq, float* xd, const int* pos0, int T, float kq_scale, int nqh, int nkvh, int n_ctx,
+                             int q8, void* stream) {
+  if (T < 1 || T > Q27B_MAX_T || nkvh < 1 || nqh != nkvh * GQA || n_ctx < 1)
+    return fail(Q27B_BAD_SHAPE, "attn_decode_noalloc: bad shape");
+  if (!qn || !qg || !kcache || !vcache || !pos0 || (!o && !xq) || (xq && !xd))
+    return fail(Q27B_BAD_SHAPE, "attn_decode_noalloc: null pointer");
+  if (!q8) return fail(Q27B_UNSUPPORTED, "attn_decode_noalloc: q8_0 KV cache only");
+  int dev = 0, n_sm = 0;
+  Q27B_CK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(Q27B_UNSUPPORTED, "device index out of range");
+  Q27B_CK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  const int nch = std::max(1, n_sm / nkvh);
+  if ((size_t)nkvh * nch > (size_t)NOALLOC_SLOTS)
+    return fail(Q27B_BAD_SHAPE, "attn_decode_noalloc: needs " + std::to_string(nkvh * nch) +
+                                    " chunk partials, the built-in scratch holds " + std::to_string(NOALLOC_SLOTS) +
+                                    " (use q27b_attn_decode, which allocates)");
+  if (int rc = noalloc_setup(dev)) return rc;
+  const CUtensorMap *kv, *ks, *vv, *vs;
+  if (int rc = get_tmaps(kcache, nkvh, n_ctx, &kv, &ks)) return rc;
+  if (int rc = get_tmaps(vcache, nkvh, n_ctx, &vv, &vs)) return rc;
+  DecodeParams p = {};
+  p.qn = qn; p.part = g_noalloc_part_ptr[dev]; p.pos0 = pos0; p.status = g_noalloc_status_ptr[dev];
+  p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nch = nch; p.kq_scale = kq_scale;
+  p.base_pos = 0; p.n_local = -1;
+  if (int rc = launch_decode_t<false>(kv, ks, vv, vs, p, 1, (cudaStream_t)stream)) return rc;
+  MergeParams mp = {};
+  mp.part = g_noalloc_part_ptr[dev]; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.qg = qg; mp.o = o; mp.xq = xq;
+  mp.xd = xd; mp.T = T; mp.nqh = nqh;
   return launch_merge(mp, true, (cudaStream_t)stream);
 }
 
