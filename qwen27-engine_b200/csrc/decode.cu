@@ -45,7 +45,9 @@ constexpr int OFF_L = OFF_MAX + 2 * 2 * 4 * MAXR * 4;       // [2 groups][4 warp
 constexpr int OFF_M1 = OFF_L + 2 * 4 * MAXR * 4;            // [24] floats: running max of group 1
 constexpr int OFF_BAR = OFF_M1 + MAXR * 4;                  // full[NSTAGE]
 constexpr int OFF_FLAG = OFF_BAR + NSTAGE * 8;
-constexpr int SMEM_USED = OFF_FLAG + 16;
+constexpr int OFF_TOK = OFF_FLAG + 16;                      // [2 groups][2 buffers] words: "move the maxima" tokens
+constexpr int SMEM_USED = OFF_TOK + 16;
+constexpr float TAU = 8.0f;                                 // a score may exceed the reference max by this much
 constexpr int SMEM_BYTES = SMEM_USED + 1024;               // slack for the 1024-byte alignment of the ring
 constexpr int O_STRIDE = AD + 4;                            // floats per row of the end-of-kernel O exchange
 static_assert(MAXR * O_STRIDE * 4 <= NSTAGE * STAGE_BYTES, "O exchange must fit in the ring");
@@ -148,6 +150,7 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   if (tid == 0) {
     for (int s = 0; s < NSTAGE; s++) mbar_init(&full[s], 1);
     *abort_flag = 0;
+    for (int i = 0; i < 4; i++) ((volatile uint32_t*)(sgen + OFF_TOK))[i] = 0;
     mbar_fence_init();
   }
   __syncthreads();
@@ -229,6 +232,7 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
 
     const uint32_t sP = sbase + OFF_P + grp * 2 * P_WORDS * 4;
     const uint32_t sMax = sbase + OFF_MAX + grp * 2 * 4 * MAXR * 4;
+    const uint32_t sTok = sbase + OFF_TOK + grp * 8;
     const uint32_t sel_sc = (tg & 2) ? 0x3232u : 0x1010u;  // which f16 of a scale word this lane's K blocks use
     const uint32_t MAGIC = 0x64646464u;
 
@@ -241,9 +245,13 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       const bool edge = tile_p0 + TILE > lim_min;  // some row of the tile is masked for some query row
 
       // ---- S^T = K Q^T for tile rows ra, rb
-      float sacc[NT][4];
+      // (two accumulator sets, even / odd 64-dim groups, so that consecutive MMAs do not depend on each other)
+      float sacc[NT][4], sacc2[NT][4];
 #pragma unroll
-      for (int nt = 0; nt < NT; nt++) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+      for (int nt = 0; nt < NT; nt++) {
+        sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+        sacc2[nt][0] = sacc2[nt][1] = sacc2[nt][2] = sacc2[nt][3] = 0.f;
+      }
       {
         const uint4 sca = lds128(st + OFF_KS + ra * 16), scb = lds128(st + OFF_KS + rb * 16);
         const uint32_t scaw[4] = {sca.x, sca.y, sca.z, sca.w}, scbw[4] = {scb.x, scb.y, scb.z, scb.w};
@@ -262,9 +270,14 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
             const uint32_t a1 = dq_pair(prmt(wb, MAGIC, 0x4140), db), a3 = dq_pair(prmt(wb, MAGIC, 0x4342), db);
             const int ks = 4 * hj + s2;
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) mma16816(sacc[nt], a0, a1, a2, a3, qf[ks][nt][0], qf[ks][nt][1]);
+            for (int nt = 0; nt < NT; nt++)
+              mma16816((hj & 1) ? sacc2[nt] : sacc[nt], a0, a1, a2, a3, qf[ks][nt][0], qf[ks][nt][1]);
           }
         }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int c = 0; c < 4; c++) sacc[nt][c] += sacc2[nt][c];
       }
       if (edge) {
         const int pa = tile_p0 + ra, pb = tile_p0 + rb;
@@ -277,10 +290,33 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
           }
       }
 
-      // ---- tile maximum per query row: over this warp's 16 positions, then over the 4 warps
+      // ---- P = exp(S - m) against the group's reference maxima m. m only moves when some score of
+      // the tile exceeds it by more than TAU (and on the group's first tile): then every warp posts
+      // its tile maxima, m, l and O are rescaled and P is recomputed. Otherwise - almost always - a
+      // tile costs one group barrier and no rescale; P stays <= e^TAU, well inside f16.
       const int buf = jt & 1;
-      {
-        float mx[NT][2];
+      const uint32_t token = (uint32_t)(jt + 1);
+      bool exceed = jt == 0;
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) exceed |= fmaxf(sacc[nt][e], sacc[nt][2 + e]) > m[nt][e] + TAU;
+      if (__any_sync(0xffffffffu, exceed) && lane == 0) sts32(sTok + buf * 4, token);
+      float lt[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          const float mb = m[nt][e] * LOG2E;
+          const float pa = ex2(fmaf(sacc[nt][e], LOG2E, -mb)), pb = ex2(fmaf(sacc[nt][2 + e], LOG2E, -mb));
+          lt[nt][e] = pa + pb;
+          // position pair (slot g, slot g + 8) of warp wq = P^T k-slot pair 8wq + g
+          sts32(sP + (buf * P_WORDS + (8 * nt + 2 * tg + e) * P_STRIDE + 8 * wq + g) * 4, pack_h2(pa, pb));
+        }
+      bar_sync(1 + grp, 128);
+      // All four warps are past the previous tile of this group: its stage can be refilled.
+      if (loader && jt >= 1 && it - 2 + NSTAGE < ntiles) issue_tile(it - 2 + NSTAGE);
+      if (lds32(sTok + buf * 4) == token) {
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
@@ -289,47 +325,38 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
             v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
             v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
             v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
-            mx[nt][e] = v;
+            if (g == 0) stsf(sMax + ((buf * 4 + wq) * MAXR + 8 * nt + 2 * tg + e) * 4, v);
           }
-        if (g == 0) {
+        bar_sync(1 + grp, 128);
 #pragma unroll
-          for (int nt = 0; nt < NT; nt++)
+        for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-            for (int e = 0; e < 2; e++) stsf(sMax + ((buf * 4 + wq) * MAXR + 8 * nt + 2 * tg + e) * 4, mx[nt][e]);
-        }
+          for (int e = 0; e < 2; e++) {
+            const int r = 8 * nt + 2 * tg + e;
+            float tm = ldsf(sMax + ((buf * 4 + 0) * MAXR + r) * 4);
+#pragma unroll
+            for (int w = 1; w < 4; w++) tm = fmaxf(tm, ldsf(sMax + ((buf * 4 + w) * MAXR + r) * 4));
+            const float mn = fmaxf(m[nt][e], tm);
+            const float f = ex2((m[nt][e] - mn) * LOG2E);
+            m[nt][e] = mn;
+            l[nt][e] *= f;
+#pragma unroll
+            for (int mt = 0; mt < 4; mt++) {
+              o[mt][nt][e] *= f;
+              o[mt][nt][2 + e] *= f;
+            }
+            const float mb = mn * LOG2E;
+            const float pa = ex2(fmaf(sacc[nt][e], LOG2E, -mb)), pb = ex2(fmaf(sacc[nt][2 + e], LOG2E, -mb));
+            lt[nt][e] = pa + pb;
+            sts32(sP + (buf * P_WORDS + r * P_STRIDE + 8 * wq + g) * 4, pack_h2(pa, pb));
+          }
+        bar_sync(1 + grp, 128);
       }
-      bar_sync(1 + grp, 128);
-      // All four warps are past the previous tile of this group: its stage can be refilled.
-      if (loader && jt >= 1 && it - 2 + NSTAGE < ntiles) issue_tile(it - 2 + NSTAGE);
-
-      float sc[NT][2];
 #pragma unroll
-      for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-        for (int e = 0; e < 2; e++) {
-          const int r = 8 * nt + 2 * tg + e;
-          float tm = ldsf(sMax + ((buf * 4 + 0) * MAXR + r) * 4);
-#pragma unroll
-          for (int w = 1; w < 4; w++) tm = fmaxf(tm, ldsf(sMax + ((buf * 4 + w) * MAXR + r) * 4));
-          const float mn = fmaxf(m[nt][e], tm);
-          sc[nt][e] = ex2((m[nt][e] - mn) * LOG2E);
-          m[nt][e] = mn;
-          const float mb = mn * LOG2E;
-          const float pa = ex2(fmaf(sacc[nt][e], LOG2E, -mb)), pb = ex2(fmaf(sacc[nt][2 + e], LOG2E, -mb));
-          l[nt][e] = fmaf(l[nt][e], sc[nt][e], pa + pb);
-          // position pair (slot g, slot g + 8) of warp wq = P^T k-slot pair 8wq + g
-          sts32(sP + (buf * P_WORDS + r * P_STRIDE + 8 * wq + g) * 4, pack_h2(pa, pb));
-        }
-#pragma unroll
-      for (int mt = 0; mt < 4; mt++)
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-          o[mt][nt][0] *= sc[nt][0];
-          o[mt][nt][1] *= sc[nt][1];
-          o[mt][nt][2] *= sc[nt][0];
-          o[mt][nt][3] *= sc[nt][1];
-        }
-      bar_sync(1 + grp, 128);
+      for (int nt = 0; nt < NT; nt++) {
+        l[nt][0] += lt[nt][0];
+        l[nt][1] += lt[nt][1];
+      }
 
       // ---- O^T += V^T P^T for head dims 64wq + 8g .. +7 (8 bytes of each V row per lane)
       {
