@@ -6,20 +6,23 @@
 // int8 with one f32 scale per 32 dims, K = the cache bytes as stored, one exact int32 dot product
 // per 32-dim block, s = sum_b (dq[b] * dk[p][b]) * float(I_b) in block order, online softmax,
 // P -> f16, V -> f16(int8 * f16 scale). Unlike the reference, O accumulates in f32 (in TMEM), so
-// no max offset is needed; the running reference max is only moved when the true max has grown
+// no max offset is needed; the reference max of a row is only moved when its true max has grown
 // by more than TAU, which keeps P <= e^TAU and makes the O rescale rare.
 //
 // One CTA = 128 query tokens of one query head (TMEM lane = token) x one split of the positions,
-// walking 64-position tiles. Roles:
-//   warps 0-3  softmax: each thread owns one query row; reads the per-block int32 accumulators
-//              from TMEM, applies the block scales, keeps (m, l), writes P (f16) into shared
-//              memory in the tensor core's K-major 128B-swizzled layout, rescales O when needed,
-//              and writes the output.
-//   warps 4-7  converter: V tile int8 -> f16 into the MN-major 128B-swizzled layout that the P V
-//              MMA reads directly (no transpose), and the K scales f16 -> f32 table.
-//   warp 8     TMA producer (one lane): K and V tiles, double buffered.
-//   warp 9     MMA issuer (one lane): per tile 8 x (128x64x32 int8) into a 4-slot ring of TMEM
-//              accumulators, then 4 x (128x256x16 f16) into the O accumulator; owns TMEM.
+// walking 64-position tiles. Roles (14 warps):
+//   warps 0-7   softmax, two warpgroups: both own the 128 rows (warp w and w+4 share TMEM lanes
+//               32(w%4)..), warpgroup 0 takes positions 0-31 of a tile, warpgroup 1 positions
+//               32-63. Each thread reads its half of the per-block int32 accumulators from TMEM,
+//               applies the block scales with packed f32x2 arithmetic, exchanges the row maximum
+//               with its partner thread, writes its half of P (f16) into shared memory in the
+//               tensor core's K-major 128B-swizzled layout, rescales its half of O when the
+//               reference max moves, and writes its half of the output columns.
+//   warps 8-11  converter: V tile int8 -> f16 into the MN-major 128B-swizzled layout that the P V
+//               MMA reads directly (no transpose), and the K scales f16 -> f32 table.
+//   warp 12     TMA producer (one lane): K and V tiles, double buffered.
+//   warp 13     MMA issuer (one lane): per tile 8 x (128x64x32 int8) into a 4-slot ring of TMEM
+//               accumulators, then 4 x (128x256x16 f16) into the O accumulator; owns TMEM.
 // TMEM: columns 0-255 O (f32), 256-511 four S slots of 64 columns (s32).
 #include "combine.h"
 #include "common.cuh"
@@ -46,7 +49,9 @@ constexpr int OFF_V = OFF_K + 2 * KST_PAD;
 constexpr int OFF_VF = OFF_V + 2 * KST_PAD;
 constexpr int OFF_P = OFF_VF + 2 * VF_BYTES;
 constexpr int OFF_DKF = OFF_P + 2 * P_BYTES;
-constexpr int OFF_BAR = OFF_DKF + 2 * DKF_BYTES;
+constexpr int OFF_DQ = OFF_DKF + 2 * DKF_BYTES;     // f32 Q scales [128 rows][8]
+constexpr int OFF_XCH = OFF_DQ + QT * 8 * 4;        // row exchange between the two softmax warpgroups [tile parity][2][128] f32
+constexpr int OFF_BAR = OFF_XCH + 2 * 2 * QT * 4;
 constexpr int NBAR = 32;
 constexpr int OFF_MISC = OFF_BAR + NBAR * 8;        // tmem base address, abort flag
 constexpr int PF_SMEM_USED = OFF_MISC + 16;
@@ -72,7 +77,9 @@ enum {
   B_ODONE = 27,
 };
 
-constexpr int PF_THREADS = 320;
+constexpr int N_SOFTMAX_WARPS = 8;
+constexpr int CONV_WARP0 = 8, TMA_WARP = 12, MMA_WARP = 13;
+constexpr int PF_THREADS = 14 * 32;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_O = 0, TM_S = 256;
 constexpr uint32_t IDESC_QK = umma_idesc(2, 1, 1, 0, 0, QT, PT);    // s32 += s8 * s8, both K-major, M128 N64
@@ -89,14 +96,17 @@ struct PrefillParams {
   float kq_scale;
 };
 
-__device__ __forceinline__ float i2f_exact(int v) { return __int_as_float(v + 0x4B400000) - 12582912.0f; }  // |v| < 2^22
+__device__ __forceinline__ void pair_sync(int q) { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); }
 
-// Quantises one query row (256 floats at src, or zeros when src is null) to int8 with an f32
-// scale per 32 dims (src/attn.cu:587-606: v = q * kq_scale, d = amax / 127, id = 127 / amax,
-// q8 = rint(v * id)) and stores it as row r of the Q tile in the K-major 128B-swizzled layout.
-__device__ __forceinline__ void quantise_q_row(const float* src, float kq_scale, uint8_t* sQ, int r, float (&dq)[8]) {
+// Quantises blocks [B0, B0 + NB) of one query row (256 floats at src, or zeros when src is null)
+// to int8 with an f32 scale per 32 dims (src/attn.cu:587-606: v = q * kq_scale, d = amax / 127,
+// id = 127 / amax, q8 = rint(v * id)) and stores them in row r of the Q tile (K-major,
+// 128B-swizzled); dq[i] = scale of block B0 + i.
+template <int B0, int NB>
+__device__ __forceinline__ void quantise_q_row(const float* src, float kq_scale, uint8_t* sQ, int r, float (&dq)[NB]) {
 #pragma unroll
-  for (int b = 0; b < 8; b++) {
+  for (int bi = 0; bi < NB; bi++) {
+    const int b = B0 + bi;
     uint32_t w[8];
     float d = 0.f;
     if (src) {
@@ -124,7 +134,7 @@ __device__ __forceinline__ void quantise_q_row(const float* src, float kq_scale,
 #pragma unroll
       for (int j = 0; j < 8; j++) w[j] = 0;
     }
-    dq[b] = d;
+    dq[bi] = d;
     uint8_t* half = sQ + (b >> 2) * (QT * 128);
     const uint32_t c = 2 * (b & 3);
     *(uint4*)(half + swz128(r, c)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -173,7 +183,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
   }
 
   if (tid == 0) {
-    mbar_init(&bar[B_QFULL], 4);
+    mbar_init(&bar[B_QFULL], N_SOFTMAX_WARPS);
     for (int s = 0; s < 2; s++) {
       mbar_init(&bar[B_KFULL + s], 1);
       mbar_init(&bar[B_KEMPTY + s], 5);
@@ -181,19 +191,19 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
       mbar_init(&bar[B_VEMPTY + s], 4);
       mbar_init(&bar[B_VFFULL + s], 4);
       mbar_init(&bar[B_VFEMPTY + s], 1);
-      mbar_init(&bar[B_DKEMPTY + s], 4);
-      mbar_init(&bar[B_PFULL + s], 4);
+      mbar_init(&bar[B_DKEMPTY + s], N_SOFTMAX_WARPS);
+      mbar_init(&bar[B_PFULL + s], N_SOFTMAX_WARPS);
       mbar_init(&bar[B_PEMPTY + s], 1);
     }
     for (int s = 0; s < 4; s++) {
       mbar_init(&bar[B_SFULL + s], 1);
-      mbar_init(&bar[B_SEMPTY + s], 4);
+      mbar_init(&bar[B_SEMPTY + s], N_SOFTMAX_WARPS);
     }
     mbar_init(&bar[B_ODONE], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == MMA_WARP) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -202,141 +212,174 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp < 4) {
+  if (warp < N_SOFTMAX_WARPS) {
     // ================================================================ softmax warps
-    const int r = tid;                 // query row = TMEM lane
+    const int wg = warp >> 2, q = warp & 3;
+    const int r = q * 32 + lane;       // query row = TMEM lane
     const int t = t0 + r;
     const bool live = t < p.M;
+    float* xch = (float*)(sgen + OFF_XCH);
     float dq[8];
-    quantise_q_row(live ? p.qn + ((size_t)t * p.nqh + h) * AD : nullptr, p.kq_scale, sgen + OFF_Q, r, dq);
-    fence_proxy_async();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&bar[B_QFULL]);
+    {
+      // this thread quantises blocks 4wg .. 4wg+3 of its row; the scales go through shared memory
+      float dqh[4];
+      const float* src = live ? p.qn + ((size_t)t * p.nqh + h) * AD : nullptr;
+      if (wg == 0) quantise_q_row<0, 4>(src, p.kq_scale, sgen + OFF_Q, r, dqh);
+      else quantise_q_row<4, 4>(src, p.kq_scale, sgen + OFF_Q, r, dqh);
+      *(float4*)(sgen + OFF_DQ + (r * 8 + 4 * wg) * 4) = make_float4(dqh[0], dqh[1], dqh[2], dqh[3]);
+      fence_proxy_async();
+      pair_sync(q);
+      const float4 a = *(const float4*)(sgen + OFF_DQ + r * 32), b = *(const float4*)(sgen + OFF_DQ + r * 32 + 16);
+      dq[0] = a.x; dq[1] = a.y; dq[2] = a.z; dq[3] = a.w;
+      dq[4] = b.x; dq[5] = b.y; dq[6] = b.z; dq[7] = b.w;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[B_QFULL]);
+    }
 
-    const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
     const int limit = pos0 + t + 1;    // positions < limit are visible
-    float m_run = M_INIT, m_ref = M_INIT, l = 0.f;
+    const int col0 = wg * 32;          // this thread's positions of a tile: col0 .. col0+31
+    float m_run = M_INIT, m_ref = M_INIT;
+    uint64_t l2 = pack2(0.f, 0.f);
+    const uint64_t negc = pack2(-12582912.0f, -12582912.0f);
+    const uint64_t log2e2 = pack2(LOG2E, LOG2E);
 
     for (int j = 0; j < nt; j++) {
       const int pb = j & 1, ph = (j >> 1) & 1;
       const int p_tile = (it0 + j) * PT;
       mbar_wait(&bar[B_VFFULL + pb], ph, abort_flag, p.status);  // K scale table of this tile is ready
-      const uint32_t dkf = sbase + OFF_DKF + pb * DKF_BYTES;
-      float s[PT];
+      const uint8_t* dkf = sgen + OFF_DKF + pb * DKF_BYTES;
+      uint64_t s2[16];
 #pragma unroll
-      for (int i = 0; i < PT; i++) s[i] = 0.f;
+      for (int i = 0; i < 16; i++) s2[i] = pack2(0.f, 0.f);
 #pragma unroll
       for (int b = 0; b < 8; b++) {
         const int slot = b & 3;
         mbar_wait(&bar[B_SFULL + slot], (b >> 2) & 1, abort_flag, p.status);
         tc_fence_after();
+        uint32_t v[32];
+        tmem_ld32(tlane + TM_S + slot * PT + col0, v);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar[B_SEMPTY + slot]);  // the slot is in registers: it can be overwritten
+        const ulonglong2* dk2 = (const ulonglong2*)(dkf + (b * PT + col0) * 4);
+        const uint64_t dqb = pack2(dq[b], dq[b]);
 #pragma unroll
-        for (int hf = 0; hf < 2; hf++) {
-          uint32_t v[32];
-          tmem_ld32(tlane + TM_S + slot * PT + hf * 32, v);
-          tc_wait_ld();
-          if (hf == 1) {  // both halves are in registers: the slot can be overwritten
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar[B_SEMPTY + slot]);
-          }
-#pragma unroll
-          for (int i4 = 0; i4 < 8; i4++) {
-            float4 dk;
-            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-                         : "=f"(dk.x), "=f"(dk.y), "=f"(dk.z), "=f"(dk.w)
-                         : "r"(dkf + (b * PT + hf * 32 + i4 * 4) * 4));
-            const int i = hf * 32 + i4 * 4;
-            s[i] = fmaf(dq[b] * dk.x, i2f_exact((int)v[i4 * 4]), s[i]);
-            s[i + 1] = fmaf(dq[b] * dk.y, i2f_exact((int)v[i4 * 4 + 1]), s[i + 1]);
-            s[i + 2] = fmaf(dq[b] * dk.z, i2f_exact((int)v[i4 * 4 + 2]), s[i + 2]);
-            s[i + 3] = fmaf(dq[b] * dk.w, i2f_exact((int)v[i4 * 4 + 3]), s[i + 3]);
-          }
+        for (int i = 0; i < 8; i++) {
+          const ulonglong2 dk = dk2[i];  // K scales of positions 4i .. 4i+3 (block b)
+          // exact int -> float: as_float(v + 0x4B400000) = 12582912 + v, then subtract
+          const uint64_t f0 = add2(pack2(__int_as_float((int)v[4 * i] + 0x4B400000), __int_as_float((int)v[4 * i + 1] + 0x4B400000)), negc);
+          const uint64_t f1 = add2(pack2(__int_as_float((int)v[4 * i + 2] + 0x4B400000), __int_as_float((int)v[4 * i + 3] + 0x4B400000)), negc);
+          s2[2 * i] = fma2(mul2(dqb, dk.x), f0, s2[2 * i]);
+          s2[2 * i + 1] = fma2(mul2(dqb, dk.y), f1, s2[2 * i + 1]);
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[B_DKEMPTY + pb]);
 
-      // causal mask (only tiles that reach past the first row's limit need it) and the tile max
+      // causal mask (only tiles that reach past the first row's limit need it) and the half-tile max
+      float s[32];
+#pragma unroll
+      for (int i = 0; i < 16; i++) unpack2(s2[i], s[2 * i], s[2 * i + 1]);
       float mt = -INFINITY;
       if (p_tile + PT > pos0 + t0 + 1) {
 #pragma unroll
-        for (int i = 0; i < PT; i++) {
-          if (p_tile + i >= limit) s[i] = -INFINITY;
+        for (int i = 0; i < 32; i++) {
+          if (p_tile + col0 + i >= limit) s[i] = -INFINITY;
           mt = fmaxf(mt, s[i]);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < PT; i++) mt = fmaxf(mt, s[i]);
+        for (int i = 0; i < 32; i++) mt = fmaxf(mt, s[i]);
       }
+      // row maximum over both halves: exchange with the partner thread (warp w <-> w + 4); the
+      // buffer alternates with the tile so that a fast thread cannot overwrite what its partner
+      // has not read yet
+      xch[(pb * 2 + wg) * QT + r] = mt;
+      pair_sync(q);
+      mt = fmaxf(mt, xch[(pb * 2 + (wg ^ 1)) * QT + r]);
       m_run = fmaxf(m_run, mt);
 
-      // Move the reference max when the true max has run away from it (or on the first tile).
+      // Move the reference max when the true max has run away from it (and on the first tile). Both
+      // threads of a row hold the same m_run and m_ref, so both warps of a pair take the same branch.
       const bool want = m_run > m_ref + TAU;
       if (__any_sync(0xffffffffu, want)) {
         const float f = ex2((m_ref - m_run) * LOG2E);  // 0 on the first move (m_ref = -1e30)
         m_ref = m_run;
-        l *= f;
+        l2 = mul2(l2, pack2(f, f));
         if (j > 0) {
-          // O holds the sum of tiles < j once the P V of tile j-1 has completed.
+          // O holds the sum of tiles < j once the P V of tile j-1 has completed. This warp rescales
+          // columns 128wg .. 128wg+127 of its 32 rows.
           mbar_wait(&bar[B_PEMPTY + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag, p.status);
           tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < AD / 32; c++) {
+          for (int c = 0; c < 4; c++) {
             uint32_t v[32];
-            tmem_ld32(tlane + TM_O + c * 32, v);
+            tmem_ld32(tlane + TM_O + wg * 128 + c * 32, v);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-            tmem_st32(tlane + TM_O + c * 32, v);
+            tmem_st32(tlane + TM_O + wg * 128 + c * 32, v);
           }
           tc_wait_st();
           tc_fence_before();
         }
       }
 
-      // P = exp(s - m_ref): f32 row sum, f16 tile for the P V MMA
+      // P = exp(s - m_ref): f32 row sum, f16 half-tile for the P V MMA (chunks 4wg .. 4wg+3 of the row)
       mbar_wait(&bar[B_PEMPTY + pb], ph ^ 1, abort_flag, p.status);
       uint8_t* sP = sgen + OFF_P + pb * P_BYTES;
-      const float mb = m_ref * LOG2E;
+      const float nmb = -m_ref * LOG2E;
+      const uint64_t nmb2 = pack2(nmb, nmb);
 #pragma unroll
-      for (int c = 0; c < 8; c++) {
+      for (int c = 0; c < 4; c++) {
         uint32_t w[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-          const float e0 = ex2(fmaf(s[c * 8 + 2 * k], LOG2E, -mb)), e1 = ex2(fmaf(s[c * 8 + 2 * k + 1], LOG2E, -mb));
-          l += e0 + e1;
+          float a0, a1;
+          unpack2(fma2(pack2(s[c * 8 + 2 * k], s[c * 8 + 2 * k + 1]), log2e2, nmb2), a0, a1);
+          const float e0 = ex2(a0), e1 = ex2(a1);
+          l2 = add2(l2, pack2(e0, e1));
           w[k] = pack_h2(e0, e1);
         }
-        *(uint4*)(sP + swz128(r, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *(uint4*)(sP + swz128(r, 4 * wg + c)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[B_PFULL + pb]);
     }
 
-    // ---- epilogue: O / l * sigmoid(gate), or the unnormalised partial of this split
+    // ---- epilogue: O / l * sigmoid(gate), or the unnormalised partial of this split; this thread
+    // writes columns 128wg .. 128wg+127 of its row
+    float la, lb;
+    unpack2(l2, la, lb);
+    float l = la + lb;
+    xch[((nt & 1) * 2 + wg) * QT + r] = l;
+    pair_sync(q);
+    l += xch[((nt & 1) * 2 + (wg ^ 1)) * QT + r];
     mbar_wait(&bar[B_ODONE], 0, abort_flag, p.status);
     tc_fence_after();
     const float inv_l = 1.0f / l;
     float* po = nsplit > 1 ? p.part + (((size_t)z * p.M + t) * p.nqh + h) * PROW : nullptr;
-    if (live && po) {
+    if (live && po && wg == 0) {
       po[0] = m_ref;
       po[1] = l;
     }
 #pragma unroll 1
-    for (int c = 0; c < AD / 32; c++) {
+    for (int c = 0; c < 4; c++) {
+      const int d0 = wg * 128 + c * 32;
       uint32_t v[32];
-      tmem_ld32(tlane + TM_O + c * 32, v);
+      tmem_ld32(tlane + TM_O + d0, v);
       tc_wait_ld();
       if (!live) continue;
       if (po) {
 #pragma unroll
         for (int i = 0; i < 32; i += 2)
-          *(float2*)(po + 2 + c * 32 + i) = make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+          *(float2*)(po + 2 + d0 + i) = make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
       } else {
-        const float* gt = p.qg + ((size_t)t * p.nqh + h) * 512 + 256 + c * 32;
-        float* dst = p.o + ((size_t)t * p.nqh + h) * AD + c * 32;
+        const float* gt = p.qg + ((size_t)t * p.nqh + h) * 512 + 256 + d0;
+        float* dst = p.o + ((size_t)t * p.nqh + h) * AD + d0;
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 gg = *(const float4*)(gt + i);
@@ -350,9 +393,9 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
       }
     }
     tc_fence_before();
-  } else if (warp < 8) {
+  } else if (warp < TMA_WARP) {
     // ================================================================ converter warps
-    const int ct = tid - 128;
+    const int ct = tid - CONV_WARP0 * 32;
     for (int j = 0; j < nt; j++) {
       const int pb = j & 1, ph = (j >> 1) & 1;
       mbar_wait(&bar[B_VFULL + pb], ph, abort_flag, p.status);
@@ -362,10 +405,14 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
       const uint8_t* vst = sgen + OFF_V + pb * KST_PAD;
       const uint8_t* kst = sgen + OFF_K + pb * KST_PAD;
       uint8_t* vf = sgen + OFF_VF + pb * VF_BYTES;
-      // V: 64 rows x 16 chunks of 16 int8 -> 16 f16 (one rounding of q * d, as src/attn.cu:59-76)
+      // V: 64 rows x 16 chunks of 16 int8 -> 16 f16 (one rounding of q * d, as src/attn.cu:59-76).
+      // Item = (row, 16-dim chunk); eight neighbouring lanes take 4 chunks of rows rho and rho ^ 5,
+      // which keeps both the swizzled 16-byte loads and the swizzled 16-byte stores conflict-free.
 #pragma unroll 2
       for (int k = 0; k < 8; k++) {
-        const int q = ct + 128 * k, row = q >> 4, c16 = q & 15;
+        const int item = ct + 128 * k;
+        const int row = (2 * (item >> 5)) ^ (5 * ((item >> 2) & 1));
+        const int c16 = (item & 3) + 4 * ((item >> 3) & 3);
         const uint4 x = *(const uint4*)(vst + (c16 >> 3) * (PT * 128) + swz128(row, c16 & 7));
         const __half d = *(const __half*)(vst + 2 * PT * 128 + row * 16 + (c16 >> 1) * 2);
         const __half2 dd = __half2half2(d);
@@ -404,7 +451,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
         mbar_arrive(&bar[B_KEMPTY + pb]);
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == TMA_WARP) {
     // ================================================================ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tm_kv);
@@ -470,7 +517,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -502,7 +549,7 @@ prefill_qk_debug_kernel(const __grid_constant__ CUtensorMap tm_kv, const QkDebug
   uint64_t* bar = (uint64_t*)(sgen + DBG_OFF_BAR);
   uint32_t* tmem_slot = (uint32_t*)(sgen + DBG_OFF_BAR + 32);
   volatile int* abort_flag = (volatile int*)(sgen + DBG_OFF_BAR + 36);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5;
   if (tid == 0) {
     mbar_init(&bar[0], 1);
     mbar_init(&bar[1], 1);
@@ -519,7 +566,7 @@ prefill_qk_debug_kernel(const __grid_constant__ CUtensorMap tm_kv, const QkDebug
   const uint32_t tmem = *tmem_slot;
 
   float dq[8];
-  quantise_q_row(tid < p.rows ? p.x + (size_t)tid * AD : nullptr, p.kq_scale, sgen, tid, dq);
+  quantise_q_row<0, 8>(tid < p.rows ? p.x + (size_t)tid * AD : nullptr, p.kq_scale, sgen, tid, dq);
   if (tid < p.rows) {
     for (int b = 0; b < 8; b++) p.q_scale[tid * 8 + b] = dq[b];
     for (int b = 0; b < 8; b++)
@@ -592,6 +639,15 @@ int get_tmaps(const void* cache, int nkvh, int n_ctx, const CUtensorMap** vals, 
   return Q27B_OK;
 }
 
+int prefill_setup(DeviceCtx* ctx) {
+  if (!ctx->prefill_attr) {
+    Q27B_CK(cudaFuncSetAttribute(prefill_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_BYTES));
+    Q27B_CK(cudaFuncSetAttribute(prefill_qk_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DBG_SMEM));
+    ctx->prefill_attr = true;
+  }
+  return Q27B_OK;
+}
+
 }  // namespace
 }  // namespace q27b
 
@@ -607,12 +663,8 @@ int q27b_attn_prefill(const float* qn, const float* qg, const void* kcache, cons
   if (!q8) return fail(Q27B_UNSUPPORTED, "attn_prefill: only the q8_0 cache (int8 Q K^T path) is built");
   DeviceCtx* ctx;
   if (int rc = device_ctx(&ctx)) return rc;
+  if (int rc = prefill_setup(ctx)) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  if (!ctx->prefill_attr) {
-    Q27B_CK(cudaFuncSetAttribute(prefill_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_BYTES));
-    Q27B_CK(cudaFuncSetAttribute(prefill_qk_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DBG_SMEM));
-    ctx->prefill_attr = true;
-  }
   const int tiles = (M + QT - 1) / QT;
   const int ctas = tiles * nqh;
   // Splits over the positions: enough CTAs for every SM, at least 2048 positions per split
@@ -649,11 +701,7 @@ int q27b_prefill_qk_debug(const float* x, int rows, float kq_scale, const void* 
   if (!x || !kcache || !q_i8 || !q_scale || !acc) return fail(Q27B_BAD_SHAPE, "prefill_qk_debug: null pointer");
   DeviceCtx* ctx;
   if (int rc = device_ctx(&ctx)) return rc;
-  if (!ctx->prefill_attr) {
-    Q27B_CK(cudaFuncSetAttribute(prefill_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_BYTES));
-    Q27B_CK(cudaFuncSetAttribute(prefill_qk_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DBG_SMEM));
-    ctx->prefill_attr = true;
-  }
+  if (int rc = prefill_setup(ctx)) return rc;
   const CUtensorMap *kv, *ks;
   if (int rc = get_tmaps(kcache, nkvh, n_ctx, &kv, &ks)) return rc;
   QkDebugParams p = {x, rows, kq_scale, kh * n_ctx + p0, npos, q_i8, q_scale, acc, ctx->status};
