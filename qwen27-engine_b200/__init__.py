@@ -13,7 +13,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libq27b_attn.so")
+# Q27B_LIB: path of another build of the same library (kernel tuning experiments)
+LIB_PATH = os.environ.get("Q27B_LIB") or os.path.join(_HERE, "libq27b_attn.so")
 
 HEAD_DIM = 256
 GQA = 6

@@ -101,9 +101,8 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
 int launch_merge(const MergeParams& p, bool decode_layout, cudaStream_t s) {
   if (p.nparts < 1 || p.nparts > MAX_PARTS) return fail(Q27B_BAD_SHAPE, "lse_merge: 1..1024 partials");
   if (p.rows < 1) return Q27B_OK;
-  if (decode_layout) merge_kernel<true><<<(unsigned)p.rows, AD, 0, s>>>(p);
-  else merge_kernel<false><<<(unsigned)p.rows, AD, 0, s>>>(p);
-  Q27B_CK(cudaGetLastError());
+  if (decode_layout) Q27B_CK(launch_pdl(merge_kernel<true>, dim3((unsigned)p.rows), dim3(AD), 0, s, p));
+  else Q27B_CK(launch_pdl(merge_kernel<false>, dim3((unsigned)p.rows), dim3(AD), 0, s, p));
   return Q27B_OK;
 }
 

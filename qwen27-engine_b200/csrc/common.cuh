@@ -74,7 +74,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-// ------------------------------------------------------------------ TMA (no multicast anywhere)
+// ------------------------------------------------------------------ TMA (plain per-CTA loads only)
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"

@@ -32,28 +32,45 @@ namespace q27b {
 namespace {
 
 constexpr int TILE = 64;                       // positions per tile
-constexpr int NSTAGE = 6;
+#ifndef Q27B_NSTAGE
+#define Q27B_NSTAGE 6
+#endif
+constexpr int NSTAGE = Q27B_NSTAGE;
 constexpr int VAL_BYTES = TILE * AD;           // int8 values of one operand: two [64][128 B] halves
 constexpr int SC_BYTES = TILE * 16;            // f16 scales [64][8]
 constexpr int STAGE_BYTES = 2 * VAL_BYTES + 2 * SC_BYTES;  // 34816
 constexpr int OFF_KV = 0, OFF_VV = VAL_BYTES, OFF_KS = 2 * VAL_BYTES, OFF_VS = 2 * VAL_BYTES + SC_BYTES;
 constexpr int P_STRIDE = 36;                   // words per P row (32 position pairs + 4 padding: no bank conflicts)
 constexpr int P_WORDS = MAXR * P_STRIDE;
-constexpr int OFF_P = NSTAGE * STAGE_BYTES;                 // [2 groups][2 buffers][24][36] words
-constexpr int OFF_MAX = OFF_P + 2 * 2 * P_WORDS * 4;        // [2 groups][2 buffers][4 warps][24] floats
-constexpr int OFF_L = OFF_MAX + 2 * 2 * 4 * MAXR * 4;       // [2 groups][4 warps][24] floats
-constexpr int OFF_M1 = OFF_L + 2 * 4 * MAXR * 4;            // [24] floats: running max of group 1
-constexpr int OFF_BAR = OFF_M1 + MAXR * 4;                  // full[NSTAGE]
+#ifndef Q27B_NGROUP
+#define Q27B_NGROUP 2
+#endif
+constexpr int NGROUP = Q27B_NGROUP;                         // groups of four warps; group g takes tiles g, g + NGROUP, ...
+constexpr int OFF_P = NSTAGE * STAGE_BYTES;                 // [groups][2 buffers][24][36] words
+constexpr int OFF_MAX = OFF_P + NGROUP * 2 * P_WORDS * 4;   // [groups][2 buffers][4 warps][24] floats
+constexpr int OFF_L = OFF_MAX + NGROUP * 2 * 4 * MAXR * 4;  // [groups][4 warps][24] floats
+constexpr int OFF_M1 = OFF_L + NGROUP * 4 * MAXR * 4;       // [groups][24] floats: reference maxima at the end
+constexpr int OFF_BAR = OFF_M1 + NGROUP * MAXR * 4;         // full[NSTAGE]
 constexpr int OFF_FLAG = OFF_BAR + NSTAGE * 8;
-constexpr int OFF_TOK = OFF_FLAG + 16;                      // [2 groups][2 buffers] words: "move the maxima" tokens
-constexpr int SMEM_USED = OFF_TOK + 16;
+constexpr int OFF_TOK = OFF_FLAG + 16;                      // [groups][2 buffers] words: "move the maxima" tokens
+// Q fragments: k-steps 0 .. QREG_KS-1 stay in registers, the others are re-read from shared
+// memory for every tile (12 bytes of shared-memory traffic per position and k-step, but 6 registers
+// per k-step freed for the scheduler).
+#ifndef Q27B_QREG_KS
+#define Q27B_QREG_KS 16
+#endif
+constexpr int QREG_KS = Q27B_QREG_KS;
+constexpr int OFF_QF = OFF_TOK + 32;                        // [16 - QREG_KS k-steps][3][32 lanes] uint2
+constexpr int SMEM_USED = OFF_QF + (16 - QREG_KS) * 3 * 32 * 8;
 constexpr float TAU = 8.0f;                                 // a score may exceed the reference max by this much
 constexpr int SMEM_BYTES = SMEM_USED + 1024;               // slack for the 1024-byte alignment of the ring
 constexpr int O_STRIDE = AD + 4;                            // floats per row of the end-of-kernel O exchange
-static_assert(MAXR * O_STRIDE * 4 <= NSTAGE * STAGE_BYTES, "O exchange must fit in the ring");
+static_assert((NGROUP - 1) * MAXR * O_STRIDE * 4 <= NSTAGE * STAGE_BYTES, "O exchange must fit in the ring");
+static_assert(NGROUP >= 2 && NGROUP <= 3 && NSTAGE > NGROUP, "group / stage counts");
 static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 
-constexpr int N_THREADS = 256;
+constexpr int N_THREADS = NGROUP * 128;
+constexpr int BAR_ALL = 1 + NGROUP;                         // named barrier of all threads (1 .. NGROUP: the groups)
 
 struct DecodeParams {
   const float* qn;   // [T][nqh][256]
@@ -150,7 +167,7 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   if (tid == 0) {
     for (int s = 0; s < NSTAGE; s++) mbar_init(&full[s], 1);
     *abort_flag = 0;
-    for (int i = 0; i < 4; i++) ((volatile uint32_t*)(sgen + OFF_TOK))[i] = 0;
+    for (int i = 0; i < 2 * NGROUP; i++) ((volatile uint32_t*)(sgen + OFF_TOK))[i] = 0;
     mbar_fence_init();
   }
   __syncthreads();
@@ -183,14 +200,16 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
     const int grp = warp >> 2, wq = warp & 3;
     const bool loader = wq == 0 && lane == 0;  // refills this group's stages
     if (loader)
-      for (int it = grp; it < min(ntiles, NSTAGE); it += 2) issue_tile(it);
+      for (int it = grp; it < min(ntiles, NSTAGE); it += NGROUP) issue_tile(it);
     const int ra = 16 * wq + slot_row(g), rb = ra + 8;  // tile rows of MMA row slots g and g + 8 (S^T)
 
     // Q fragments (B operand of S^T = K Q^T), permuted to the k-slot order of the K loads:
     // k-step ks = 8h + 4j + s covers dims 128h + 64j + 16tg + 4s .. +3 of query row 8nt + g.
-    uint32_t qf[16][NT][2];
+    uint32_t qf[QREG_KS > 0 ? QREG_KS : 1][NT][2];
+    const uint32_t sQf = sbase + OFF_QF + lane * 8;
 #pragma unroll
     for (int ks = 0; ks < 16; ks++) {
+      if (ks >= QREG_KS && (ks & 7) != warp) continue;  // one warp fills each shared-memory k-step
       const int dim0 = 128 * (ks >> 3) + 64 * ((ks >> 2) & 1) + 16 * tg + 4 * (ks & 3);
 #pragma unroll
       for (int nt = 0; nt < NT; nt++) {
@@ -201,10 +220,16 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
           b0 = pack_h2(q.x * p.kq_scale, q.y * p.kq_scale);
           b1 = pack_h2(q.z * p.kq_scale, q.w * p.kq_scale);
         }
-        qf[ks][nt][0] = b0;
-        qf[ks][nt][1] = b1;
+        if (ks < QREG_KS) {
+          qf[ks][nt][0] = b0;
+          qf[ks][nt][1] = b1;
+        } else {
+          sts32(sQf + ((ks - QREG_KS) * 3 + nt) * 256, b0);
+          sts32(sQf + ((ks - QREG_KS) * 3 + nt) * 256 + 4, b1);
+        }
       }
     }
+    if (QREG_KS < 16) bar_sync(BAR_ALL, N_THREADS);
 
     // Visible end (local row index, exclusive) of this lane's query rows 8nt + 2tg + e.
     int lim[NT][2];
@@ -237,7 +262,7 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
     const uint32_t MAGIC = 0x64646464u;
 
     int jt = 0;
-    for (int it = grp; it < ntiles; it += 2, jt++) {
+    for (int it = grp; it < ntiles; it += NGROUP, jt++) {
       const int s = it % NSTAGE;
       mbar_wait(&full[s], (it / NSTAGE) & 1, abort_flag, p.status);
       const uint32_t st = sbase + s * STAGE_BYTES;
@@ -270,8 +295,18 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
             const uint32_t a1 = dq_pair(prmt(wb, MAGIC, 0x4140), db), a3 = dq_pair(prmt(wb, MAGIC, 0x4342), db);
             const int ks = 4 * hj + s2;
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-              mma16816((hj & 1) ? sacc2[nt] : sacc[nt], a0, a1, a2, a3, qf[ks][nt][0], qf[ks][nt][1]);
+            for (int nt = 0; nt < NT; nt++) {
+              uint32_t q0, q1;
+              if (ks < QREG_KS) {
+                q0 = qf[ks][nt][0];
+                q1 = qf[ks][nt][1];
+              } else {
+                const uint2 qv = lds64(sQf + ((ks - QREG_KS) * 3 + nt) * 256);
+                q0 = qv.x;
+                q1 = qv.y;
+              }
+              mma16816((hj & 1) ? sacc2[nt] : sacc[nt], a0, a1, a2, a3, q0, q1);
+            }
           }
         }
 #pragma unroll
@@ -315,7 +350,7 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
         }
       bar_sync(1 + grp, 128);
       // All four warps are past the previous tile of this group: its stage can be refilled.
-      if (loader && jt >= 1 && it - 2 + NSTAGE < ntiles) issue_tile(it - 2 + NSTAGE);
+      if (loader && jt >= 1 && it - NGROUP + NSTAGE < ntiles) issue_tile(it - NGROUP + NSTAGE);
       if (lds32(sTok + buf * 4) == token) {
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
@@ -420,26 +455,31 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
         l[nt][e] = v;
         if (g == 0) stsf(sbase + OFF_L + ((grp * 4 + wq) * MAXR + 8 * nt + 2 * tg + e) * 4, v);
       }
-    bar_sync(3, N_THREADS);  // every tile consumed: the ring is free for the O exchange
+    if (wq == 0 && g == 0) {
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) stsf(sbase + OFF_M1 + (grp * MAXR + 8 * nt + 2 * tg + e) * 4, m[nt][e]);
+    }
+    bar_sync(BAR_ALL, N_THREADS);  // every tile consumed: the ring is free for the O exchange
 
-    // ---- merge the two groups (log-sum-exp) and write the chunk partial
+    // ---- merge the groups (log-sum-exp) and write the chunk partial
     const uint32_t sO = sbase;
-    if (grp == 1) {
+    if (grp > 0) {
 #pragma unroll
       for (int nt = 0; nt < NT; nt++)
 #pragma unroll
         for (int e = 0; e < 2; e++) {
           const int r = 8 * nt + 2 * tg + e;
-          if (wq == 0 && g == 0) stsf(sbase + OFF_M1 + r * 4, m[nt][e]);
 #pragma unroll
           for (int mt = 0; mt < 4; mt++) {
             const int d = 64 * wq + 8 * g + 2 * mt;
-            stsf(sO + (r * O_STRIDE + d) * 4, o[mt][nt][e]);
-            stsf(sO + (r * O_STRIDE + d + 1) * 4, o[mt][nt][2 + e]);
+            stsf(sO + (((grp - 1) * MAXR + r) * O_STRIDE + d) * 4, o[mt][nt][e]);
+            stsf(sO + (((grp - 1) * MAXR + r) * O_STRIDE + d + 1) * 4, o[mt][nt][2 + e]);
           }
         }
     }
-    bar_sync(3, N_THREADS);
+    bar_sync(BAR_ALL, N_THREADS);
     if (grp == 0) {
 #pragma unroll
       for (int nt = 0; nt < NT; nt++)
@@ -447,26 +487,39 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
         for (int e = 0; e < 2; e++) {
           const int r = 8 * nt + 2 * tg + e;
           if (r >= R) continue;
-          const float m0 = m[nt][e], m1 = ldsf(sbase + OFF_M1 + r * 4);
-          const float M = fmaxf(m0, m1);
-          const float f0 = ex2((m0 - M) * LOG2E), f1 = ex2((m1 - M) * LOG2E);
+          float mg[NGROUP], f[NGROUP];
+          float M = m[nt][e];
+#pragma unroll
+          for (int k = 1; k < NGROUP; k++) {
+            mg[k] = ldsf(sbase + OFF_M1 + (k * MAXR + r) * 4);
+            M = fmaxf(M, mg[k]);
+          }
+          f[0] = ex2((m[nt][e] - M) * LOG2E);
+#pragma unroll
+          for (int k = 1; k < NGROUP; k++) f[k] = ex2((mg[k] - M) * LOG2E);
           float* po = out + (size_t)r * PROW;
 #pragma unroll
           for (int mt = 0; mt < 4; mt++) {
             const int d = 64 * wq + 8 * g + 2 * mt;
-            const float v0 = o[mt][nt][e] * f0 + ldsf(sO + (r * O_STRIDE + d) * 4) * f1;
-            const float v1 = o[mt][nt][2 + e] * f0 + ldsf(sO + (r * O_STRIDE + d + 1) * 4) * f1;
+            float v0 = o[mt][nt][e] * f[0], v1 = o[mt][nt][2 + e] * f[0];
+#pragma unroll
+            for (int k = 1; k < NGROUP; k++) {
+              v0 += ldsf(sO + (((k - 1) * MAXR + r) * O_STRIDE + d) * 4) * f[k];
+              v1 += ldsf(sO + (((k - 1) * MAXR + r) * O_STRIDE + d + 1) * 4) * f[k];
+            }
             *(float2*)(po + 2 + d) = make_float2(v0, v1);
           }
           if (wq == 0 && g == 0) {
-            float l0 = 0.f, l1 = 0.f;
+            float lsum = 0.f;
 #pragma unroll
-            for (int w = 0; w < 4; w++) {
-              l0 += ldsf(sbase + OFF_L + ((0 * 4 + w) * MAXR + r) * 4);
-              l1 += ldsf(sbase + OFF_L + ((1 * 4 + w) * MAXR + r) * 4);
+            for (int k = 0; k < NGROUP; k++) {
+              float lk = 0.f;
+#pragma unroll
+              for (int w = 0; w < 4; w++) lk += ldsf(sbase + OFF_L + ((k * 4 + w) * MAXR + r) * 4);
+              lsum += lk * f[k];
             }
             po[0] = M;
-            po[1] = l0 * f0 + l1 * f1;
+            po[1] = lsum;
           }
         }
     }
@@ -515,8 +568,8 @@ int launch_decode(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMa
     Q27B_CK(cudaFuncSetAttribute(decode_q8_kernel<NT, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     attr[dev] = true;
   }
-  decode_q8_kernel<NT, PAGED><<<dim3(p.nch, p.nkvh, nseq), N_THREADS, SMEM_BYTES, s>>>(*kv, *ks, *vv, *vs, p);
-  Q27B_CK(cudaGetLastError());
+  Q27B_CK(launch_pdl(decode_q8_kernel<NT, PAGED>, dim3(p.nch, p.nkvh, nseq), dim3(N_THREADS), SMEM_BYTES, s, *kv, *ks, *vv,
+                     *vs, p));
   return Q27B_OK;
 }
 template <bool PAGED>

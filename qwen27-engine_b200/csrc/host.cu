@@ -2,6 +2,7 @@
 #include "host.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 namespace q27b {
@@ -15,6 +16,14 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeFn g_encode = nullptr;
 }  // namespace
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("Q27_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 
 int fail(int code, const std::string& msg) {
   g_err = msg;

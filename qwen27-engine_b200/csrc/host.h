@@ -43,6 +43,27 @@ int device_ctx(DeviceCtx** out);
 int ensure_part(DeviceCtx* ctx, size_t floats);
 int ensure_work(DeviceCtx* ctx, size_t ints);
 
+// True unless Q27_PDL=0: kernels are launched with the programmatic-stream-serialization attribute,
+// so a kernel's CTAs may be scheduled while its predecessor drains (every kernel here begins with
+// griddepcontrol.wait, which holds it until the predecessor has completed and flushed). The
+// reference has the same switch, off by default (src/ops.cu:12-15, src/common.cuh:28-42).
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // 2-D byte tensor map over `rows` rows of `row_bytes` bytes (row pitch `pitch_bytes`), copied in
 // boxes of box_bytes x box_rows. swizzle128: 128-byte swizzle (box_bytes must then be 128).
 // Rows past the end read as zero.
