@@ -97,11 +97,30 @@ class ClockSampler:
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def fill_caches(q, nkvh, n, n_ctx, seed):
-    """K and V caches of n positions, quantised by the library's own append kernel from N(0,1) rows."""
+def graph_us(fn, calls=20, replays=5):
+    """Microseconds per call of fn(i), from `calls` calls captured in one CUDA graph and replayed."""
+    fn(0)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(calls):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (calls * replays)
+
+
+def fill_caches(q, nkvh, n, n_ctx, seed, q8=True):
+    """K and V caches of n positions, written by the library's own append kernel from N(0,1) rows."""
     g = torch.Generator(device="cuda")
     g.manual_seed(seed)
-    kc, vc = q.new_cache(nkvh, n_ctx), q.new_cache(nkvh, n_ctx)
+    kc, vc = q.new_cache(nkvh, n_ctx, q8), q.new_cache(nkvh, n_ctx, q8)
     pos = torch.zeros(1, dtype=torch.int32, device="cuda")
     step = 8192
     for p0 in range(0, n, step):
@@ -109,7 +128,7 @@ def fill_caches(q, nkvh, n, n_ctx, seed):
         k = torch.randn((m, nkvh, AD), generator=g, device="cuda")
         v = torch.randn((m, nkvh, AD), generator=g, device="cuda")
         pos.fill_(p0)
-        q.kv_append(k, v, kc, vc, pos, m, nkvh, n_ctx)
+        q.kv_append(k, v, kc, vc, pos, m, nkvh, n_ctx, q8)
     torch.cuda.synchronize()
     return kc, vc
 
@@ -386,14 +405,27 @@ def extras(q, caches, qn, qg, o, n_ctx):
     """Other depths of the metric, the prefill TOPS, the batched paged decode and the reference's kernels."""
     out = {"decode_us": {}, "prefill": {}}
     pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # the other depths of the metric, timed as the reference times them (tools/bench_attn.cu:131-147):
+    # 20 calls captured in one CUDA graph, replayed 5 times, so that host launch time does not count
     for depth in (1024, 30000, 100000, 150000):
         pos.fill_(depth - T)
 
         def step(i):
             kc, vc = caches[i % NBUF]
             q.attn_decode(qn, qg, kc, vc, o, None, None, pos, T, SCALE, NQH, NKVH, n_ctx)
-        ms = time_steps(step, 200, 10)
-        out["decode_us"][str(depth)] = {"us": ms * 1e3, "gbs": kv_bytes(NKVH, depth) / (ms * 1e-3) / 1e9}
+        us = graph_us(step)
+        out["decode_us"][str(depth)] = {"us": us, "gbs": kv_bytes(NKVH, depth) / (us * 1e-6) / 1e9}
+    # spec-verify decode at 32,768 positions with the q8_0 and with the f16 KV cache
+    n2 = 32768
+    pos.fill_(n2 - T)
+    f16c = [fill_caches(q, NKVH, n2, n2 + 64, 2002 + i, q8=False) for i in range(NBUF)]
+    us_q8 = graph_us(lambda i: q.attn_decode(qn, qg, caches[i % NBUF][0], caches[i % NBUF][1], o, None, None, pos, T,
+                                             SCALE, NQH, NKVH, n_ctx))
+    us_f16 = graph_us(lambda i: q.attn_decode(qn, qg, f16c[i % NBUF][0], f16c[i % NBUF][1], o, None, None, pos, T,
+                                              SCALE, NQH, NKVH, n2 + 64, False))
+    out["spec_verify_32768"] = {"q8_0": {"us": us_q8, "gbs": kv_bytes(NKVH, n2) / (us_q8 * 1e-6) / 1e9},
+                                "f16": {"us": us_f16, "gbs": 2.0 * NKVH * n2 * 512 / (us_f16 * 1e-6) / 1e9}}
+    del f16c
     # prefill chunk: 2048 new tokens on a prefix of P tokens (int8 Q K^T, f16 P V); ops as the reference counts them
     M = 2048
     g = torch.Generator(device="cuda")
@@ -416,6 +448,11 @@ def extras(q, caches, qn, qg, o, n_ctx):
         pos.fill_(N_POS - T)
         ms = time_steps(lambda i: ref.decode(qn, qg, caches[i % NBUF][0], caches[i % NBUF][1], o, pos, T, NQH, NKVH, n_ctx), 100, 5)
         out["reference_kernels_same_gpu"] = {"decode_150k_us": ms * 1e3, "decode_150k_gbs": kv_bytes(NKVH, N_POS) / (ms * 1e-3) / 1e9}
+        out["reference_kernels_same_gpu"]["decode_us_graph"] = {}
+        for depth in (1024, 30000, 100000, 150000):
+            pos.fill_(depth - T)
+            us = graph_us(lambda i: ref.decode(qn, qg, caches[i % NBUF][0], caches[i % NBUF][1], o, pos, T, NQH, NKVH, n_ctx))
+            out["reference_kernels_same_gpu"]["decode_us_graph"][str(depth)] = us
         for P in (32768,):
             pos.fill_(P)
             ops = NQH * 1024.0 * (M * P + M * (M + 1) / 2)

@@ -50,6 +50,19 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
     np = min(np, max(1, (p.seq_len[seq] + p.chunk_len - 1) / p.chunk_len));
   }
 
+  // The first PRE partials of this thread's column (and their sums l) are requested before the
+  // maxima are reduced, so that the kernel makes one trip to L2 instead of two.
+  constexpr int PRE = 48;
+  const float* col = rm.first + 2 + d;
+  float av[PRE], lv[PRE];
+#pragma unroll
+  for (int c = 0; c < PRE; c++)
+    if (c < np) {
+      av[c] = col[c * rm.stride];
+      lv[c] = rm.first[c * rm.stride + 1];
+    }
+  const float gate = rm.gate ? rm.gate[d] : 0.f;
+
   // M and the factors
   float mx = M_INIT;
   for (int c = d; c < np; c += AD) mx = fmaxf(mx, rm.first[c * rm.stride]);
@@ -64,9 +77,15 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
   __syncthreads();
 
   float L = 0.f, A = 0.f;
-  const float* col = rm.first + 2 + d;
+#pragma unroll
+  for (int c = 0; c < PRE; c++)
+    if (c < np) {
+      const float f = sf[c];
+      L += lv[c] * f;
+      A += av[c] * f;
+    }
 #pragma unroll 8
-  for (int c = 0; c < np; c++) {
+  for (int c = PRE; c < np; c++) {
     const float f = sf[c];
     L += rm.first[c * rm.stride + 1] * f;
     A += col[c * rm.stride] * f;
@@ -83,7 +102,7 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
     return;
   }
   float y = A / L;
-  if (rm.gate) y *= 1.0f / (1.0f + expf(-rm.gate[d]));
+  if (rm.gate) y *= 1.0f / (1.0f + expf(-gate));
   if (!p.xq) {
     p.o[oi] = y;
     return;

@@ -1,4 +1,4 @@
-// Split-K flash-decode over a q8_0 (or f16) KV cache for 1..4 speculative-verify query tokens.
+// Split-K flash-decode over a q8_0 or f16 KV cache for 1..4 speculative-verify query tokens.
 //
 // Replaces attn_mma_kernel + the host wrapper attn_decode of the reference (src/attn.cu:95-292,
 // 894-918). Same decomposition of the work (one CTA per (position chunk, KV head), all 6*T query
@@ -7,22 +7,25 @@
 // scale), P -> f16, f32 accumulation, row sums from the f32 P; src/attn.cu:10-11). The kernel
 // itself is built for B200:
 //
-//  * 64-position tiles (K and V values as two 128-byte-swizzled 64x128 B boxes each, plus the
-//    two 64x16 B scale boxes) are streamed by TMA into a 6-stage mbarrier ring. A stage is
-//    refilled by one elected lane right after the group barrier that proves all four warps are
-//    done with it, so there is no producer warp and no "empty" barrier: ~140 KB stay in flight
-//    per SM, which is what HBM3e needs to stay busy.
+//  * 64-position tiles (K and V values as 128-byte-swizzled 64x128 B boxes, plus for q8_0 the two
+//    64x16 B scale boxes) are streamed by TMA into an mbarrier ring (6 stages of 34 KB for q8_0,
+//    3 of 64 KB for f16). A stage is refilled by one elected lane right after the group barrier
+//    that proves all four warps are done with it, so there is no producer warp and no "empty"
+//    barrier: ~140 KB stay in flight per SM, which is what HBM3e needs to stay busy.
 //  * Eight consumer warps in two groups of four; the groups take alternate tiles and keep their
 //    own running (m, l, O), merged once at the end. Within a group, warp w computes
 //    S^T = K Q^T for tile rows 16w..16w+15 (positions on the MMA M axis, the 6*T query rows on
 //    N = 8/16/24: no padding waste), then O^T += V^T P^T for head dims 64w..64w+63 over all 64
 //    positions. P (64 x 24 f16) is the only thing exchanged between warps.
 //  * K and V go from shared memory straight into mma.sync fragments: each lane loads 16 (K) or
-//    8 (V) consecutive int8 of a row, and the byte -> f16 conversion (0x64xx magic, minus 1152,
-//    times the block scale: one rounding) happens in registers. The contraction index of an MMA
-//    may be permuted freely, so the k-slots are chosen to match what a coalesced 16-byte load
-//    delivers; Q is pre-permuted to match, once, into registers. With the 128-byte swizzle and a
-//    bit-reversed row order inside each 16-row slab every shared-memory load is conflict-free.
+//    8 (V) consecutive bytes of a row, and for q8_0 the byte -> f16 conversion (0x64xx magic,
+//    minus 1152, times the block scale: one rounding) happens in registers. The contraction index
+//    of an MMA may be permuted freely, so the k-slots are chosen to match what a coalesced 16-byte
+//    load delivers; Q is pre-permuted to match, once, into registers. With the 128-byte swizzle
+//    and a bit-reversed row order inside each 16-row slab every shared-memory load is
+//    conflict-free.
+//  * The reference maxima of a group only move when a score exceeds them by more than TAU (and on
+//    the group's first tile): a tile normally costs one group barrier and no rescale of O.
 #include "combine.h"
 #include "common.cuh"
 
@@ -35,38 +38,43 @@ constexpr int TILE = 64;                       // positions per tile
 #ifndef Q27B_NSTAGE
 #define Q27B_NSTAGE 6
 #endif
-constexpr int NSTAGE = Q27B_NSTAGE;
-constexpr int VAL_BYTES = TILE * AD;           // int8 values of one operand: two [64][128 B] halves
-constexpr int SC_BYTES = TILE * 16;            // f16 scales [64][8]
-constexpr int STAGE_BYTES = 2 * VAL_BYTES + 2 * SC_BYTES;  // 34816
-constexpr int OFF_KV = 0, OFF_VV = VAL_BYTES, OFF_KS = 2 * VAL_BYTES, OFF_VS = 2 * VAL_BYTES + SC_BYTES;
-constexpr int P_STRIDE = 36;                   // words per P row (32 position pairs + 4 padding: no bank conflicts)
-constexpr int P_WORDS = MAXR * P_STRIDE;
 #ifndef Q27B_NGROUP
 #define Q27B_NGROUP 2
 #endif
-constexpr int NGROUP = Q27B_NGROUP;                         // groups of four warps; group g takes tiles g, g + NGROUP, ...
-constexpr int OFF_P = NSTAGE * STAGE_BYTES;                 // [groups][2 buffers][24][36] words
+constexpr int NGROUP = Q27B_NGROUP;            // groups of four warps; group g takes tiles g, g + NGROUP, ...
+
+// Geometry of one pipeline stage. Values: ROWB bytes per position = NSEG segments of 128 bytes, each
+// segment stored as a [64 rows][128 B] swizzled box; q8_0 adds [64][16 B] scale boxes.
+template <bool Q8>
+struct Geo {
+  static constexpr int ROWB = Q8 ? AD : 2 * AD;
+  static constexpr int NSEG = ROWB / 128;
+  static constexpr int SEG_BYTES = TILE * 128;
+  static constexpr int VAL_BYTES = NSEG * SEG_BYTES;
+  static constexpr int SC_BYTES = Q8 ? TILE * 16 : 0;
+  static constexpr int STAGE_BYTES = 2 * VAL_BYTES + 2 * SC_BYTES;  // 34816 (q8_0) / 65536 (f16)
+  static constexpr int NSTAGE = Q8 ? Q27B_NSTAGE : 3;
+  static constexpr int OFF_KV = 0, OFF_VV = VAL_BYTES, OFF_KS = 2 * VAL_BYTES, OFF_VS = 2 * VAL_BYTES + SC_BYTES;
+};
+constexpr int RING_BYTES = Geo<true>::NSTAGE * Geo<true>::STAGE_BYTES > Geo<false>::NSTAGE * Geo<false>::STAGE_BYTES
+                               ? Geo<true>::NSTAGE * Geo<true>::STAGE_BYTES
+                               : Geo<false>::NSTAGE * Geo<false>::STAGE_BYTES;
+constexpr int MAX_STAGES = Geo<true>::NSTAGE > Geo<false>::NSTAGE ? Geo<true>::NSTAGE : Geo<false>::NSTAGE;
+constexpr int P_STRIDE = 36;                   // words per P row (32 position pairs + 4 padding: no bank conflicts)
+constexpr int P_WORDS = MAXR * P_STRIDE;
+constexpr int OFF_P = RING_BYTES;                           // [groups][2 buffers][24][36] words
 constexpr int OFF_MAX = OFF_P + NGROUP * 2 * P_WORDS * 4;   // [groups][2 buffers][4 warps][24] floats
 constexpr int OFF_L = OFF_MAX + NGROUP * 2 * 4 * MAXR * 4;  // [groups][4 warps][24] floats
 constexpr int OFF_M1 = OFF_L + NGROUP * 4 * MAXR * 4;       // [groups][24] floats: reference maxima at the end
-constexpr int OFF_BAR = OFF_M1 + NGROUP * MAXR * 4;         // full[NSTAGE]
-constexpr int OFF_FLAG = OFF_BAR + NSTAGE * 8;
+constexpr int OFF_BAR = OFF_M1 + NGROUP * MAXR * 4;         // full[stages]
+constexpr int OFF_FLAG = OFF_BAR + MAX_STAGES * 8;
 constexpr int OFF_TOK = OFF_FLAG + 16;                      // [groups][2 buffers] words: "move the maxima" tokens
-// Q fragments: k-steps 0 .. QREG_KS-1 stay in registers, the others are re-read from shared
-// memory for every tile (12 bytes of shared-memory traffic per position and k-step, but 6 registers
-// per k-step freed for the scheduler).
-#ifndef Q27B_QREG_KS
-#define Q27B_QREG_KS 16
-#endif
-constexpr int QREG_KS = Q27B_QREG_KS;
-constexpr int OFF_QF = OFF_TOK + 32;                        // [16 - QREG_KS k-steps][3][32 lanes] uint2
-constexpr int SMEM_USED = OFF_QF + (16 - QREG_KS) * 3 * 32 * 8;
+constexpr int SMEM_USED = OFF_TOK + 32;
 constexpr float TAU = 8.0f;                                 // a score may exceed the reference max by this much
 constexpr int SMEM_BYTES = SMEM_USED + 1024;               // slack for the 1024-byte alignment of the ring
 constexpr int O_STRIDE = AD + 4;                            // floats per row of the end-of-kernel O exchange
-static_assert((NGROUP - 1) * MAXR * O_STRIDE * 4 <= NSTAGE * STAGE_BYTES, "O exchange must fit in the ring");
-static_assert(NGROUP >= 2 && NGROUP <= 3 && NSTAGE > NGROUP, "group / stage counts");
+static_assert((NGROUP - 1) * MAXR * O_STRIDE * 4 <= RING_BYTES, "O exchange must fit in the ring");
+static_assert(NGROUP == 2, "the register budget (Q fragments in registers) is sized for two groups");
 static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 
 constexpr int N_THREADS = NGROUP * 128;
@@ -120,12 +128,23 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 // Row of a 16-row slab that MMA row slot s (0..15) stands for: 8 * (s >> 3) + bitrev3(s & 7).
 __device__ __forceinline__ int slot_row(int s) { return (s & 8) | ((s & 1) << 2) | (s & 2) | ((s & 4) >> 2); }
 
-// NT = 8-row groups of query rows (ceil(6 T / 8)). PAGED: batched decode over 256-position pages.
-template <int NT, bool PAGED>
+// First of the 4 head dims that k-step ks (0..15) of the S^T MMAs covers for lane quarter tg.
+// q8_0: a 16-byte load is 16 dims = 4 k-steps; f16: a 16-byte load is 8 dims = 2 k-steps.
+template <bool Q8>
+__device__ __forceinline__ int ks_dim0(int ks, int tg) {
+  if (Q8) return 128 * (ks >> 3) + 64 * ((ks >> 2) & 1) + 16 * tg + 4 * (ks & 3);
+  return 64 * (ks >> 2) + 32 * ((ks >> 1) & 1) + 8 * tg + 4 * (ks & 1);
+}
+
+// NT = 8-row groups of query rows (ceil(6 T / 8)). PAGED: batched decode over 256-position pages
+// (q8_0 only). Q8: q8_0 cache (else f16).
+template <int NT, bool PAGED, bool Q8>
 __global__ void __launch_bounds__(N_THREADS, 1)
-decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_ks,
-                 const __grid_constant__ CUtensorMap tm_vv, const __grid_constant__ CUtensorMap tm_vs,
-                 const DecodeParams p) {
+decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_ks,
+              const __grid_constant__ CUtensorMap tm_vv, const __grid_constant__ CUtensorMap tm_vs,
+              const DecodeParams p) {
+  using G = Geo<Q8>;
+  constexpr int NSTAGE = G::NSTAGE;
   pdl_wait();
   pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
@@ -135,11 +154,20 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   volatile int* abort_flag = (volatile int*)(sgen + OFF_FLAG);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {  // start fetching the tensor maps while the position is being read
+    tma_prefetch_desc(&tm_kv);
+    tma_prefetch_desc(&tm_vv);
+    if (Q8) {
+      tma_prefetch_desc(&tm_ks);
+      tma_prefetch_desc(&tm_vs);
+    }
+  }
   const int ch = blockIdx.x, kh = blockIdx.y;
   const int T = p.T, R = GQA * T;
   const int seq = PAGED ? blockIdx.z : 0;
   const int pos0 = PAGED ? p.seq_len[seq] - T : *p.pos0;
   const float* qn = p.qn + (size_t)seq * T * p.nqh * AD;
+  const int g = lane >> 2, tg = lane & 3;
 
   // Local rows to attend, and this CTA's chunk [c0, c1) of them (multiples of TILE).
   int n = pos0 + T - p.base_pos;
@@ -172,236 +200,239 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   }
   __syncthreads();
 
-  {
-    // TMA of tile `it` into stage it % NSTAGE (one thread).
-    const int row0 = kh * p.n_ctx + c0;
-    auto issue_tile = [&](int it) {
-      const int s = it % NSTAGE;
-      uint8_t* st = sgen + (size_t)s * STAGE_BYTES;
-      mbar_expect_tx(&full[s], STAGE_BYTES);
-      int row = row0 + it * TILE;
-      if (PAGED) {  // a tile never straddles a page (64 | 256)
-        const int pp = c0 + it * TILE;
-        int pg = p.page_table[(size_t)seq * p.max_pages + pp / Q27B_PAGE];
-        if (pg < 0 || pg >= p.n_pages) {  // never read outside the pool: flag it and read page 0
-          atomicOr(p.status, ST_BAD_PAGE);
-          pg = 0;
-        }
-        row = (pg * p.nkvh + kh) * Q27B_PAGE + pp % Q27B_PAGE;
+  // TMA of tile `it` into stage it % NSTAGE (one thread).
+  const int row0 = kh * p.n_ctx + c0;
+  auto issue_tile = [&](int it) {
+    const int s = it % NSTAGE;
+    uint8_t* st = sgen + (size_t)s * G::STAGE_BYTES;
+    mbar_expect_tx(&full[s], G::STAGE_BYTES);
+    int row = row0 + it * TILE;
+    if (PAGED) {  // a tile never straddles a page (64 | 256)
+      const int pp = c0 + it * TILE;
+      int pg = p.page_table[(size_t)seq * p.max_pages + pp / Q27B_PAGE];
+      if (pg < 0 || pg >= p.n_pages) {  // never read outside the pool: flag it and read page 0
+        atomicOr(p.status, ST_BAD_PAGE);
+        pg = 0;
       }
-      tma_load_2d(st + OFF_KV, &tm_kv, 0, row, &full[s]);
-      tma_load_2d(st + OFF_KV + VAL_BYTES / 2, &tm_kv, 128, row, &full[s]);
-      tma_load_2d(st + OFF_VV, &tm_vv, 0, row, &full[s]);
-      tma_load_2d(st + OFF_VV + VAL_BYTES / 2, &tm_vv, 128, row, &full[s]);
-      tma_load_2d(st + OFF_KS, &tm_ks, 0, row, &full[s]);
-      tma_load_2d(st + OFF_VS, &tm_vs, 0, row, &full[s]);
-    };
-    const int g = lane >> 2, tg = lane & 3;
-    const int grp = warp >> 2, wq = warp & 3;
-    const bool loader = wq == 0 && lane == 0;  // refills this group's stages
-    if (loader)
-      for (int it = grp; it < min(ntiles, NSTAGE); it += NGROUP) issue_tile(it);
-    const int ra = 16 * wq + slot_row(g), rb = ra + 8;  // tile rows of MMA row slots g and g + 8 (S^T)
+      row = (pg * p.nkvh + kh) * Q27B_PAGE + pp % Q27B_PAGE;
+    }
+#pragma unroll
+    for (int sg = 0; sg < G::NSEG; sg++) {
+      tma_load_2d(st + G::OFF_KV + sg * G::SEG_BYTES, &tm_kv, 128 * sg, row, &full[s]);
+      tma_load_2d(st + G::OFF_VV + sg * G::SEG_BYTES, &tm_vv, 128 * sg, row, &full[s]);
+    }
+    if (Q8) {
+      tma_load_2d(st + G::OFF_KS, &tm_ks, 0, row, &full[s]);
+      tma_load_2d(st + G::OFF_VS, &tm_vs, 0, row, &full[s]);
+    }
+  };
 
-    // Q fragments (B operand of S^T = K Q^T), permuted to the k-slot order of the K loads:
-    // k-step ks = 8h + 4j + s covers dims 128h + 64j + 16tg + 4s .. +3 of query row 8nt + g.
-    uint32_t qf[QREG_KS > 0 ? QREG_KS : 1][NT][2];
-    const uint32_t sQf = sbase + OFF_QF + lane * 8;
+  const int grp = warp >> 2, wq = warp & 3;
+  const bool loader = wq == 0 && lane == 0;  // refills this group's stages
+  if (loader)
+    for (int it = grp; it < min(ntiles, NSTAGE); it += NGROUP) issue_tile(it);
+  const int ra = 16 * wq + slot_row(g), rb = ra + 8;  // tile rows of MMA row slots g and g + 8 (S^T)
+
+  // Q fragments (B operand of S^T = K Q^T), permuted to the k-slot order of the K loads:
+  // k-step ks covers dims ks_dim0(ks, tg) .. +3 of query row 8nt + g.
+  uint32_t qf[16][NT][2];
 #pragma unroll
-    for (int ks = 0; ks < 16; ks++) {
-      if (ks >= QREG_KS && (ks & 7) != warp) continue;  // one warp fills each shared-memory k-step
-      const int dim0 = 128 * (ks >> 3) + 64 * ((ks >> 2) & 1) + 16 * tg + 4 * (ks & 3);
+  for (int ks = 0; ks < 16; ks++) {
+    const int dim0 = ks_dim0<Q8>(ks, tg);
 #pragma unroll
-      for (int nt = 0; nt < NT; nt++) {
-        const int r = 8 * nt + g;
-        uint32_t b0 = 0, b1 = 0;
-        if (r < R) {
-          const float4 q = *(const float4*)(qn + ((size_t)(r / GQA) * p.nqh + kh * GQA + r % GQA) * AD + dim0);
-          b0 = pack_h2(q.x * p.kq_scale, q.y * p.kq_scale);
-          b1 = pack_h2(q.z * p.kq_scale, q.w * p.kq_scale);
+    for (int nt = 0; nt < NT; nt++) {
+      const int r = 8 * nt + g;
+      uint32_t b0 = 0, b1 = 0;
+      if (r < R) {
+        const float4 q = *(const float4*)(qn + ((size_t)(r / GQA) * p.nqh + kh * GQA + r % GQA) * AD + dim0);
+        b0 = pack_h2(q.x * p.kq_scale, q.y * p.kq_scale);
+        b1 = pack_h2(q.z * p.kq_scale, q.w * p.kq_scale);
+      }
+      qf[ks][nt][0] = b0;
+      qf[ks][nt][1] = b1;
+    }
+  }
+
+
+
+  // Visible end (local row index, exclusive) of this lane's query rows 8nt + 2tg + e.
+  int lim[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+      const int r = 8 * nt + 2 * tg + e;
+      lim[nt][e] = min(c1, pos0 + min(r / GQA, T - 1) + 1 - p.base_pos);
+    }
+  const int lim_min = min(c1, pos0 + 1 - p.base_pos);
+
+  float o[4][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) o[mt][nt][0] = o[mt][nt][1] = o[mt][nt][2] = o[mt][nt][3] = 0.f;
+  float m[NT][2], l[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++) {
+    m[nt][0] = m[nt][1] = M_INIT;
+    l[nt][0] = l[nt][1] = 0.f;
+  }
+
+  const uint32_t sP = sbase + OFF_P + grp * 2 * P_WORDS * 4;
+  const uint32_t sMax = sbase + OFF_MAX + grp * 2 * 4 * MAXR * 4;
+  const uint32_t sTok = sbase + OFF_TOK + grp * 8;
+  const uint32_t sel_sc = (tg & 2) ? 0x3232u : 0x1010u;  // which f16 of a scale word this lane's K blocks use
+  const uint32_t MAGIC = 0x64646464u;
+
+  int jt = 0;
+  for (int it = grp; it < ntiles; it += NGROUP, jt++) {
+    const int s = it % NSTAGE;
+    mbar_wait(&full[s], (it / NSTAGE) & 1, abort_flag, p.status);
+    const uint32_t st = sbase + s * G::STAGE_BYTES;
+    const int tile_p0 = c0 + it * TILE;
+    const bool edge = tile_p0 + TILE > lim_min;  // some row of the tile is masked for some query row
+
+    // ---- S^T = K Q^T for tile rows ra, rb
+    // (two accumulator sets, alternating, so that consecutive MMAs do not depend on each other)
+    float sacc[NT][4], sacc2[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+      sacc2[nt][0] = sacc2[nt][1] = sacc2[nt][2] = sacc2[nt][3] = 0.f;
+    }
+    if constexpr (Q8) {
+      const uint4 sca = lds128(st + G::OFF_KS + ra * 16), scb = lds128(st + G::OFF_KS + rb * 16);
+      const uint32_t scaw[4] = {sca.x, sca.y, sca.z, sca.w}, scbw[4] = {scb.x, scb.y, scb.z, scb.w};
+#pragma unroll
+      for (int hj = 0; hj < 4; hj++) {
+        const int h = hj >> 1, j = hj & 1;
+        const uint4 xa = lds128(st + G::OFF_KV + h * G::SEG_BYTES + swz128(ra, 4 * j + tg));
+        const uint4 xb = lds128(st + G::OFF_KV + h * G::SEG_BYTES + swz128(rb, 4 * j + tg));
+        const __half2 da = u32_as_h2(prmt(scaw[hj], scaw[hj], sel_sc));
+        const __half2 db = u32_as_h2(prmt(scbw[hj], scbw[hj], sel_sc));
+        const uint32_t xaw[4] = {xa.x, xa.y, xa.z, xa.w}, xbw[4] = {xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int s2 = 0; s2 < 4; s2++) {
+          const uint32_t wa = xaw[s2] ^ 0x80808080u, wb = xbw[s2] ^ 0x80808080u;
+          const uint32_t a0 = dq_pair(prmt(wa, MAGIC, 0x4140), da), a2 = dq_pair(prmt(wa, MAGIC, 0x4342), da);
+          const uint32_t a1 = dq_pair(prmt(wb, MAGIC, 0x4140), db), a3 = dq_pair(prmt(wb, MAGIC, 0x4342), db);
+          const int ks = 4 * hj + s2;
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++)
+            mma16816((hj & 1) ? sacc2[nt] : sacc[nt], a0, a1, a2, a3, qf[ks][nt][0], qf[ks][nt][1]);
         }
-        if (ks < QREG_KS) {
-          qf[ks][nt][0] = b0;
-          qf[ks][nt][1] = b1;
-        } else {
-          sts32(sQf + ((ks - QREG_KS) * 3 + nt) * 256, b0);
-          sts32(sQf + ((ks - QREG_KS) * 3 + nt) * 256 + 4, b1);
+      }
+    } else {
+#pragma unroll
+      for (int sj = 0; sj < 8; sj++) {  // segment sj >> 1 (64 dims), 16-byte chunk 4 (sj & 1) + tg of it
+        const uint4 xa = lds128(st + G::OFF_KV + (sj >> 1) * G::SEG_BYTES + swz128(ra, 4 * (sj & 1) + tg));
+        const uint4 xb = lds128(st + G::OFF_KV + (sj >> 1) * G::SEG_BYTES + swz128(rb, 4 * (sj & 1) + tg));
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          mma16816(sacc[nt], xa.x, xb.x, xa.y, xb.y, qf[2 * sj][nt][0], qf[2 * sj][nt][1]);
+          mma16816(sacc2[nt], xa.z, xb.z, xa.w, xb.w, qf[2 * sj + 1][nt][0], qf[2 * sj + 1][nt][1]);
         }
       }
     }
-    if (QREG_KS < 16) bar_sync(BAR_ALL, N_THREADS);
-
-    // Visible end (local row index, exclusive) of this lane's query rows 8nt + 2tg + e.
-    int lim[NT][2];
-    int lim_min = c1;
 #pragma unroll
     for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-      for (int e = 0; e < 2; e++) {
-        const int r = 8 * nt + 2 * tg + e;
-        lim[nt][e] = min(c1, pos0 + min(r / GQA, T - 1) + 1 - p.base_pos);
-      }
-    lim_min = min(c1, pos0 + 1 - p.base_pos);
-
-    float o[4][NT][4];
-#pragma unroll
-    for (int mt = 0; mt < 4; mt++)
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++) o[mt][nt][0] = o[mt][nt][1] = o[mt][nt][2] = o[mt][nt][3] = 0.f;
-    float m[NT][2], l[NT][2];
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-      m[nt][0] = m[nt][1] = M_INIT;
-      l[nt][0] = l[nt][1] = 0.f;
-    }
-
-    const uint32_t sP = sbase + OFF_P + grp * 2 * P_WORDS * 4;
-    const uint32_t sMax = sbase + OFF_MAX + grp * 2 * 4 * MAXR * 4;
-    const uint32_t sTok = sbase + OFF_TOK + grp * 8;
-    const uint32_t sel_sc = (tg & 2) ? 0x3232u : 0x1010u;  // which f16 of a scale word this lane's K blocks use
-    const uint32_t MAGIC = 0x64646464u;
-
-    int jt = 0;
-    for (int it = grp; it < ntiles; it += NGROUP, jt++) {
-      const int s = it % NSTAGE;
-      mbar_wait(&full[s], (it / NSTAGE) & 1, abort_flag, p.status);
-      const uint32_t st = sbase + s * STAGE_BYTES;
-      const int tile_p0 = c0 + it * TILE;
-      const bool edge = tile_p0 + TILE > lim_min;  // some row of the tile is masked for some query row
-
-      // ---- S^T = K Q^T for tile rows ra, rb
-      // (two accumulator sets, even / odd 64-dim groups, so that consecutive MMAs do not depend on each other)
-      float sacc[NT][4], sacc2[NT][4];
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++) {
-        sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
-        sacc2[nt][0] = sacc2[nt][1] = sacc2[nt][2] = sacc2[nt][3] = 0.f;
-      }
-      {
-        const uint4 sca = lds128(st + OFF_KS + ra * 16), scb = lds128(st + OFF_KS + rb * 16);
-        const uint32_t scaw[4] = {sca.x, sca.y, sca.z, sca.w}, scbw[4] = {scb.x, scb.y, scb.z, scb.w};
-#pragma unroll
-        for (int hj = 0; hj < 4; hj++) {
-          const int h = hj >> 1, j = hj & 1;
-          const uint4 xa = lds128(st + OFF_KV + h * (VAL_BYTES / 2) + swz128(ra, 4 * j + tg));
-          const uint4 xb = lds128(st + OFF_KV + h * (VAL_BYTES / 2) + swz128(rb, 4 * j + tg));
-          const __half2 da = u32_as_h2(prmt(scaw[hj], scaw[hj], sel_sc));
-          const __half2 db = u32_as_h2(prmt(scbw[hj], scbw[hj], sel_sc));
-          const uint32_t xaw[4] = {xa.x, xa.y, xa.z, xa.w}, xbw[4] = {xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-          for (int s2 = 0; s2 < 4; s2++) {
-            const uint32_t wa = xaw[s2] ^ 0x80808080u, wb = xbw[s2] ^ 0x80808080u;
-            const uint32_t a0 = dq_pair(prmt(wa, MAGIC, 0x4140), da), a2 = dq_pair(prmt(wa, MAGIC, 0x4342), da);
-            const uint32_t a1 = dq_pair(prmt(wb, MAGIC, 0x4140), db), a3 = dq_pair(prmt(wb, MAGIC, 0x4342), db);
-            const int ks = 4 * hj + s2;
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-              uint32_t q0, q1;
-              if (ks < QREG_KS) {
-                q0 = qf[ks][nt][0];
-                q1 = qf[ks][nt][1];
-              } else {
-                const uint2 qv = lds64(sQf + ((ks - QREG_KS) * 3 + nt) * 256);
-                q0 = qv.x;
-                q1 = qv.y;
-              }
-              mma16816((hj & 1) ? sacc2[nt] : sacc[nt], a0, a1, a2, a3, q0, q1);
-            }
-          }
-        }
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-          for (int c = 0; c < 4; c++) sacc[nt][c] += sacc2[nt][c];
-      }
-      if (edge) {
-        const int pa = tile_p0 + ra, pb = tile_p0 + rb;
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-          for (int e = 0; e < 2; e++) {
-            if (pa >= lim[nt][e]) sacc[nt][e] = -INFINITY;
-            if (pb >= lim[nt][e]) sacc[nt][2 + e] = -INFINITY;
-          }
-      }
-
-      // ---- P = exp(S - m) against the group's reference maxima m. m only moves when some score of
-      // the tile exceeds it by more than TAU (and on the group's first tile): then every warp posts
-      // its tile maxima, m, l and O are rescaled and P is recomputed. Otherwise - almost always - a
-      // tile costs one group barrier and no rescale; P stays <= e^TAU, well inside f16.
-      const int buf = jt & 1;
-      const uint32_t token = (uint32_t)(jt + 1);
-      bool exceed = jt == 0;
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-        for (int e = 0; e < 2; e++) exceed |= fmaxf(sacc[nt][e], sacc[nt][2 + e]) > m[nt][e] + TAU;
-      if (__any_sync(0xffffffffu, exceed) && lane == 0) sts32(sTok + buf * 4, token);
-      float lt[NT][2];
+      for (int c = 0; c < 4; c++) sacc[nt][c] += sacc2[nt][c];
+    if (edge) {
+      const int pa = tile_p0 + ra, pb = tile_p0 + rb;
 #pragma unroll
       for (int nt = 0; nt < NT; nt++)
 #pragma unroll
         for (int e = 0; e < 2; e++) {
-          const float mb = m[nt][e] * LOG2E;
-          const float pa = ex2(fmaf(sacc[nt][e], LOG2E, -mb)), pb = ex2(fmaf(sacc[nt][2 + e], LOG2E, -mb));
-          lt[nt][e] = pa + pb;
-          // position pair (slot g, slot g + 8) of warp wq = P^T k-slot pair 8wq + g
-          sts32(sP + (buf * P_WORDS + (8 * nt + 2 * tg + e) * P_STRIDE + 8 * wq + g) * 4, pack_h2(pa, pb));
+          if (pa >= lim[nt][e]) sacc[nt][e] = -INFINITY;
+          if (pb >= lim[nt][e]) sacc[nt][2 + e] = -INFINITY;
+        }
+    }
+
+    // ---- P = exp(S - m) against the group's reference maxima m. m only moves when some score of
+    // the tile exceeds it by more than TAU (and on the group's first tile): then every warp posts
+    // its tile maxima, m, l and O are rescaled and P is recomputed. Otherwise - almost always - a
+    // tile costs one group barrier and no rescale; P stays <= e^TAU, well inside f16.
+    const int buf = jt & 1;
+    const uint32_t token = (uint32_t)(jt + 1);
+    bool exceed = jt == 0;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int e = 0; e < 2; e++) exceed |= fmaxf(sacc[nt][e], sacc[nt][2 + e]) > m[nt][e] + TAU;
+    if (__any_sync(0xffffffffu, exceed) && lane == 0) sts32(sTok + buf * 4, token);
+    float lt[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const float mb = m[nt][e] * LOG2E;
+        const float pa = ex2(fmaf(sacc[nt][e], LOG2E, -mb)), pb = ex2(fmaf(sacc[nt][2 + e], LOG2E, -mb));
+        lt[nt][e] = pa + pb;
+        // position pair (slot g, slot g + 8) of warp wq = P^T k-slot pair 8wq + g
+        sts32(sP + (buf * P_WORDS + (8 * nt + 2 * tg + e) * P_STRIDE + 8 * wq + g) * 4, pack_h2(pa, pb));
+      }
+    bar_sync(1 + grp, 128);
+    // All four warps are past the previous tile of this group: its stage can be refilled.
+    if (loader && jt >= 1 && it - NGROUP + NSTAGE < ntiles) issue_tile(it - NGROUP + NSTAGE);
+    if (lds32(sTok + buf * 4) == token) {
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          float v = fmaxf(sacc[nt][e], sacc[nt][2 + e]);
+          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+          if (g == 0) stsf(sMax + ((buf * 4 + wq) * MAXR + 8 * nt + 2 * tg + e) * 4, v);
         }
       bar_sync(1 + grp, 128);
-      // All four warps are past the previous tile of this group: its stage can be refilled.
-      if (loader && jt >= 1 && it - NGROUP + NSTAGE < ntiles) issue_tile(it - NGROUP + NSTAGE);
-      if (lds32(sTok + buf * 4) == token) {
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++)
+      for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-          for (int e = 0; e < 2; e++) {
-            float v = fmaxf(sacc[nt][e], sacc[nt][2 + e]);
-            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
-            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
-            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
-            if (g == 0) stsf(sMax + ((buf * 4 + wq) * MAXR + 8 * nt + 2 * tg + e) * 4, v);
+        for (int e = 0; e < 2; e++) {
+          const int r = 8 * nt + 2 * tg + e;
+          float tm = ldsf(sMax + ((buf * 4 + 0) * MAXR + r) * 4);
+#pragma unroll
+          for (int w = 1; w < 4; w++) tm = fmaxf(tm, ldsf(sMax + ((buf * 4 + w) * MAXR + r) * 4));
+          const float mn = fmaxf(m[nt][e], tm);
+          const float f = ex2((m[nt][e] - mn) * LOG2E);
+          m[nt][e] = mn;
+          l[nt][e] *= f;
+#pragma unroll
+          for (int mt = 0; mt < 4; mt++) {
+            o[mt][nt][e] *= f;
+            o[mt][nt][2 + e] *= f;
           }
-        bar_sync(1 + grp, 128);
+          const float mb = mn * LOG2E;
+          const float pa = ex2(fmaf(sacc[nt][e], LOG2E, -mb)), pb = ex2(fmaf(sacc[nt][2 + e], LOG2E, -mb));
+          lt[nt][e] = pa + pb;
+          sts32(sP + (buf * P_WORDS + r * P_STRIDE + 8 * wq + g) * 4, pack_h2(pa, pb));
+        }
+      bar_sync(1 + grp, 128);
+    }
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-          for (int e = 0; e < 2; e++) {
-            const int r = 8 * nt + 2 * tg + e;
-            float tm = ldsf(sMax + ((buf * 4 + 0) * MAXR + r) * 4);
-#pragma unroll
-            for (int w = 1; w < 4; w++) tm = fmaxf(tm, ldsf(sMax + ((buf * 4 + w) * MAXR + r) * 4));
-            const float mn = fmaxf(m[nt][e], tm);
-            const float f = ex2((m[nt][e] - mn) * LOG2E);
-            m[nt][e] = mn;
-            l[nt][e] *= f;
-#pragma unroll
-            for (int mt = 0; mt < 4; mt++) {
-              o[mt][nt][e] *= f;
-              o[mt][nt][2 + e] *= f;
-            }
-            const float mb = mn * LOG2E;
-            const float pa = ex2(fmaf(sacc[nt][e], LOG2E, -mb)), pb = ex2(fmaf(sacc[nt][2 + e], LOG2E, -mb));
-            lt[nt][e] = pa + pb;
-            sts32(sP + (buf * P_WORDS + r * P_STRIDE + 8 * wq + g) * 4, pack_h2(pa, pb));
-          }
-        bar_sync(1 + grp, 128);
-      }
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++) {
-        l[nt][0] += lt[nt][0];
-        l[nt][1] += lt[nt][1];
-      }
+    for (int nt = 0; nt < NT; nt++) {
+      l[nt][0] += lt[nt][0];
+      l[nt][1] += lt[nt][1];
+    }
 
-      // ---- O^T += V^T P^T for head dims 64wq + 8g .. +7 (8 bytes of each V row per lane)
-      {
-        const uint32_t vbase = st + OFF_VV + (wq >> 1) * (VAL_BYTES / 2) + (g & 1) * 8;
-        const uint32_t cb = (wq & 1) * 4 + (g >> 1);
-        const uint32_t vsc = st + OFF_VS + (2 * wq + (g >> 2)) * 2;
-        const uint32_t pP = sP + (buf * P_WORDS + g * P_STRIDE + tg) * 4;
+    // ---- O^T += V^T P^T for head dims 64wq + 8g .. +7 (8 values of each V row per lane)
+    {
+      const uint32_t pP = sP + (buf * P_WORDS + g * P_STRIDE + tg) * 4;
 #pragma unroll
-        for (int ks = 0; ks < 4; ks++) {
-          const int pa = 16 * ks + slot_row(tg), pb = pa + 8, pc = pa + 1, pd = pa + 9;
+      for (int ks = 0; ks < 4; ks++) {
+        const int pa = 16 * ks + slot_row(tg), pb = pa + 8, pc = pa + 1, pd = pa + 9;
+        uint32_t b0[NT], b1[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          b0[nt] = lds32(pP + (8 * nt * P_STRIDE + 8 * ks) * 4);
+          b1[nt] = lds32(pP + (8 * nt * P_STRIDE + 8 * ks + 4) * 4);
+        }
+        if constexpr (Q8) {
+          const uint32_t vbase = st + G::OFF_VV + (wq >> 1) * G::SEG_BYTES + (g & 1) * 8;
+          const uint32_t cb = (wq & 1) * 4 + (g >> 1);
+          const uint32_t vsc = st + G::OFF_VS + (2 * wq + (g >> 2)) * 2;
           const uint2 xa = lds64(vbase + swz128(pa, cb)), xb = lds64(vbase + swz128(pb, cb));
           const uint2 xc = lds64(vbase + swz128(pc, cb)), xd = lds64(vbase + swz128(pd, cb));
           uint32_t sa = ldsu16(vsc + pa * 16), sb = ldsu16(vsc + pb * 16);
@@ -413,12 +444,6 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
             if (tile_p0 + pd >= c1) sd = 0;
           }
           const __half2 sab = u32_as_h2(sa | (sb << 16)), scd = u32_as_h2(scc | (sd << 16));
-          uint32_t b0[NT], b1[NT];
-#pragma unroll
-          for (int nt = 0; nt < NT; nt++) {
-            b0[nt] = lds32(pP + (8 * nt * P_STRIDE + 8 * ks) * 4);
-            b1[nt] = lds32(pP + (8 * nt * P_STRIDE + 8 * ks + 4) * 4);
-          }
           const uint32_t xaw[2] = {xa.x, xa.y}, xbw[2] = {xb.x, xb.y}, xcw[2] = {xc.x, xc.y}, xdw[2] = {xd.x, xd.y};
 #pragma unroll
           for (int wi = 0; wi < 2; wi++) {
@@ -439,96 +464,117 @@ decode_q8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
               for (int nt = 0; nt < NT; nt++) mma16816(o[2 * wi + 1][nt], a0, a1, a2, a3, b0[nt], b1[nt]);
             }
           }
+        } else {
+          // f16: segment wq holds dims 64wq .. 64wq+63; chunk g of a row = dims 64wq + 8g .. +7
+          const uint32_t vbase = st + G::OFF_VV + wq * G::SEG_BYTES;
+          uint4 xa = lds128(vbase + swz128(pa, g)), xb = lds128(vbase + swz128(pb, g));
+          uint4 xc = lds128(vbase + swz128(pc, g)), xd = lds128(vbase + swz128(pd, g));
+          if (edge) {  // rows past the end of the sequence may hold anything: make them exact zeros
+            if (tile_p0 + pa >= c1) xa = make_uint4(0, 0, 0, 0);
+            if (tile_p0 + pb >= c1) xb = make_uint4(0, 0, 0, 0);
+            if (tile_p0 + pc >= c1) xc = make_uint4(0, 0, 0, 0);
+            if (tile_p0 + pd >= c1) xd = make_uint4(0, 0, 0, 0);
+          }
+          const uint32_t xaw[4] = {xa.x, xa.y, xa.z, xa.w}, xbw[4] = {xb.x, xb.y, xb.z, xb.w};
+          const uint32_t xcw[4] = {xc.x, xc.y, xc.z, xc.w}, xdw[4] = {xd.x, xd.y, xd.z, xd.w};
+#pragma unroll
+          for (int mt = 0; mt < 4; mt++) {
+            // word mt of a row = dims 2mt (d-slot g) and 2mt+1 (d-slot g+8); pair them across positions
+            const uint32_t a0 = prmt(xaw[mt], xbw[mt], 0x5410), a1 = prmt(xaw[mt], xbw[mt], 0x7632);
+            const uint32_t a2 = prmt(xcw[mt], xdw[mt], 0x5410), a3 = prmt(xcw[mt], xdw[mt], 0x7632);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) mma16816(o[mt][nt], a0, a1, a2, a3, b0[nt], b1[nt]);
+          }
         }
       }
     }
+  }
 
-    // ---- row sums over this warp's positions
+  // ---- row sums over this warp's positions
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+      float v = l[nt][e];
+      v += __shfl_xor_sync(0xffffffffu, v, 4);
+      v += __shfl_xor_sync(0xffffffffu, v, 8);
+      v += __shfl_xor_sync(0xffffffffu, v, 16);
+      l[nt][e] = v;
+      if (g == 0) stsf(sbase + OFF_L + ((grp * 4 + wq) * MAXR + 8 * nt + 2 * tg + e) * 4, v);
+    }
+  if (wq == 0 && g == 0) {
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int e = 0; e < 2; e++) stsf(sbase + OFF_M1 + (grp * MAXR + 8 * nt + 2 * tg + e) * 4, m[nt][e]);
+  }
+  bar_sync(BAR_ALL, N_THREADS);  // every tile consumed: the ring is free for the O exchange
+
+  // ---- merge the groups (log-sum-exp) and write the chunk partial
+  const uint32_t sO = sbase;
+  if (grp > 0) {
 #pragma unroll
     for (int nt = 0; nt < NT; nt++)
 #pragma unroll
       for (int e = 0; e < 2; e++) {
-        float v = l[nt][e];
-        v += __shfl_xor_sync(0xffffffffu, v, 4);
-        v += __shfl_xor_sync(0xffffffffu, v, 8);
-        v += __shfl_xor_sync(0xffffffffu, v, 16);
-        l[nt][e] = v;
-        if (g == 0) stsf(sbase + OFF_L + ((grp * 4 + wq) * MAXR + 8 * nt + 2 * tg + e) * 4, v);
-      }
-    if (wq == 0 && g == 0) {
+        const int r = 8 * nt + 2 * tg + e;
 #pragma unroll
-      for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-        for (int e = 0; e < 2; e++) stsf(sbase + OFF_M1 + (grp * MAXR + 8 * nt + 2 * tg + e) * 4, m[nt][e]);
-    }
-    bar_sync(BAR_ALL, N_THREADS);  // every tile consumed: the ring is free for the O exchange
-
-    // ---- merge the groups (log-sum-exp) and write the chunk partial
-    const uint32_t sO = sbase;
-    if (grp > 0) {
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-        for (int e = 0; e < 2; e++) {
-          const int r = 8 * nt + 2 * tg + e;
-#pragma unroll
-          for (int mt = 0; mt < 4; mt++) {
-            const int d = 64 * wq + 8 * g + 2 * mt;
-            stsf(sO + (((grp - 1) * MAXR + r) * O_STRIDE + d) * 4, o[mt][nt][e]);
-            stsf(sO + (((grp - 1) * MAXR + r) * O_STRIDE + d + 1) * 4, o[mt][nt][2 + e]);
-          }
+        for (int mt = 0; mt < 4; mt++) {
+          const int d = 64 * wq + 8 * g + 2 * mt;
+          stsf(sO + (((grp - 1) * MAXR + r) * O_STRIDE + d) * 4, o[mt][nt][e]);
+          stsf(sO + (((grp - 1) * MAXR + r) * O_STRIDE + d + 1) * 4, o[mt][nt][2 + e]);
         }
-    }
-    bar_sync(BAR_ALL, N_THREADS);
-    if (grp == 0) {
+      }
+  }
+  bar_sync(BAR_ALL, N_THREADS);
+  if (grp == 0) {
 #pragma unroll
-      for (int nt = 0; nt < NT; nt++)
+    for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-          const int r = 8 * nt + 2 * tg + e;
-          if (r >= R) continue;
-          float mg[NGROUP], f[NGROUP];
-          float M = m[nt][e];
+      for (int e = 0; e < 2; e++) {
+        const int r = 8 * nt + 2 * tg + e;
+        if (r >= R) continue;
+        float mg[NGROUP], f[NGROUP];
+        float M = m[nt][e];
+#pragma unroll
+        for (int k = 1; k < NGROUP; k++) {
+          mg[k] = ldsf(sbase + OFF_M1 + (k * MAXR + r) * 4);
+          M = fmaxf(M, mg[k]);
+        }
+        f[0] = ex2((m[nt][e] - M) * LOG2E);
+#pragma unroll
+        for (int k = 1; k < NGROUP; k++) f[k] = ex2((mg[k] - M) * LOG2E);
+        float* po = out + (size_t)r * PROW;
+#pragma unroll
+        for (int mt = 0; mt < 4; mt++) {
+          const int d = 64 * wq + 8 * g + 2 * mt;
+          float v0 = o[mt][nt][e] * f[0], v1 = o[mt][nt][2 + e] * f[0];
 #pragma unroll
           for (int k = 1; k < NGROUP; k++) {
-            mg[k] = ldsf(sbase + OFF_M1 + (k * MAXR + r) * 4);
-            M = fmaxf(M, mg[k]);
+            v0 += ldsf(sO + (((k - 1) * MAXR + r) * O_STRIDE + d) * 4) * f[k];
+            v1 += ldsf(sO + (((k - 1) * MAXR + r) * O_STRIDE + d + 1) * 4) * f[k];
           }
-          f[0] = ex2((m[nt][e] - M) * LOG2E);
-#pragma unroll
-          for (int k = 1; k < NGROUP; k++) f[k] = ex2((mg[k] - M) * LOG2E);
-          float* po = out + (size_t)r * PROW;
-#pragma unroll
-          for (int mt = 0; mt < 4; mt++) {
-            const int d = 64 * wq + 8 * g + 2 * mt;
-            float v0 = o[mt][nt][e] * f[0], v1 = o[mt][nt][2 + e] * f[0];
-#pragma unroll
-            for (int k = 1; k < NGROUP; k++) {
-              v0 += ldsf(sO + (((k - 1) * MAXR + r) * O_STRIDE + d) * 4) * f[k];
-              v1 += ldsf(sO + (((k - 1) * MAXR + r) * O_STRIDE + d + 1) * 4) * f[k];
-            }
-            *(float2*)(po + 2 + d) = make_float2(v0, v1);
-          }
-          if (wq == 0 && g == 0) {
-            float lsum = 0.f;
-#pragma unroll
-            for (int k = 0; k < NGROUP; k++) {
-              float lk = 0.f;
-#pragma unroll
-              for (int w = 0; w < 4; w++) lk += ldsf(sbase + OFF_L + ((k * 4 + w) * MAXR + r) * 4);
-              lsum += lk * f[k];
-            }
-            po[0] = M;
-            po[1] = lsum;
-          }
+          *(float2*)(po + 2 + d) = make_float2(v0, v1);
         }
-    }
+        if (wq == 0 && g == 0) {
+          float lsum = 0.f;
+#pragma unroll
+          for (int k = 0; k < NGROUP; k++) {
+            float lk = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; w++) lk += ldsf(sbase + OFF_L + ((k * 4 + w) * MAXR + r) * 4);
+            lsum += lk * f[k];
+          }
+          po[0] = M;
+          po[1] = lsum;
+        }
+      }
   }
 }
 
 struct TmapKey {
   const void* base;
-  int nkvh, n_ctx;
+  int nkvh, n_ctx, q8;
   CUtensorMap vals, scales;
 };
 // Small cache of tensor maps per (cache pointer, shape): the reference's caches never move
@@ -537,9 +583,9 @@ constexpr int TMAP_CACHE = 64;
 TmapKey g_tmaps[TMAP_CACHE];
 int g_tmap_next = 0;
 
-int get_tmaps(const void* cache, int nkvh, int n_ctx, const CUtensorMap** vals, const CUtensorMap** scales) {
+int get_tmaps(const void* cache, int nkvh, int n_ctx, bool q8, const CUtensorMap** vals, const CUtensorMap** scales) {
   for (int i = 0; i < TMAP_CACHE; i++)
-    if (g_tmaps[i].base == cache && g_tmaps[i].nkvh == nkvh && g_tmaps[i].n_ctx == n_ctx) {
+    if (g_tmaps[i].base == cache && g_tmaps[i].nkvh == nkvh && g_tmaps[i].n_ctx == n_ctx && g_tmaps[i].q8 == (int)q8) {
       *vals = &g_tmaps[i].vals;
       *scales = &g_tmaps[i].scales;
       return Q27B_OK;
@@ -548,55 +594,62 @@ int get_tmaps(const void* cache, int nkvh, int n_ctx, const CUtensorMap** vals, 
   g_tmap_next = (g_tmap_next + 1) % TMAP_CACHE;
   k.base = nullptr;
   const uint64_t rows = (uint64_t)nkvh * n_ctx;
-  if (int rc = make_tmap_2d(&k.vals, cache, rows, AD, AD, 128, TILE, true)) return rc;
-  if (int rc = make_tmap_2d(&k.scales, (const uint8_t*)cache + rows * AD, rows, 16, 16, 16, TILE, false)) return rc;
+  const uint32_t rowb = q8 ? AD : 2 * AD;
+  if (int rc = make_tmap_2d(&k.vals, cache, rows, rowb, rowb, 128, TILE, true)) return rc;
+  if (q8) {
+    if (int rc = make_tmap_2d(&k.scales, (const uint8_t*)cache + rows * AD, rows, 16, 16, 16, TILE, false)) return rc;
+  } else {
+    k.scales = k.vals;  // unused by the f16 kernel
+  }
   k.base = cache;
   k.nkvh = nkvh;
   k.n_ctx = n_ctx;
+  k.q8 = q8;
   *vals = &k.vals;
   *scales = &k.scales;
   return Q27B_OK;
 }
 
-template <int NT, bool PAGED>
+template <int NT, bool PAGED, bool Q8>
 int launch_decode(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
                   const DecodeParams& p, int nseq, cudaStream_t s) {
   static bool attr[64] = {};
   int dev;
   Q27B_CK(cudaGetDevice(&dev));
   if (!attr[dev]) {
-    Q27B_CK(cudaFuncSetAttribute(decode_q8_kernel<NT, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    Q27B_CK(cudaFuncSetAttribute(decode_kernel<NT, PAGED, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     attr[dev] = true;
   }
-  Q27B_CK(launch_pdl(decode_q8_kernel<NT, PAGED>, dim3(p.nch, p.nkvh, nseq), dim3(N_THREADS), SMEM_BYTES, s, *kv, *ks, *vv,
+  Q27B_CK(launch_pdl(decode_kernel<NT, PAGED, Q8>, dim3(p.nch, p.nkvh, nseq), dim3(N_THREADS), SMEM_BYTES, s, *kv, *ks, *vv,
                      *vs, p));
   return Q27B_OK;
 }
-template <bool PAGED>
+template <bool PAGED, bool Q8>
 int launch_decode_t(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
                     const DecodeParams& p, int nseq, cudaStream_t s) {
   const int nt = (GQA * p.T + 7) / 8;
-  if (nt == 1) return launch_decode<1, PAGED>(kv, ks, vv, vs, p, nseq, s);
-  if (nt == 2) return launch_decode<2, PAGED>(kv, ks, vv, vs, p, nseq, s);
-  return launch_decode<3, PAGED>(kv, ks, vv, vs, p, nseq, s);
+  if (nt == 1) return launch_decode<1, PAGED, Q8>(kv, ks, vv, vs, p, nseq, s);
+  if (nt == 2) return launch_decode<2, PAGED, Q8>(kv, ks, vv, vs, p, nseq, s);
+  return launch_decode<3, PAGED, Q8>(kv, ks, vv, vs, p, nseq, s);
 }
 
 // Split-K pass of one sequence into ctx->part [nkvh][nch][24][258].
 int decode_split(DeviceCtx* ctx, const float* qn, const void* kcache, const void* vcache, const int* pos0, int T,
                  float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos, int n_local, int* nch_out,
                  cudaStream_t s) {
-  if (!q8) return fail(Q27B_UNSUPPORTED, "attn_decode: f16 KV cache is not built yet");
   const int nch = std::max(1, ctx->n_sm / nkvh);
   if (int rc = ensure_part(ctx, (size_t)nkvh * nch * MAXR * PROW)) return rc;
   const CUtensorMap *kv, *ks, *vv, *vs;
-  if (int rc = get_tmaps(kcache, nkvh, n_ctx, &kv, &ks)) return rc;
-  if (int rc = get_tmaps(vcache, nkvh, n_ctx, &vv, &vs)) return rc;
+  if (int rc = get_tmaps(kcache, nkvh, n_ctx, q8 != 0, &kv, &ks)) return rc;
+  if (int rc = get_tmaps(vcache, nkvh, n_ctx, q8 != 0, &vv, &vs)) return rc;
   DecodeParams p = {};
   p.qn = qn; p.part = ctx->part; p.pos0 = pos0; p.status = ctx->status;
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nch = nch; p.kq_scale = kq_scale;
   p.base_pos = base_pos; p.n_local = n_local;
   *nch_out = nch;
-  if (int rc = launch_decode_t<false>(kv, ks, vv, vs, p, 1, s)) return rc;
+  if (int rc = q8 ? launch_decode_t<false, true>(kv, ks, vv, vs, p, 1, s)
+                  : launch_decode_t<false, false>(kv, ks, vv, vs, p, 1, s))
+    return rc;
   if (ctx->split_event) Q27B_CK(cudaEventRecord(ctx->split_event, s));
   return Q27B_OK;
 }
@@ -623,9 +676,9 @@ int noalloc_setup(int dev) {
   Q27B_CK(cudaGetSymbolAddress((void**)&part, g_noalloc_part));
   Q27B_CK(cudaGetSymbolAddress((void**)&status, g_noalloc_status));
   // the kernels' shared-memory opt-in, done here so that later calls only launch
-  Q27B_CK(cudaFuncSetAttribute(decode_q8_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-  Q27B_CK(cudaFuncSetAttribute(decode_q8_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-  Q27B_CK(cudaFuncSetAttribute(decode_q8_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  Q27B_CK(cudaFuncSetAttribute(decode_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  Q27B_CK(cudaFuncSetAttribute(decode_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  Q27B_CK(cudaFuncSetAttribute(decode_kernel<3, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
   g_noalloc_status_ptr[dev] = status;
   g_noalloc_part_ptr[dev] = part;
   return Q27B_OK;
@@ -694,13 +747,13 @@ int q27b_attn_decode_noalloc(const float* qn, const float* qg, const void* kcach
                                     " (use q27b_attn_decode, which allocates)");
   if (int rc = noalloc_setup(dev)) return rc;
   const CUtensorMap *kv, *ks, *vv, *vs;
-  if (int rc = get_tmaps(kcache, nkvh, n_ctx, &kv, &ks)) return rc;
-  if (int rc = get_tmaps(vcache, nkvh, n_ctx, &vv, &vs)) return rc;
+  if (int rc = get_tmaps(kcache, nkvh, n_ctx, true, &kv, &ks)) return rc;
+  if (int rc = get_tmaps(vcache, nkvh, n_ctx, true, &vv, &vs)) return rc;
   DecodeParams p = {};
   p.qn = qn; p.part = g_noalloc_part_ptr[dev]; p.pos0 = pos0; p.status = g_noalloc_status_ptr[dev];
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nch = nch; p.kq_scale = kq_scale;
   p.base_pos = 0; p.n_local = -1;
-  if (int rc = launch_decode_t<false>(kv, ks, vv, vs, p, 1, (cudaStream_t)stream)) return rc;
+  if (int rc = launch_decode_t<false, true>(kv, ks, vv, vs, p, 1, (cudaStream_t)stream)) return rc;
   MergeParams mp = {};
   mp.part = g_noalloc_part_ptr[dev]; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.qg = qg; mp.o = o; mp.xq = xq;
   mp.xd = xd; mp.T = T; mp.nqh = nqh;
@@ -734,14 +787,14 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
   // One pool = n_pages * nkvh pages of 256 rows: the same row tensor as a cache of that many rows.
   const int pool_rows_per_head = n_pages * Q27B_PAGE;
   const CUtensorMap *kv, *ks, *vv, *vs;
-  if (int rc = get_tmaps(kpool, nkvh, pool_rows_per_head, &kv, &ks)) return rc;
-  if (int rc = get_tmaps(vpool, nkvh, pool_rows_per_head, &vv, &vs)) return rc;
+  if (int rc = get_tmaps(kpool, nkvh, pool_rows_per_head, true, &kv, &ks)) return rc;
+  if (int rc = get_tmaps(vpool, nkvh, pool_rows_per_head, true, &vv, &vs)) return rc;
   DecodeParams p = {};
   p.qn = qn; p.part = ctx->part; p.status = ctx->status;
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = max_pages * Q27B_PAGE; p.nch = nch; p.kq_scale = kq_scale;
   p.base_pos = 0; p.n_local = -1;
   p.page_table = page_table; p.seq_len = seq_len; p.max_pages = max_pages; p.n_pages = n_pages; p.chunk_len = chunk;
-  if (int rc = launch_decode_t<true>(kv, ks, vv, vs, p, B, (cudaStream_t)stream)) return rc;
+  if (int rc = launch_decode_t<true, true>(kv, ks, vv, vs, p, B, (cudaStream_t)stream)) return rc;
   MergeParams mp = {};
   mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)B * T * nqh; mp.qg = qg; mp.o = o; mp.T = T; mp.nqh = nqh;
   mp.seq_len = seq_len; mp.chunk_len = chunk;

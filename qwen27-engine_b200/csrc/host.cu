@@ -20,7 +20,7 @@ EncodeFn g_encode = nullptr;
 bool pdl_enabled() {
   static const bool on = [] {
     const char* e = getenv("Q27_PDL");
-    return !(e && e[0] == '0');
+    return e && e[0] == '1';
   }();
   return on;
 }

@@ -153,10 +153,10 @@ def test_lse_merge_generic(q27, orc):
     assert np.abs(o.cpu().numpy() - ref2).max() <= 1e-5 * max(1.0, np.abs(ref2).max())
 
 
-def test_f16_cache_is_reported_unsupported_or_correct(q27, orc):
-    """The f16 KV variant: either built (then it must match the oracle) or refused loudly."""
+@pytest.mark.parametrize("T,nkvh,n", [(4, 2, 777), (1, 1, 5), (4, 4, 64), (3, 2, 129), (2, 1, 4100), (4, 4, 32768)])
+def test_f16_kv_cache(q27, orc, T, nkvh, n):
+    """The f16 KV cache variant of the decode kernel (config: the 32,768 spec-verify case also with f16 KV)."""
     from qwen27_engine_b200 import synth
-    T, nkvh, n = 4, 2, 777
     nqh = nkvh * GQA
     qn, qg, kf, vf = synth.decode_inputs(T, nqh, nkvh, n)
     kc_ref, vc_ref = orc.fill_cache(kf, vf, n + 5, q8=False)
