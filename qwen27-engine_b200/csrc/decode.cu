@@ -283,6 +283,17 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__
   const uint32_t sTok = sbase + OFF_TOK + grp * 8;
   const uint32_t sel_sc = (tg & 2) ? 0x3232u : 0x1010u;  // which f16 of a scale word this lane's K blocks use
   const uint32_t MAGIC = 0x64646464u;
+  // Byte offsets inside a stage that do not depend on the tile (q8_0 layout). K: chunk tg of rows
+  // ra / rb in a segment; chunk 4 + tg is the same address with bit 6 flipped. V: 8 bytes of rows
+  // slot_row(tg) (+8) and slot_row(tg) + 1 (+8) in this warp's 64-dim quarter; 16 positions further
+  // is 2048 bytes further. Scales: this lane's block of those rows.
+  const uint32_t kA = G::OFF_KV + ra * 128 + ((tg ^ (ra & 7)) << 4);
+  const uint32_t kB = G::OFF_KV + rb * 128 + ((tg ^ (rb & 7)) << 4);
+  const uint32_t vrow = slot_row(tg), vcb = (wq & 1) * 4 + (g >> 1);
+  const uint32_t vQ = G::OFF_VV + (wq >> 1) * G::SEG_BYTES + (g & 1) * 8;
+  const uint32_t vA = vQ + vrow * 128 + ((vcb ^ (vrow & 7)) << 4);
+  const uint32_t vC = vQ + (vrow + 1) * 128 + ((vcb ^ ((vrow + 1) & 7)) << 4);
+  const uint32_t sA = G::OFF_VS + (2 * wq + (g >> 2)) * 2 + vrow * 16;
 
   int jt = 0;
   for (int it = grp; it < ntiles; it += NGROUP, jt++) {
@@ -306,8 +317,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__
 #pragma unroll
       for (int hj = 0; hj < 4; hj++) {
         const int h = hj >> 1, j = hj & 1;
-        const uint4 xa = lds128(st + G::OFF_KV + h * G::SEG_BYTES + swz128(ra, 4 * j + tg));
-        const uint4 xb = lds128(st + G::OFF_KV + h * G::SEG_BYTES + swz128(rb, 4 * j + tg));
+        const uint4 xa = lds128(st + (kA ^ (j << 6)) + h * G::SEG_BYTES);  // = swz128(ra, 4j + tg)
+        const uint4 xb = lds128(st + (kB ^ (j << 6)) + h * G::SEG_BYTES);
         const __half2 da = u32_as_h2(prmt(scaw[hj], scaw[hj], sel_sc));
         const __half2 db = u32_as_h2(prmt(scbw[hj], scbw[hj], sel_sc));
         const uint32_t xaw[4] = {xa.x, xa.y, xa.z, xa.w}, xbw[4] = {xb.x, xb.y, xb.z, xb.w};
@@ -430,20 +441,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__
           b1[nt] = lds32(pP + (8 * nt * P_STRIDE + 8 * ks + 4) * 4);
         }
         if constexpr (Q8) {
-          const uint32_t vbase = st + G::OFF_VV + (wq >> 1) * G::SEG_BYTES + (g & 1) * 8;
-          const uint32_t cb = (wq & 1) * 4 + (g >> 1);
-          const uint32_t vsc = st + G::OFF_VS + (2 * wq + (g >> 2)) * 2;
-          const uint2 xa = lds64(vbase + swz128(pa, cb)), xb = lds64(vbase + swz128(pb, cb));
-          const uint2 xc = lds64(vbase + swz128(pc, cb)), xd = lds64(vbase + swz128(pd, cb));
-          uint32_t sa = ldsu16(vsc + pa * 16), sb = ldsu16(vsc + pb * 16);
-          uint32_t scc = ldsu16(vsc + pc * 16), sd = ldsu16(vsc + pd * 16);
+          // rows pa, pb = pa + 8 share one swizzle term, pc = pa + 1, pd = pa + 9 the other
+          const uint2 xa = lds64(st + vA + ks * 2048), xb = lds64(st + vA + ks * 2048 + 1024);
+          const uint2 xc = lds64(st + vC + ks * 2048), xd = lds64(st + vC + ks * 2048 + 1024);
+          uint32_t sa = ldsu16(st + sA + ks * 256), sb = ldsu16(st + sA + ks * 256 + 128);
+          uint32_t scc = ldsu16(st + sA + ks * 256 + 16), sd = ldsu16(st + sA + ks * 256 + 144);
           if (edge) {  // rows past the end of the sequence may hold anything: make them exact zeros
             if (tile_p0 + pa >= c1) sa = 0;
             if (tile_p0 + pb >= c1) sb = 0;
             if (tile_p0 + pc >= c1) scc = 0;
             if (tile_p0 + pd >= c1) sd = 0;
           }
-          const __half2 sab = u32_as_h2(sa | (sb << 16)), scd = u32_as_h2(scc | (sd << 16));
+          const __half2 sab = u32_as_h2(prmt(sa, sb, 0x5410)), scd = u32_as_h2(prmt(scc, sd, 0x5410));
           const uint32_t xaw[2] = {xa.x, xa.y}, xbw[2] = {xb.x, xb.y}, xcw[2] = {xc.x, xc.y}, xdw[2] = {xd.x, xd.y};
 #pragma unroll
           for (int wi = 0; wi < 2; wi++) {
