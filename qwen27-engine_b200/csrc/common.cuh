@@ -181,6 +181,17 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint
       : "memory");
 }
 
+// Same with the A operand in tensor memory (lane = row, two f16 per 32-bit column along K).
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor of tcgen05.mma (64 bit): start address >> 4 in bits 0-13,
 // leading byte offset >> 4 in 16-29, stride byte offset >> 4 in 32-45, descriptor version 1 in
 // 46-47, swizzle mode in 61-63 (2 = 128-byte swizzle).

@@ -28,8 +28,10 @@
 //    the group's first tile): a tile normally costs one group barrier and no rescale of O.
 #include "combine.h"
 #include "common.cuh"
+#include "decode_params.h"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace q27b {
 namespace {
@@ -79,21 +81,6 @@ static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 
 constexpr int N_THREADS = NGROUP * 128;
 constexpr int BAR_ALL = 1 + NGROUP;                         // named barrier of all threads (1 .. NGROUP: the groups)
-
-struct DecodeParams {
-  const float* qn;   // [T][nqh][256]
-  float* part;       // [nkvh][nch][24][258]
-  const int* pos0;
-  int* status;
-  int T, nqh, nkvh, n_ctx, nch;
-  float kq_scale;
-  int base_pos;      // global position of local cache row 0
-  int n_local;       // local rows to attend; < 0: all rows up to *pos0 + T
-  // paged / batched variant: grid (chunks, nkvh, B), fixed chunk length, rows through the page table
-  const int* page_table;  // [B][max_pages]
-  const int* seq_len;     // [B], counts the T new tokens
-  int max_pages, n_pages, chunk_len;
-};
 
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
   uint32_t v;
@@ -642,6 +629,16 @@ int launch_decode_t(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensor
   return launch_decode<3, PAGED, Q8>(kv, ks, vv, vs, p, nseq, s);
 }
 
+// q8_0 caches go to the warp-MMA kernel of this file unless Q27B_DECODE_KERNEL=tc asks for the
+// tcgen05 kernel (decode_tc.cu); f16 caches always use the warp-MMA kernel.
+bool use_tc_kernel() {
+  static const bool tc = [] {
+    const char* e = getenv("Q27B_DECODE_KERNEL");
+    return e && e[0] == 't';
+  }();
+  return tc;
+}
+
 // Split-K pass of one sequence into ctx->part [nkvh][nch][24][258].
 int decode_split(DeviceCtx* ctx, const float* qn, const void* kcache, const void* vcache, const int* pos0, int T,
                  float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos, int n_local, int* nch_out,
@@ -656,8 +653,9 @@ int decode_split(DeviceCtx* ctx, const float* qn, const void* kcache, const void
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nch = nch; p.kq_scale = kq_scale;
   p.base_pos = base_pos; p.n_local = n_local;
   *nch_out = nch;
-  if (int rc = q8 ? launch_decode_t<false, true>(kv, ks, vv, vs, p, 1, s)
-                  : launch_decode_t<false, false>(kv, ks, vv, vs, p, 1, s))
+  if (int rc = !q8             ? launch_decode_t<false, false>(kv, ks, vv, vs, p, 1, s)
+               : use_tc_kernel() ? launch_decode_tc(kv, ks, vv, vs, p, false, 1, s)
+                                 : launch_decode_t<false, true>(kv, ks, vv, vs, p, 1, s))
     return rc;
   if (ctx->split_event) Q27B_CK(cudaEventRecord(ctx->split_event, s));
   return Q27B_OK;
@@ -803,7 +801,9 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = max_pages * Q27B_PAGE; p.nch = nch; p.kq_scale = kq_scale;
   p.base_pos = 0; p.n_local = -1;
   p.page_table = page_table; p.seq_len = seq_len; p.max_pages = max_pages; p.n_pages = n_pages; p.chunk_len = chunk;
-  if (int rc = launch_decode_t<true, true>(kv, ks, vv, vs, p, B, (cudaStream_t)stream)) return rc;
+  if (int rc = use_tc_kernel() ? launch_decode_tc(kv, ks, vv, vs, p, true, B, (cudaStream_t)stream)
+                               : launch_decode_t<true, true>(kv, ks, vv, vs, p, B, (cudaStream_t)stream))
+    return rc;
   MergeParams mp = {};
   mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)B * T * nqh; mp.qg = qg; mp.o = o; mp.T = T; mp.nqh = nqh;
   mp.seq_len = seq_len; mp.chunk_len = chunk;
