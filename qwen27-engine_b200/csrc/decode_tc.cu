@@ -5,78 +5,112 @@
 // kernel in decode.cu (reference: attn_mma_kernel, src/attn.cu:95-292): Q * scale -> f16,
 // K / V -> f16(int8 * f16 scale), P -> f16, f32 accumulation, row sums from the f32 P.
 // Why a second kernel: measured on B200, the legacy mma.sync path shares its issue bandwidth with
-// the int8 -> f16 conversion arithmetic (one group of four warps alone reaches 86 % of the
-// throughput of two), so the warp-MMA kernel is bound by instruction issue at about 5 TB/s. Here
-// the SIMT lanes only dequantise; everything else is asynchronous hardware:
+// the int8 -> f16 conversion arithmetic, so the warp-MMA kernel is bound by instruction issue. Here
+// the SIMT lanes only dequantise and do the softmax; the contractions are asynchronous hardware.
+// Two measured properties of tcgen05.mma shape the design: an MMA costs time in proportion to its
+// A operand (about 54 cycles per 128 x 16 f16 block, whatever N is), and operands read from shared
+// memory compete with TMA writes and converter traffic for the 128 B per clock of the SM. So the
+// large streamed operand goes where it is cheapest:
 //
-//   warp 12     one lane: TMA of 64-position raw tiles (int8 values + f16 scales) into a 4-stage ring.
-//   warps 0-7   converters: raw tile -> f16 K tile and f16 V tile in shared memory, both as
-//               [64-dim segment][position][128 B] with the 128-byte swizzle. Read as "K-major" this
-//               is the A operand K[p][d] of S^T = K Q^T; read as "MN-major" it is the A operand
-//               V^T[d][p] of O^T = V^T P^T. No transpose, no fragment shuffling.
-//   warp 13     one lane: issues the MMAs. S^T (positions on the 128 TMEM lanes, of which 64 are
-//               used; the 6T query rows on 32 columns) = 16 x (128x32x16); O^T (head dims on the
-//               lanes, two halves of 128; query rows on the columns) += 2 x 4 x (128x32x16).
-//   warps 8-11  softmax group. Warps 8 and 9 own one position each per lane: they read their row
-//               of S^T from TMEM, form P = exp(S - m) against the reference maxima m[r] (moved only
-//               when a score exceeds them by more than TAU), keep per-lane partial row sums, and
-//               write P^T (f16, [query row][position], swizzled) for the second MMA. All four warps
-//               rescale O^T in TMEM on the rare tiles where m moves, and write the partial at the end.
-// TMEM: columns 0-31 and 32-63 two S^T buffers, 64-95 and 96-127 the two halves of O^T.
+//   S^T = K Q^T   K (128 positions x 256 dims, f16) is the A operand and lives in TMEM: the K
+//                 converters store their f16 values straight into TMEM and K never returns to
+//                 shared memory. Q^T (32 rows) is the small B operand in shared memory.
+//   O   = P V     P (query rows x 128 positions, f16) is the A operand in TMEM; V (f16, shared
+//                 memory, [64-dim segment][position][128 B], 128-byte swizzle) is the B operand
+//                 read "MN-major": four MMAs of N = 256 per 64 positions.
+//
+// Warps: 0-7 K converters (warp w: TMEM lane quarter w % 4 = 32 positions, dims 128 (w / 4) ..+127),
+// 8-15 V converters, 16-19 softmax (a thread owns one position of the tile: S^T row from TMEM,
+// P = exp(S - m) against reference maxima kept in shared memory and moved only when a score exceeds
+// them by more than TAU, per-lane partial row sums), 20 "mover" (lanes = query rows: transposes P
+// from the softmax staging buffer into TMEM, rescales O when the maxima moved, writes the partial),
+// 21 TMA producer, 22 issuer of the first MMA (owns the TMEM allocation), 23 issuer of the second.
+// Raw data arrives in 17 KB items (K or V of 64 positions: int8 values + f16 scales) through one
+// ring of seven slots, K two tiles ahead of V, so that S^T of a tile is ready long before its V.
+// TMEM columns: 0-127 K (two halves of 64, each recycled as soon as its eight MMAs have completed),
+// 128-191 two S^T buffers, 192-255 P, 256-511 O.
 #include "common.cuh"
 #include "decode_params.h"
 
 namespace q27b {
+#ifdef Q27B_TRACE
+__device__ long long g_trace[16][64];
+#define TR(e, j) do { if (blockIdx.x == 5 && blockIdx.y == 0 && (j) < 64) g_trace[e][j] = clock64(); } while (0)
+#else
+#define TR(e, j) do {} while (0)
+#endif
 namespace {
 
-constexpr int TILE = 64;                    // positions per tile
-constexpr int NST = 4;                      // raw stages
-constexpr int RAW_BYTES = 2 * TILE * AD + 2 * TILE * 16;  // 34816: K values, V values, K scales, V scales
-constexpr int R_KV = 0, R_VV = TILE * AD, R_KS = 2 * TILE * AD, R_VS = 2 * TILE * AD + TILE * 16;
-constexpr int SEG = TILE * 128;             // one 64-dim segment of an f16 tile: [64 positions][128 B]
-constexpr int F16_TILE = 4 * SEG;           // 32 KB
+constexpr int SUB = 64;                     // positions per raw item
+constexpr int TILE = 128;                   // positions per tile (two items of K, two of V)
+constexpr int NSLOT = 7;                    // raw ring slots
+constexpr int SEG = SUB * 128;              // [64 positions][128 B]
+constexpr int ITEM_BYTES = 2 * SEG + SUB * 16;      // 17408: int8 values (two halves of 128 dims) + f16 scales
+constexpr int I_SC = 2 * SEG;
+constexpr int VF_BYTES = 4 * SEG;           // f16 V of 64 positions, 32 KB
 constexpr int QSEG = 32 * 128;              // one 64-dim segment of Q^T: [32 rows][128 B]
-constexpr int P_BYTES = 32 * 128;           // P^T: [32 query rows][64 positions] f16
+constexpr int PS_ROW = 2 * TILE + 16;       // staging row of P: 128 f16 + padding (bank spread)
+constexpr int PS_BYTES = MAXR * PS_ROW;     // 6528
 constexpr int OFF_RAW = 0;
-constexpr int OFF_KF = OFF_RAW + NST * RAW_BYTES;
-constexpr int OFF_VF = OFF_KF + F16_TILE;
-constexpr int OFF_Q = OFF_VF + F16_TILE;
-constexpr int OFF_PB = OFF_Q + 4 * QSEG;    // two buffers
-constexpr int OFF_X = OFF_PB + 2 * P_BYTES; // softmax exchange area (floats): colmax [2][24], f [24], l [2][24], m [24], tokens [2]
-constexpr int X_CMAX = 0, X_F = 48, X_L = 72, X_M = 120, X_TOK = 144;
-constexpr int OFF_BAR = OFF_X + 160 * 4;
-constexpr int NBAR = 2 * NST + 4 + 8 + 2;   // raw full/empty, kf/vf full/empty, s/p full/empty x2, q_full, o_done
+constexpr int OFF_VF = OFF_RAW + NSLOT * ITEM_BYTES;   // two buffers; reused to stage the partial at the end
+constexpr int OFF_Q = OFF_VF + 2 * VF_BYTES;
+constexpr int OFF_PS = OFF_Q + 4 * QSEG;               // two buffers
+constexpr int OFF_X = OFF_PS + 2 * PS_BYTES;           // floats
+constexpr int X_M = 0, X_F = 24, X_CMAX = 72, X_L = 168, X_TOK = 264;  // m[24], f[2][24], colmax[4][24], l[4][24], token[2]
+constexpr int OFF_BAR = OFF_X + 272 * 4;
+enum {
+  B_RAWFULL = 0,     // [7]
+  B_RAWEMPTY = 7,    // [7]
+  B_KTFULL = 14,     // [2] K half in TMEM
+  B_KTEMPTY = 16,    // [2]
+  B_VFFULL = 18,     // [2]
+  B_VFEMPTY = 20,    // [2]
+  B_SFULL = 22,      // [2]
+  B_SEMPTY = 24,     // [2]
+  B_PSFULL = 26,     // [2] P staged in shared memory
+  B_PSEMPTY = 28,    // [2]
+  B_PTFULL = 30,     // P in TMEM
+  B_PTEMPTY = 31,
+  B_QFULL = 32,
+  B_ODONE = 33,
+  NBAR = 34,
+};
+static_assert(NSLOT == 7, "barrier numbering assumes seven raw slots");
 constexpr int OFF_MISC = OFF_BAR + NBAR * 8;
 constexpr int TC_SMEM_USED = OFF_MISC + 16;
 constexpr int TC_SMEM_BYTES = TC_SMEM_USED + 1024;
-static_assert(OFF_KF % 1024 == 0 && OFF_VF % 1024 == 0 && OFF_Q % 1024 == 0 && OFF_PB % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+static_assert(OFF_VF % 1024 == 0 && OFF_Q % 1024 == 0 && ITEM_BYTES % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+static_assert(OFF_PS % 16 == 0 && OFF_X % 16 == 0 && OFF_BAR % 8 == 0, "alignment");
 static_assert(TC_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+static_assert(MAXR * PROW * 4 <= 2 * VF_BYTES, "partial staging fits the V buffers");
 
-enum {
-  B_RAWFULL = 0,             // [NST]
-  B_RAWEMPTY = NST,          // [NST]
-  B_KFFULL = 2 * NST,
-  B_KFEMPTY = 2 * NST + 1,
-  B_VFFULL = 2 * NST + 2,
-  B_VFEMPTY = 2 * NST + 3,
-  B_SFULL = 2 * NST + 4,     // [2]
-  B_SEMPTY = 2 * NST + 6,    // [2]
-  B_PFULL = 2 * NST + 8,     // [2]
-  B_PEMPTY = 2 * NST + 10,   // [2]
-  B_QFULL = 2 * NST + 12,
-  B_ODONE = 2 * NST + 13,
-};
-
-constexpr int N_CONV_WARPS = 8, SM_WARP0 = 8, TMA_WARP = 12, MMA_WARP = 13;
-constexpr int TC_THREADS = 14 * 32;
+constexpr int KW0 = 0, VW0 = 8, SM_WARP0 = 16, MOVER_WARP = 20, TMA_WARP = 21, QK_WARP = 22, PV_WARP = 23;
+constexpr int TC_THREADS = 24 * 32;
 constexpr int BAR_SM = 1;                   // named barrier of the softmax group (128 threads)
-constexpr uint32_t TMEM_COLS = 128;
-constexpr uint32_t TM_S = 0, TM_O = 64;
+constexpr int BAR_OUT = 2;                  // softmax group + mover (160 threads)
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TM_K = 0, TM_S = 128, TM_P = 192, TM_O = 256;
 constexpr float TAU = 8.0f;
-constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, 128, 32);  // f32 += f16 * f16, A and B K-major, M128 N32
-constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 1, 0, 128, 32);  // A (V^T) MN-major, B (P^T) K-major
+constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, 128, 32);   // f32 += f16 * f16, A (TMEM) and B K-major, M128 N32
+constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, 128, 256);  // A (TMEM) K-major, B (V) MN-major, M128 N256
 
 __device__ __forceinline__ void sm_sync() { asm volatile("bar.sync %0, 128;" ::"r"(BAR_SM) : "memory"); }
+__device__ __forceinline__ void out_sync() { asm volatile("bar.sync %0, 160;" ::"r"(BAR_OUT) : "memory"); }
+
+// Position of the raw items in the ring's sequence: K(0), K(1), then V(j), K(j + 2) for j = 0, 1, ...
+// (each tile has two items, s = 0, 1).
+__device__ __forceinline__ int k_item(int j, int s) { return j < 2 ? 2 * j + s : 4 * j - 2 + s; }
+__device__ __forceinline__ int v_item(int j, int s) { return 4 * j + 4 + s; }
+
+// 16 int8 (one 16-byte chunk, biased to unsigned by the caller's xor) -> 16 f16 = 8 words.
+__device__ __forceinline__ void dq16(const uint4 x, const __half2 dd, uint32_t* o) {
+  const uint32_t xw[4] = {x.x ^ 0x80808080u, x.y ^ 0x80808080u, x.z ^ 0x80808080u, x.w ^ 0x80808080u};
+#pragma unroll
+  for (int w = 0; w < 4; w++) {
+    o[2 * w] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4140), dd);
+    o[2 * w + 1] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4342), dd);
+  }
+}
 
 template <bool PAGED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -92,6 +126,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   uint32_t* tmem_slot = (uint32_t*)(sgen + OFF_MISC);
   volatile int* abort_flag = (volatile int*)(sgen + OFF_MISC + 4);
   float* xf = (float*)(sgen + OFF_X);
+  volatile uint32_t* tok = (volatile uint32_t*)(xf + X_TOK);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int ch = blockIdx.x, kh = blockIdx.y;
@@ -100,7 +135,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   const int pos0 = PAGED ? p.seq_len[seq] - T : *p.pos0;
   const float* qn = p.qn + (size_t)seq * T * p.nqh * AD;
 
-  // Local rows to attend, and this CTA's chunk [c0, c1) of them (multiples of TILE).
+  // Local rows to attend, and this CTA's chunk [c0, c1) of them (chunk starts are multiples of SUB).
   int n = pos0 + T - p.base_pos;
   if (p.n_local >= 0) n = min(n, p.n_local);
   n = max(0, min(n, p.n_ctx));
@@ -109,7 +144,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
     chunk = p.chunk_len;
   } else {
     chunk = (n + p.nch - 1) / p.nch;
-    chunk = max(TILE, (chunk + TILE - 1) / TILE * TILE);
+    chunk = max(SUB, (chunk + SUB - 1) / SUB * SUB);
   }
   const int c0 = min(n, ch * chunk), c1 = min(n, c0 + chunk);
   float* out = p.part + (((size_t)seq * p.nkvh + kh) * p.nch + ch) * MAXR * PROW;
@@ -118,31 +153,35 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       for (int i = tid; i < R * PROW; i += TC_THREADS) out[i] = (i % PROW == 0) ? M_INIT : 0.f;
     return;
   }
-  const int nt = (c1 - c0 + TILE - 1) / TILE;
+  const int nsub = (c1 - c0 + SUB - 1) / SUB;  // raw items of K (and of V)
+  const int nt = (nsub + 1) / 2;               // tiles; the last one may have one item only
 
   if (tid == 0) {
-    for (int s = 0; s < NST; s++) {
+    for (int s = 0; s < NSLOT; s++) {
       mbar_init(&bar[B_RAWFULL + s], 1);
-      mbar_init(&bar[B_RAWEMPTY + s], N_CONV_WARPS);
+      mbar_init(&bar[B_RAWEMPTY + s], 8);
     }
-    mbar_init(&bar[B_KFFULL], N_CONV_WARPS);
-    mbar_init(&bar[B_KFEMPTY], 1);
-    mbar_init(&bar[B_VFFULL], N_CONV_WARPS);
-    mbar_init(&bar[B_VFEMPTY], 1);
     for (int s = 0; s < 2; s++) {
+      mbar_init(&bar[B_KTFULL + s], 4);
+      mbar_init(&bar[B_KTEMPTY + s], 1);
+      mbar_init(&bar[B_VFFULL + s], 8);
+      mbar_init(&bar[B_VFEMPTY + s], 1);
       mbar_init(&bar[B_SFULL + s], 1);
-      mbar_init(&bar[B_SEMPTY + s], 2);
-      mbar_init(&bar[B_PFULL + s], 2);
-      mbar_init(&bar[B_PEMPTY + s], 1);
+      mbar_init(&bar[B_SEMPTY + s], 4);
+      mbar_init(&bar[B_PSFULL + s], 4);
+      mbar_init(&bar[B_PSEMPTY + s], 1);
     }
+    mbar_init(&bar[B_PTFULL], 1);
+    mbar_init(&bar[B_PTEMPTY], 1);
     mbar_init(&bar[B_QFULL], 4);
     mbar_init(&bar[B_ODONE], 1);
     *abort_flag = 0;
-    ((volatile uint32_t*)(xf + X_TOK))[0] = 0;
-    ((volatile uint32_t*)(xf + X_TOK))[1] = 0;
+    tok[0] = 0;
+    tok[1] = 0;
     mbar_fence_init();
   }
-  if (warp == MMA_WARP) {
+  if (tid < MAXR) xf[X_M + tid] = M_INIT;
+  if (warp == QK_WARP) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -151,33 +190,71 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp < N_CONV_WARPS) {
-    // ================================================================ converters
-    // One item = 16 int8 of one row -> 16 f16 (32 bytes = two 16-byte chunks of a segment row). Eight
-    // neighbouring lanes take 4 items of rows rho and rho ^ 5, which keeps the swizzled 16-byte loads
-    // and stores free of bank conflicts. 1024 items per operand and tile, 4 per thread.
+  if (warp < VW0) {
+    // ================================================================ K converters: raw item -> TMEM
+    const int kq = warp & 3, kh2 = warp >> 2;
+    const int ksub = kq >> 1, krow = (kq & 1) * 32 + lane;
+    const uint32_t ktaddr = tmem + ((uint32_t)(kq * 32) << 16) + TM_K + kh2 * 64;
+    for (int j = 0; j < nt; j++) {
+      mbar_wait(&bar[B_KTEMPTY + kh2], (j & 1) ^ 1, abort_flag, p.status);
+      if (2 * j + ksub < nsub) {
+        const int item = k_item(j, ksub), slot = item % NSLOT;
+        const uint8_t* raw = sgen + OFF_RAW + slot * ITEM_BYTES;
+        mbar_wait(&bar[B_RAWFULL + slot], (item / NSLOT) & 1, abort_flag, p.status);
+        if (tid == 0) TR(0, j);
+        const uint8_t* vals = raw + kh2 * SEG;
+        const uint2 sc = *(const uint2*)(raw + I_SC + krow * 16 + kh2 * 8);
+        tc_fence_after();
+#pragma unroll
+        for (int hh = 0; hh < 2; hh++) {
+          uint32_t o[32];
+          const __half2 d0 = __half2half2(__ushort_as_half((unsigned short)((hh ? sc.y : sc.x) & 0xffffu)));
+          const __half2 d1 = __half2half2(__ushort_as_half((unsigned short)((hh ? sc.y : sc.x) >> 16)));
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            const uint4 x = *(const uint4*)(vals + swz128(krow, hh * 4 + c));
+            dq16(x, c < 2 ? d0 : d1, o + 8 * c);
+          }
+          tmem_st32(ktaddr + hh * 32, o);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_n(&bar[B_RAWEMPTY + slot], 2);  // four warps share an item
+      }
+      if (tid == 0) TR(1, j);
+      if (lane == 0) mbar_arrive(&bar[B_KTFULL + kh2]);
+    }
+  } else if (warp < SM_WARP0) {
+    // ================================================================ V converters: raw item -> f16 tile
+    // One unit = 16 int8 of one row -> 16 f16 (two 16-byte chunks of a segment row). Eight
+    // neighbouring lanes take 4 units of rows rho and rho ^ 5, which keeps the swizzled 16-byte loads
+    // and stores free of bank conflicts. 1024 units per item, 4 per thread.
+    const int vt = tid - VW0 * 32;
     int it_row[4], it_c16[4];
 #pragma unroll
     for (int k = 0; k < 4; k++) {
-      const int item = tid + 256 * k;
-      it_row[k] = (2 * (item >> 5)) ^ (5 * ((item >> 2) & 1));
-      it_c16[k] = (item & 3) + 4 * ((item >> 3) & 3);
+      const int u = vt + 256 * k;
+      it_row[k] = (2 * (u >> 5)) ^ (5 * ((u >> 2) & 1));
+      it_c16[k] = (u & 3) + 4 * ((u >> 3) & 3);
     }
-    auto convert = [&](const uint8_t* vals, const uint8_t* scales, uint8_t* dst, int rows_valid, bool zero_tail) {
+    for (int g = 0; g < nsub; g++) {
+      const int j = g >> 1, s = g & 1;
+      const int item = v_item(j, s), slot = item % NSLOT;
+      const uint8_t* raw = sgen + OFF_RAW + slot * ITEM_BYTES;
+      uint8_t* dst = sgen + OFF_VF + s * VF_BYTES;
+      const int rows_valid = c1 - (c0 + g * SUB);
+      mbar_wait(&bar[B_RAWFULL + slot], (item / NSLOT) & 1, abort_flag, p.status);
+      mbar_wait(&bar[B_VFEMPTY + s], (j & 1) ^ 1, abort_flag, p.status);
+      if (vt == 0) TR(2, g);
 #pragma unroll
       for (int k = 0; k < 4; k++) {
         const int row = it_row[k], c16 = it_c16[k];
-        const uint4 x = *(const uint4*)(vals + (c16 >> 3) * SEG + swz128(row, c16 & 7));
-        const __half d = *(const __half*)(scales + row * 16 + (c16 >> 1) * 2);
-        const __half2 dd = __half2half2(d);
-        const uint32_t xw[4] = {x.x ^ 0x80808080u, x.y ^ 0x80808080u, x.z ^ 0x80808080u, x.w ^ 0x80808080u};
+        const uint4 x = *(const uint4*)(raw + (c16 >> 3) * SEG + swz128(row, c16 & 7));
+        const __half d = *(const __half*)(raw + I_SC + row * 16 + (c16 >> 1) * 2);
         uint32_t o[8];
-#pragma unroll
-        for (int w = 0; w < 4; w++) {
-          o[2 * w] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4140), dd);
-          o[2 * w + 1] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4342), dd);
-        }
-        if (zero_tail && row >= rows_valid) {  // rows past the end may hold anything: P is 0 there, V must be too
+        dq16(x, __half2half2(d), o);
+        if (row >= rows_valid) {  // rows past the end may hold anything: P is 0 there, V must be too
 #pragma unroll
           for (int w = 0; w < 8; w++) o[w] = 0;
         }
@@ -186,31 +263,18 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
         *(uint4*)(seg + swz128(row, cc)) = make_uint4(o[0], o[1], o[2], o[3]);
         *(uint4*)(seg + swz128(row, cc + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
       }
-    };
-    for (int j = 0; j < nt; j++) {
-      const int st = j % NST;
-      const uint8_t* raw = sgen + OFF_RAW + st * RAW_BYTES;
-      const int rows_valid = c1 - (c0 + j * TILE);
-      mbar_wait(&bar[B_RAWFULL + st], (j / NST) & 1, abort_flag, p.status);
-      mbar_wait(&bar[B_KFEMPTY], (j & 1) ^ 1, abort_flag, p.status);
-      convert(raw + R_KV, raw + R_KS, sgen + OFF_KF, rows_valid, false);
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bar[B_KFFULL]);
-      mbar_wait(&bar[B_VFEMPTY], (j & 1) ^ 1, abort_flag, p.status);
-      convert(raw + R_VV, raw + R_VS, sgen + OFF_VF, rows_valid, rows_valid < TILE);
-      fence_proxy_async();
-      __syncwarp();
+      if (vt == 0) TR(3, g);
       if (lane == 0) {
-        mbar_arrive(&bar[B_VFFULL]);
-        mbar_arrive(&bar[B_RAWEMPTY + st]);
+        mbar_arrive(&bar[B_VFFULL + s]);
+        mbar_arrive(&bar[B_RAWEMPTY + slot]);
       }
     }
-  } else if (warp < TMA_WARP) {
+  } else if (warp < MOVER_WARP) {
     // ================================================================ softmax group
     const int sw = warp - SM_WARP0;          // TMEM lane quarter
-    const int st_tid = tid - SM_WARP0 * 32;  // 0..127
-    const bool active = sw < 2;              // owns positions 32 sw + lane of every tile
+    const int st_tid = tid - SM_WARP0 * 32;  // 0..127 = position within the tile = TMEM lane
     const uint32_t tlane = tmem + ((uint32_t)(sw * 32) << 16);
     // Q^T (B operand of S^T = K Q^T): [4 segments][32 rows][128 B], scaled, f16; rows >= 6T are zero.
     {
@@ -234,129 +298,152 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       if (lane == 0) mbar_arrive(&bar[B_QFULL]);
     }
 
-    float m_ref[MAXR], lacc[MAXR];
+    float lacc[MAXR];
 #pragma unroll
-    for (int r = 0; r < MAXR; r++) {
-      m_ref[r] = M_INIT;
-      lacc[r] = 0.f;
-    }
+    for (int r = 0; r < MAXR; r++) lacc[r] = 0.f;
     const int lim_base = pos0 + 1 - p.base_pos;  // local rows < lim_base + t are visible to token t
-    volatile uint32_t* tok = (volatile uint32_t*)(xf + X_TOK);
+    const int lim_min = min(c1, lim_base);       // positions below this are visible to every row
 
     for (int j = 0; j < nt; j++) {
       const int slot = j & 1;
-      const int tile_p0 = c0 + j * TILE;
+      const int pos = c0 + j * TILE + st_tid;
       float s[MAXR];
-      if (active) {
-        mbar_wait(&bar[B_SFULL + slot], (j >> 1) & 1, abort_flag, p.status);
-        tc_fence_after();
+      mbar_wait(&bar[B_SFULL + slot], (j >> 1) & 1, abort_flag, p.status);
+      tc_fence_after();
+      if (st_tid == 0) TR(9, j);
+      {
         uint32_t v[32];
         tmem_ld32(tlane + TM_S + slot * 32, v);
         tc_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar[B_SEMPTY + slot]);
-        const int pos = tile_p0 + sw * 32 + lane;
-        bool exceed = j == 0;
 #pragma unroll
-        for (int r = 0; r < MAXR; r++) {
-          s[r] = __uint_as_float(v[r]);
-          if (pos >= min(c1, lim_base + min(r / GQA, T - 1))) s[r] = -INFINITY;
-          exceed |= s[r] > m_ref[r] + TAU;
-        }
-        if (__any_sync(0xffffffffu, exceed) && lane == 0) tok[slot] = (uint32_t)(j + 1);
+        for (int r = 0; r < MAXR; r++) s[r] = __uint_as_float(v[r]);
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[B_SEMPTY + slot]);
+      // The mover has finished with this slot's staging buffer, token and factors (tile j - 2).
+      mbar_wait(&bar[B_PSEMPTY + slot], ((j >> 1) & 1) ^ 1, abort_flag, p.status);
+      if (c0 + (j + 1) * TILE > lim_min) {  // edge tile: causal limit per token, end of the chunk, absent item
+#pragma unroll
+        for (int r = 0; r < MAXR; r++)
+          if (pos >= min(c1, lim_base + min(r / GQA, T - 1))) s[r] = -INFINITY;
+      }
+      bool exceed = j == 0;
+#pragma unroll
+      for (int r = 0; r < MAXR; r++) exceed |= s[r] > xf[X_M + r] + TAU;
+      if (__any_sync(0xffffffffu, exceed) && lane == 0) tok[slot] = (uint32_t)(j + 1);
       sm_sync();
       if (tok[slot] == (uint32_t)(j + 1)) {
         // ---- some score ran away from the reference maxima (always on the first tile): move them
-        if (active) {
-#pragma unroll
-          for (int r = 0; r < MAXR; r++) {
-            float v = s[r];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-            if (lane == 0) xf[X_CMAX + sw * MAXR + r] = v;
-          }
-        }
-        sm_sync();
-        if (active) {
-#pragma unroll
-          for (int r = 0; r < MAXR; r++) {
-            const float mn = fmaxf(m_ref[r], fmaxf(xf[X_CMAX + r], xf[X_CMAX + MAXR + r]));
-            const float f = ex2((m_ref[r] - mn) * LOG2E);
-            m_ref[r] = mn;
-            lacc[r] *= f;
-            if (sw == 0 && lane == 0) xf[X_F + r] = f;
-          }
-        }
-        sm_sync();
-        if (j > 0) {
-          // O^T holds the tiles < j once the second MMA of tile j-1 has completed; every warp of the
-          // group rescales its 32 lanes (head dims), column r by f[r].
-          mbar_wait(&bar[B_PEMPTY + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag, p.status);
-          tc_fence_after();
-#pragma unroll 1
-          for (int h = 0; h < 2; h++) {
-            uint32_t v[32];
-            tmem_ld32(tlane + TM_O + h * 32, v);
-            tc_wait_ld();
-#pragma unroll
-            for (int r = 0; r < MAXR; r++) v[r] = __float_as_uint(__uint_as_float(v[r]) * xf[X_F + r]);
-            tmem_st32(tlane + TM_O + h * 32, v);
-          }
-          tc_wait_st();
-          tc_fence_before();
-        }
-        sm_sync();  // the rescale is complete before anybody releases the next second MMA
-      }
-      if (active) {
-        // P = exp(S - m): per-lane partial row sums; P^T[r][position] as f16 for the second MMA
-        mbar_wait(&bar[B_PEMPTY + slot], ((j >> 1) & 1) ^ 1, abort_flag, p.status);
-        uint8_t* pb = sgen + OFF_PB + slot * P_BYTES;
-        const int pp = sw * 32 + lane;
 #pragma unroll
         for (int r = 0; r < MAXR; r++) {
-          const float e = ex2(fmaf(s[r], LOG2E, -m_ref[r] * LOG2E));
-          lacc[r] += e;
-          *(__half*)(pb + r * 128 + ((((uint32_t)pp >> 3) ^ (r & 7)) << 4) + (pp & 7) * 2) = __float2half_rn(e);
+          float v = s[r];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+          if (lane == 0) xf[X_CMAX + sw * MAXR + r] = v;
         }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar[B_PFULL + slot]);
+        sm_sync();
+        if (st_tid < MAXR) {  // everybody compared against the old maxima before the first barrier of this tile
+          const int r = st_tid;
+          const float mo = xf[X_M + r];
+          const float mn = fmaxf(fmaxf(mo, xf[X_CMAX + r]),
+                                 fmaxf(fmaxf(xf[X_CMAX + MAXR + r], xf[X_CMAX + 2 * MAXR + r]), xf[X_CMAX + 3 * MAXR + r]));
+          xf[X_F + slot * MAXR + r] = ex2((mo - mn) * LOG2E);  // the mover rescales O by it
+          xf[X_M + r] = mn;
+        }
+        sm_sync();
+#pragma unroll
+        for (int r = 0; r < MAXR; r++) lacc[r] *= xf[X_F + slot * MAXR + r];
       }
-    }
-
-    // ---- epilogue: row sums over the 64 position lanes, then the partial (m, l, O[256]) per query row
-    if (active) {
+      // P = exp(S - m): per-lane partial row sums; f16 P[r][position] staged for the mover
+      uint8_t* ps = sgen + OFF_PS + slot * PS_BYTES + st_tid * 2;
 #pragma unroll
       for (int r = 0; r < MAXR; r++) {
-        float v = lacc[r];
+        const float e = ex2(fmaf(s[r], LOG2E, -xf[X_M + r] * LOG2E));
+        lacc[r] += e;
+        *(__half*)(ps + r * PS_ROW) = __float2half_rn(e);
+      }
+      __syncwarp();
+      if (st_tid == 0) TR(10, j);
+      if (lane == 0) mbar_arrive(&bar[B_PSFULL + slot]);
+    }
+
+    // ---- row sums over the 128 position lanes; then help the mover write the partial
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0) {
-          xf[X_L + sw * MAXR + r] = v;
-          if (sw == 0) xf[X_M + r] = m_ref[r];
+    for (int r = 0; r < MAXR; r++) {
+      float v = lacc[r];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) xf[X_L + sw * MAXR + r] = v;
+    }
+    out_sync();  // row sums visible to the mover
+    out_sync();  // partial staged
+    const float* ost = (const float*)(sgen + OFF_VF);
+    for (int i = st_tid; i < R * PROW; i += 160) out[i] = ost[i];
+  } else if (warp == MOVER_WARP) {
+    // ================================================================ mover (lanes = query rows)
+    const bool row_ok = lane < MAXR;
+    for (int j = 0; j < nt; j++) {
+      const int slot = j & 1;
+      mbar_wait(&bar[B_PSFULL + slot], (j >> 1) & 1, abort_flag, p.status);
+      mbar_wait(&bar[B_PTEMPTY], (j & 1) ^ 1, abort_flag, p.status);  // second MMA of tile j - 1 complete
+      tc_fence_after();
+      if (lane == 0) TR(11, j);
+      if (j > 0 && tok[slot] == (uint32_t)(j + 1)) {
+        const float f = row_ok ? xf[X_F + slot * MAXR + lane] : 1.f;
+#pragma unroll 1
+        for (int c = 0; c < 8; c++) {
+          uint32_t v[32];
+          tmem_ld32(tmem + TM_O + c * 32, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+          tmem_st32(tmem + TM_O + c * 32, v);
         }
       }
+      const uint8_t* ps = sgen + OFF_PS + slot * PS_BYTES + (row_ok ? lane : 0) * PS_ROW;
+#pragma unroll
+      for (int hh = 0; hh < 2; hh++) {
+        uint32_t w[32];
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+          uint4 x = *(const uint4*)(ps + (hh * 8 + c) * 16);
+          if (!row_ok) x = make_uint4(0, 0, 0, 0);
+          w[4 * c] = x.x; w[4 * c + 1] = x.y; w[4 * c + 2] = x.z; w[4 * c + 3] = x.w;
+        }
+        tmem_st32(tmem + TM_P + hh * 32, w);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        TR(12, j);
+        mbar_arrive(&bar[B_PSEMPTY + slot]);
+        mbar_arrive(&bar[B_PTFULL]);
+      }
     }
-    sm_sync();
+    // ---- partial (m, l, O[256]) per query row, staged in shared memory and written by five warps
+    out_sync();
     mbar_wait(&bar[B_ODONE], 0, abort_flag, p.status);
     tc_fence_after();
-    if (st_tid < R) {
-      out[(size_t)st_tid * PROW] = xf[X_M + st_tid];
-      out[(size_t)st_tid * PROW + 1] = xf[X_L + st_tid] + xf[X_L + MAXR + st_tid];
+    float* ost = (float*)(sgen + OFF_VF);
+    if (lane < R) {
+      ost[lane * PROW] = xf[X_M + lane];
+      ost[lane * PROW + 1] = (xf[X_L + lane] + xf[X_L + MAXR + lane]) + (xf[X_L + 2 * MAXR + lane] + xf[X_L + 3 * MAXR + lane]);
     }
 #pragma unroll 1
-    for (int h = 0; h < 2; h++) {
+    for (int c = 0; c < 8; c++) {
       uint32_t v[32];
-      tmem_ld32(tlane + TM_O + h * 32, v);
+      tmem_ld32(tmem + TM_O + c * 32, v);
       tc_wait_ld();
-      const int d = h * 128 + st_tid;  // TMEM lane = head dim within the half
+      if (lane < R) {
 #pragma unroll
-      for (int r = 0; r < MAXR; r++)
-        if (r < R) out[(size_t)r * PROW + 2 + d] = __uint_as_float(v[r]);
+        for (int i = 0; i < 32; i++) ost[lane * PROW + 2 + c * 32 + i] = __uint_as_float(v[i]);
+      }
     }
     tc_fence_before();
+    out_sync();
+    for (int i = 128 + lane; i < R * PROW; i += 160) out[i] = ost[i];
   } else if (warp == TMA_WARP) {
     // ================================================================ TMA producer
     if (lane == 0) {
@@ -365,12 +452,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       tma_prefetch_desc(&tm_vv);
       tma_prefetch_desc(&tm_vs);
       const int row0 = kh * p.n_ctx + c0;
-      for (int j = 0; j < nt; j++) {
-        const int st = j % NST;
-        uint8_t* raw = sgen + OFF_RAW + st * RAW_BYTES;
-        int row = row0 + j * TILE;
-        if (PAGED) {  // a tile never straddles a page (64 | 256)
-          const int pp = c0 + j * TILE;
+      auto load = [&](const CUtensorMap* tv, const CUtensorMap* ts, int g, int item) {
+        if (g >= nsub) return;
+        const int slot = item % NSLOT;
+        uint8_t* raw = sgen + OFF_RAW + slot * ITEM_BYTES;
+        int row = row0 + g * SUB;
+        if (PAGED) {  // an item never straddles a page (64 | 256)
+          const int pp = c0 + g * SUB;
           int pg = p.page_table[(size_t)seq * p.max_pages + pp / Q27B_PAGE];
           if (pg < 0 || pg >= p.n_pages) {  // never read outside the pool: flag it and read page 0
             atomicOr(p.status, ST_BAD_PAGE);
@@ -378,62 +466,73 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
           }
           row = (pg * p.nkvh + kh) * Q27B_PAGE + pp % Q27B_PAGE;
         }
-        mbar_wait(&bar[B_RAWEMPTY + st], ((j / NST) & 1) ^ 1, abort_flag, p.status);
-        mbar_expect_tx(&bar[B_RAWFULL + st], RAW_BYTES);
-        tma_load_2d(raw + R_KV, &tm_kv, 0, row, &bar[B_RAWFULL + st]);
-        tma_load_2d(raw + R_KV + SEG, &tm_kv, 128, row, &bar[B_RAWFULL + st]);
-        tma_load_2d(raw + R_KS, &tm_ks, 0, row, &bar[B_RAWFULL + st]);
-        tma_load_2d(raw + R_VV, &tm_vv, 0, row, &bar[B_RAWFULL + st]);
-        tma_load_2d(raw + R_VV + SEG, &tm_vv, 128, row, &bar[B_RAWFULL + st]);
-        tma_load_2d(raw + R_VS, &tm_vs, 0, row, &bar[B_RAWFULL + st]);
+        mbar_wait(&bar[B_RAWEMPTY + slot], ((item / NSLOT) & 1) ^ 1, abort_flag, p.status);
+        mbar_expect_tx(&bar[B_RAWFULL + slot], ITEM_BYTES);
+        tma_load_2d(raw, tv, 0, row, &bar[B_RAWFULL + slot]);
+        tma_load_2d(raw + SEG, tv, 128, row, &bar[B_RAWFULL + slot]);
+        tma_load_2d(raw + I_SC, ts, 0, row, &bar[B_RAWFULL + slot]);
+      };
+      for (int g = 0; g < 4; g++) load(&tm_kv, &tm_ks, g, g);
+      for (int j = 0; j < nt; j++) {
+        load(&tm_vv, &tm_vs, 2 * j, v_item(j, 0));
+        load(&tm_vv, &tm_vs, 2 * j + 1, v_item(j, 1));
+        load(&tm_kv, &tm_ks, 2 * j + 4, k_item(j + 2, 0));
+        load(&tm_kv, &tm_ks, 2 * j + 5, k_item(j + 2, 1));
+      }
+    }
+  } else if (warp == QK_WARP) {
+    // ================================================================ issuer of S^T = K Q^T
+    if (lane == 0) {
+      mbar_wait(&bar[B_QFULL], 0, abort_flag, p.status);
+      for (int j = 0; j < nt; j++) {
+        const int slot = j & 1;
+        mbar_wait(&bar[B_SEMPTY + slot], ((j >> 1) & 1) ^ 1, abort_flag, p.status);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          mbar_wait(&bar[B_KTFULL + h], j & 1, abort_flag, p.status);
+          tc_fence_after();
+          if (h == 0) TR(5, j);
+#pragma unroll
+          for (int k8 = 0; k8 < 8; k8++) {
+            const int kk = h * 8 + k8;
+            // A = K[128 positions][16 dims] in TMEM, B = Q^T[32 rows][16 dims]
+            const uint64_t db = umma_desc_sw128(sbase + OFF_Q + (kk >> 2) * QSEG + (kk & 3) * 32, 16, 1024);
+            tc_mma_f16_ts(tmem + TM_S + slot * 32, tmem + TM_K + kk * 8, db, IDESC_QK, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(&bar[B_KTEMPTY + h]);
+        }
+        tc_commit(&bar[B_SFULL + slot]);
+        TR(6, j);
       }
     }
   } else {
-    // ================================================================ MMA issuer
+    // ================================================================ issuer of O += P V
     if (lane == 0) {
-      mbar_wait(&bar[B_QFULL], 0, abort_flag, p.status);
-      tc_fence_after();
-      auto issue_pv = [&](int jj) {
-        const int slot = jj & 1;
-        mbar_wait(&bar[B_PFULL + slot], (jj >> 1) & 1, abort_flag, p.status);
-        mbar_wait(&bar[B_VFFULL], jj & 1, abort_flag, p.status);
-        tc_fence_after();
-#pragma unroll
-        for (int h = 0; h < 2; h++)
-#pragma unroll
-          for (int kk = 0; kk < TILE / 16; kk++) {
-            // A = V^T[head dims 128h..][16 positions]: two 64-dim segments (8192 B apart), MN-major
-            const uint64_t da = umma_desc_sw128(sbase + OFF_VF + 2 * h * SEG + kk * 2048, SEG, 1024);
-            const uint64_t db = umma_desc_sw128(sbase + OFF_PB + slot * P_BYTES + kk * 32, 16, 1024);
-            tc_mma_f16(tmem + TM_O + h * 32, da, db, IDESC_PV, (jj > 0 || kk > 0) ? 1u : 0u);
-          }
-        tc_commit(&bar[B_VFEMPTY]);
-        tc_commit(&bar[B_PEMPTY + slot]);
-      };
       for (int j = 0; j < nt; j++) {
-        const int slot = j & 1;
-        mbar_wait(&bar[B_KFFULL], j & 1, abort_flag, p.status);
-        mbar_wait(&bar[B_SEMPTY + slot], ((j >> 1) & 1) ^ 1, abort_flag, p.status);
-        tc_fence_after();
+        const int ns = min(2, nsub - 2 * j);
+        mbar_wait(&bar[B_PTFULL], j & 1, abort_flag, p.status);
+        TR(7, j);
+        for (int s = 0; s < ns; s++) {
+          mbar_wait(&bar[B_VFFULL + s], j & 1, abort_flag, p.status);
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < AD / 16; kk++) {
-          // A = K[128 rows, of which 64 are this tile][16 dims], B = Q^T[32 rows][16 dims]
-          const uint64_t da = umma_desc_sw128(sbase + OFF_KF + (kk >> 2) * SEG + (kk & 3) * 32, 16, 1024);
-          const uint64_t db = umma_desc_sw128(sbase + OFF_Q + (kk >> 2) * QSEG + (kk & 3) * 32, 16, 1024);
-          tc_mma_f16(tmem + TM_S + slot * 32, da, db, IDESC_QK, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < SUB / 16; kk++) {
+            // A = P[128 rows][16 positions] in TMEM, B = V[16 positions][256 dims], MN-major
+            const uint64_t db = umma_desc_sw128(sbase + OFF_VF + s * VF_BYTES + kk * 2048, SEG, 1024);
+            tc_mma_f16_ts(tmem + TM_O, tmem + TM_P + (s * 4 + kk) * 8, db, IDESC_PV, (j > 0 || s > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&bar[B_VFEMPTY + s]);
         }
-        tc_commit(&bar[B_SFULL + slot]);
-        tc_commit(&bar[B_KFEMPTY]);
-        if (j >= 1) issue_pv(j - 1);
+        tc_commit(&bar[B_PTEMPTY]);
+        TR(8, j);
       }
-      issue_pv(nt - 1);
       tc_commit(&bar[B_ODONE]);
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == MMA_WARP) {
+  if (warp == QK_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -457,4 +556,7 @@ int launch_decode_tc(const CUtensorMap* kv, const CUtensorMap* ks, const CUtenso
   return Q27B_OK;
 }
 
+#ifdef Q27B_TRACE
+extern "C" int q27b_trace_read(long long* dst) { return (int)cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace)); }
+#endif
 }  // namespace q27b
