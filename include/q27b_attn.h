@@ -135,6 +135,14 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
                            const int* page_table, const int* seq_len, float* o, int B, int T, float kq_scale, int nqh,
                            int nkvh, int n_pages, int max_pages, int max_seq_len, void* stream);
 
+/* Which split-K kernel q27b_attn_decode* uses for q8_0 caches: 0 = default (the warp-MMA kernel),
+ * 1 = warp-MMA kernel, 2 = tcgen05 kernel (both contractions on the 5th-generation tensor cores;
+ * faster at long contexts in its best builds, less predictable: see csrc/decode.cu). Both compute
+ * the same operator with the same roundings (src/attn.cu:95-292). Process-wide; the environment
+ * variable Q27B_DECODE_KERNEL=mma|tc sets the initial value. No counterpart in the reference (it
+ * has one kernel). */
+int q27b_set_decode_kernel(int which);
+
 /* Measurement hook, no counterpart in the reference: while `event` (a cudaEvent_t) is set, every
  * q27b_attn_decode / q27b_attn_decode_partial call on the current device records it on the
  * caller's stream between its split-K kernel and its merge kernel, so that a benchmark can time

@@ -90,9 +90,15 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // pressure (measured on the prefill kernel: +40 % throughput from moving this loop out of line at
 // its ~50 call sites). The inlined part is one try_wait, which is all that a wait on a barrier that
 // has already completed costs.
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // two seconds
+constexpr long long WAIT_LIMIT_NS = 2000000000ll;  // two seconds ...
+constexpr uint32_t WAIT_MIN_POLLS = 1u << 20;      // ... and at least this many polls (a jump of the timer alone never ends a wait)
 constexpr uint32_t WAIT_HINT_NS = 1000u;
-static __device__ __noinline__ void mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+#ifdef Q27B_INLINE_WAITS  // a kernel whose warps all run the same code may prefer the loop inline
+#define Q27B_WAIT_SLOW_ATTR __forceinline__
+#else
+#define Q27B_WAIT_SLOW_ATTR __noinline__
+#endif
+static __device__ Q27B_WAIT_SLOW_ATTR void mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
   unsigned long long t0 = 0;
   for (uint32_t i = 1;; i++) {
     if (mbar_try_wait_hint(bar, parity, WAIT_HINT_NS)) return;
@@ -100,7 +106,7 @@ static __device__ __noinline__ void mbar_wait_slow(uint64_t* bar, uint32_t parit
       if (*abort_flag) return;
       const unsigned long long t = global_ns();
       if (t0 == 0) t0 = t;
-      else if (t - t0 > WAIT_LIMIT_NS) break;
+      else if (i >= WAIT_MIN_POLLS && (long long)(t - t0) > WAIT_LIMIT_NS) break;
     }
   }
   *abort_flag = 1;
@@ -109,6 +115,15 @@ static __device__ __noinline__ void mbar_wait_slow(uint64_t* bar, uint32_t parit
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
   if (mbar_try_wait(bar, parity)) return;
   mbar_wait_slow(bar, parity, abort_flag, status);
+}
+
+// After a wait has given up, a CTA drains to its end without synchronisation. Before it frees
+// tensor memory and exits it gives the copies and MMAs that it issued earlier time to land
+// (microseconds of work; this sleeps 100 us), so that nothing is still writing into shared or
+// tensor memory that the next CTA on this SM will own.
+__device__ __forceinline__ void drain_after_abort(volatile int* abort_flag) {
+  if (*abort_flag)
+    for (int i = 0; i < 100; i++) __nanosleep(1000);
 }
 
 // ------------------------------------------------------------------ TMA (plain per-CTA loads only)

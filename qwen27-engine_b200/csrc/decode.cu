@@ -26,6 +26,7 @@
 //    conflict-free.
 //  * The reference maxima of a group only move when a score exceeds them by more than TAU (and on
 //    the group's first tile): a tile normally costs one group barrier and no rescale of O.
+#define Q27B_INLINE_WAITS  // all eight warps of this kernel run the same code: the wait loops stay inline
 #include "combine.h"
 #include "common.cuh"
 #include "decode_params.h"
@@ -629,14 +630,20 @@ int launch_decode_t(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensor
   return launch_decode<3, PAGED, Q8>(kv, ks, vv, vs, p, nseq, s);
 }
 
-// q8_0 caches go to the warp-MMA kernel of this file unless Q27B_DECODE_KERNEL=tc asks for the
-// tcgen05 kernel (decode_tc.cu); f16 caches always use the warp-MMA kernel.
+// Which split-K kernel serves a q8_0 cache: the warp-MMA kernel of this file unless
+// Q27B_DECODE_KERNEL=tc or q27b_set_decode_kernel(2) asks for the tcgen05 kernel (decode_tc.cu).
+// Measured on B200 (same call, CUDA-graph timing): the tcgen05 kernel reaches 73.7 us against
+// 77.7 us at 150k positions in its best builds, but its speed moves by up to 10 % with small changes
+// of its code (it runs eight differently specialised warp roles per SM and is sensitive to
+// instruction-cache layout), and it starts 1.4 us later (13.2 us against 11.7 us at 64 positions).
+// The warp-MMA kernel is stable at 76.7 us, so it stays the default. f16 caches always use it.
+int g_kernel_choice = -1;  // -1: not read yet; 0 default, 1 warp-MMA, 2 tcgen05
 bool use_tc_kernel() {
-  static const bool tc = [] {
+  if (g_kernel_choice < 0) {
     const char* e = getenv("Q27B_DECODE_KERNEL");
-    return e && e[0] == 't';
-  }();
-  return tc;
+    g_kernel_choice = !e ? 0 : e[0] == 'm' ? 1 : e[0] == 't' ? 2 : 0;
+  }
+  return g_kernel_choice == 2;
 }
 
 // Split-K pass of one sequence into ctx->part [nkvh][nch][24][258].
@@ -765,6 +772,12 @@ int q27b_attn_decode_noalloc(const float* qn, const float* qg, const void* kcach
   mp.part = g_noalloc_part_ptr[dev]; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.qg = qg; mp.o = o; mp.xq = xq;
   mp.xd = xd; mp.T = T; mp.nqh = nqh;
   return launch_merge(mp, true, (cudaStream_t)stream);
+}
+
+int q27b_set_decode_kernel(int which) {
+  if (which < 0 || which > 2) return fail(Q27B_BAD_SHAPE, "set_decode_kernel: 0 auto, 1 warp-MMA, 2 tcgen05");
+  g_kernel_choice = which;
+  return Q27B_OK;
 }
 
 int q27b_debug_split_event(void* event) {

@@ -33,12 +33,6 @@
 #include "decode_params.h"
 
 namespace q27b {
-#ifdef Q27B_TRACE
-__device__ long long g_trace[16][64];
-#define TR(e, j) do { if (blockIdx.x == 5 && blockIdx.y == 0 && (j) < 64) g_trace[e][j] = clock64(); } while (0)
-#else
-#define TR(e, j) do {} while (0)
-#endif
 namespace {
 
 constexpr int SUB = 64;                     // positions per raw item
@@ -195,15 +189,19 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
     const int kq = warp & 3, kh2 = warp >> 2;
     const int ksub = kq >> 1, krow = (kq & 1) * 32 + lane;
     const uint32_t ktaddr = tmem + ((uint32_t)(kq * 32) << 16) + TM_K + kh2 * 64;
-    for (int j = 0; j < nt; j++) {
+    _Pragma("unroll 1") for (int j = 0; j < nt && !*abort_flag; j++) {
       mbar_wait(&bar[B_KTEMPTY + kh2], (j & 1) ^ 1, abort_flag, p.status);
       if (2 * j + ksub < nsub) {
         const int item = k_item(j, ksub), slot = item % NSLOT;
         const uint8_t* raw = sgen + OFF_RAW + slot * ITEM_BYTES;
         mbar_wait(&bar[B_RAWFULL + slot], (item / NSLOT) & 1, abort_flag, p.status);
-        if (tid == 0) TR(0, j);
         const uint8_t* vals = raw + kh2 * SEG;
         const uint2 sc = *(const uint2*)(raw + I_SC + krow * 16 + kh2 * 8);
+        // All loads first: the compiler cannot move a shared-memory load above an earlier store or
+        // TMEM store, so interleaving them would serialise the load latencies.
+        uint4 x[8];
+#pragma unroll
+        for (int c = 0; c < 8; c++) x[c] = *(const uint4*)(vals + swz128(krow, c));
         tc_fence_after();
 #pragma unroll
         for (int hh = 0; hh < 2; hh++) {
@@ -211,10 +209,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
           const __half2 d0 = __half2half2(__ushort_as_half((unsigned short)((hh ? sc.y : sc.x) & 0xffffu)));
           const __half2 d1 = __half2half2(__ushort_as_half((unsigned short)((hh ? sc.y : sc.x) >> 16)));
 #pragma unroll
-          for (int c = 0; c < 4; c++) {
-            const uint4 x = *(const uint4*)(vals + swz128(krow, hh * 4 + c));
-            dq16(x, c < 2 ? d0 : d1, o + 8 * c);
-          }
+          for (int c = 0; c < 4; c++) dq16(x[hh * 4 + c], c < 2 ? d0 : d1, o + 8 * c);
           tmem_st32(ktaddr + hh * 32, o);
         }
         tc_wait_st();
@@ -222,7 +217,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive_n(&bar[B_RAWEMPTY + slot], 2);  // four warps share an item
       }
-      if (tid == 0) TR(1, j);
       if (lane == 0) mbar_arrive(&bar[B_KTFULL + kh2]);
     }
   } else if (warp < SM_WARP0) {
@@ -238,7 +232,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       it_row[k] = (2 * (u >> 5)) ^ (5 * ((u >> 2) & 1));
       it_c16[k] = (u & 3) + 4 * ((u >> 3) & 3);
     }
-    for (int g = 0; g < nsub; g++) {
+    _Pragma("unroll 1") for (int g = 0; g < nsub && !*abort_flag; g++) {
       const int j = g >> 1, s = g & 1;
       const int item = v_item(j, s), slot = item % NSLOT;
       const uint8_t* raw = sgen + OFF_RAW + slot * ITEM_BYTES;
@@ -246,14 +240,19 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       const int rows_valid = c1 - (c0 + g * SUB);
       mbar_wait(&bar[B_RAWFULL + slot], (item / NSLOT) & 1, abort_flag, p.status);
       mbar_wait(&bar[B_VFEMPTY + s], (j & 1) ^ 1, abort_flag, p.status);
-      if (vt == 0) TR(2, g);
+      uint4 x[4];
+      __half d[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) {  // loads first (a load cannot be moved above an earlier shared-memory store)
+        const int row = it_row[k], c16 = it_c16[k];
+        x[k] = *(const uint4*)(raw + (c16 >> 3) * SEG + swz128(row, c16 & 7));
+        d[k] = *(const __half*)(raw + I_SC + row * 16 + (c16 >> 1) * 2);
+      }
 #pragma unroll
       for (int k = 0; k < 4; k++) {
         const int row = it_row[k], c16 = it_c16[k];
-        const uint4 x = *(const uint4*)(raw + (c16 >> 3) * SEG + swz128(row, c16 & 7));
-        const __half d = *(const __half*)(raw + I_SC + row * 16 + (c16 >> 1) * 2);
         uint32_t o[8];
-        dq16(x, __half2half2(d), o);
+        dq16(x[k], __half2half2(d[k]), o);
         if (row >= rows_valid) {  // rows past the end may hold anything: P is 0 there, V must be too
 #pragma unroll
           for (int w = 0; w < 8; w++) o[w] = 0;
@@ -265,7 +264,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       }
       fence_proxy_async();
       __syncwarp();
-      if (vt == 0) TR(3, g);
       if (lane == 0) {
         mbar_arrive(&bar[B_VFFULL + s]);
         mbar_arrive(&bar[B_RAWEMPTY + slot]);
@@ -304,13 +302,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
     const int lim_base = pos0 + 1 - p.base_pos;  // local rows < lim_base + t are visible to token t
     const int lim_min = min(c1, lim_base);       // positions below this are visible to every row
 
-    for (int j = 0; j < nt; j++) {
+    _Pragma("unroll 1") for (int j = 0; j < nt; j++) {
       const int slot = j & 1;
       const int pos = c0 + j * TILE + st_tid;
       float s[MAXR];
       mbar_wait(&bar[B_SFULL + slot], (j >> 1) & 1, abort_flag, p.status);
       tc_fence_after();
-      if (st_tid == 0) TR(9, j);
       {
         uint32_t v[32];
         tmem_ld32(tlane + TM_S + slot * 32, v);
@@ -358,13 +355,19 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       // P = exp(S - m): per-lane partial row sums; f16 P[r][position] staged for the mover
       uint8_t* ps = sgen + OFF_PS + slot * PS_BYTES + st_tid * 2;
 #pragma unroll
-      for (int r = 0; r < MAXR; r++) {
-        const float e = ex2(fmaf(s[r], LOG2E, -xf[X_M + r] * LOG2E));
-        lacc[r] += e;
-        *(__half*)(ps + r * PS_ROW) = __float2half_rn(e);
+      for (int g6 = 0; g6 < MAXR / 6; g6++) {  // maxima in batches: their loads cannot pass the stores of P
+        float nm[6];
+#pragma unroll
+        for (int k = 0; k < 6; k++) nm[k] = -xf[X_M + g6 * 6 + k] * LOG2E;
+#pragma unroll
+        for (int k = 0; k < 6; k++) {
+          const int r = g6 * 6 + k;
+          const float e = ex2(fmaf(s[r], LOG2E, nm[k]));
+          lacc[r] += e;
+          *(__half*)(ps + r * PS_ROW) = __float2half_rn(e);
+        }
       }
       __syncwarp();
-      if (st_tid == 0) TR(10, j);
       if (lane == 0) mbar_arrive(&bar[B_PSFULL + slot]);
     }
 
@@ -383,12 +386,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   } else if (warp == MOVER_WARP) {
     // ================================================================ mover (lanes = query rows)
     const bool row_ok = lane < MAXR;
-    for (int j = 0; j < nt; j++) {
+    _Pragma("unroll 1") for (int j = 0; j < nt; j++) {
       const int slot = j & 1;
       mbar_wait(&bar[B_PSFULL + slot], (j >> 1) & 1, abort_flag, p.status);
       mbar_wait(&bar[B_PTEMPTY], (j & 1) ^ 1, abort_flag, p.status);  // second MMA of tile j - 1 complete
       tc_fence_after();
-      if (lane == 0) TR(11, j);
       if (j > 0 && tok[slot] == (uint32_t)(j + 1)) {
         const float f = row_ok ? xf[X_F + slot * MAXR + lane] : 1.f;
 #pragma unroll 1
@@ -417,7 +419,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        TR(12, j);
         mbar_arrive(&bar[B_PSEMPTY + slot]);
         mbar_arrive(&bar[B_PTFULL]);
       }
@@ -453,7 +454,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       tma_prefetch_desc(&tm_vs);
       const int row0 = kh * p.n_ctx + c0;
       auto load = [&](const CUtensorMap* tv, const CUtensorMap* ts, int g, int item) {
-        if (g >= nsub) return;
+        if (g >= nsub || *abort_flag) return;  // after a wait has given up nothing new is issued
         const int slot = item % NSLOT;
         uint8_t* raw = sgen + OFF_RAW + slot * ITEM_BYTES;
         int row = row0 + g * SUB;
@@ -472,8 +473,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
         tma_load_2d(raw + SEG, tv, 128, row, &bar[B_RAWFULL + slot]);
         tma_load_2d(raw + I_SC, ts, 0, row, &bar[B_RAWFULL + slot]);
       };
-      for (int g = 0; g < 4; g++) load(&tm_kv, &tm_ks, g, g);
-      for (int j = 0; j < nt; j++) {
+      _Pragma("unroll 1") for (int g = 0; g < 4; g++) load(&tm_kv, &tm_ks, g, g);
+      _Pragma("unroll 1") for (int j = 0; j < nt; j++) {
         load(&tm_vv, &tm_vs, 2 * j, v_item(j, 0));
         load(&tm_vv, &tm_vs, 2 * j + 1, v_item(j, 1));
         load(&tm_kv, &tm_ks, 2 * j + 4, k_item(j + 2, 0));
@@ -484,14 +485,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
     // ================================================================ issuer of S^T = K Q^T
     if (lane == 0) {
       mbar_wait(&bar[B_QFULL], 0, abort_flag, p.status);
-      for (int j = 0; j < nt; j++) {
+      _Pragma("unroll 1") for (int j = 0; j < nt && !*abort_flag; j++) {
         const int slot = j & 1;
         mbar_wait(&bar[B_SEMPTY + slot], ((j >> 1) & 1) ^ 1, abort_flag, p.status);
 #pragma unroll
         for (int h = 0; h < 2; h++) {
           mbar_wait(&bar[B_KTFULL + h], j & 1, abort_flag, p.status);
           tc_fence_after();
-          if (h == 0) TR(5, j);
 #pragma unroll
           for (int k8 = 0; k8 < 8; k8++) {
             const int kk = h * 8 + k8;
@@ -502,17 +502,15 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
           tc_commit(&bar[B_KTEMPTY + h]);
         }
         tc_commit(&bar[B_SFULL + slot]);
-        TR(6, j);
       }
     }
   } else {
     // ================================================================ issuer of O += P V
     if (lane == 0) {
-      for (int j = 0; j < nt; j++) {
+      _Pragma("unroll 1") for (int j = 0; j < nt && !*abort_flag; j++) {
         const int ns = min(2, nsub - 2 * j);
         mbar_wait(&bar[B_PTFULL], j & 1, abort_flag, p.status);
-        TR(7, j);
-        for (int s = 0; s < ns; s++) {
+        _Pragma("unroll 1") for (int s = 0; s < ns; s++) {
           mbar_wait(&bar[B_VFFULL + s], j & 1, abort_flag, p.status);
           tc_fence_after();
 #pragma unroll
@@ -524,12 +522,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
           tc_commit(&bar[B_VFEMPTY + s]);
         }
         tc_commit(&bar[B_PTEMPTY]);
-        TR(8, j);
       }
       tc_commit(&bar[B_ODONE]);
     }
   }
 
+  drain_after_abort(abort_flag);
   tc_fence_before();
   __syncthreads();
   if (warp == QK_WARP) {
@@ -556,7 +554,4 @@ int launch_decode_tc(const CUtensorMap* kv, const CUtensorMap* ks, const CUtenso
   return Q27B_OK;
 }
 
-#ifdef Q27B_TRACE
-extern "C" int q27b_trace_read(long long* dst) { return (int)cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace)); }
-#endif
 }  // namespace q27b

@@ -515,6 +515,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
     }
   }
 
+  drain_after_abort(abort_flag);
   tc_fence_before();
   __syncthreads();
   if (warp == MMA_WARP) {

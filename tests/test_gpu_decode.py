@@ -11,6 +11,14 @@ AD, GQA = 256, 6
 SCALE = 1.0 / 16.0
 
 
+@pytest.fixture(autouse=True, params=[1, 2], ids=["mma", "tc"])
+def decode_kernel(request, q27):
+    """Every test of this module runs on both split-K kernels (warp-MMA and tcgen05)."""
+    q27.set_decode_kernel(request.param)
+    yield request.param
+    q27.set_decode_kernel(0)
+
+
 def run_decode(q27, orc, T, nkvh, n, n_ctx=None, seed_shift=0, check=True, q8_1=False):
     from qwen27_engine_b200 import synth
     nqh = nkvh * GQA

@@ -11,6 +11,14 @@ AD, GQA, PAGE = 256, 6, 256
 SCALE = 1.0 / 16.0
 
 
+@pytest.fixture(autouse=True, params=[1, 2], ids=["mma", "tc"])
+def decode_kernel(request, q27):
+    """Every test of this module runs on both split-K kernels (warp-MMA and tcgen05)."""
+    q27.set_decode_kernel(request.param)
+    yield request.param
+    q27.set_decode_kernel(0)
+
+
 def build_pool(orc, kfs, nkvh, n_pages, tables):
     """Scatters each sequence's q8_0 rows into a pool [n_pages][nkvh][256] rows (+ scales)."""
     vals = np.full((n_pages, nkvh, PAGE, AD), 0x7F, np.uint8)
