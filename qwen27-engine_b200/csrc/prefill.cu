@@ -408,29 +408,40 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
       // V: 64 rows x 16 chunks of 16 int8 -> 16 f16 (one rounding of q * d, as src/attn.cu:59-76).
       // Item = (row, 16-dim chunk); eight neighbouring lanes take 4 chunks of rows rho and rho ^ 5,
       // which keeps both the swizzled 16-byte loads and the swizzled 16-byte stores conflict-free.
-#pragma unroll 2
-      for (int k = 0; k < 8; k++) {
-        const int item = ct + 128 * k;
-        const int row = (2 * (item >> 5)) ^ (5 * ((item >> 2) & 1));
-        const int c16 = (item & 3) + 4 * ((item >> 3) & 3);
-        const uint4 x = *(const uint4*)(vst + (c16 >> 3) * (PT * 128) + swz128(row, c16 & 7));
-        const __half d = *(const __half*)(vst + 2 * PT * 128 + row * 16 + (c16 >> 1) * 2);
-        const __half2 dd = __half2half2(d);
-        const uint32_t xw[4] = {x.x ^ 0x80808080u, x.y ^ 0x80808080u, x.z ^ 0x80808080u, x.w ^ 0x80808080u};
-        uint32_t o[8];
+#pragma unroll 1
+      for (int k0 = 0; k0 < 8; k0 += 4) {
+        // Loads of four items first: a shared-memory load cannot be moved above an earlier store, so
+        // load / convert / store per item would serialise the load latencies.
+        uint4 x[4];
+        __half d[4];
+        int row[4], c16[4];
 #pragma unroll
-        for (int w = 0; w < 4; w++) {
-          o[2 * w] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4140), dd);
-          o[2 * w + 1] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4342), dd);
+        for (int k = 0; k < 4; k++) {
+          const int item = ct + 128 * (k0 + k);
+          row[k] = (2 * (item >> 5)) ^ (5 * ((item >> 2) & 1));
+          c16[k] = (item & 3) + 4 * ((item >> 3) & 3);
+          x[k] = *(const uint4*)(vst + (c16[k] >> 3) * (PT * 128) + swz128(row[k], c16[k] & 7));
+          d[k] = *(const __half*)(vst + 2 * PT * 128 + row[k] * 16 + (c16[k] >> 1) * 2);
         }
-        if ((it0 + j) * PT + row >= n_end) {  // rows past the end may hold anything: P is 0 there, V must be too
 #pragma unroll
-          for (int w = 0; w < 8; w++) o[w] = 0;
+        for (int k = 0; k < 4; k++) {
+          const __half2 dd = __half2half2(d[k]);
+          const uint32_t xw[4] = {x[k].x ^ 0x80808080u, x[k].y ^ 0x80808080u, x[k].z ^ 0x80808080u, x[k].w ^ 0x80808080u};
+          uint32_t o[8];
+#pragma unroll
+          for (int w = 0; w < 4; w++) {
+            o[2 * w] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4140), dd);
+            o[2 * w + 1] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4342), dd);
+          }
+          if ((it0 + j) * PT + row[k] >= n_end) {  // rows past the end may hold anything: P is 0 there, V must be too
+#pragma unroll
+            for (int w = 0; w < 8; w++) o[w] = 0;
+          }
+          uint8_t* dst = vf + (c16[k] >> 2) * (PT * 128);
+          const uint32_t cc = 2 * (c16[k] & 3);
+          *(uint4*)(dst + swz128(row[k], cc)) = make_uint4(o[0], o[1], o[2], o[3]);
+          *(uint4*)(dst + swz128(row[k], cc + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
         }
-        uint8_t* dst = vf + (c16 >> 2) * (PT * 128);
-        const uint32_t cc = 2 * (c16 & 3);
-        *(uint4*)(dst + swz128(row, cc)) = make_uint4(o[0], o[1], o[2], o[3]);
-        *(uint4*)(dst + swz128(row, cc + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
       }
       // K scales f16 [64][8] -> f32 [8][64]
       {
