@@ -306,7 +306,7 @@ def main():
     kms = statistics.mean(a.elapsed_time(b) for a, b in zip(ev0, ev1))
     pk, pk_kind = peaks()
     ach = kv_bytes(NKVH, n) / (kms * 1e-3) / 1e9
-    line["roofline"] = {"bound": "hbm", "kernel": "decode_q8_kernel<3,false>", "achieved": ach, "peak": pk["hbm_gbs"],
+    line["roofline"] = {"bound": "hbm", "kernel": "decode_kernel<3,false,true> (q8_0, T=4)", "achieved": ach, "peak": pk["hbm_gbs"],
                         "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "peak_kind": pk_kind + " copy bandwidth (burst)",
                         "frac_of_8TBs_nominal": ach / 8000.0, "kernel_us": kms * 1e3,
                         "traffic": env_float("Q27B_NCU_TRAFFIC_BYTES")}
@@ -318,6 +318,9 @@ def main():
         line["cpu_baseline"] = cpu_baseline(n)
     if world > 1:
         line["strong"] = strong_scaling(q, dist, rank, world, n, steps, warmup)
+        del caches
+        torch.cuda.empty_cache()
+        line["batched_paged"] = batched_paged(q, rank, world, dist)
     if rank == 0 and world == 1 and not args.no_extras:
         line["extras"] = extras(q, caches, qn, qg, o, n_ctx)
     if rank == 0:
@@ -401,6 +404,56 @@ def strong_scaling(q, dist, rank, world, n, steps, warmup):
             "us_per_step": ms * 1e3, "value": kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong"}
 
 
+def batched_paged(q, rank, world, dist=None):
+    """Config 5: 64 sequences, 4 query tokens each, lengths ~U{1,024..131,072} (seed 1005), q8_0 KV in
+    256-token pages behind a random page table; sequences sharded over the ranks (greedy by length,
+    no exchange). The pool holds random int8 values and scales of the size q8_0 gives N(0,1) rows:
+    timing does not depend on the values. One step = one q27b_attn_decode_paged call per rank."""
+    from qwen27_engine_b200 import shard
+    PAGE, B_ALL = 256, 64
+    rng = np.random.default_rng(1005)
+    lengths = rng.integers(1024, 131072 + 1, size=B_ALL)
+    mine = shard.shard_sequences(lengths, world)[rank]
+    lens = [int(lengths[i]) for i in mine]
+    B = len(lens)
+    max_pages = (131072 + PAGE - 1) // PAGE
+    need = [(n + PAGE - 1) // PAGE for n in lens]
+    n_pages = sum(need)
+    perm = rng.permutation(n_pages).astype(np.int32)
+    table = np.full((B, max_pages), -1, np.int32)
+    at = 0
+    for b in range(B):
+        table[b, :need[b]] = perm[at:at + need[b]]
+        at += need[b]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1005 + rank)
+    nval = n_pages * NKVH * PAGE * AD
+    nsc = n_pages * NKVH * PAGE * 8
+
+    def pool():
+        buf = torch.empty(q.kv_pool_bytes(NKVH, n_pages), dtype=torch.uint8, device="cuda")
+        buf[:nval] = torch.randint(0, 256, (nval,), generator=g, device="cuda", dtype=torch.uint8)
+        sc = (torch.rand((nsc,), generator=g, device="cuda") * 0.01 + 0.02).to(torch.float16)
+        buf[nval:nval + 2 * nsc] = sc.view(torch.uint8)
+        return buf
+    kpool, vpool = pool(), pool()
+    qn = torch.randn((B, T, NQH, AD), generator=g, device="cuda")
+    qg = torch.randn((B, T, NQH, 512), generator=g, device="cuda")
+    o = torch.empty((B, T, NQH, AD), device="cuda")
+    d_table = torch.from_numpy(table).cuda()
+    d_len = torch.tensor(lens, dtype=torch.int32, device="cuda")
+
+    def step(i):
+        q.attn_decode_paged(qn, qg, kpool, vpool, d_table, d_len, o, B, T, SCALE, NQH, NKVH, n_pages, max_pages, max(lens))
+    ms = time_steps(step, 10, 3, dist)
+    assert q.device_status() == 0, "a kernel reported a device-side problem"
+    total = float(sum(2.0 * NKVH * int(n) * 272 for n in lengths))
+    return {"what": "64 sequences x 4 query tokens, lengths U{1024..131072} (seed 1005), 256-token pages, random page "
+                    "table; %d sequence(s) on rank 0 of %d" % (B, world),
+            "positions_total": int(lengths.sum()), "kv_bytes_total": total, "ms_per_step": ms,
+            "value": total / (ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong (sequences sharded by KV length)"}
+
+
 def extras(q, caches, qn, qg, o, n_ctx):
     """Other depths of the metric, the prefill TOPS, the batched paged decode and the reference's kernels."""
     out = {"decode_us": {}, "prefill": {}}
@@ -443,6 +496,10 @@ def extras(q, caches, qn, qg, o, n_ctx):
         except Exception as e:  # report, do not hide
             out["prefill"][str(P)] = {"error": str(e)}
     out["device_status"] = q.device_status()
+    try:
+        out["batched_paged"] = batched_paged(q, 0, 1)
+    except Exception as e:  # report, do not hide
+        out["batched_paged"] = {"error": str(e)}
     try:
         ref = RefLib()
         pos.fill_(N_POS - T)
