@@ -78,8 +78,10 @@ enum {
 };
 
 constexpr int N_SOFTMAX_WARPS = 8;
-constexpr int CONV_WARP0 = 8, TMA_WARP = 12, MMA_WARP = 13;
-constexpr int PF_THREADS = 14 * 32;
+constexpr int N_CONV_WARPS = 4;   // measured: 2 converter warps (and 162 registers for the softmax warps) lose 8 %
+constexpr int N_CONV_THREADS = N_CONV_WARPS * 32;
+constexpr int CONV_WARP0 = 8, TMA_WARP = CONV_WARP0 + N_CONV_WARPS, MMA_WARP = TMA_WARP + 1;
+constexpr int PF_THREADS = (MMA_WARP + 1) * 32;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_O = 0, TM_S = 256;
 constexpr uint32_t IDESC_QK = umma_idesc(2, 1, 1, 0, 0, QT, PT);    // s32 += s8 * s8, both K-major, M128 N64
@@ -186,10 +188,10 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
     mbar_init(&bar[B_QFULL], N_SOFTMAX_WARPS);
     for (int s = 0; s < 2; s++) {
       mbar_init(&bar[B_KFULL + s], 1);
-      mbar_init(&bar[B_KEMPTY + s], 5);
+      mbar_init(&bar[B_KEMPTY + s], N_CONV_WARPS + 1);
       mbar_init(&bar[B_VFULL + s], 1);
-      mbar_init(&bar[B_VEMPTY + s], 4);
-      mbar_init(&bar[B_VFFULL + s], 4);
+      mbar_init(&bar[B_VEMPTY + s], N_CONV_WARPS);
+      mbar_init(&bar[B_VFFULL + s], N_CONV_WARPS);
       mbar_init(&bar[B_VFEMPTY + s], 1);
       mbar_init(&bar[B_DKEMPTY + s], N_SOFTMAX_WARPS);
       mbar_init(&bar[B_PFULL + s], N_SOFTMAX_WARPS);
@@ -241,7 +243,6 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
     const int col0 = wg * 32;          // this thread's positions of a tile: col0 .. col0+31
     float m_run = M_INIT, m_ref = M_INIT;
     uint64_t l2 = pack2(0.f, 0.f);
-    const uint64_t negc = pack2(-12582912.0f, -12582912.0f);
     const uint64_t log2e2 = pack2(LOG2E, LOG2E);
 
     for (int j = 0; j < nt; j++) {
@@ -268,9 +269,9 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           const ulonglong2 dk = dk2[i];  // K scales of positions 4i .. 4i+3 (block b)
-          // exact int -> float: as_float(v + 0x4B400000) = 12582912 + v, then subtract
-          const uint64_t f0 = add2(pack2(__int_as_float((int)v[4 * i] + 0x4B400000), __int_as_float((int)v[4 * i + 1] + 0x4B400000)), negc);
-          const uint64_t f1 = add2(pack2(__int_as_float((int)v[4 * i + 2] + 0x4B400000), __int_as_float((int)v[4 * i + 3] + 0x4B400000)), negc);
+          // int32 -> f32 is exact here (|sum| <= 32 * 127 * 127 < 2^24)
+          const uint64_t f0 = pack2(__int2float_rn((int)v[4 * i]), __int2float_rn((int)v[4 * i + 1]));
+          const uint64_t f1 = pack2(__int2float_rn((int)v[4 * i + 2]), __int2float_rn((int)v[4 * i + 3]));
           s2[2 * i] = fma2(mul2(dqb, dk.x), f0, s2[2 * i]);
           s2[2 * i + 1] = fma2(mul2(dqb, dk.y), f1, s2[2 * i + 1]);
         }
@@ -409,7 +410,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
       // Item = (row, 16-dim chunk); eight neighbouring lanes take 4 chunks of rows rho and rho ^ 5,
       // which keeps both the swizzled 16-byte loads and the swizzled 16-byte stores conflict-free.
 #pragma unroll 1
-      for (int k0 = 0; k0 < 8; k0 += 4) {
+      for (int k0 = 0; k0 < 1024 / N_CONV_THREADS; k0 += 4) {
         // Loads of four items first: a shared-memory load cannot be moved above an earlier store, so
         // load / convert / store per item would serialise the load latencies.
         uint4 x[4];
@@ -417,7 +418,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
         int row[4], c16[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-          const int item = ct + 128 * (k0 + k);
+          const int item = ct + N_CONV_THREADS * (k0 + k);
           row[k] = (2 * (item >> 5)) ^ (5 * ((item >> 2) & 1));
           c16[k] = (item & 3) + 4 * ((item >> 3) & 3);
           x[k] = *(const uint4*)(vst + (c16[k] >> 3) * (PT * 128) + swz128(row[k], c16[k] & 7));
@@ -446,13 +447,16 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
       // K scales f16 [64][8] -> f32 [8][64]
       {
         float* dkf = (float*)(sgen + OFF_DKF + pb * DKF_BYTES);
-        const int row = ct >> 1, b0 = (ct & 1) * 4;
-        const uint2 sc = *(const uint2*)(kst + 2 * PT * 128 + row * 16 + b0 * 2);
-        const __half2 s01 = u32_as_h2(sc.x), s23 = u32_as_h2(sc.y);
-        dkf[(b0 + 0) * PT + row] = __low2float(s01);
-        dkf[(b0 + 1) * PT + row] = __high2float(s01);
-        dkf[(b0 + 2) * PT + row] = __low2float(s23);
-        dkf[(b0 + 3) * PT + row] = __high2float(s23);
+#pragma unroll
+        for (int u = ct; u < 128; u += N_CONV_THREADS) {
+          const int row = u >> 1, b0 = (u & 1) * 4;
+          const uint2 sc = *(const uint2*)(kst + 2 * PT * 128 + row * 16 + b0 * 2);
+          const __half2 s01 = u32_as_h2(sc.x), s23 = u32_as_h2(sc.y);
+          dkf[(b0 + 0) * PT + row] = __low2float(s01);
+          dkf[(b0 + 1) * PT + row] = __high2float(s01);
+          dkf[(b0 + 2) * PT + row] = __low2float(s23);
+          dkf[(b0 + 3) * PT + row] = __high2float(s23);
+        }
       }
       fence_proxy_async();
       __syncwarp();
