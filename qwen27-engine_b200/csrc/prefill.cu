@@ -51,7 +51,7 @@ constexpr int OFF_P = OFF_VF + 2 * VF_BYTES;
 constexpr int OFF_DKF = OFF_P + 2 * P_BYTES;
 constexpr int OFF_DQ = OFF_DKF + 2 * DKF_BYTES;     // f32 Q scales [128 rows][8]
 constexpr int OFF_XCH = OFF_DQ + QT * 8 * 4;        // row exchange between the two softmax warpgroups [tile parity][2][128] f32
-constexpr int OFF_BAR = OFF_XCH + 2 * 2 * QT * 4;
+constexpr int OFF_BAR = OFF_XCH + 2 * 4 * QT * 4;   // room for four warpgroups
 constexpr int NBAR = 32;
 constexpr int OFF_MISC = OFF_BAR + NBAR * 8;        // tmem base address, abort flag
 constexpr int PF_SMEM_USED = OFF_MISC + 16;
@@ -77,10 +77,16 @@ enum {
   B_ODONE = 27,
 };
 
-constexpr int N_SOFTMAX_WARPS = 8;
+#ifndef Q27B_PF_NWG
+#define Q27B_PF_NWG 2
+#endif
+constexpr int NWG = Q27B_PF_NWG;               // softmax warpgroups: each takes PT / NWG columns of a tile
+constexpr int WCOLS = PT / NWG;                // columns per softmax thread
+constexpr int OCOLS = AD / NWG;                // columns of O per softmax thread (rescale, epilogue)
+constexpr int N_SOFTMAX_WARPS = 4 * NWG;
 constexpr int N_CONV_WARPS = 4;   // measured: 2 converter warps (and 162 registers for the softmax warps) lose 8 %
 constexpr int N_CONV_THREADS = N_CONV_WARPS * 32;
-constexpr int CONV_WARP0 = 8, TMA_WARP = CONV_WARP0 + N_CONV_WARPS, MMA_WARP = TMA_WARP + 1;
+constexpr int CONV_WARP0 = N_SOFTMAX_WARPS, TMA_WARP = CONV_WARP0 + N_CONV_WARPS, MMA_WARP = TMA_WARP + 1;
 constexpr int PF_THREADS = (MMA_WARP + 1) * 32;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_O = 0, TM_S = 256;
@@ -98,7 +104,8 @@ struct PrefillParams {
   float kq_scale;
 };
 
-__device__ __forceinline__ void pair_sync(int q) { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); }
+// Barrier of the NWG threads' warps that share query rows 32q .. 32q+31.
+__device__ __forceinline__ void pair_sync(int q) { asm volatile("bar.sync %0, %1;" ::"r"(1 + q), "n"(32 * NWG) : "memory"); }
 
 // Quantises blocks [B0, B0 + NB) of one query row (256 floats at src, or zeros when src is null)
 // to int8 with an f32 scale per 32 dims (src/attn.cu:587-606: v = q * kq_scale, d = amax / 127,
@@ -223,12 +230,21 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
     float* xch = (float*)(sgen + OFF_XCH);
     float dq[8];
     {
-      // this thread quantises blocks 4wg .. 4wg+3 of its row; the scales go through shared memory
-      float dqh[4];
+      // this thread quantises 8 / NWG blocks of its row; the scales go through shared memory
+      constexpr int NB = 8 / NWG;
+      float dqh[NB];
       const float* src = live ? p.qn + ((size_t)t * p.nqh + h) * AD : nullptr;
-      if (wg == 0) quantise_q_row<0, 4>(src, p.kq_scale, sgen + OFF_Q, r, dqh);
-      else quantise_q_row<4, 4>(src, p.kq_scale, sgen + OFF_Q, r, dqh);
-      *(float4*)(sgen + OFF_DQ + (r * 8 + 4 * wg) * 4) = make_float4(dqh[0], dqh[1], dqh[2], dqh[3]);
+      if (NWG == 2) {
+        if (wg == 0) quantise_q_row<0, NB>(src, p.kq_scale, sgen + OFF_Q, r, dqh);
+        else quantise_q_row<NB, NB>(src, p.kq_scale, sgen + OFF_Q, r, dqh);
+      } else {
+        if (wg == 0) quantise_q_row<0, NB>(src, p.kq_scale, sgen + OFF_Q, r, dqh);
+        else if (wg == 1) quantise_q_row<NB, NB>(src, p.kq_scale, sgen + OFF_Q, r, dqh);
+        else if (wg == 2) quantise_q_row<(2 * NB) % 8, NB>(src, p.kq_scale, sgen + OFF_Q, r, dqh);
+        else quantise_q_row<(3 * NB) % 8, NB>(src, p.kq_scale, sgen + OFF_Q, r, dqh);
+      }
+#pragma unroll
+      for (int i = 0; i < NB; i++) *(float*)(sgen + OFF_DQ + (r * 8 + NB * wg + i) * 4) = dqh[i];
       fence_proxy_async();
       pair_sync(q);
       const float4 a = *(const float4*)(sgen + OFF_DQ + r * 32), b = *(const float4*)(sgen + OFF_DQ + r * 32 + 16);
@@ -240,26 +256,27 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
 
     const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
     const int limit = pos0 + t + 1;    // positions < limit are visible
-    const int col0 = wg * 32;          // this thread's positions of a tile: col0 .. col0+31
+    const int col0 = wg * WCOLS;       // this thread's positions of a tile: col0 .. col0 + WCOLS - 1
     float m_run = M_INIT, m_ref = M_INIT;
     uint64_t l2 = pack2(0.f, 0.f);
     const uint64_t log2e2 = pack2(LOG2E, LOG2E);
 
+#pragma unroll 1
     for (int j = 0; j < nt; j++) {
       const int pb = j & 1, ph = (j >> 1) & 1;
       const int p_tile = (it0 + j) * PT;
       mbar_wait(&bar[B_VFFULL + pb], ph, abort_flag, p.status);  // K scale table of this tile is ready
       const uint8_t* dkf = sgen + OFF_DKF + pb * DKF_BYTES;
-      uint64_t s2[16];
+      uint64_t s2[WCOLS / 2];
 #pragma unroll
-      for (int i = 0; i < 16; i++) s2[i] = pack2(0.f, 0.f);
+      for (int i = 0; i < WCOLS / 2; i++) s2[i] = pack2(0.f, 0.f);
 #pragma unroll
       for (int b = 0; b < 8; b++) {
         const int slot = b & 3;
         mbar_wait(&bar[B_SFULL + slot], (b >> 2) & 1, abort_flag, p.status);
         tc_fence_after();
-        uint32_t v[32];
-        tmem_ld32(tlane + TM_S + slot * PT + col0, v);
+        uint32_t v[WCOLS];
+        tmem_ld(tlane + TM_S + slot * PT + col0, v);
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
@@ -267,7 +284,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
         const ulonglong2* dk2 = (const ulonglong2*)(dkf + (b * PT + col0) * 4);
         const uint64_t dqb = pack2(dq[b], dq[b]);
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
+        for (int i = 0; i < WCOLS / 4; i++) {
           const ulonglong2 dk = dk2[i];  // K scales of positions 4i .. 4i+3 (block b)
           // int32 -> f32 is exact here (|sum| <= 32 * 127 * 127 < 2^24)
           const uint64_t f0 = pack2(__int2float_rn((int)v[4 * i]), __int2float_rn((int)v[4 * i + 1]));
@@ -279,31 +296,31 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[B_DKEMPTY + pb]);
 
-      // causal mask (only tiles that reach past the first row's limit need it) and the half-tile max
-      float s[32];
+      // causal mask (only tiles that reach past the first row's limit need it) and this thread's max
+      float s[WCOLS];
 #pragma unroll
-      for (int i = 0; i < 16; i++) unpack2(s2[i], s[2 * i], s[2 * i + 1]);
+      for (int i = 0; i < WCOLS / 2; i++) unpack2(s2[i], s[2 * i], s[2 * i + 1]);
       float mt = -INFINITY;
       if (p_tile + PT > pos0 + t0 + 1) {
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
+        for (int i = 0; i < WCOLS; i++) {
           if (p_tile + col0 + i >= limit) s[i] = -INFINITY;
           mt = fmaxf(mt, s[i]);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; i++) mt = fmaxf(mt, s[i]);
+        for (int i = 0; i < WCOLS; i++) mt = fmaxf(mt, s[i]);
       }
-      // row maximum over both halves: exchange with the partner thread (warp w <-> w + 4); the
-      // buffer alternates with the tile so that a fast thread cannot overwrite what its partner
-      // has not read yet
-      xch[(pb * 2 + wg) * QT + r] = mt;
+      // row maximum over the NWG threads of the row; the buffer alternates with the tile so that a
+      // fast thread cannot overwrite what a partner has not read yet
+      xch[(pb * NWG + wg) * QT + r] = mt;
       pair_sync(q);
-      mt = fmaxf(mt, xch[(pb * 2 + (wg ^ 1)) * QT + r]);
+#pragma unroll
+      for (int o = 1; o < NWG; o++) mt = fmaxf(mt, xch[(pb * NWG + ((wg + o) % NWG)) * QT + r]);
       m_run = fmaxf(m_run, mt);
 
-      // Move the reference max when the true max has run away from it (and on the first tile). Both
-      // threads of a row hold the same m_run and m_ref, so both warps of a pair take the same branch.
+      // Move the reference max when the true max has run away from it (and on the first tile). All
+      // threads of a row hold the same m_run and m_ref, so all their warps take the same branch.
       const bool want = m_run > m_ref + TAU;
       if (__any_sync(0xffffffffu, want)) {
         const float f = ex2((m_ref - m_run) * LOG2E);  // 0 on the first move (m_ref = -1e30)
@@ -311,30 +328,30 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
         l2 = mul2(l2, pack2(f, f));
         if (j > 0) {
           // O holds the sum of tiles < j once the P V of tile j-1 has completed. This warp rescales
-          // columns 128wg .. 128wg+127 of its 32 rows.
+          // columns OCOLS wg .. OCOLS wg + OCOLS - 1 of its 32 rows.
           mbar_wait(&bar[B_PEMPTY + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag, p.status);
           tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < 4; c++) {
+          for (int c = 0; c < OCOLS / 32; c++) {
             uint32_t v[32];
-            tmem_ld32(tlane + TM_O + wg * 128 + c * 32, v);
+            tmem_ld32(tlane + TM_O + wg * OCOLS + c * 32, v);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-            tmem_st32(tlane + TM_O + wg * 128 + c * 32, v);
+            tmem_st32(tlane + TM_O + wg * OCOLS + c * 32, v);
           }
           tc_wait_st();
           tc_fence_before();
         }
       }
 
-      // P = exp(s - m_ref): f32 row sum, f16 half-tile for the P V MMA (chunks 4wg .. 4wg+3 of the row)
+      // P = exp(s - m_ref): f32 row sum, f16 part of the tile for the P V MMA (WCOLS / 8 chunks of the row)
       mbar_wait(&bar[B_PEMPTY + pb], ph ^ 1, abort_flag, p.status);
       uint8_t* sP = sgen + OFF_P + pb * P_BYTES;
       const float nmb = -m_ref * LOG2E;
       const uint64_t nmb2 = pack2(nmb, nmb);
 #pragma unroll
-      for (int c = 0; c < 4; c++) {
+      for (int c = 0; c < WCOLS / 8; c++) {
         uint32_t w[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
@@ -344,7 +361,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
           l2 = add2(l2, pack2(e0, e1));
           w[k] = pack_h2(e0, e1);
         }
-        *(uint4*)(sP + swz128(r, 4 * wg + c)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *(uint4*)(sP + swz128(r, (WCOLS / 8) * wg + c)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
       fence_proxy_async();
       __syncwarp();
@@ -352,13 +369,14 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
     }
 
     // ---- epilogue: O / l * sigmoid(gate), or the unnormalised partial of this split; this thread
-    // writes columns 128wg .. 128wg+127 of its row
+    // writes columns OCOLS wg .. OCOLS wg + OCOLS - 1 of its row
     float la, lb;
     unpack2(l2, la, lb);
     float l = la + lb;
-    xch[((nt & 1) * 2 + wg) * QT + r] = l;
+    xch[((nt & 1) * NWG + wg) * QT + r] = l;
     pair_sync(q);
-    l += xch[((nt & 1) * 2 + (wg ^ 1)) * QT + r];
+#pragma unroll
+    for (int o = 1; o < NWG; o++) l += xch[((nt & 1) * NWG + ((wg + o) % NWG)) * QT + r];
     mbar_wait(&bar[B_ODONE], 0, abort_flag, p.status);
     tc_fence_after();
     const float inv_l = 1.0f / l;
@@ -368,8 +386,8 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
       po[1] = l;
     }
 #pragma unroll 1
-    for (int c = 0; c < 4; c++) {
-      const int d0 = wg * 128 + c * 32;
+    for (int c = 0; c < OCOLS / 32; c++) {
+      const int d0 = wg * OCOLS + c * 32;
       uint32_t v[32];
       tmem_ld32(tlane + TM_O + d0, v);
       tc_wait_ld();
