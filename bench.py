@@ -336,8 +336,9 @@ def env_float(name):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel at the bench
-# workload, from the ncu capture summarised under profiles/ (None until a capture exists).
-NCU_TRAFFIC_BYTES = None
+# workload, from the ncu capture summarised under profiles/ (captured at 60,000 positions and scaled:
+# the reads grow in proportion to the positions, the writes are the partials and do not).
+NCU_TRAFFIC_BYTES = 333.5e6  # 130.82 MB read at 60,000 positions scaled by 2.5, plus 6.46 MB written (profiles/decode_q8_60k.md)
 
 
 def e2e(q, caches, n, n_ctx, steps, warmup, dist, world):
