@@ -344,32 +344,32 @@ NCU_TRAFFIC_BYTES = 333.5e6  # 130.82 MB read at 60,000 positions scaled by 2.5,
 def e2e(q, caches, n, n_ctx, steps, warmup, dist, world):
     """Host buffers in, host buffer out, every step: query + gate + the 4 new K/V rows from pinned
     memory, KV append at the tail of the cache, decode, result back to pinned memory."""
-    h_qn = torch.randn((T, NQH, AD)).pin_memory()
-    h_qg = torch.randn((T, NQH, 512)).pin_memory()
-    h_k = torch.randn((T, NKVH, AD)).pin_memory()
-    h_v = torch.randn((T, NKVH, AD)).pin_memory()
+    # one pinned staging buffer and one device buffer for all inputs of a step: a single H2D copy
+    sizes = [T * NQH * AD, T * NQH * 512, T * NKVH * AD, T * NKVH * AD]
+    h_in = torch.randn((sum(sizes),)).pin_memory()
+    d_in = torch.empty((sum(sizes),), device="cuda")
+    offs = [0, sizes[0], sizes[0] + sizes[1], sizes[0] + sizes[1] + sizes[2]]
+    d_qn = d_in[offs[0]:offs[0] + sizes[0]].view(T, NQH, AD)
+    d_qg = d_in[offs[1]:offs[1] + sizes[1]].view(T, NQH, 512)
+    d_k = d_in[offs[2]:offs[2] + sizes[2]].view(T, NKVH, AD)
+    d_v = d_in[offs[3]:offs[3] + sizes[3]].view(T, NKVH, AD)
     h_o = torch.empty((T, NQH, AD)).pin_memory()
-    d_qn, d_qg = torch.empty_like(h_qn, device="cuda"), torch.empty_like(h_qg, device="cuda")
-    d_k, d_v = torch.empty_like(h_k, device="cuda"), torch.empty_like(h_v, device="cuda")
     d_o = torch.empty((T, NQH, AD), device="cuda")
     pos = torch.tensor([n - T], dtype=torch.int32, device="cuda")
 
     def step(i):
         kc, vc = caches[i % NBUF]
-        d_qn.copy_(h_qn, non_blocking=True)
-        d_qg.copy_(h_qg, non_blocking=True)
-        d_k.copy_(h_k, non_blocking=True)
-        d_v.copy_(h_v, non_blocking=True)
+        d_in.copy_(h_in, non_blocking=True)
         q.kv_append(d_k, d_v, kc, vc, pos, T, NKVH, n_ctx)
         q.attn_decode(d_qn, d_qg, kc, vc, d_o, None, None, pos, T, SCALE, NQH, NKVH, n_ctx)
         h_o.copy_(d_o, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the result before the next step
 
     ms = time_steps(step, steps, warmup, dist)
-    h2d = (h_qn.numel() + h_qg.numel() + h_k.numel() + h_v.numel()) * 4
+    h2d = h_in.numel() * 4
     return {"value": world * kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": h_o.numel() * 4,
-            "what": "pinned host q/gate/new K,V rows -> device, kv_append, attn_decode, result -> pinned host, sync"}
+            "what": "pinned host q/gate/new K,V rows -> device (one copy), kv_append, attn_decode, result -> pinned host, sync"}
 
 
 def strong_scaling(q, dist, rank, world, n, steps, warmup):
