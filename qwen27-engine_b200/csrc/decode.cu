@@ -632,11 +632,12 @@ int launch_decode_t(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensor
 
 // Which split-K kernel serves a q8_0 cache: the warp-MMA kernel of this file unless
 // Q27B_DECODE_KERNEL=tc or q27b_set_decode_kernel(2) asks for the tcgen05 kernel (decode_tc.cu).
-// Measured on B200 (same call, CUDA-graph timing): the tcgen05 kernel reaches 73.7 us against
-// 77.7 us at 150k positions in its best builds, but its speed moves by up to 10 % with small changes
-// of its code (it runs eight differently specialised warp roles per SM and is sensitive to
-// instruction-cache layout), and it starts 1.4 us later (13.2 us against 11.7 us at 64 positions).
-// The warp-MMA kernel is stable at 76.7 us, so it stays the default. f16 caches always use it.
+// Measured on B200 (same call, CUDA-graph timing, 150k positions): builds of the tcgen05 kernel that
+// differ only in immaterial details (an extra loop condition, a helper moved out of line) ran at
+// 73.7, 75.7 and 80.8 us; the warp-MMA kernel stays within 76.5-77.7 us. The tcgen05 kernel runs eight
+// differently specialised warp roles per SM with a serial hand-off chain between them and is that
+// sensitive to code layout; it also starts 1.5 us later (13.2 us against 11.7 us at 64 positions).
+// So the warp-MMA kernel is the default. f16 caches always use it.
 int g_kernel_choice = -1;  // -1: not read yet; 0 default, 1 warp-MMA, 2 tcgen05
 bool use_tc_kernel() {
   if (g_kernel_choice < 0) {
