@@ -152,6 +152,21 @@ __device__ __forceinline__ void quantise_q_row(const float* src, float kq_scale,
   }
 }
 
+// Multiplies OCOLS accumulator columns of this warp's 32 TMEM lanes by f. Rare (the reference max
+// of a row moves a few times per call), and deliberately not inlined: inlined, its 32 registers of
+// payload sit on top of the live state of the hot loop and push that loop into spills.
+__device__ __noinline__ void rescale_o(uint32_t taddr, float f) {
+#pragma unroll 1
+  for (int c = 0; c < OCOLS / 32; c++) {
+    uint32_t v[32];
+    tmem_ld32(taddr + c * 32, v);
+    tc_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+    tmem_st32(taddr + c * 32, v);
+  }
+}
+
 // Descriptors of the 32-byte k-block b of a K-major 128B-swizzled int8 tile made of two halves
 // of `rows` rows x 128 B.
 __device__ __forceinline__ uint64_t desc_kblock(uint32_t tile_addr, int rows, int b) {
@@ -344,15 +359,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
           // columns OCOLS wg .. OCOLS wg + OCOLS - 1 of its 32 rows.
           mbar_wait(&bar[B_PEMPTY + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag, p.status);
           tc_fence_after();
-#pragma unroll 1
-          for (int c = 0; c < OCOLS / 32; c++) {
-            uint32_t v[32];
-            tmem_ld32(tlane + TM_O + wg * OCOLS + c * 32, v);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-            tmem_st32(tlane + TM_O + wg * OCOLS + c * 32, v);
-          }
+          rescale_o(tlane + TM_O + wg * OCOLS, f);
           tc_wait_st();
           tc_fence_before();
         }
