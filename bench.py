@@ -365,11 +365,37 @@ def e2e(q, caches, n, n_ctx, steps, warmup, dist, world):
         h_o.copy_(d_o, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the result before the next step
 
-    ms = time_steps(step, steps, warmup, dist)
+    ms_eager = time_steps(step, steps, warmup, dist)
+
+    # The same step the way the reference's engine issues a decode step: captured once in a CUDA graph
+    # (src/model.cu:910-955), one graph per cache of the rotation; a step is one replay plus the
+    # synchronise before the host reads the result. The copies are memcpy nodes of the graph.
+    def body(i):
+        kc, vc = caches[i % NBUF]
+        d_in.copy_(h_in, non_blocking=True)
+        q.kv_append(d_k, d_v, kc, vc, pos, T, NKVH, n_ctx)
+        q.attn_decode(d_qn, d_qg, kc, vc, d_o, None, None, pos, T, SCALE, NQH, NKVH, n_ctx)
+        h_o.copy_(d_o, non_blocking=True)
+    graphs = []
+    for i in range(NBUF):
+        body(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            body(i)
+        graphs.append(g)
+
+    def gstep(i):
+        graphs[i % NBUF].replay()
+        torch.cuda.current_stream().synchronize()
+    ms = time_steps(gstep, steps, warmup, dist)
     h2d = h_in.numel() * 4
     return {"value": world * kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": h_o.numel() * 4,
-            "what": "pinned host q/gate/new K,V rows -> device (one copy), kv_append, attn_decode, result -> pinned host, sync"}
+            "eager_ms_per_step": ms_eager, "eager_value": world * kv_bytes(NKVH, n) / (ms_eager * 1e-3) / 1e9,
+            "what": "every step: pinned host q/gate/new K,V rows -> device (one copy), kv_append, attn_decode, result -> "
+                    "pinned host, synchronise; the step is captured in a CUDA graph as the reference's engine does "
+                    "(value), and also issued call by call (eager_*)"}
 
 
 def strong_scaling(q, dist, rank, world, n, steps, warmup):
