@@ -143,6 +143,12 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
  * has one kernel). */
 int q27b_set_decode_kernel(int which);
 
+/* Test hook for the failure path, no counterpart in the reference: launches one warp that waits on
+ * a barrier nobody arrives at, with the bounded wait every kernel of this library uses. After the
+ * limit (about two seconds) the wait gives up, the kernel returns normally and
+ * q27b_device_status reports bit 0 (wait expired); the context stays usable. */
+int q27b_debug_expire_wait(void* stream);
+
 /* Measurement hook, no counterpart in the reference: while `event` (a cudaEvent_t) is set, every
  * q27b_attn_decode / q27b_attn_decode_partial call on the current device records it on the
  * caller's stream between its split-K kernel and its merge kernel, so that a benchmark can time

@@ -28,7 +28,7 @@ OK, BAD_SHAPE, CUDA_ERROR, UNSUPPORTED, DEVICE_STATUS = 0, 1, 2, 3, 4
 SYMBOLS = [
     "q27b_last_error", "q27b_device_status", "q27b_kv_cache_bytes", "q27b_attn_chunks", "q27b_kv_append",
     "q27b_attn_prep", "q27b_attn_decode", "q27b_attn_decode_partial", "q27b_lse_merge", "q27b_attn_decode_paged",
-    "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_set_decode_kernel",
+    "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_set_decode_kernel", "q27b_debug_expire_wait",
     "q27b_attn_decode_noalloc",
 ]
 
@@ -99,6 +99,11 @@ def device_status():
     if rc not in (OK, DEVICE_STATUS):
         _check(rc)
     return st.value
+
+
+def debug_expire_wait():
+    """Test hook: one warp waits on a barrier nobody arrives at; the bounded wait gives up (status bit 0)."""
+    _check(_lib.q27b_debug_expire_wait(_stream()))
 
 
 def set_decode_kernel(which):

@@ -1,6 +1,8 @@
 // Host-side state and the entry points that launch nothing.
 #include "host.h"
 
+#include "common.cuh"
+
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
@@ -111,6 +113,30 @@ int q27b_device_status(int* status_out) {
   if (st) Q27B_CK(cudaMemset(ctx->status, 0, sizeof(int)));
   if (status_out) *status_out = st;
   return st ? fail(Q27B_DEVICE_STATUS, "device status word = " + std::to_string(st)) : Q27B_OK;
+}
+
+// One CTA, one warp: waits on an mbarrier that nobody arrives at, with the same bounded wait the
+// attention kernels use. The wait gives up after its limit, records ST_WAIT_EXPIRED and the kernel
+// returns normally: what a lost signal looks like to the host, without a hang and without a trap.
+__global__ void expire_wait_kernel(int* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    q27b::mbar_init(&bar, 1);
+    abort_flag = 0;
+    q27b::mbar_fence_init();
+  }
+  __syncthreads();
+  q27b::mbar_wait(&bar, 0, &abort_flag, status);
+  q27b::drain_after_abort(&abort_flag);
+}
+
+int q27b_debug_expire_wait(void* stream) {
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  expire_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ctx->status);
+  Q27B_CK(cudaGetLastError());
+  return Q27B_OK;
 }
 
 uint64_t q27b_kv_cache_bytes(int nkvh, int n_ctx, int q8) {
