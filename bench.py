@@ -481,6 +481,28 @@ def batched_paged(q, rank, world, dist=None):
             "value": total / (ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong (sequences sharded by KV length)"}
 
 
+def kv_wire_bench(q):
+    """Rows of one 131,072-position sequence (4 KV heads) from the page pool into the reference's host
+    layout on the device and back (q27b_kv_pages_to_wire / q27b_kv_wire_to_pages): a copy kernel,
+    272 B read + 272 B written per (head, position)."""
+    PAGE, n = 256, 131072
+    need = n // PAGE
+    n_pages = need + 8
+    g = torch.Generator(device="cuda")
+    g.manual_seed(7)
+    pool = torch.randint(0, 256, (q.kv_pool_bytes(NKVH, n_pages),), generator=g, device="cuda", dtype=torch.uint8)
+    table = torch.randperm(n_pages, generator=g, device="cuda")[:need].to(torch.int32)
+    wire = torch.empty(q.kv_wire_bytes(NKVH, n), dtype=torch.uint8, device="cuda")
+    moved = 2.0 * NKVH * n * 272
+    us_out = graph_us(lambda i: q.kv_pages_to_wire(pool, table, wire, NKVH, n_pages, 0, n))
+    us_in = graph_us(lambda i: q.kv_wire_to_pages(pool, table, wire, NKVH, n_pages, 0, n))
+    pk, _ = peaks()
+    return {"what": "131,072 positions x 4 KV heads, q8_0, page pool <-> reference host layout (device side)",
+            "bytes_moved": moved, "pages_to_wire_us": us_out, "wire_to_pages_us": us_in,
+            "pages_to_wire_gbs": moved / (us_out * 1e-6) / 1e9, "wire_to_pages_gbs": moved / (us_in * 1e-6) / 1e9,
+            "frac_of_measured_copy_peak": moved / (us_out * 1e-6) / 1e9 / pk["hbm_gbs"]}
+
+
 def extras(q, caches, qn, qg, o, n_ctx):
     """Other depths of the metric, the prefill TOPS, the batched paged decode and the reference's kernels."""
     out = {"decode_us": {}, "prefill": {}}
@@ -527,6 +549,10 @@ def extras(q, caches, qn, qg, o, n_ctx):
         out["batched_paged"] = batched_paged(q, 0, 1)
     except Exception as e:  # report, do not hide
         out["batched_paged"] = {"error": str(e)}
+    try:
+        out["kv_wire"] = kv_wire_bench(q)
+    except Exception as e:  # report, do not hide
+        out["kv_wire"] = {"error": str(e)}
     try:
         ref = RefLib()
         pos.fill_(N_POS - T)

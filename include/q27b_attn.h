@@ -155,6 +155,23 @@ int q27b_debug_expire_wait(void* stream);
  * the dominant kernel alone with CUDA events. NULL switches it off. */
 int q27b_debug_split_event(void* event);
 
+/* The reference's host ("wire") layout of rows [p0, p1) of one cache, used for its RAM swap of idle
+ * slots and its prompt-cache checkpoints (Decoder::kv_copy, src/model.cu:1809-1830): the values
+ * [nkvh][p1-p0][256 B], then the scales [nkvh][p1-p0][16 B]; q27b_kv_wire_bytes gives its size
+ * (q8_0 caches only). The four functions pack such a buffer on the device from, and unpack it into,
+ * the page pool of one sequence (`pages` = its page table row on the device, as in
+ * q27b_attn_decode_paged) or a contiguous cache [nkvh][n_ctx]; one contiguous copy between `wire`
+ * and pinned host memory completes the transfer. With them a slot written by a paged engine can be
+ * restored into the reference's contiguous cache and the other way round. A page index outside
+ * [0, n_pages) sets device status bit 1 and skips the row. */
+uint64_t q27b_kv_wire_bytes(int nkvh, int n_rows);
+int q27b_kv_pages_to_wire(const void* pool, const int* pages, void* wire, int nkvh, int n_pages, int p0, int p1,
+                          void* stream);
+int q27b_kv_wire_to_pages(void* pool, const int* pages, const void* wire, int nkvh, int n_pages, int p0, int p1,
+                          void* stream);
+int q27b_kv_cache_to_wire(const void* cache, void* wire, int nkvh, int n_ctx, int p0, int p1, void* stream);
+int q27b_kv_wire_to_cache(void* cache, const void* wire, int nkvh, int n_ctx, int p0, int p1, void* stream);
+
 /* Bytes of the K (or V) page pool of q27b_attn_decode_paged. */
 uint64_t q27b_kv_pool_bytes(int nkvh, int n_pages);
 

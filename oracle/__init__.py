@@ -150,3 +150,21 @@ def attn_prefill_i8(qn, qg, kcache, vcache, pos0, kq_scale, nkvh, n_ctx, t_lo=0,
     lib().orc_attn_prefill_i8(_p(qn), _p(qg), _p(kcache), _p(vcache), _p(o), int(pos0), int(M),
                               ctypes.c_float(kq_scale), int(nqh), int(nkvh), int(n_ctx), int(t_lo), int(t_hi))
     return o
+
+
+def kv_wire_from_cache(cache, nkvh, n_ctx, p0, p1):
+    """Rows [p0, p1) of a contiguous q8_0 cache in the reference's host layout: the values
+    [nkvh][p1-p0][256], then the scales [nkvh][p1-p0][16 B] (Decoder::kv_copy, src/model.cu:1809-1830:
+    two strided copies per cache, values first)."""
+    cache = np.asarray(cache, np.uint8)
+    vals = cache[: nkvh * n_ctx * AD].reshape(nkvh, n_ctx, AD)[:, p0:p1]
+    sc = cache[nkvh * n_ctx * AD:].reshape(nkvh, n_ctx, 16)[:, p0:p1]
+    return np.concatenate([np.ascontiguousarray(vals).reshape(-1), np.ascontiguousarray(sc).reshape(-1)])
+
+
+def kv_wire_to_cache(cache, wire, nkvh, n_ctx, p0, p1):
+    """Inverse of kv_wire_from_cache, in place (the host-to-device direction of Decoder::kv_copy)."""
+    n = p1 - p0
+    wire = np.asarray(wire, np.uint8)
+    cache[: nkvh * n_ctx * AD].reshape(nkvh, n_ctx, AD)[:, p0:p1] = wire[: nkvh * n * AD].reshape(nkvh, n, AD)
+    cache[nkvh * n_ctx * AD:].reshape(nkvh, n_ctx, 16)[:, p0:p1] = wire[nkvh * n * AD:].reshape(nkvh, n, 16)

@@ -29,6 +29,7 @@ SYMBOLS = [
     "q27b_last_error", "q27b_device_status", "q27b_kv_cache_bytes", "q27b_attn_chunks", "q27b_kv_append",
     "q27b_attn_prep", "q27b_attn_decode", "q27b_attn_decode_partial", "q27b_lse_merge", "q27b_attn_decode_paged",
     "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_set_decode_kernel", "q27b_debug_expire_wait",
+    "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
     "q27b_attn_decode_noalloc",
 ]
 
@@ -41,6 +42,7 @@ def _load():
     lib.q27b_last_error.restype = ctypes.c_char_p
     lib.q27b_kv_cache_bytes.restype = ctypes.c_uint64
     lib.q27b_kv_pool_bytes.restype = ctypes.c_uint64
+    lib.q27b_kv_wire_bytes.restype = ctypes.c_uint64
     return lib
 
 
@@ -85,6 +87,31 @@ def kv_cache_bytes(nkvh, n_ctx, q8=True):
 
 def kv_pool_bytes(nkvh, n_pages):
     return int(_lib.q27b_kv_pool_bytes(int(nkvh), int(n_pages)))
+
+
+def kv_wire_bytes(nkvh, n_rows):
+    """Bytes of rows [p0, p1) of one q8_0 cache in the reference's host layout (src/model.cu:1809-1830)."""
+    return int(_lib.q27b_kv_wire_bytes(int(nkvh), int(n_rows)))
+
+
+def kv_pages_to_wire(pool, pages, wire, nkvh, n_pages, p0, p1):
+    """Rows [p0, p1) of one sequence of the page pool -> device buffer in the reference's host layout."""
+    _check(_lib.q27b_kv_pages_to_wire(_ptr(pool), _ptr(pages, torch.int32), _ptr(wire), int(nkvh), int(n_pages),
+                                      int(p0), int(p1), _stream()))
+
+
+def kv_wire_to_pages(pool, pages, wire, nkvh, n_pages, p0, p1):
+    _check(_lib.q27b_kv_wire_to_pages(_ptr(pool), _ptr(pages, torch.int32), _ptr(wire), int(nkvh), int(n_pages),
+                                      int(p0), int(p1), _stream()))
+
+
+def kv_cache_to_wire(cache, wire, nkvh, n_ctx, p0, p1):
+    """Rows [p0, p1) of a contiguous cache -> the reference's host layout (Decoder::kv_copy)."""
+    _check(_lib.q27b_kv_cache_to_wire(_ptr(cache), _ptr(wire), int(nkvh), int(n_ctx), int(p0), int(p1), _stream()))
+
+
+def kv_wire_to_cache(cache, wire, nkvh, n_ctx, p0, p1):
+    _check(_lib.q27b_kv_wire_to_cache(_ptr(cache), _ptr(wire), int(nkvh), int(n_ctx), int(p0), int(p1), _stream()))
 
 
 def attn_chunks(nkvh):

@@ -186,3 +186,26 @@ def test_prefill_i8_matches_numpy(orc):
             A = e.astype(np.float16).astype(np.float64) @ V[:m]
             ref = A / e.astype(np.float64).sum() / (1 + np.exp(-qg[t, h, 256:].astype(np.float64)))
             assert np.abs(o[t, h] - ref).max() < 2e-5
+
+
+def test_kv_wire_layout_round_trip(orc):
+    """Reference host layout of cache rows (Decoder::kv_copy, src/model.cu:1809-1830): values of all
+    heads first, then the scales; packing and unpacking are inverse and touch only rows [p0, p1)."""
+    rng = np.random.default_rng(5)
+    nkvh, n_ctx, p0, p1 = 3, 50, 7, 31
+    cache = rng.integers(0, 256, orc.kv_cache_bytes(nkvh, n_ctx, True), dtype=np.uint8)
+    wire = orc.kv_wire_from_cache(cache, nkvh, n_ctx, p0, p1)
+    n = p1 - p0
+    assert wire.size == nkvh * n * 272
+    # head 1, row p0 + 2: its 256 value bytes and its 16 scale bytes
+    assert np.array_equal(wire[(1 * n + 2) * 256:(1 * n + 3) * 256], cache[(1 * n_ctx + p0 + 2) * 256:(1 * n_ctx + p0 + 3) * 256])
+    s0 = nkvh * n_ctx * 256
+    assert np.array_equal(wire[nkvh * n * 256 + (1 * n + 2) * 16:nkvh * n * 256 + (1 * n + 3) * 16],
+                          cache[s0 + (1 * n_ctx + p0 + 2) * 16:s0 + (1 * n_ctx + p0 + 3) * 16])
+    other = np.zeros_like(cache)
+    orc.kv_wire_to_cache(other, wire, nkvh, n_ctx, p0, p1)
+    assert np.array_equal(orc.kv_wire_from_cache(other, nkvh, n_ctx, p0, p1), wire)
+    mask = np.ones(cache.size, bool)
+    vals = mask[:s0].reshape(nkvh, n_ctx, 256); vals[:, p0:p1] = False
+    sc = mask[s0:].reshape(nkvh, n_ctx, 16); sc[:, p0:p1] = False
+    assert (other[mask] == 0).all()
