@@ -9,8 +9,7 @@
 // host memory follows) and unpack it again, so that a slot swapped out by a paged engine can be
 // read by the reference's contiguous engine and the other way round.
 //
-// HBM bound: 272 B read and 272 B written per (KV head, position). One warp moves one row: lanes
-// 0-15 a 16-byte piece of the values each, lane 16 the 16 bytes of scales.
+// HBM bound: 272 B read and 272 B written per (KV head, position).
 #include "common.cuh"
 #include "host.h"
 
@@ -26,42 +25,58 @@ struct WireParams {
   int nkvh, n_pages, n_ctx, p0, n;
 };
 
+// One CTA moves the rows of one (KV head, 256-position page) that fall into [p0, p0 + n): on both
+// sides they are one contiguous run of values (rows x 256 B) and one of scales (rows x 16 B), so the
+// CTA is a plain copy loop with four 16-byte loads in flight per thread.
 template <bool TO_WIRE>
 __global__ void __launch_bounds__(256) kv_wire_kernel(const WireParams p) {
   pdl_wait();
   pdl_trigger();
-  const int lane = threadIdx.x & 31;
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);  // (head, position) pairs
-  if (row >= (long long)p.nkvh * p.n || lane > 16) return;
-  const int kh = (int)(row / p.n), i = (int)(row % p.n), pos = p.p0 + i;
-  size_t vrow, srow;  // byte offsets of the row's values and scales on the cache side
+  const int kh = blockIdx.y;
+  const int pj = p.p0 / Q27B_PAGE + blockIdx.x;                     // page index within the sequence
+  const int r0 = max(p.p0, pj * Q27B_PAGE), r1 = min(p.p0 + p.n, (pj + 1) * Q27B_PAGE);
+  if (r0 >= r1) return;
+  const int rows = r1 - r0, i0 = r0 - p.p0;
+  size_t vrow, srow;  // byte offsets of the first row's values and scales on the cache side
   uint8_t* base;
   if (p.pool) {
-    int pg = p.pages[pos / Q27B_PAGE];
-    if (pg < 0 || pg >= p.n_pages) {  // never touch memory outside the pool: flag it and skip the row
-      if (lane == 0) atomicOr(p.status, ST_BAD_PAGE);
+    const int pg = p.pages[pj];
+    if (pg < 0 || pg >= p.n_pages) {  // never touch memory outside the pool: flag it and skip the page
+      if (threadIdx.x == 0) atomicOr(p.status, ST_BAD_PAGE);
       return;
     }
-    const size_t r = ((size_t)pg * p.nkvh + kh) * Q27B_PAGE + pos % Q27B_PAGE;
+    const size_t r = ((size_t)pg * p.nkvh + kh) * Q27B_PAGE + r0 % Q27B_PAGE;
     base = p.pool;
     vrow = r * AD;
     srow = (size_t)p.n_pages * p.nkvh * Q27B_PAGE * AD + r * 16;
   } else {
-    const size_t r = (size_t)kh * p.n_ctx + pos;
+    const size_t r = (size_t)kh * p.n_ctx + r0;
     base = p.cache;
     vrow = r * AD;
     srow = (size_t)p.nkvh * p.n_ctx * AD + r * 16;
   }
-  const size_t wv = ((size_t)kh * p.n + i) * AD, ws = (size_t)p.nkvh * p.n * AD + ((size_t)kh * p.n + i) * 16;
-  uint4* c = (uint4*)(base + (lane < 16 ? vrow + lane * 16 : srow));
-  uint4* w = (uint4*)(p.wire + (lane < 16 ? wv + lane * 16 : ws));
-  if (TO_WIRE) *w = *c;
-  else *c = *w;
+  const size_t wv = ((size_t)kh * p.n + i0) * AD, ws = (size_t)p.nkvh * p.n * AD + ((size_t)kh * p.n + i0) * 16;
+  {
+    const uint4* src = (const uint4*)(TO_WIRE ? base + vrow : p.wire + wv);
+    uint4* dst = (uint4*)(TO_WIRE ? p.wire + wv : base + vrow);
+    const int nv = rows * (AD / 16);
+    int k = threadIdx.x;
+    for (; k + 3 * 256 < nv; k += 4 * 256) {
+      const uint4 a = src[k], b = src[k + 256], c = src[k + 512], d = src[k + 768];
+      dst[k] = a; dst[k + 256] = b; dst[k + 512] = c; dst[k + 768] = d;
+    }
+    for (; k < nv; k += 256) dst[k] = src[k];
+  }
+  {
+    const uint4* src = (const uint4*)(TO_WIRE ? base + srow : p.wire + ws);
+    uint4* dst = (uint4*)(TO_WIRE ? p.wire + ws : base + srow);
+    for (int k = threadIdx.x; k < rows; k += 256) dst[k] = src[k];
+  }
 }
 
 int launch(const WireParams& p, bool to_wire, cudaStream_t s) {
-  const long long rows = (long long)p.nkvh * p.n;
-  const dim3 grid((unsigned)((rows + 7) / 8));
+  const int pages = (p.p0 + p.n - 1) / Q27B_PAGE - p.p0 / Q27B_PAGE + 1;
+  const dim3 grid((unsigned)pages, (unsigned)p.nkvh);
   if (to_wire) Q27B_CK(launch_pdl(kv_wire_kernel<true>, grid, dim3(256), 0, s, p));
   else Q27B_CK(launch_pdl(kv_wire_kernel<false>, grid, dim3(256), 0, s, p));
   return Q27B_OK;
@@ -69,7 +84,7 @@ int launch(const WireParams& p, bool to_wire, cudaStream_t s) {
 
 int check(const void* a, const void* wire, int nkvh, int p0, int p1, const char* who) {
   if (!a || !wire) return fail(Q27B_BAD_SHAPE, std::string(who) + ": null pointer");
-  if (nkvh < 1 || p0 < 0 || p1 <= p0) return fail(Q27B_BAD_SHAPE, std::string(who) + ": bad shape");
+  if (nkvh < 1 || nkvh > 65535 || p0 < 0 || p1 <= p0) return fail(Q27B_BAD_SHAPE, std::string(who) + ": bad shape");
   return Q27B_OK;
 }
 
