@@ -185,6 +185,14 @@ int q27b_attn_prefill(const float* qn, const float* qg, const void* kcache, cons
                       const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, int q8, void* stream,
                       int depth_hint);
 
+/* The same with the output quantised to q8_1 in the kernel's epilogue, which is what the reference
+ * does with the attention output before its next GEMM (quantize_q8_1 after attn_prefill,
+ * src/model.cu:1230,1499; numerics of q8_store, src/common.cuh:72-81): xq int8 [M][nqh][256],
+ * xd f32 [M*nqh*8] = f32(f16(amax / 127)) per 32 values. The f32 round trip through `o` is saved. */
+int q27b_attn_prefill_q8_1(const float* qn, const float* qg, const void* kcache, const void* vcache, int8_t* xq,
+                           float* xd, const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, int q8,
+                           void* stream, int depth_hint);
+
 /* Test hook of the prefill kernel's integer stage: quantises `rows` (<= 128) query rows
  * (x [rows][256] f32, already the rows of one head) as the prefill kernel does and multiplies
  * them on the int8 tensor path with npos (<= 64) K rows taken from a q8_0 cache (head kh,

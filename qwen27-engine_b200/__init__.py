@@ -29,7 +29,7 @@ SYMBOLS = [
     "q27b_last_error", "q27b_device_status", "q27b_kv_cache_bytes", "q27b_attn_chunks", "q27b_kv_append",
     "q27b_attn_prep", "q27b_attn_decode", "q27b_attn_decode_partial", "q27b_lse_merge", "q27b_attn_decode_paged",
     "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_set_decode_kernel", "q27b_debug_expire_wait",
-    "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
+    "q27b_attn_prefill_q8_1", "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
     "q27b_attn_decode_noalloc",
 ]
 
@@ -213,6 +213,14 @@ def attn_prefill(qn, qg, kcache, vcache, o, pos0, M, kq_scale, nqh, nkvh, n_ctx,
     _check(_lib.q27b_attn_prefill(_ptr(qn, torch.float32), _ptr(qg, torch.float32), _ptr(kcache), _ptr(vcache),
                                   _ptr(o, torch.float32), _ptr(pos0, torch.int32), int(M), _f(kq_scale), int(nqh),
                                   int(nkvh), int(n_ctx), int(bool(q8)), _stream(), int(depth_hint)))
+
+
+def attn_prefill_q8_1(qn, qg, kcache, vcache, xq, xd, pos0, M, kq_scale, nqh, nkvh, n_ctx, q8=True, depth_hint=-1):
+    """attn_prefill with the q8_1 quantisation of the output (src/model.cu:1230) done in the epilogue."""
+    _check(_lib.q27b_attn_prefill_q8_1(_ptr(qn, torch.float32), _ptr(qg, torch.float32), _ptr(kcache), _ptr(vcache),
+                                       _ptr(xq, torch.int8), _ptr(xd, torch.float32), _ptr(pos0, torch.int32), int(M),
+                                       _f(kq_scale), int(nqh), int(nkvh), int(n_ctx), int(bool(q8)), _stream(),
+                                       int(depth_hint)))
 
 
 def prefill_qk_debug(x, rows, kq_scale, kcache, nkvh, n_ctx, kh, p0, npos, q_i8, q_scale, acc):

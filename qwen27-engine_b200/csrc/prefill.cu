@@ -103,6 +103,8 @@ struct PrefillParams {
   int M, nqh, nkvh, n_ctx, nsplit;
   float kq_scale;
   int tile_major;  // CTA order, see the kernel
+  int8_t* xq;      // q8_1 output instead of o: int8 [M][nqh][256] ...
+  float* xd;       // ... and one scale per 32 values, as f32(f16(d)) (q8_store, src/common.cuh:72-81)
 };
 
 // Barrier of the NWG threads' warps that share query rows 32q .. 32q+31.
@@ -418,7 +420,8 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
           *(float2*)(po + 2 + d0 + i) = make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
       } else {
         const float* gt = p.qg + ((size_t)t * p.nqh + h) * 512 + 256 + d0;
-        float* dst = p.o + ((size_t)t * p.nqh + h) * AD + d0;
+        float* dst = p.xq ? nullptr : p.o + ((size_t)t * p.nqh + h) * AD + d0;
+        float amax = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 gg = *(const float4*)(gt + i);
@@ -427,7 +430,31 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
           y.y = (__uint_as_float(v[i + 1]) * inv_l) * (1.0f / (1.0f + __expf(-gg.y)));
           y.z = (__uint_as_float(v[i + 2]) * inv_l) * (1.0f / (1.0f + __expf(-gg.z)));
           y.w = (__uint_as_float(v[i + 3]) * inv_l) * (1.0f / (1.0f + __expf(-gg.w)));
-          *(float4*)(dst + i) = y;
+          if (dst) {
+            *(float4*)(dst + i) = y;
+          } else {  // keep the values for the q8_1 block below (these 32 columns are exactly one block)
+            v[i] = __float_as_uint(y.x); v[i + 1] = __float_as_uint(y.y);
+            v[i + 2] = __float_as_uint(y.z); v[i + 3] = __float_as_uint(y.w);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(y.x), fabsf(y.y)), fmaxf(fabsf(y.z), fabsf(y.w))));
+          }
+        }
+        if (!dst) {
+          // q8_1 as the reference's quantize_q8_1 / q8_store (src/common.cuh:72-81): d = amax / 127,
+          // q = round(y / d) (half away from zero), the scale leaves as f32(f16(d)); IEEE division
+          const float dd = __fdiv_rn(amax, 127.0f);
+          const size_t oi = ((size_t)t * p.nqh + h) * AD + d0;
+          uint32_t w[8];
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            uint32_t b[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+              b[k] = amax == 0.0f ? 0u : (uint32_t)(uint8_t)(int8_t)roundf(__fdiv_rn(__uint_as_float(v[i + k]), dd));
+            w[i / 4] = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+          }
+          *(uint4*)(p.xq + oi) = make_uint4(w[0], w[1], w[2], w[3]);
+          *(uint4*)(p.xq + oi + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+          p.xd[oi / 32] = __half2float(__float2half_rn(dd));
         }
       }
     }
@@ -709,11 +736,12 @@ using namespace q27b;
 
 extern "C" {
 
-int q27b_attn_prefill(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
-                      const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, int q8, void* stream,
-                      int depth_hint) {
+static int prefill_impl(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o, int8_t* xq,
+                        float* xd, const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, int q8,
+                        void* stream, int depth_hint) {
   if (nkvh < 1 || nqh != nkvh * GQA || M < 1 || n_ctx < 1) return fail(Q27B_BAD_SHAPE, "attn_prefill: bad shape");
-  if (!qn || !qg || !kcache || !vcache || !o || !pos0) return fail(Q27B_BAD_SHAPE, "attn_prefill: null pointer");
+  if (!qn || !qg || !kcache || !vcache || (!o && !xq) || (xq && !xd) || !pos0)
+    return fail(Q27B_BAD_SHAPE, "attn_prefill: null pointer");
   if (!q8) return fail(Q27B_UNSUPPORTED, "attn_prefill: only the q8_0 cache (int8 Q K^T path) is built");
   DeviceCtx* ctx;
   if (int rc = device_ctx(&ctx)) return rc;
@@ -735,7 +763,7 @@ int q27b_attn_prefill(const float* qn, const float* qg, const void* kcache, cons
   if (int rc = get_tmaps(kcache, nkvh, n_ctx, &kv, &ks)) return rc;
   if (int rc = get_tmaps(vcache, nkvh, n_ctx, &vv, &vs)) return rc;
   PrefillParams p = {};
-  p.qn = qn; p.qg = qg; p.o = o; p.part = nsplit > 1 ? ctx->part : nullptr; p.pos0 = pos0; p.status = ctx->status;
+  p.qn = qn; p.qg = qg; p.o = o; p.xq = xq; p.xd = xd; p.part = nsplit > 1 ? ctx->part : nullptr; p.pos0 = pos0; p.status = ctx->status;
   p.M = M; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nsplit = nsplit; p.kq_scale = kq_scale;
   p.tile_major = depth_hint >= 0 && depth_hint < 4 * M;  // short prefix: the causal part dominates
   prefill_i8_kernel<<<dim3(tiles * nqh, 1, nsplit), PF_THREADS, PF_SMEM_BYTES, s>>>(*kv, *ks, *vv, *vs, p);
@@ -743,10 +771,24 @@ int q27b_attn_prefill(const float* qn, const float* qg, const void* kcache, cons
   if (nsplit > 1) {
     MergeParams mp = {};
     mp.part = ctx->part; mp.nparts = nsplit; mp.part_stride = (int64_t)M * nqh * PROW; mp.rows = (int64_t)M * nqh;
-    mp.qg = qg; mp.o = o;
+    mp.qg = qg; mp.o = o; mp.xq = xq; mp.xd = xd;
     return launch_merge(mp, false, s);
   }
   return Q27B_OK;
+}
+
+int q27b_attn_prefill(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
+                      const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, int q8, void* stream,
+                      int depth_hint) {
+  if (!o) return fail(Q27B_BAD_SHAPE, "attn_prefill: null pointer");
+  return prefill_impl(qn, qg, kcache, vcache, o, nullptr, nullptr, pos0, M, kq_scale, nqh, nkvh, n_ctx, q8, stream, depth_hint);
+}
+
+int q27b_attn_prefill_q8_1(const float* qn, const float* qg, const void* kcache, const void* vcache, int8_t* xq, float* xd,
+                           const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, int q8, void* stream,
+                           int depth_hint) {
+  if (!xq || !xd) return fail(Q27B_BAD_SHAPE, "attn_prefill: null pointer");
+  return prefill_impl(qn, qg, kcache, vcache, nullptr, xq, xd, pos0, M, kq_scale, nqh, nkvh, n_ctx, q8, stream, depth_hint);
 }
 
 int q27b_prefill_qk_debug(const float* x, int rows, float kq_scale, const void* kcache, int nkvh, int n_ctx, int kh,

@@ -109,3 +109,24 @@ def test_prefill_agrees_with_decode(q27, orc):
     q27.attn_decode(dev(qn[-4:]), dev(qg[-4:]), kc, vc, o4, None, None, pos_tensor(n - 4), 4, SCALE, 6, nkvh, n_ctx)
     torch.cuda.synchronize()
     assert_close(o[-4:].cpu().numpy(), o4.cpu().numpy(), "prefill vs decode", abs_tol=5e-3, rel_tol=5e-2)
+
+
+@pytest.mark.parametrize("pos0,M,depth_hint", [(700, 200, -1), (3000, 256, 8192), (0, 129, -1)])
+def test_prefill_q8_1_epilogue(q27, orc, pos0, M, depth_hint):
+    """With xq the result leaves as q8_1 (what the reference computes with quantize_q8_1 after
+    attn_prefill, src/model.cu:1230): exactly the oracle's q8_1 of the kernel's own f32 result, with
+    and without the split over the positions (the split path quantises in the merge kernel)."""
+    nkvh = 2
+    nqh = nkvh * GQA
+    qn, qg, kc_ref, vc_ref, n, n_ctx = make_case(orc, M, pos0, nkvh)
+    kc, vc = dev(kc_ref), dev(vc_ref)
+    o = torch.full((M, nqh, AD), float("nan"), device="cuda")
+    q27.attn_prefill(dev(qn), dev(qg), kc, vc, o, pos_tensor(pos0), M, SCALE, nqh, nkvh, n_ctx, True, depth_hint)
+    xq = torch.zeros((M, nqh, AD), dtype=torch.int8, device="cuda")
+    xd = torch.zeros((M * nqh * 8,), dtype=torch.float32, device="cuda")
+    q27.attn_prefill_q8_1(dev(qn), dev(qg), kc, vc, xq, xd, pos_tensor(pos0), M, SCALE, nqh, nkvh, n_ctx, True, depth_hint)
+    torch.cuda.synchronize()
+    rq, rd = orc.q8_1(o.cpu().numpy().reshape(-1))
+    assert np.array_equal(xq.cpu().numpy().reshape(-1), rq)
+    assert np.array_equal(xd.cpu().numpy(), rd)
+    assert q27.device_status() == 0
