@@ -135,6 +135,24 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
                            const int* page_table, const int* seq_len, float* o, int B, int T, float kq_scale, int nqh,
                            int nkvh, int n_pages, int max_pages, int max_seq_len, void* stream);
 
+/* One sequence split by KV length over the nz GPUs of a head group, exchanged over peer memory
+ * instead of a collective. Every rank owns an exchange buffer of q27b_xbuf_bytes(nz, T * nqh) bytes,
+ * zeroed once, that its peers can store into (peer-mapped device memory; how it is mapped is the
+ * caller's business: CUDA IPC, symmetric memory, one process with several devices).
+ * q27b_attn_decode_partial_push = q27b_attn_decode_partial whose merge kernel stores the slice's
+ * (m, l, O) rows into slot my_z of all nz buffers (peer_xbuf[k] = buffer of rank k of the group, as
+ * seen from this GPU; peer_xbuf[my_z] is this rank's own) and then raises flag my_z in each with a
+ * system-scope release store. q27b_lse_merge_wait waits (bounded: about a second, then device status
+ * bit 0) until the nz flags of its own buffer show the current step, merges the nz slices and applies
+ * the gate. Steps are counted on the device, so the pair can sit in a CUDA graph; two parities of the
+ * data area make it safe for a rank to run one step ahead of a peer. No counterpart in the reference
+ * (its two cards split KV heads, never the KV length: src/model.cu:161-164). */
+uint64_t q27b_xbuf_bytes(int nz, int64_t rows);
+int q27b_attn_decode_partial_push(const float* qn, const void* kcache, const void* vcache, const int* pos0, int T,
+                                  float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos, int n_local,
+                                  void* const* peer_xbuf, int my_z, int nz, void* stream);
+int q27b_lse_merge_wait(void* xbuf, int nz, int64_t rows, const float* qg, float* o, void* stream);
+
 /* Which split-K kernel q27b_attn_decode* uses for q8_0 caches: 0 = default (the warp-MMA kernel),
  * 1 = warp-MMA kernel, 2 = tcgen05 kernel (both contractions on the 5th-generation tensor cores;
  * faster at long contexts in its best builds, less predictable: see csrc/decode.cu). Both compute

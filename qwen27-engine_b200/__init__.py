@@ -29,7 +29,8 @@ SYMBOLS = [
     "q27b_last_error", "q27b_device_status", "q27b_kv_cache_bytes", "q27b_attn_chunks", "q27b_kv_append",
     "q27b_attn_prep", "q27b_attn_decode", "q27b_attn_decode_partial", "q27b_lse_merge", "q27b_attn_decode_paged",
     "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_set_decode_kernel", "q27b_debug_expire_wait",
-    "q27b_attn_prefill_q8_1", "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
+    "q27b_attn_prefill_q8_1", "q27b_xbuf_bytes", "q27b_attn_decode_partial_push", "q27b_lse_merge_wait",
+    "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
     "q27b_attn_decode_noalloc",
 ]
 
@@ -43,6 +44,7 @@ def _load():
     lib.q27b_kv_cache_bytes.restype = ctypes.c_uint64
     lib.q27b_kv_pool_bytes.restype = ctypes.c_uint64
     lib.q27b_kv_wire_bytes.restype = ctypes.c_uint64
+    lib.q27b_xbuf_bytes.restype = ctypes.c_uint64
     return lib
 
 
@@ -131,6 +133,27 @@ def device_status():
 def debug_expire_wait():
     """Test hook: one warp waits on a barrier nobody arrives at; the bounded wait gives up (status bit 0)."""
     _check(_lib.q27b_debug_expire_wait(_stream()))
+
+
+def xbuf_bytes(nz, rows):
+    """Bytes of one rank's exchange buffer for the peer-memory merge of nz KV-length slices."""
+    return int(_lib.q27b_xbuf_bytes(int(nz), ctypes.c_int64(int(rows))))
+
+
+def attn_decode_partial_push(qn, kcache, vcache, pos0, T, kq_scale, nqh, nkvh, n_ctx, base_pos, n_local, peer_ptrs,
+                             my_z, q8=True):
+    """Split-K decode of one KV-length slice whose merged partial is stored into slot my_z of the
+    exchange buffers of all ranks of the group (peer_ptrs: their device addresses as seen from here)."""
+    arr = (ctypes.c_void_p * len(peer_ptrs))(*[ctypes.c_void_p(int(x)) for x in peer_ptrs])
+    _check(_lib.q27b_attn_decode_partial_push(_ptr(qn, torch.float32), _ptr(kcache), _ptr(vcache), _ptr(pos0, torch.int32),
+                                              int(T), _f(kq_scale), int(nqh), int(nkvh), int(n_ctx), int(bool(q8)),
+                                              int(base_pos), int(n_local), arr, int(my_z), len(peer_ptrs), _stream()))
+
+
+def lse_merge_wait(xbuf, nz, rows, qg, o):
+    """Waits for the nz slices of this step in this rank's exchange buffer, merges them, applies the gate."""
+    _check(_lib.q27b_lse_merge_wait(_ptr(xbuf), int(nz), ctypes.c_int64(int(rows)),
+                                    _ptr(qg, torch.float32) if qg is not None else None, _ptr(o, torch.float32), _stream()))
 
 
 def set_decode_kernel(which):

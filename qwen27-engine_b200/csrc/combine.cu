@@ -43,8 +43,39 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
   __shared__ float sred[2][8];
   const int64_t row = blockIdx.x;
   const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
-  const RowMap rm = DECODE_LAYOUT ? map_decode(p, row) : map_generic(p, row);
+  RowMap rm = DECODE_LAYOUT ? map_decode(p, row) : map_generic(p, row);
   int np = p.nparts;
+  int epoch = 0;
+  if (p.push_n > 0 || p.wait_n > 0) epoch = *(volatile int*)p.xbuf;
+  if (!DECODE_LAYOUT && p.wait_n > 0) {
+    // Slices of the other GPUs arrive by plain stores followed by a released flag: wait for the flags
+    // of this step (bounded; a lost peer ends in the status word, not in a hang), then read.
+    __shared__ int s_ok;
+    if (d == 0) {
+      bool ok = true;
+      for (int z = 0; z < p.wait_n && ok; z++) {
+        const int* flag = p.xbuf + 16 + z;
+        ok = false;
+        for (uint32_t i = 0; i < (1u << 22); i++) {  // about a second with the sleeps
+          int v;
+          asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+          if (v - (epoch + 1) >= 0) {
+            ok = true;
+            break;
+          }
+          if (i > 64) __nanosleep(200);
+        }
+      }
+      if (!ok && p.status) atomicOr(p.status, ST_WAIT_EXPIRED);
+      s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const float* data = (const float*)((const uint8_t*)p.xbuf + XBUF_HEADER_BYTES) + (size_t)(epoch & 1) * p.wait_n * p.rows * PROW;
+    rm.first = data + row * PROW;
+    rm.stride = (size_t)p.rows * PROW;
+    np = p.wait_n;
+  }
   if (DECODE_LAYOUT && p.seq_len) {
     const int64_t seq = row / ((int64_t)p.nqh * p.T);
     np = min(np, max(1, (p.seq_len[seq] + p.chunk_len - 1) / p.chunk_len));
@@ -92,6 +123,36 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
   }
 
   const size_t oi = (size_t)row * AD + d;
+  if (!DECODE_LAYOUT && p.wait_n > 0 && d == 0) {
+    // the last CTA of the step advances the epoch (nobody reads it again before the next launch)
+    __threadfence();
+    if (atomicAdd(p.xbuf + 2, 1) == (int)p.rows - 1) {
+      p.xbuf[2] = 0;
+      *(volatile int*)p.xbuf = epoch + 1;
+    }
+  }
+  if (p.push_n > 0) {  // merged, not normalised, into slot push_z of every rank's exchange buffer
+    for (int k = 0; k < p.push_n; k++) {
+      float* po = (float*)((uint8_t*)p.push_buf[k] + XBUF_HEADER_BYTES) +
+                  (((size_t)(epoch & 1) * p.push_n + p.push_z) * p.rows + row) * PROW;
+      po[2 + d] = A;
+      if (d == 0) {
+        po[0] = M;
+        po[1] = L;
+      }
+    }
+    __threadfence_system();  // the rows are visible to the peers before the flag below can be
+    __syncthreads();
+    if (d == 0 && atomicAdd(p.xbuf + 1, 1) == (int)p.rows - 1) {
+      p.xbuf[1] = 0;
+      __threadfence_system();
+      for (int k = 0; k < p.push_n; k++) {
+        int* flag = (int*)p.push_buf[k] + 16 + p.push_z;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch + 1) : "memory");
+      }
+    }
+    return;
+  }
   if (p.part_out) {  // merged but not normalised: (M, L, A) for a later merge
     float* po = p.part_out + (size_t)row * PROW;
     po[2 + d] = A;
@@ -128,6 +189,20 @@ int launch_merge(const MergeParams& p, bool decode_layout, cudaStream_t s) {
 }  // namespace q27b
 
 using namespace q27b;
+
+extern "C" uint64_t q27b_xbuf_bytes(int nz, int64_t rows) {
+  return (uint64_t)XBUF_HEADER_BYTES + 2ull * (uint64_t)nz * (uint64_t)rows * PROW * sizeof(float);
+}
+
+extern "C" int q27b_lse_merge_wait(void* xbuf, int nz, int64_t rows, const float* qg, float* o, void* stream) {
+  if (!xbuf || !o) return fail(Q27B_BAD_SHAPE, "lse_merge_wait: null pointer");
+  if (nz < 1 || nz > 8 || rows < 1 || rows > 0x7fffffff) return fail(Q27B_BAD_SHAPE, "lse_merge_wait: bad shape");
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  MergeParams p = {};
+  p.nparts = nz; p.rows = rows; p.qg = qg; p.o = o; p.xbuf = (int*)xbuf; p.wait_n = nz; p.status = ctx->status;
+  return launch_merge(p, false, (cudaStream_t)stream);
+}
 
 extern "C" int q27b_lse_merge(const float* part, int nparts, int64_t part_stride, int64_t rows, const float* qg, float* o,
                               int8_t* xq, float* xd, void* stream) {

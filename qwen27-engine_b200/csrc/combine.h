@@ -17,7 +17,21 @@ struct MergeParams {
   int T, nqh;           // decode layout only
   const int* seq_len;   // decode layout, batched: sequence s has ceil(seq_len[s] / chunk_len) partials
   int chunk_len;
+  // Exchange over peer memory (KV-length slices of one sequence on several GPUs). An exchange buffer
+  // is [64 ints header][2 parities][nz slices][rows][258 floats]; header: [0] epoch, [1] and [2]
+  // arrival counters, [16 + z] flag of slice z (= epoch + 1 once slice z of that step has landed).
+  // push_n > 0: the merged (M, L, A) rows go, instead of part_out, into slot push_z of the buffers of
+  // all push_n ranks of the group (plain stores, this rank's own buffer included), and the last CTA
+  // raises flag push_z in each of them. wait_n > 0: `part` is this rank's own buffer: the kernel waits
+  // (bounded) until all wait_n flags show the current epoch, merges those slices, and the last CTA
+  // advances the epoch.
+  void* push_buf[8];
+  int push_n, push_z;
+  int* xbuf;            // this rank's own exchange buffer (push: epoch and counter; wait: everything)
+  int wait_n;
+  int* status;
 };
+constexpr int XBUF_HEADER_BYTES = 256;
 
 // decode_layout: part is [seq][kvh][chunk][24][258] and rows = seqs * T * nqh.
 int launch_merge(const MergeParams& p, bool decode_layout, cudaStream_t s);

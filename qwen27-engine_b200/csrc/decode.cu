@@ -743,6 +743,50 @@ int q27b_attn_decode_partial(const float* qn, const void* kcache, const void* vc
   return launch_merge(mp, true, (cudaStream_t)stream);
 }
 
+int q27b_attn_decode_partial_push(const float* qn, const void* kcache, const void* vcache, const int* pos0, int T,
+                                  float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos, int n_local,
+                                  void* const* peer_xbuf, int my_z, int nz, void* stream) {
+  if (T < 1 || T > Q27B_MAX_T || nkvh < 1 || nqh != nkvh * GQA || n_ctx < 1 || base_pos < 0 || n_local < 0 ||
+      n_local > n_ctx || nz < 1 || nz > 8 || my_z < 0 || my_z >= nz)
+    return fail(Q27B_BAD_SHAPE, "attn_decode_partial_push: bad shape");
+  if (!qn || !kcache || !vcache || !pos0 || !peer_xbuf) return fail(Q27B_BAD_SHAPE, "attn_decode_partial_push: null pointer");
+  for (int k = 0; k < nz; k++)
+    if (!peer_xbuf[k]) return fail(Q27B_BAD_SHAPE, "attn_decode_partial_push: null pointer");
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  // Every buffer must be device memory that kernels of this GPU may store into: a peer's buffer needs
+  // peer access from this device to the peer's, which is enabled here (once per pointer) rather than
+  // left to whoever mapped the memory. Anything else is refused before a kernel can touch it.
+  static const void* checked[64] = {};
+  static int n_checked = 0;
+  for (int k = 0; k < nz; k++) {
+    bool seen = false;
+    for (int i = 0; i < n_checked; i++) seen |= checked[i] == peer_xbuf[k];
+    if (seen) continue;
+    cudaPointerAttributes a;
+    Q27B_CK(cudaPointerGetAttributes(&a, peer_xbuf[k]));
+    if (a.type != cudaMemoryTypeDevice) return fail(Q27B_BAD_SHAPE, "attn_decode_partial_push: exchange buffer is not device memory");
+    if (a.device != ctx->dev) {
+      int can = 0;
+      Q27B_CK(cudaDeviceCanAccessPeer(&can, ctx->dev, a.device));
+      if (!can) return fail(Q27B_UNSUPPORTED, "attn_decode_partial_push: no peer access to the device of an exchange buffer");
+      const cudaError_t e = cudaDeviceEnablePeerAccess(a.device, 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError();
+      else Q27B_CK(e);
+    }
+    if (n_checked < 64) checked[n_checked++] = peer_xbuf[k];
+  }
+  int nch;
+  if (int rc = decode_split(ctx, qn, kcache, vcache, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8, base_pos, n_local, &nch,
+                            (cudaStream_t)stream))
+    return rc;
+  MergeParams mp = {};
+  mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.T = T; mp.nqh = nqh;
+  for (int k = 0; k < nz; k++) mp.push_buf[k] = peer_xbuf[k];
+  mp.push_n = nz; mp.push_z = my_z; mp.xbuf = (int*)peer_xbuf[my_z]; mp.status = ctx->status;
+  return launch_merge(mp, true, (cudaStream_t)stream);
+}
+
 int q27b_attn_decode_noalloc(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
                              int8_t* xq, float* xd, const int* pos0, int T, float kq_scale, int nqh, int nkvh, int n_ctx,
                              int q8, void* stream) {

@@ -91,3 +91,4 @@ def gather_partials(part, shard, group=None):
         lst = [out[i] for i in range(shard.nz)]
         dist.all_gather(lst, part.contiguous(), group=group)
     return out
+

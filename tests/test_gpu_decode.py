@@ -178,3 +178,58 @@ def test_f16_kv_cache(q27, orc, T, nkvh, n):
         pytest.skip("f16 KV decode not built: " + str(e))
     torch.cuda.synchronize()
     assert_close(o.cpu().numpy(), orc.attn_ref(qn, qg, kc_ref, vc_ref, n - T, SCALE, nkvh, n + 5, q8=False), "f16 KV")
+
+
+@pytest.mark.parametrize("n,cuts", [(5000, [0, 2560, 5000]), (3000, [0, 1024, 2048, 3000])])
+def test_kv_length_slices_exchanged_over_peer_memory(q27, orc, n, cuts):
+    """The peer-memory exchange of the KV-length split, with all "ranks" emulated on one GPU one after
+    the other (every wait finds its flag already set: kernels that wait on one another never run
+    concurrently on one GPU): each rank pushes its slice into every rank's exchange buffer, each rank's
+    waiting merge then gives the whole result, bit-identical to the gathered merge; three steps in a
+    row exercise the step counter and the two parities of the buffers."""
+    from qwen27_engine_b200 import synth
+    T, nkvh = 4, 1
+    nqh = nkvh * GQA
+    nz = len(cuts) - 1
+    rows = T * nqh
+    bufs = [torch.zeros(q27.xbuf_bytes(nz, rows), dtype=torch.uint8, device="cuda") for _ in range(nz)]
+    ptrs = [b.data_ptr() for b in bufs]
+    for step in range(3):
+        qn, qg, kf, vf = synth.decode_inputs(T, nqh, nkvh, n, start_kv=step)
+        full_k, full_v = orc.fill_cache(kf, vf, n)
+        slices = []
+        for z in range(nz):
+            lo, hi = cuts[z], cuts[z + 1]
+            n_ctx = hi - lo + 3
+            kc_ref, vc_ref = orc.fill_cache(kf[:, lo:hi], vf[:, lo:hi], n_ctx)
+            slices.append((poisoned_cache(q27, kc_ref, nkvh, n_ctx, hi - lo), poisoned_cache(q27, vc_ref, nkvh, n_ctx, hi - lo),
+                           n_ctx, lo, hi))
+        parts = []
+        for z, (kc, vc, n_ctx, lo, hi) in enumerate(slices):
+            q27.attn_decode_partial_push(dev(qn), kc, vc, pos_tensor(n - T), T, SCALE, nqh, nkvh, n_ctx, lo, hi - lo, ptrs, z)
+            part = torch.empty((T, nqh, 258), device="cuda")
+            q27.attn_decode_partial(dev(qn), kc, vc, part, pos_tensor(n - T), T, SCALE, nqh, nkvh, n_ctx, lo, hi - lo)
+            parts.append(part)
+        gathered = torch.empty((T, nqh, AD), device="cuda")
+        q27.lse_merge(torch.stack(parts).contiguous(), nz, rows * 258, rows, dev(qg), gathered)
+        whole = orc.attn_ref(qn, qg, full_k, full_v, n - T, SCALE, nkvh, n)
+        for z in range(nz):
+            o = torch.full((T, nqh, AD), float("nan"), device="cuda")
+            q27.lse_merge_wait(bufs[z], nz, rows, dev(qg), o)
+            torch.cuda.synchronize()
+            assert torch.equal(o, gathered), "rank %d, step %d" % (z, step)
+            assert_close(o.cpu().numpy(), whole, "peer-memory merge, rank %d, step %d" % (z, step))
+        assert int(bufs[0][:4].view(torch.int32).item()) == step + 1  # the step counter advanced
+    assert q27.device_status() == 0
+
+
+def test_peer_memory_merge_reports_a_missing_slice(q27):
+    """A slice that never arrives: the waiting merge gives up after its limit and says so in the status
+    word (nothing hangs, nothing traps); the output is left alone."""
+    nz, rows = 2, 6
+    buf = torch.zeros(q27.xbuf_bytes(nz, rows), dtype=torch.uint8, device="cuda")
+    buf[64:68] = torch.tensor([1, 0, 0, 0], dtype=torch.uint8, device="cuda")  # flag of slice 0 set, slice 1 missing
+    o = torch.full((rows, AD), 7.0, device="cuda")
+    q27.lse_merge_wait(buf, nz, rows, None, o)
+    assert q27.device_status() & 1
+    assert bool((o == 7.0).all())
