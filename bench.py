@@ -426,9 +426,33 @@ def strong_scaling(q, dist, rank, world, n, steps, warmup):
             q.lse_merge(allp, sh.nz, T * nq * 258, T * nq, qg, o)
 
     ms = time_steps(step, steps, warmup, dist)
-    return {"what": "one 150k sequence sharded over %d GPUs: %d KV head(s) per GPU x %d KV-length slice(s)%s" % (
-                world, nk, sh.nz, ", NCCL all-gather of partials + LSE merge" if sh.nz > 1 else ", no exchange"),
-            "us_per_step": ms * 1e3, "value": kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong"}
+    out = {"what": "one 150k sequence sharded over %d GPUs: %d KV head(s) per GPU x %d KV-length slice(s)%s" % (
+               world, nk, sh.nz, ", NCCL all-gather of partials + LSE merge" if sh.nz > 1 else ", no exchange"),
+           "us_per_step": ms * 1e3, "value": kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong"}
+    if sh.nz > 1 and os.environ.get("Q27B_P2P_MERGE", "1") != "0":
+        # the same exchange over peer memory: the merge kernel of each slice stores its rows into every
+        # rank's exchange buffer and raises a flag; the final merge waits for the flags of its own buffer
+        own, peers = shard.make_exchange(q, sh, group, T * nq)
+        o2 = torch.empty((T, nq, AD), device="cuda")
+
+        def step_p2p(i):
+            kc, vc = caches[i % NBUF]
+            q.attn_decode_partial_push(qn, kc, vc, pos, T, SCALE, nq, nk, n_ctx, lo, hi - lo, peers, sh.z)
+            q.lse_merge_wait(own, sh.nz, T * nq, qg, o2)
+        step(0)
+        step_p2p(0)
+        torch.cuda.synchronize()
+        same = bool(torch.equal(o, o2))
+        ms2 = time_steps(step_p2p, steps, warmup, dist)
+        assert q.device_status() == 0, "a kernel reported a device-side problem"
+        out["nccl_us_per_step"] = out["us_per_step"]
+        out["us_per_step"] = ms2 * 1e3
+        out["value"] = kv_bytes(NKVH, n) / (ms2 * 1e-3) / 1e9
+        out["what"] = out["what"].replace("NCCL all-gather of partials + LSE merge",
+                                          "partials stored into the peers' exchange buffers over NVLink by the merge kernel "
+                                          "+ waiting LSE merge (nccl_us_per_step: the same with an NCCL all-gather)")
+        out["p2p_equals_nccl_bitwise"] = same
+    return out
 
 
 def batched_paged(q, rank, world, dist=None):

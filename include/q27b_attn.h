@@ -148,6 +148,15 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
  * data area make it safe for a rank to run one step ahead of a peer. No counterpart in the reference
  * (its two cards split KV heads, never the KV length: src/model.cu:161-164). */
 uint64_t q27b_xbuf_bytes(int nz, int64_t rows);
+/* Helpers for one process per GPU: an exchange buffer as a cudaMalloc allocation of its own (zeroed),
+ * its CUDA IPC handle (64 bytes, to be sent to the peers by any means), and the mapping of a peer's
+ * handle into the address space of the calling thread's CURRENT device, which must be the device
+ * whose kernels will store into it (a handle opened under another device is not reachable). */
+int q27b_xbuf_alloc(int nz, int64_t rows, void** out);
+int q27b_xbuf_free(void* xbuf);
+int q27b_ipc_export(const void* ptr, unsigned char handle[64]);
+int q27b_ipc_open(const unsigned char handle[64], void** out);
+int q27b_ipc_close(void* mapped);
 int q27b_attn_decode_partial_push(const float* qn, const void* kcache, const void* vcache, const int* pos0, int T,
                                   float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos, int n_local,
                                   void* const* peer_xbuf, int my_z, int nz, void* stream);

@@ -30,6 +30,7 @@ SYMBOLS = [
     "q27b_attn_prep", "q27b_attn_decode", "q27b_attn_decode_partial", "q27b_lse_merge", "q27b_attn_decode_paged",
     "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_set_decode_kernel", "q27b_debug_expire_wait",
     "q27b_attn_prefill_q8_1", "q27b_xbuf_bytes", "q27b_attn_decode_partial_push", "q27b_lse_merge_wait",
+    "q27b_xbuf_alloc", "q27b_xbuf_free", "q27b_ipc_export", "q27b_ipc_open", "q27b_ipc_close",
     "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
     "q27b_attn_decode_noalloc",
 ]
@@ -63,6 +64,8 @@ def _check(rc):
 
 
 def _ptr(t, dtype=None, optional=False):
+    if isinstance(t, int):  # a raw device address (exchange buffers mapped from other processes)
+        return ctypes.c_void_p(t)
     if t is None:
         if not optional:
             raise Q27Error(BAD_SHAPE, "null tensor")
@@ -138,6 +141,36 @@ def debug_expire_wait():
 def xbuf_bytes(nz, rows):
     """Bytes of one rank's exchange buffer for the peer-memory merge of nz KV-length slices."""
     return int(_lib.q27b_xbuf_bytes(int(nz), ctypes.c_int64(int(rows))))
+
+
+def xbuf_alloc(nz, rows):
+    """Device address of a new zeroed exchange buffer (an allocation of its own, exportable over CUDA IPC)."""
+    out = ctypes.c_void_p(0)
+    _check(_lib.q27b_xbuf_alloc(int(nz), ctypes.c_int64(int(rows)), ctypes.byref(out)))
+    return int(out.value)
+
+
+def xbuf_free(ptr):
+    _check(_lib.q27b_xbuf_free(ctypes.c_void_p(int(ptr))))
+
+
+def ipc_export(ptr):
+    """The 64-byte CUDA IPC handle of an allocation."""
+    h = (ctypes.c_ubyte * 64)()
+    _check(_lib.q27b_ipc_export(ctypes.c_void_p(int(ptr)), h))
+    return bytes(h)
+
+
+def ipc_open(handle):
+    """Maps a peer's allocation into the current device's address space; returns the device address."""
+    h = (ctypes.c_ubyte * 64).from_buffer_copy(handle)
+    out = ctypes.c_void_p(0)
+    _check(_lib.q27b_ipc_open(h, ctypes.byref(out)))
+    return int(out.value)
+
+
+def ipc_close(ptr):
+    _check(_lib.q27b_ipc_close(ctypes.c_void_p(int(ptr))))
 
 
 def attn_decode_partial_push(qn, kcache, vcache, pos0, T, kq_scale, nqh, nkvh, n_ctx, base_pos, n_local, peer_ptrs,

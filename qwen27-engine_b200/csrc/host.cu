@@ -139,6 +139,50 @@ int q27b_debug_expire_wait(void* stream) {
   return Q27B_OK;
 }
 
+// ---- exchange buffers of the peer-memory merge, and their mapping between processes
+int q27b_xbuf_alloc(int nz, int64_t rows, void** out) {
+  if (!out || nz < 1 || nz > 8 || rows < 1) return fail(Q27B_BAD_SHAPE, "xbuf_alloc: bad shape");
+  const size_t bytes = 256 + 2ull * (size_t)nz * (size_t)rows * (Q27B_HEAD_DIM + 2) * sizeof(float);
+  void* p = nullptr;
+  Q27B_CK(cudaMalloc(&p, bytes));  // an allocation of its own: an IPC handle names whole allocations
+  Q27B_CK(cudaMemset(p, 0, bytes));
+  Q27B_CK(cudaDeviceSynchronize());
+  *out = p;
+  return Q27B_OK;
+}
+
+int q27b_xbuf_free(void* p) {
+  if (p) Q27B_CK(cudaFree(p));
+  return Q27B_OK;
+}
+
+int q27b_ipc_export(const void* ptr, unsigned char handle[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (!ptr || !handle) return fail(Q27B_BAD_SHAPE, "ipc_export: null pointer");
+  cudaIpcMemHandle_t h;
+  Q27B_CK(cudaIpcGetMemHandle(&h, const_cast<void*>(ptr)));
+  memcpy(handle, &h, 64);
+  return Q27B_OK;
+}
+
+// Maps a peer's buffer into the address space of the CURRENT device (the one whose kernels will store
+// into it), with peer access enabled as part of the mapping. A handle opened while another device is
+// current is not reachable from this one, whatever is enabled afterwards.
+int q27b_ipc_open(const unsigned char handle[64], void** out) {
+  if (!handle || !out) return fail(Q27B_BAD_SHAPE, "ipc_open: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  void* p = nullptr;
+  Q27B_CK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *out = p;
+  return Q27B_OK;
+}
+
+int q27b_ipc_close(void* p) {
+  if (p) Q27B_CK(cudaIpcCloseMemHandle(p));
+  return Q27B_OK;
+}
+
 uint64_t q27b_kv_cache_bytes(int nkvh, int n_ctx, int q8) {
   return q8 ? (uint64_t)nkvh * n_ctx * (Q27B_HEAD_DIM + 16) : (uint64_t)nkvh * n_ctx * Q27B_HEAD_DIM * 2;
 }

@@ -92,3 +92,16 @@ def gather_partials(part, shard, group=None):
         dist.all_gather(lst, part.contiguous(), group=group)
     return out
 
+
+
+def make_exchange(q, shard, group, rows):
+    """Exchange buffers for the peer-memory merge of a KV-length split (q27b_attn_decode_partial_push /
+    q27b_lse_merge_wait), one process per GPU: every rank of the head group allocates one, sends its
+    CUDA IPC handle to the group and maps the peers' handles with ITS OWN device current. Returns
+    (address of the own buffer, [address of rank k's buffer as seen from this GPU, k in group order])."""
+    own = q.xbuf_alloc(shard.nz, rows)
+    handles = [None] * shard.nz
+    dist.all_gather_object(handles, q.ipc_export(own), group=group)
+    peers = [own if k == shard.z else q.ipc_open(h) for k, h in enumerate(handles)]
+    dist.barrier(group=group)
+    return own, peers
