@@ -432,14 +432,14 @@ def strong_scaling(q, dist, rank, world, n, steps, warmup):
     if sh.nz > 1 and os.environ.get("Q27B_P2P_MERGE", "1") != "0":
         # the same exchange over peer memory: the merge kernel of each slice stores its rows into every
         # rank's exchange buffer and raises a flag; the final merge waits for the flags of its own buffer
-        try:
+        ok = torch.ones(1, device="cuda")
+        try:  # raises on every rank of the head group or on none
             own, peers = shard.make_exchange(q, sh, group, T * nq)
-            ok = torch.tensor([1], device="cuda")
-        except Exception as e:  # report, do not hide: the NCCL figure above stands
+        except RuntimeError as e:  # report, do not hide: the NCCL figure above stands
             out["p2p_error"] = str(e)
-            ok = torch.tensor([0], device="cuda")
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)  # all ranks take the same path
-        if int(ok.item()) == 0:
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)  # every rank of the job takes the same path
+        if ok.item() == 0:
             return out
         o2 = torch.empty((T, nq, AD), device="cuda")
 

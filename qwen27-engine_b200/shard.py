@@ -98,10 +98,26 @@ def make_exchange(q, shard, group, rows):
     """Exchange buffers for the peer-memory merge of a KV-length split (q27b_attn_decode_partial_push /
     q27b_lse_merge_wait), one process per GPU: every rank of the head group allocates one, sends its
     CUDA IPC handle to the group and maps the peers' handles with ITS OWN device current. Returns
-    (address of the own buffer, [address of rank k's buffer as seen from this GPU, k in group order])."""
-    own = q.xbuf_alloc(shard.nz, rows)
+    (address of the own buffer, [address of rank k's buffer as seen from this GPU, k in group order]).
+    If any rank of the group fails, every rank raises (the ranks agree before they return)."""
+    err, own, peers = None, 0, []
+    try:
+        own = q.xbuf_alloc(shard.nz, rows)
+        mine = q.ipc_export(own)
+    except Exception as e:  # still take part in the collectives below
+        err, mine = str(e), None
     handles = [None] * shard.nz
-    dist.all_gather_object(handles, q.ipc_export(own), group=group)
-    peers = [own if k == shard.z else q.ipc_open(h) for k, h in enumerate(handles)]
-    dist.barrier(group=group)
+    dist.all_gather_object(handles, mine, group=group)
+    if err is None and all(h is not None for h in handles):
+        try:
+            peers = [own if k == shard.z else q.ipc_open(h) for k, h in enumerate(handles)]
+        except Exception as e:
+            err = str(e)
+    elif err is None:
+        err = "a peer could not export its buffer"
+    errs = [None] * shard.nz
+    dist.all_gather_object(errs, err, group=group)
+    bad = [e for e in errs if e]
+    if bad:
+        raise RuntimeError("peer-memory exchange not available: " + bad[0])
     return own, peers
