@@ -49,7 +49,7 @@ constexpr int OFF_V = OFF_K + 2 * KST_PAD;
 constexpr int OFF_VF = OFF_V + 2 * KST_PAD;
 constexpr int OFF_P = OFF_VF + 2 * VF_BYTES;
 constexpr int OFF_DKF = OFF_P + 2 * P_BYTES;
-constexpr int OFF_DQ = OFF_DKF + 2 * DKF_BYTES;     // f32 Q scales [128 rows][8]
+constexpr int OFF_DQ = OFF_DKF + 2 * DKF_BYTES;     // f32 Q scales [8 blocks][128 rows] (a warp reads one block of 32 rows: no bank conflict)
 constexpr int OFF_XCH = OFF_DQ + QT * 8 * 4;        // row exchange between the two softmax warpgroups [tile parity][2][128] f32
 constexpr int OFF_BAR = OFF_XCH + 2 * 4 * QT * 4;   // room for four warpgroups
 constexpr int NBAR = 32;
@@ -253,7 +253,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
     const int t = t0 + r;
     const bool live = t < p.M;
     float* xch = (float*)(sgen + OFF_XCH);
-    const float* dqs = (const float*)(sgen + OFF_DQ + r * 32);
+    const float* dqs = (const float*)(sgen + OFF_DQ) + r;  // block b of this row at dqs[b * QT]
     {
       // this thread quantises 8 / NWG blocks of its row; the scales go through shared memory
       constexpr int NB = 8 / NWG;
@@ -269,7 +269,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
         else quantise_q_row<(3 * NB) % 8, NB>(src, p.kq_scale, sgen + OFF_Q, r, dqh);
       }
 #pragma unroll
-      for (int i = 0; i < NB; i++) *(float*)(sgen + OFF_DQ + (r * 8 + NB * wg + i) * 4) = dqh[i];
+      for (int i = 0; i < NB; i++) *(float*)(sgen + OFF_DQ + ((NB * wg + i) * QT + r) * 4) = dqh[i];
       fence_proxy_async();
       pair_sync(q);
       __syncwarp();
@@ -299,7 +299,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
         tc_fence_after();
         // The accumulators come in two halves of 16 columns: 16 registers fewer are live at a time
         // than with one 32-column load, and this kernel runs at its register limit.
-        const float dqv = dqs[b];  // this row's Q scale of block b (shared memory: eight registers fewer)
+        const float dqv = dqs[b * QT];  // this row's Q scale of block b (shared memory: eight registers fewer)
         const uint64_t dqb = pack2(dqv, dqv);
 #pragma unroll
         for (int hf = 0; hf < WCOLS / 16; hf++) {
