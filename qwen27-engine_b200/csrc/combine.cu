@@ -35,7 +35,8 @@ __device__ __forceinline__ RowMap map_decode(const MergeParams& p, int64_t row) 
   return {first, (size_t)MAXR * PROW, p.qg ? p.qg + row * 512 + 256 : nullptr};
 }
 
-template <bool DECODE_LAYOUT>
+// XCHG: the peer-memory exchange modes (push_n / wait_n of MergeParams) are compiled in.
+template <bool DECODE_LAYOUT, bool XCHG>
 __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
   pdl_wait();
   pdl_trigger();
@@ -46,8 +47,8 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
   RowMap rm = DECODE_LAYOUT ? map_decode(p, row) : map_generic(p, row);
   int np = p.nparts;
   int epoch = 0;
-  if (p.push_n > 0 || p.wait_n > 0) epoch = *(volatile int*)p.xbuf;
-  if (!DECODE_LAYOUT && p.wait_n > 0) {
+  if (XCHG && (p.push_n > 0 || p.wait_n > 0)) epoch = *(volatile int*)p.xbuf;
+  if (XCHG && !DECODE_LAYOUT && p.wait_n > 0) {
     // Slices of the other GPUs arrive by plain stores followed by a released flag: wait for the flags
     // of this step (bounded; a lost peer ends in the status word, not in a hang), then read.
     __shared__ int s_ok;
@@ -123,7 +124,7 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
   }
 
   const size_t oi = (size_t)row * AD + d;
-  if (!DECODE_LAYOUT && p.wait_n > 0 && d == 0) {
+  if (XCHG && !DECODE_LAYOUT && p.wait_n > 0 && d == 0) {
     // the last CTA of the step advances the epoch (nobody reads it again before the next launch)
     __threadfence();
     if (atomicAdd(p.xbuf + 2, 1) == (int)p.rows - 1) {
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
       *(volatile int*)p.xbuf = epoch + 1;
     }
   }
-  if (p.push_n > 0) {  // merged, not normalised, into slot push_z of every rank's exchange buffer
+  if (XCHG && p.push_n > 0) {  // merged, not normalised, into slot push_z of every rank's exchange buffer
     for (int k = 0; k < p.push_n; k++) {
       float* po = (float*)((uint8_t*)p.push_buf[k] + XBUF_HEADER_BYTES) +
                   (((size_t)(epoch & 1) * p.push_n + p.push_z) * p.rows + row) * PROW;
@@ -181,8 +182,12 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
 int launch_merge(const MergeParams& p, bool decode_layout, cudaStream_t s) {
   if (p.nparts < 1 || p.nparts > MAX_PARTS) return fail(Q27B_BAD_SHAPE, "lse_merge: 1..1024 partials");
   if (p.rows < 1) return Q27B_OK;
-  if (decode_layout) Q27B_CK(launch_pdl(merge_kernel<true>, dim3((unsigned)p.rows), dim3(AD), 0, s, p));
-  else Q27B_CK(launch_pdl(merge_kernel<false>, dim3((unsigned)p.rows), dim3(AD), 0, s, p));
+  const bool xchg = p.push_n > 0 || p.wait_n > 0;
+  const dim3 grid((unsigned)p.rows);
+  if (decode_layout && xchg) Q27B_CK(launch_pdl(merge_kernel<true, true>, grid, dim3(AD), 0, s, p));
+  else if (decode_layout) Q27B_CK(launch_pdl(merge_kernel<true, false>, grid, dim3(AD), 0, s, p));
+  else if (xchg) Q27B_CK(launch_pdl(merge_kernel<false, true>, grid, dim3(AD), 0, s, p));
+  else Q27B_CK(launch_pdl(merge_kernel<false, false>, grid, dim3(AD), 0, s, p));
   return Q27B_OK;
 }
 
