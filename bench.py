@@ -182,10 +182,10 @@ class RefLib:
         self._ck(self.lib.ref_attn_decode(self._p(qn), self._p(qg), self._p(kc), self._p(vc), self._p(o), None, None,
                                           self._p(pos), T_, ctypes.c_float(SCALE), nqh, nkvh, n_ctx, 1, s))
 
-    def prefill(self, qn, qg, kc, vc, o, pos, M, nqh, nkvh, n_ctx, hint):
+    def prefill(self, qn, qg, kc, vc, o, pos, M, nqh, nkvh, n_ctx, hint, q8=True):
         s = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         self._ck(self.lib.ref_attn_prefill(self._p(qn), self._p(qg), self._p(kc), self._p(vc), self._p(o), self._p(pos), M,
-                                           ctypes.c_float(SCALE), nqh, nkvh, n_ctx, 1, s, hint))
+                                           ctypes.c_float(SCALE), nqh, nkvh, n_ctx, int(q8), s, hint))
 
 
 def cpu_baseline(n=N_POS):
@@ -229,6 +229,7 @@ def main():
     ap.add_argument("--n", type=int, default=N_POS)
     ap.add_argument("--mode", default="decode", help="decode (the headline) or prefill (second half of the metric)")
     ap.add_argument("--prefix", type=int, default=32768, help="prefill mode: tokens already in the cache")
+    ap.add_argument("--kv", default="q8", help="prefill mode: q8 (int8 Q K^T on the q8_0 cache) or f16 (f16 Q K^T on an f16 cache)")
     args = ap.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     world = env_int("WORLD_SIZE", 1)
@@ -576,6 +577,17 @@ def extras(q, caches, qn, qg, o, n_ctx):
             out["prefill"][str(P)] = {"ms": ms, "tops": ops / (ms * 1e-3) / 1e12}
         except Exception as e:  # report, do not hide
             out["prefill"][str(P)] = {"error": str(e)}
+    # the same chunk on an f16 KV cache (f16 Q K^T and P V, no per-block scale arithmetic)
+    try:
+        P = 32768
+        f16c = fill_caches(q, NKVH, P + M, P + M + 64, 3002, q8=False)
+        pos.fill_(P)
+        ops = NQH * 1024.0 * (M * P + M * (M + 1) / 2)
+        ms = time_steps(lambda i: q.attn_prefill(pqn, pqg, f16c[0], f16c[1], po, pos, M, SCALE, NQH, NKVH, P + M + 64, False, P), 3, 3)
+        out["prefill_f16_cache"] = {str(P): {"ms": ms, "tflops": ops / (ms * 1e-3) / 1e12}}
+        del f16c
+    except Exception as e:  # report, do not hide
+        out["prefill_f16_cache"] = {"error": str(e)}
     out["device_status"] = q.device_status()
     try:
         out["batched_paged"] = batched_paged(q, 0, 1)
@@ -611,7 +623,8 @@ def prefill_mode(q, args, steps, warmup):
     (tools/bench_attn.cu:104): nqh * 1024 * (M * P + M (M + 1) / 2)."""
     M, P = 2048, args.prefix
     n_ctx = P + M + 8
-    kc, vc = fill_caches(q, NKVH, P + M, n_ctx, 1002)
+    q8 = args.kv != "f16"
+    kc, vc = fill_caches(q, NKVH, P + M, n_ctx, 1002, q8=q8)
     g = torch.Generator(device="cuda")
     g.manual_seed(3)
     qn = torch.randn((M, NQH, AD), generator=g, device="cuda")
@@ -623,9 +636,9 @@ def prefill_mode(q, args, steps, warmup):
 
     def step(i):
         if use_ref:
-            ref.prefill(qn, qg, kc, vc, o, pos, M, NQH, NKVH, n_ctx, P)
+            ref.prefill(qn, qg, kc, vc, o, pos, M, NQH, NKVH, n_ctx, P, q8)
         else:
-            q.attn_prefill(qn, qg, kc, vc, o, pos, M, SCALE, NQH, NKVH, n_ctx, True, P)
+            q.attn_prefill(qn, qg, kc, vc, o, pos, M, SCALE, NQH, NKVH, n_ctx, q8, P)
 
     sampler = ClockSampler(env_int("LOCAL_RANK", 0))
     sampler.start()
@@ -645,6 +658,13 @@ def prefill_mode(q, args, steps, warmup):
             "roofline": {"bound": "tensor", "achieved": tops, "peak": 2 * f16, "unit": "TOP/s",
                          "frac": tops / (2 * f16), "peak_kind": "2 x %s bf16 GEMM rate (sustained) as the int8 peak" % pk_kind,
                          "frac_of_mixed_int8_f16_bound": t_min_ms / ms, "traffic": None}}
+    if not q8:  # all of the ops on the f16 pipe
+        line["metric"] = "f16 prefill-attn TFLOPS (2048-token chunk, 24q/4kv heads, head dim 256, f16 prefix)"
+        line["unit"] = "TFLOP/s"
+        line["dtype"] = "f16 -> f32 (QK and PV)"
+        line["config"] = {"workload": "prefill chunk M=2048 on an f16 prefix of %d tokens" % P}
+        line["roofline"] = {"bound": "tensor", "achieved": tops, "peak": f16, "unit": "TFLOP/s", "frac": tops / f16,
+                            "peak_kind": "%s bf16 GEMM rate (sustained)" % pk_kind, "traffic": None}
     if use_ref:
         line["impl"] = "reference"
     if not use_ref:

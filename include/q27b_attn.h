@@ -206,6 +206,8 @@ uint64_t q27b_kv_pool_bytes(int nkvh, int n_pages);
  * cache), causal, o [M][nqh][256] f32 with the gate applied. q8_0 cache: Q K^T on the int8
  * tensor path (Q rounded to int8 with an f32 scale per 32 dims, K = the cache bytes, one int32
  * dot product per 32-dim block, scaled and summed in f32), P V in f16 with f32 accumulation.
+ * f16 cache (q8 = 0): Q * kq_scale rounded to f16, Q K^T and P V in f16 with f32 accumulation
+ * (attn_prefill_kernel<PT, false>, src/attn.cu:338-528).
  * depth_hint: host copy of *pos0 or -1. Replaces q27::attn_prefill (src/ops.h:68-72,
  * src/attn.cu:920-974; kernel attn_prefill_i8_kernel src/attn.cu:557-801). */
 int q27b_attn_prefill(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,

@@ -26,6 +26,7 @@
 // TMEM: columns 0-255 O (f32), 256-511 four S slots of 64 columns (s32).
 #include "combine.h"
 #include "common.cuh"
+#include "prefill_f16.h"
 
 #include <algorithm>
 
@@ -742,9 +743,11 @@ static int prefill_impl(const float* qn, const float* qg, const void* kcache, co
   if (nkvh < 1 || nqh != nkvh * GQA || M < 1 || n_ctx < 1) return fail(Q27B_BAD_SHAPE, "attn_prefill: bad shape");
   if (!qn || !qg || !kcache || !vcache || (!o && !xq) || (xq && !xd) || !pos0)
     return fail(Q27B_BAD_SHAPE, "attn_prefill: null pointer");
-  if (!q8) return fail(Q27B_UNSUPPORTED, "attn_prefill: only the q8_0 cache (int8 Q K^T path) is built");
   DeviceCtx* ctx;
   if (int rc = device_ctx(&ctx)) return rc;
+  if (!q8)  // f16 cache: the f16-QK kernel (the reference's attn_prefill_kernel<PT, false>, src/attn.cu:338-528)
+    return launch_prefill_f16(ctx, qn, qg, kcache, vcache, o, xq, xd, pos0, M, kq_scale, nqh, nkvh, n_ctx, depth_hint,
+                              (cudaStream_t)stream);
   if (int rc = prefill_setup(ctx)) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   const int tiles = (M + QT - 1) / QT;

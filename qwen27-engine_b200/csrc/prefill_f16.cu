@@ -1,0 +1,447 @@
+// Causal flash-attention prefill over an f16 KV cache: Q K^T and P V both on tcgen05.mma kind::f16.
+//
+// The f16-QK variant of the reference (attn_prefill_kernel<PT, false>, src/attn.cu:338-528, used
+// for f16 caches): Q * kq_scale rounded to f16, K and V as stored, S in f32, P -> f16, online
+// softmax. Unlike the reference, O accumulates in f32 (in TMEM), so its max offset (P <= 1/8,
+// src/attn.cu:323) is not needed; the reference max of a row moves only when the true max has
+// grown by more than TAU. The 64-position K and V tiles that TMA brings from the cache are the
+// operands of the tensor core as they land ([64-dim segment][position][128 B], 128-byte swizzle:
+// K-major for K, read MN-major for V): no converter warps, no per-block scale arithmetic.
+//
+// One CTA = 128 query tokens of one query head (TMEM lane = token) x one split of the positions.
+// Warps 0-7 softmax (two warpgroups, 32 columns of a tile each), warp 8 TMA producer, warp 9 MMA
+// issuer: per tile 16 x (128x64x16) into one of two S buffers, then 4 x (128x256x16) into O.
+// TMEM: columns 0-255 O (f32), 256-383 two S buffers of 64 columns (f32).
+#include "combine.h"
+#include "common.cuh"
+#include "prefill_f16.h"
+
+#include <algorithm>
+#include <cstdlib>
+
+namespace q27b {
+namespace {
+
+constexpr int QT = 128;          // query tokens per CTA
+constexpr int PT = 64;           // positions per tile
+constexpr float TAU = 5.0f;
+constexpr int SEGQ = QT * 128;   // one 64-dim segment of the Q tile: [128 rows][128 B]
+constexpr int SEGK = PT * 128;   // one 64-dim segment of a K or V tile: [64 positions][128 B]
+constexpr int KV_BYTES = 4 * SEGK;          // 32 KB
+constexpr int P_BYTES = QT * 128;           // f16 P: [128][64 positions]
+constexpr int OFF_Q = 0;                    // 64 KB
+constexpr int OFF_K = OFF_Q + 4 * SEGQ;     // two stages
+constexpr int OFF_V = OFF_K + 2 * KV_BYTES; // two stages
+constexpr int OFF_P = OFF_V + 2 * KV_BYTES; // one buffer
+constexpr int OFF_XCH = OFF_P + P_BYTES;    // [tile parity][2 warpgroups][128] f32
+constexpr int OFF_BAR = OFF_XCH + 2 * 2 * QT * 4;
+enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_SEMPTY = 11, B_PFULL = 13, B_PEMPTY = 14, B_ODONE = 15, NBAR = 16 };
+constexpr int OFF_MISC = OFF_BAR + NBAR * 8;
+constexpr int F16_SMEM_BYTES = OFF_MISC + 16 + 1024;
+static_assert(OFF_K % 1024 == 0 && OFF_V % 1024 == 0 && OFF_P % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+static_assert(F16_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+
+constexpr int N_SOFTMAX_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9;
+constexpr int F16_THREADS = 10 * 32;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TM_O = 0, TM_S = 256;
+constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, QT, PT);   // f32 += f16 * f16, both K-major, M128 N64
+constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, QT, AD);   // B (V) MN-major, M128 N256
+
+struct F16Params {
+  const float* qn;   // [M][nqh][256]
+  const float* qg;   // [M][nqh][512]
+  float* o;          // [M][nqh][256]
+  float* part;       // [nsplit][M][nqh][258] when nsplit > 1
+  const int* pos0;
+  int* status;
+  int M, nqh, nkvh, n_ctx, nsplit;
+  float kq_scale;
+};
+
+__device__ __forceinline__ void pair_sync(int q) { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); }
+
+// Rare, and kept out of line: inlined, its 32 registers of payload would sit on the loop's state.
+__device__ __noinline__ void rescale_o_f16(uint32_t taddr, float f) {
+#pragma unroll 1
+  for (int c = 0; c < 4; c++) {
+    uint32_t v[32];
+    tmem_ld32(taddr + c * 32, v);
+    tc_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+    tmem_st32(taddr + c * 32, v);
+  }
+}
+
+__global__ void __launch_bounds__(F16_THREADS, 1)
+prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const F16Params p) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  uint64_t* bar = (uint64_t*)(sgen + OFF_BAR);
+  uint32_t* tmem_slot = (uint32_t*)(sgen + OFF_MISC);
+  volatile int* abort_flag = (volatile int*)(sgen + OFF_MISC + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // CTA order: head by head, the query tiles with the most positions first (src/attn.cu:567)
+  const int n_tiles = (p.M + QT - 1) / QT;
+  const int L = (int)blockIdx.x;
+  const int h = L / n_tiles, kh = h / GQA;
+  const int t0 = (n_tiles - 1 - L % n_tiles) * QT;
+  const int z = blockIdx.z, nsplit = p.nsplit;
+  const int pos0 = *p.pos0;
+  const int n_end = min(pos0 + min(t0 + QT, p.M), p.n_ctx);
+  const int ntot = (n_end + PT - 1) / PT;
+  const int per = (ntot + nsplit - 1) / nsplit;
+  const int it0 = min(ntot, z * per), it1 = min(ntot, it0 + per);
+  const int nt = it1 - it0;
+
+  if (nt <= 0) {  // nothing in this split: neutral partials
+    if (nsplit > 1 && tid < QT && t0 + tid < p.M) {
+      float* po = p.part + (((size_t)z * p.M + t0 + tid) * p.nqh + h) * PROW;
+      po[0] = M_INIT;
+      po[1] = 0.f;
+      for (int d = 0; d < AD; d++) po[2 + d] = 0.f;
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    mbar_init(&bar[B_QFULL], N_SOFTMAX_WARPS);
+    for (int s = 0; s < 2; s++) {
+      mbar_init(&bar[B_KFULL + s], 1);
+      mbar_init(&bar[B_KEMPTY + s], 1);
+      mbar_init(&bar[B_VFULL + s], 1);
+      mbar_init(&bar[B_VEMPTY + s], 1);
+      mbar_init(&bar[B_SFULL + s], 1);
+      mbar_init(&bar[B_SEMPTY + s], N_SOFTMAX_WARPS);
+    }
+    mbar_init(&bar[B_PFULL], N_SOFTMAX_WARPS);
+    mbar_init(&bar[B_PEMPTY], 1);
+    mbar_init(&bar[B_ODONE], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp < N_SOFTMAX_WARPS) {
+    // ================================================================ softmax warps
+    const int wg = warp >> 2, q = warp & 3;
+    const int r = q * 32 + lane;       // query row = TMEM lane
+    const int t = t0 + r;
+    const bool live = t < p.M;
+    float* xch = (float*)(sgen + OFF_XCH);
+    {
+      // Q tile: this thread writes dims 128 wg .. 128 wg + 127 of its row (segments 2wg, 2wg + 1),
+      // scaled, f16, K-major with the 128-byte swizzle; rows past M are zero
+      const float* src = live ? p.qn + ((size_t)t * p.nqh + h) * AD + 128 * wg : nullptr;
+#pragma unroll
+      for (int sg = 0; sg < 2; sg++) {
+        uint8_t* dst = sgen + OFF_Q + (2 * wg + sg) * SEGQ;
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+          uint32_t w[4] = {0, 0, 0, 0};
+          if (src) {
+            const float4 a = *(const float4*)(src + sg * 64 + c * 8), b = *(const float4*)(src + sg * 64 + c * 8 + 4);
+            w[0] = pack_h2(a.x * p.kq_scale, a.y * p.kq_scale);
+            w[1] = pack_h2(a.z * p.kq_scale, a.w * p.kq_scale);
+            w[2] = pack_h2(b.x * p.kq_scale, b.y * p.kq_scale);
+            w[3] = pack_h2(b.z * p.kq_scale, b.w * p.kq_scale);
+          }
+          *(uint4*)(dst + swz128(r, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[B_QFULL]);
+    }
+
+    const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
+    const int limit = pos0 + t + 1;    // positions < limit are visible
+    const int col0 = wg * 32;          // this thread's positions of a tile
+    float m_run = M_INIT, m_ref = M_INIT;
+    uint64_t l2 = pack2(0.f, 0.f);
+    const uint64_t log2e2 = pack2(LOG2E, LOG2E);
+
+#pragma unroll 1
+    for (int j = 0; j < nt; j++) {
+      const int slot = j & 1;
+      const int p_tile = (it0 + j) * PT;
+      mbar_wait(&bar[B_SFULL + slot], (j >> 1) & 1, abort_flag, p.status);
+      tc_fence_after();
+      float s[32];
+      {
+        uint32_t v[32];
+        tmem_ld32(tlane + TM_S + slot * PT + col0, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i++) s[i] = __uint_as_float(v[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[B_SEMPTY + slot]);  // the buffer is in registers: it can be overwritten
+
+      // causal mask (only tiles that reach past the first row's limit need it) and this thread's max
+      if (p_tile + PT > pos0 + t0 + 1) {
+#pragma unroll
+        for (int i = 0; i < 32; i++)
+          if (p_tile + col0 + i >= limit) s[i] = -INFINITY;
+      }
+      float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        mq[0] = fmaxf(mq[0], s[i]);
+        mq[1] = fmaxf(mq[1], s[i + 1]);
+        mq[2] = fmaxf(mq[2], s[i + 2]);
+        mq[3] = fmaxf(mq[3], s[i + 3]);
+      }
+      float mt = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
+      // row maximum over the two threads of the row; the buffer alternates with the tile
+      xch[(slot * 2 + wg) * QT + r] = mt;
+      pair_sync(q);
+      mt = fmaxf(mt, xch[(slot * 2 + (wg ^ 1)) * QT + r]);
+      m_run = fmaxf(m_run, mt);
+
+      // Move the reference max when the true max has run away from it (and on the first tile). Both
+      // threads of a row hold the same m_run and m_ref, so both warps of a pair take the same branch.
+      const bool want = m_run > m_ref + TAU;
+      if (__any_sync(0xffffffffu, want)) {
+        const float f = ex2((m_ref - m_run) * LOG2E);  // 0 on the first move (m_ref = -1e30)
+        m_ref = m_run;
+        l2 = mul2(l2, pack2(f, f));
+        if (j > 0) {
+          // O holds the sum of tiles < j once the P V of tile j-1 has completed
+          mbar_wait(&bar[B_PEMPTY], (j - 1) & 1, abort_flag, p.status);
+          tc_fence_after();
+          rescale_o_f16(tlane + TM_O + wg * 128, f);
+          tc_wait_st();
+          tc_fence_before();
+        }
+      }
+
+      // P = exp(s - m_ref): f32 row sum, f16 half-tile for the P V MMA (chunks 4wg .. 4wg+3 of the row)
+      mbar_wait(&bar[B_PEMPTY], (j & 1) ^ 1, abort_flag, p.status);  // P V of tile j-1 has read the buffer
+      uint8_t* sP = sgen + OFF_P;
+      const float nmb = -m_ref * LOG2E;
+      const uint64_t nmb2 = pack2(nmb, nmb);
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          float a0, a1;
+          unpack2(fma2(pack2(s[c * 8 + 2 * k], s[c * 8 + 2 * k + 1]), log2e2, nmb2), a0, a1);
+          const float e0 = ex2(a0), e1 = ex2(a1);
+          l2 = add2(l2, pack2(e0, e1));
+          w[k] = pack_h2(e0, e1);
+        }
+        *(uint4*)(sP + swz128(r, 4 * wg + c)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      if (p_tile + PT > n_end) {
+        // The last tile reaches past the sequence: those cache rows hold whatever was there before
+        // (possibly NaN or Inf, and 0 * NaN = NaN in the P V product), so the V rows past the end are
+        // cleared in shared memory. Thread = (segment, position); a row of a segment is 128 bytes,
+        // and the swizzle only permutes within it.
+        mbar_wait(&bar[B_VFULL + slot], (j >> 1) & 1, abort_flag, p.status);
+        const int sg = tid >> 6, row = tid & 63;
+        if (p_tile + row >= n_end) {
+          uint4* vrow = (uint4*)(sgen + OFF_V + slot * KV_BYTES + sg * SEGK + row * 128);
+#pragma unroll
+          for (int c = 0; c < 8; c++) vrow[c] = make_uint4(0, 0, 0, 0);
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[B_PFULL]);
+    }
+
+    // ---- epilogue: O / l * sigmoid(gate), or the unnormalised partial of this split
+    float la, lb;
+    unpack2(l2, la, lb);
+    float l = la + lb;
+    xch[((nt & 1) * 2 + wg) * QT + r] = l;
+    pair_sync(q);
+    l += xch[((nt & 1) * 2 + (wg ^ 1)) * QT + r];
+    mbar_wait(&bar[B_ODONE], 0, abort_flag, p.status);
+    tc_fence_after();
+    const float inv_l = 1.0f / l;
+    float* po = nsplit > 1 ? p.part + (((size_t)z * p.M + t) * p.nqh + h) * PROW : nullptr;
+    if (live && po && wg == 0) {
+      po[0] = m_ref;
+      po[1] = l;
+    }
+#pragma unroll 1
+    for (int c = 0; c < 4; c++) {
+      const int d0 = wg * 128 + c * 32;
+      uint32_t v[32];
+      tmem_ld32(tlane + TM_O + d0, v);
+      tc_wait_ld();
+      if (!live) continue;
+      if (po) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          *(float2*)(po + 2 + d0 + i) = make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+      } else {
+        const float* gt = p.qg + ((size_t)t * p.nqh + h) * 512 + 256 + d0;
+        float* dst = p.o + ((size_t)t * p.nqh + h) * AD + d0;
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 gg = *(const float4*)(gt + i);
+          float4 y;
+          y.x = (__uint_as_float(v[i]) * inv_l) * (1.0f / (1.0f + __expf(-gg.x)));
+          y.y = (__uint_as_float(v[i + 1]) * inv_l) * (1.0f / (1.0f + __expf(-gg.y)));
+          y.z = (__uint_as_float(v[i + 2]) * inv_l) * (1.0f / (1.0f + __expf(-gg.z)));
+          y.w = (__uint_as_float(v[i + 3]) * inv_l) * (1.0f / (1.0f + __expf(-gg.w)));
+          *(float4*)(dst + i) = y;
+        }
+      }
+    }
+    tc_fence_before();
+  } else if (warp == TMA_WARP) {
+    // ================================================================ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+#pragma unroll 1
+      for (int j = 0; j < nt; j++) {
+        const int st = j & 1, ph = (j >> 1) & 1;
+        const int row = kh * p.n_ctx + (it0 + j) * PT;
+        uint8_t* ks = sgen + OFF_K + st * KV_BYTES;
+        uint8_t* vs = sgen + OFF_V + st * KV_BYTES;
+        mbar_wait(&bar[B_KEMPTY + st], ph ^ 1, abort_flag, p.status);
+        mbar_expect_tx(&bar[B_KFULL + st], KV_BYTES);
+#pragma unroll
+        for (int sg = 0; sg < 4; sg++) tma_load_2d(ks + sg * SEGK, &tm_k, sg * 128, row, &bar[B_KFULL + st]);
+        mbar_wait(&bar[B_VEMPTY + st], ph ^ 1, abort_flag, p.status);
+        mbar_expect_tx(&bar[B_VFULL + st], KV_BYTES);
+#pragma unroll
+        for (int sg = 0; sg < 4; sg++) tma_load_2d(vs + sg * SEGK, &tm_v, sg * 128, row, &bar[B_VFULL + st]);
+      }
+    }
+  } else {
+    // ================================================================ MMA issuer
+    if (lane == 0) {
+      mbar_wait(&bar[B_QFULL], 0, abort_flag, p.status);
+      tc_fence_after();
+      auto issue_pv = [&](int jj) {
+        const int st = jj & 1, ph = (jj >> 1) & 1;
+        mbar_wait(&bar[B_PFULL], jj & 1, abort_flag, p.status);
+        mbar_wait(&bar[B_VFULL + st], ph, abort_flag, p.status);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < PT / 16; kk++) {
+          const uint64_t da = umma_desc_sw128(sbase + OFF_P + kk * 32, 16, 1024);
+          const uint64_t db = umma_desc_sw128(sbase + OFF_V + st * KV_BYTES + kk * 2048, SEGK, 1024);
+          tc_mma_f16(tmem + TM_O, da, db, IDESC_PV, (jj > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&bar[B_PEMPTY]);
+        tc_commit(&bar[B_VEMPTY + st]);
+      };
+#pragma unroll 1
+      for (int j = 0; j < nt; j++) {
+        const int st = j & 1, ph = (j >> 1) & 1;
+        mbar_wait(&bar[B_KFULL + st], ph, abort_flag, p.status);
+        mbar_wait(&bar[B_SEMPTY + st], ph ^ 1, abort_flag, p.status);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < AD / 16; kk++) {
+          const uint64_t da = umma_desc_sw128(sbase + OFF_Q + (kk >> 2) * SEGQ + (kk & 3) * 32, 16, 1024);
+          const uint64_t db = umma_desc_sw128(sbase + OFF_K + st * KV_BYTES + (kk >> 2) * SEGK + (kk & 3) * 32, 16, 1024);
+          tc_mma_f16(tmem + TM_S + st * PT, da, db, IDESC_QK, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(&bar[B_SFULL + st]);
+        tc_commit(&bar[B_KEMPTY + st]);
+        if (j >= 1) issue_pv(j - 1);
+      }
+      issue_pv(nt - 1);
+      tc_commit(&bar[B_ODONE]);
+    }
+  }
+
+  drain_after_abort(abort_flag);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+struct TmapF16 {
+  const void* base;
+  int nkvh, n_ctx;
+  CUtensorMap map;
+};
+constexpr int TMAP_CACHE = 64;
+TmapF16 g_tmaps[TMAP_CACHE];
+int g_tmap_next = 0;
+
+int get_tmap(const void* cache, int nkvh, int n_ctx, const CUtensorMap** out) {
+  for (int i = 0; i < TMAP_CACHE; i++)
+    if (g_tmaps[i].base == cache && g_tmaps[i].nkvh == nkvh && g_tmaps[i].n_ctx == n_ctx) {
+      *out = &g_tmaps[i].map;
+      return Q27B_OK;
+    }
+  TmapF16& k = g_tmaps[g_tmap_next];
+  g_tmap_next = (g_tmap_next + 1) % TMAP_CACHE;
+  k.base = nullptr;
+  // rows of 512 bytes (256 halves), fetched as 128-byte wide, 64-row boxes with the 128-byte swizzle
+  if (int rc = make_tmap_2d(&k.map, cache, (uint64_t)nkvh * n_ctx, 2 * AD, 2 * AD, 128, PT, true)) return rc;
+  k.base = cache;
+  k.nkvh = nkvh;
+  k.n_ctx = n_ctx;
+  *out = &k.map;
+  return Q27B_OK;
+}
+
+}  // namespace
+
+int launch_prefill_f16(DeviceCtx* ctx, const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
+                       int8_t* xq, float* xd, const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx,
+                       int depth_hint, cudaStream_t s) {
+  static bool attr[64] = {};
+  if (!attr[ctx->dev]) {
+    Q27B_CK(cudaFuncSetAttribute(prefill_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F16_SMEM_BYTES));
+    attr[ctx->dev] = true;
+  }
+  const int tiles = (M + QT - 1) / QT;
+  const int ctas = tiles * nqh;
+  // splits over the positions as for the q8_0 kernel (the reference's rule, src/attn.cu:945-951); the
+  // q8_1 output is written by the merge kernel, so it needs the split path (at least one merge)
+  int nsplit = 1;
+  if (depth_hint >= 0) nsplit = std::max(1, std::min({8, (2 * ctx->n_sm + ctas - 1) / ctas, (depth_hint + M) / 2048}));
+  if (const char* e = getenv("Q27_ATTN_SPLIT")) {
+    const int f = atoi(e);
+    if (f > 0) nsplit = std::min(f, 64);
+  }
+  if (xq && nsplit < 2) nsplit = 2;
+  if (nsplit > 1)
+    if (int rc = ensure_part(ctx, (size_t)nsplit * M * nqh * PROW)) return rc;
+  const CUtensorMap *tk, *tv;
+  if (int rc = get_tmap(kcache, nkvh, n_ctx, &tk)) return rc;
+  if (int rc = get_tmap(vcache, nkvh, n_ctx, &tv)) return rc;
+  F16Params p = {};
+  p.qn = qn; p.qg = qg; p.o = o; p.part = nsplit > 1 ? ctx->part : nullptr; p.pos0 = pos0; p.status = ctx->status;
+  p.M = M; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nsplit = nsplit; p.kq_scale = kq_scale;
+  prefill_f16_kernel<<<dim3(tiles * nqh, 1, nsplit), F16_THREADS, F16_SMEM_BYTES, s>>>(*tk, *tv, p);
+  Q27B_CK(cudaGetLastError());
+  if (nsplit > 1) {
+    MergeParams mp = {};
+    mp.part = ctx->part; mp.nparts = nsplit; mp.part_stride = (int64_t)M * nqh * PROW; mp.rows = (int64_t)M * nqh;
+    mp.qg = qg; mp.o = o; mp.xq = xq; mp.xd = xd;
+    return launch_merge(mp, false, s);
+  }
+  return Q27B_OK;
+}
+
+}  // namespace q27b

@@ -130,3 +130,58 @@ def test_prefill_q8_1_epilogue(q27, orc, pos0, M, depth_hint):
     assert np.array_equal(xq.cpu().numpy().reshape(-1), rq)
     assert np.array_equal(xd.cpu().numpy(), rd)
     assert q27.device_status() == 0
+
+
+@pytest.mark.parametrize("pos0,M,depth_hint", [(0, 37, -1), (0, 128, -1), (1000, 64, -1), (5000, 128, 8000), (63, 2, -1),
+                                               (300, 200, -1), (129, 257, 4096)])
+def test_prefill_f16_cache(q27, orc, pos0, M, depth_hint):
+    """f16 KV cache: the f16-QK kernel (the reference's attn_prefill_kernel<PT, false>,
+    src/attn.cu:338-528) against the oracle's statement of the same numerics (Q*scale -> f16, K and V
+    as stored, f32 scores, P -> f16), with and without the split over the positions."""
+    from qwen27_engine_b200 import synth
+    nkvh = 2
+    nqh = nkvh * GQA
+    n = pos0 + M
+    n_ctx = n + 9
+    qn = synth.normal(synth.SEED_Q, (M, nqh, AD))
+    qg = np.zeros((M, nqh, 512), np.float32)
+    qg[..., 256:] = synth.normal(synth.SEED_GATE, (M, nqh, AD))
+    kf = synth.normal(synth.SEED_K, (nkvh, n, AD))
+    vf = synth.normal(synth.SEED_V, (nkvh, n, AD))
+    kc_ref, vc_ref = orc.fill_cache(kf, vf, n_ctx, q8=False)
+    kc_ref.view(np.uint16).reshape(nkvh, n_ctx, AD)[:, n:] = 0x7E00   # NaN rows past the sequence
+    vc_ref.view(np.uint16).reshape(nkvh, n_ctx, AD)[:, n:] = 0x7E00
+    o = torch.full((M, nqh, AD), float("nan"), device="cuda")
+    q27.attn_prefill(dev(qn), dev(qg), dev(kc_ref), dev(vc_ref), o, pos_tensor(pos0), M, SCALE, nqh, nkvh, n_ctx, False,
+                     depth_hint)
+    torch.cuda.synchronize()
+    ref = orc.attn_ref(qn, qg, kc_ref, vc_ref, pos0, SCALE, nkvh, n_ctx, q8=False)
+    assert_close(o.cpu().numpy(), ref, "f16-cache prefill pos0=%d M=%d" % (pos0, M))
+    assert q27.device_status() == 0
+
+
+def test_prefill_f16_cache_q8_1(q27, orc):
+    from qwen27_engine_b200 import synth
+    nkvh, pos0, M = 1, 500, 130
+    nqh = nkvh * GQA
+    n = pos0 + M
+    n_ctx = n + 5
+    qn = synth.normal(synth.SEED_Q, (M, nqh, AD))
+    qg = np.zeros((M, nqh, 512), np.float32)
+    qg[..., 256:] = synth.normal(synth.SEED_GATE, (M, nqh, AD))
+    kc_ref, vc_ref = orc.fill_cache(synth.normal(synth.SEED_K, (nkvh, n, AD)), synth.normal(synth.SEED_V, (nkvh, n, AD)),
+                                    n_ctx, q8=False)
+    kc, vc = dev(kc_ref), dev(vc_ref)
+    # the f32 result of the same (split) path, then its q8_1
+    o = torch.empty((M, nqh, AD), device="cuda")
+    os.environ["Q27_ATTN_SPLIT"] = "2"
+    try:
+        q27.attn_prefill(dev(qn), dev(qg), kc, vc, o, pos_tensor(pos0), M, SCALE, nqh, nkvh, n_ctx, False, -1)
+        xq = torch.zeros((M, nqh, AD), dtype=torch.int8, device="cuda")
+        xd = torch.zeros((M * nqh * 8,), dtype=torch.float32, device="cuda")
+        q27.attn_prefill_q8_1(dev(qn), dev(qg), kc, vc, xq, xd, pos_tensor(pos0), M, SCALE, nqh, nkvh, n_ctx, False, -1)
+        torch.cuda.synchronize()
+    finally:
+        del os.environ["Q27_ATTN_SPLIT"]
+    rq, rd = orc.q8_1(o.cpu().numpy().reshape(-1))
+    assert np.array_equal(xq.cpu().numpy().reshape(-1), rq) and np.array_equal(xd.cpu().numpy(), rd)
