@@ -252,7 +252,7 @@ def main():
 
     q = ge.load_package()
     if args.mode == "prefill":
-        prefill_mode(q, args, steps, warmup)
+        prefill_mode(q, args, steps, warmup, dist, rank, world)
         return
     line = {
         "metric": "q8_0 decode-attn HBM GB/s @150k ctx (4-token verify block, 24q/4kv heads, head dim 256)",
@@ -617,33 +617,41 @@ def extras(q, caches, qn, qg, o, n_ctx):
     return out
 
 
-def prefill_mode(q, args, steps, warmup):
+def prefill_mode(q, args, steps, warmup, dist=None, rank=0, world=1):
     """Second half of the metric: one 2048-token prefill chunk on a q8_0 prefix of --prefix tokens
     (int8 Q K^T, f16 P V). One step = one attn_prefill call; ops as the reference counts them
     (tools/bench_attn.cu:104): nqh * 1024 * (M * P + M (M + 1) / 2)."""
     M, P = 2048, args.prefix
     n_ctx = P + M + 8
     q8 = args.kv != "f16"
-    kc, vc = fill_caches(q, NKVH, P + M, n_ctx, 1002, q8=q8)
-    g = torch.Generator(device="cuda")
-    g.manual_seed(3)
-    qn = torch.randn((M, NQH, AD), generator=g, device="cuda")
-    qg = torch.randn((M, NQH, 512), generator=g, device="cuda")
-    o = torch.empty((M, NQH, AD), device="cuda")
-    pos = torch.tensor([P], dtype=torch.int32, device="cuda")
     use_ref = args.impl == "reference"
     ref = RefLib() if use_ref else None
+    # N > 1: the one chunk is shared out (strong scaling): KV-head groups, then query-token ranges within a
+    # group (shard.plan_prefill); every rank holds the K and V rows of its heads, nothing is exchanged
+    from qwen27_engine_b200 import shard
+    plan = shard.plan_prefill(rank, world, M, P, NKVH)
+    nkvh, nqh = plan.n_kv_heads, plan.n_kv_heads * GQA
+    kc, vc = fill_caches(q, nkvh, P + M, n_ctx, 1002 + plan.kv_head0, q8=q8)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3 + plan.kv_head0)
+    qn = torch.randn((M, nqh, AD), generator=g, device="cuda")
+    qg = torch.randn((M, nqh, 512), generator=g, device="cuda")
+    o = torch.empty((M, nqh, AD), device="cuda")
+    calls = [(a, b, torch.tensor([P + a], dtype=torch.int32, device="cuda")) for a, b in plan.ranges]
 
     def step(i):
-        if use_ref:
-            ref.prefill(qn, qg, kc, vc, o, pos, M, NQH, NKVH, n_ctx, P, q8)
-        else:
-            q.attn_prefill(qn, qg, kc, vc, o, pos, M, SCALE, NQH, NKVH, n_ctx, q8, P)
+        for a, b, pos in calls:
+            if use_ref:
+                ref.prefill(qn[a:b], qg[a:b], kc, vc, o[a:b], pos, b - a, nqh, nkvh, n_ctx, P + a, q8)
+            else:
+                q.attn_prefill(qn[a:b], qg[a:b], kc, vc, o[a:b], pos, b - a, SCALE, nqh, nkvh, n_ctx, q8, P + a)
 
     sampler = ClockSampler(env_int("LOCAL_RANK", 0))
     sampler.start()
-    ms = time_steps(step, steps, warmup)
+    ms = time_steps(step, steps, warmup, dist)
     clocks = sampler.stop()
+    if rank != 0:
+        return
     ops = NQH * 1024.0 * (M * P + M * (M + 1) / 2)
     tops = ops / (ms * 1e-3) / 1e12
     pk, pk_kind = peaks()
@@ -651,10 +659,11 @@ def prefill_mode(q, args, steps, warmup):
     # half of the ops run on the int8 pipe (taken as twice the measured 16-bit rate), half on the f16 pipe
     t_min_ms = (ops / 2 / (2 * f16 * 1e12) + ops / 2 / (f16 * 1e12)) * 1e3
     line = {"metric": "int8 prefill-attn TOPS (2048-token chunk, 24q/4kv heads, head dim 256, q8_0 prefix)",
-            "value": tops, "unit": "TOPS", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8 x s8 -> s32 (QK), f16 -> f32 (PV)",
+            "value": tops, "unit": "TOPS", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "s8 x s8 -> s32 (QK), f16 -> f32 (PV)",
             "data": "synthetic", "config": {"workload": "prefill chunk M=2048 on a q8_0 prefix of %d tokens" % P},
-            "gpu_launches": steps, "clocks": clocks,
+            "gpu_launches": steps * len(calls), "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": tops, "peak": 2 * f16, "unit": "TOP/s",
                          "frac": tops / (2 * f16), "peak_kind": "2 x %s bf16 GEMM rate (sustained) as the int8 peak" % pk_kind,
                          "frac_of_mixed_int8_f16_bound": t_min_ms / ms, "traffic": None}}
@@ -665,6 +674,12 @@ def prefill_mode(q, args, steps, warmup):
         line["config"] = {"workload": "prefill chunk M=2048 on an f16 prefix of %d tokens" % P}
         line["roofline"] = {"bound": "tensor", "achieved": tops, "peak": f16, "unit": "TFLOP/s", "frac": tops / f16,
                             "peak_kind": "%s bf16 GEMM rate (sustained)" % pk_kind, "traffic": None}
+    if world > 1:
+        line["config"]["sharding"] = "KV-head groups x %d query-token slices per group, no exchange; rank 0: heads %d..%d, tokens %s" % (
+            max(1, world // NKVH), plan.kv_head0, plan.kv_head0 + nkvh - 1, list(plan.ranges))
+        line["roofline"]["peak"] *= world
+        line["roofline"]["frac"] /= world
+        line["roofline"].pop("frac_of_mixed_int8_f16_bound", None)
     if use_ref:
         line["impl"] = "reference"
     if not use_ref:

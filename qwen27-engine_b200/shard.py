@@ -63,6 +63,64 @@ def shard_sequences(lengths, world):
     return [sorted(x) for x in out]
 
 
+@dataclass
+class PrefillShard:
+    rank: int
+    world: int
+    kv_head0: int     # first KV head of this rank
+    n_kv_heads: int   # KV heads of this rank
+    ranges: tuple     # query-token ranges [a, b) of the chunk this rank computes, ascending
+
+
+Q_TILE = 128
+
+
+def plan_prefill(rank, world, M, pos0=0, nkvh=4):
+    """One prefill chunk of M tokens over the ranks: KV-head groups first (the reference's split,
+    src/model.cu:161-164), then query-token ranges within a head group. Every rank of a head group
+    holds the group's K and V rows, so nothing is exchanged: outputs are disjoint [token][head]
+    slices. A token's cost grows with its position (causal), so the chunk is cut into 2 * nq blocks
+    of equal cost area and slice s takes blocks s and 2 nq - 1 - s (an early one and a late one);
+    block boundaries are multiples of the kernel's 128-token query tile. Each range is one
+    attn_prefill call at pos0 + a."""
+    if world < 1 or rank < 0 or rank >= world or M < 1:
+        raise ValueError("bad rank/world/M")
+    if world <= nkvh:
+        if nkvh % world:
+            raise ValueError("world must divide the KV heads")
+        per = nkvh // world
+        return PrefillShard(rank, world, rank * per, per, ((0, M),))
+    if world % nkvh:
+        raise ValueError("world must be a multiple of the KV heads")
+    nq = world // nkvh
+    hg, s = rank // nq, rank % nq
+    tiles = -(-M // Q_TILE)
+    nb = 2 * nq
+    # cost of tile i ~ positions it attends: pos0 + (i + 1) * Q_TILE; cuts at equal cumulative cost
+    cost = [pos0 + min(M, (i + 1) * Q_TILE) for i in range(tiles)]
+    total = float(sum(cost))
+    cuts, acc, k = [0], 0.0, 1
+    for i, c in enumerate(cost):
+        acc += c
+        while k < nb and acc >= total * k / nb - 1e-9:
+            cuts.append(i + 1)
+            k += 1
+    while len(cuts) < nb + 1:
+        cuts.append(tiles)
+    cuts[nb] = tiles
+    blocks = [(min(M, cuts[b] * Q_TILE), min(M, cuts[b + 1] * Q_TILE)) for b in range(nb)]
+    mine = sorted([blocks[s], blocks[nb - 1 - s]])
+    out = []
+    for a, b in mine:
+        if b <= a:
+            continue
+        if out and out[-1][1] == a:
+            out[-1] = (out[-1][0], b)
+        else:
+            out.append((a, b))
+    return PrefillShard(rank, world, hg, 1, tuple(out))
+
+
 _groups = {}
 
 

@@ -185,3 +185,40 @@ def test_prefill_f16_cache_q8_1(q27, orc):
         del os.environ["Q27_ATTN_SPLIT"]
     rq, rd = orc.q8_1(o.cpu().numpy().reshape(-1))
     assert np.array_equal(xq.cpu().numpy().reshape(-1), rq) and np.array_equal(xd.cpu().numpy(), rd)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("q8", [True, False])
+def test_prefill_sharded_over_ranks(q27, orc, world, q8):
+    """One chunk shared out by shard.plan_prefill (KV-head groups, then query-token ranges), the ranks
+    run one after the other on this GPU: every rank writes its [token][head] slice, nothing is exchanged."""
+    from qwen27_engine_b200 import shard, synth
+    pos0, M, nkvh = 700, 300, 4
+    nqh, n = nkvh * GQA, pos0 + M
+    n_ctx = n + 9
+    qn = synth.normal(synth.SEED_Q, (M, nqh, AD))
+    qg = np.zeros((M, nqh, 512), np.float32)
+    qg[..., 256:] = synth.normal(synth.SEED_GATE, (M, nqh, AD))
+    kf = synth.normal(synth.SEED_K, (nkvh, n, AD))
+    vf = synth.normal(synth.SEED_V, (nkvh, n, AD))
+    out = np.full((M, nqh, AD), np.nan, np.float32)
+    for r in range(world):
+        s = shard.plan_prefill(r, world, M, pos0, nkvh)
+        h0, nh = s.kv_head0, s.n_kv_heads
+        kc, vc = orc.fill_cache(kf[h0:h0 + nh], vf[h0:h0 + nh], n_ctx, q8=q8)
+        lq, lg = np.ascontiguousarray(qn[:, h0 * GQA:(h0 + nh) * GQA]), np.ascontiguousarray(qg[:, h0 * GQA:(h0 + nh) * GQA])
+        dq, dg, dk, dv = dev(lq), dev(lg), dev(kc), dev(vc)
+        o = torch.full((M, nh * GQA, AD), float("nan"), device="cuda")
+        for a, b in s.ranges:
+            q27.attn_prefill(dq[a:b], dg[a:b], dk, dv, o[a:b], pos_tensor(pos0 + a), b - a, SCALE, nh * GQA, nh, n_ctx, q8,
+                             depth_hint=pos0 + a)
+        torch.cuda.synchronize()
+        got = o.cpu().numpy()
+        for a, b in s.ranges:
+            assert np.isnan(out[a:b, h0 * GQA:(h0 + nh) * GQA]).all()  # nobody else wrote this slice
+            out[a:b, h0 * GQA:(h0 + nh) * GQA] = got[a:b]
+    kc, vc = orc.fill_cache(kf, vf, n_ctx, q8=q8)
+    ref = orc.attn_prefill_i8(qn, qg, kc, vc, pos0, SCALE, nkvh, n_ctx) if q8 else \
+        orc.attn_ref(qn, qg, kc, vc, pos0, SCALE, nkvh, n_ctx, q8=False)
+    assert_close(out, ref, "prefill over %d ranks" % world)
+    assert q27.device_status() == 0

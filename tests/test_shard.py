@@ -51,6 +51,28 @@ def test_shard_sequences_balance(q27):
         assert max(loads) - min(loads) <= int(lens.max())
 
 
+def test_plan_prefill_covers_every_token_once_and_balances(q27):
+    from qwen27_engine_b200 import shard
+    for M, pos0 in [(2048, 0), (2048, 32768), (2048, 148000), (300, 0), (100, 5), (129, 0), (1, 0)]:
+        for world in (1, 2, 4, 8, 16):
+            seen = {}
+            cost = {}
+            for r in range(world):
+                s = shard.plan_prefill(r, world, M, pos0, 4)
+                for a, b in s.ranges:
+                    assert 0 <= a < b <= M and (a % 128 == 0) and (b % 128 == 0 or b == M)
+                    for h in range(s.kv_head0, s.kv_head0 + s.n_kv_heads):
+                        for t in range(a, b, 64):
+                            assert (h, t) not in seen
+                            seen[(h, t)] = r
+                cost[r] = sum((b - a) * (2 * pos0 + a + b + 1) / 2 for a, b in s.ranges) * s.n_kv_heads
+            assert len(seen) == 4 * len(range(0, M, 64))
+            if M == 2048:  # an early and a late block per slice: close to each other (whole 128-token tiles)
+                assert max(cost.values()) <= (1.1 if world <= 8 else 1.25) * min(cost.values())
+    with pytest.raises(ValueError):
+        shard.plan_prefill(0, 3, 2048)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
