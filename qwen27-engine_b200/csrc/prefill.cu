@@ -98,10 +98,11 @@ struct PrefillParams {
   const float* qn;   // [M][nqh][256]
   const float* qg;   // [M][nqh][512]
   float* o;          // [M][nqh][256]
-  float* part;       // [nsplit][M][nqh][258] when nsplit > 1
+  float* part;       // [nsplit][Ms][nqh][258], Ms = min(M, 128 ts): the tokens whose positions are split
   const int* pos0;
   int* status;
-  int M, nqh, nkvh, n_ctx, nsplit;
+  int M, nqh, nkvh, n_ctx;
+  int ts, nsplit;    // query tiles [0, ts) are split nsplit ways over their positions, the others are not
   float kq_scale;
   int tile_major;  // CTA order, see the kernel
   int8_t* xq;      // q8_1 output instead of o: int8 [M][nqh][256] ...
@@ -195,11 +196,19 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
   // where the tiles differ a lot in length and the longest tiles of the last heads would start last.
   // Otherwise head by head (block L = tile rank L % n_tiles of head L / n_tiles), so that the CTAs
   // that run at the same time stream the same K/V rows and share them in L2 (measured: 7 % at 32k).
-  const int n_tiles = (p.M + QT - 1) / QT;
-  const int L = (int)blockIdx.x;
-  const int h = p.tile_major ? L % p.nqh : L / n_tiles, kh = h / GQA;
-  const int t0 = (n_tiles - 1 - (p.tile_major ? L / p.nqh : L % n_tiles)) * QT;
-  const int z = blockIdx.z, nsplit = p.nsplit;
+  // The unsplit CTAs (tiles >= ts) come first, then the pieces of the split tiles, split index slowest.
+  int L = (int)blockIdx.x, z = 0, nsplit = 1, ntl = (p.M + QT - 1) / QT - p.ts, tile_base = p.ts;
+  if (L >= ntl * p.nqh) {
+    L -= ntl * p.nqh;
+    ntl = p.ts;
+    tile_base = 0;
+    nsplit = p.nsplit;
+    z = L / (ntl * p.nqh);
+    L -= z * ntl * p.nqh;
+  }
+  const int h = p.tile_major ? L % p.nqh : L / ntl, kh = h / GQA;
+  const int t0 = (tile_base + ntl - 1 - (p.tile_major ? L / p.nqh : L % ntl)) * QT;
+  const int Ms = min(p.M, p.ts * QT);
   const int pos0 = *p.pos0;
   const int n_end = min(pos0 + min(t0 + QT, p.M), p.n_ctx);
   const int ntot = (n_end + PT - 1) / PT;
@@ -209,7 +218,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
 
   if (nt <= 0) {  // nothing in this split: neutral partials
     if (nsplit > 1 && tid < QT && t0 + tid < p.M) {
-      float* po = p.part + (((size_t)z * p.M + t0 + tid) * p.nqh + h) * PROW;
+      float* po = p.part + (((size_t)z * Ms + t0 + tid) * p.nqh + h) * PROW;
       po[0] = M_INIT;
       po[1] = 0.f;
       for (int d = 0; d < AD; d++) po[2 + d] = 0.f;
@@ -403,7 +412,7 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
     mbar_wait(&bar[B_ODONE], 0, abort_flag, p.status);
     tc_fence_after();
     const float inv_l = 1.0f / l;
-    float* po = nsplit > 1 ? p.part + (((size_t)z * p.M + t) * p.nqh + h) * PROW : nullptr;
+    float* po = nsplit > 1 ? p.part + (((size_t)z * Ms + t) * p.nqh + h) * PROW : nullptr;
     if (live && po && wg == 0) {
       po[0] = m_ref;
       po[1] = l;
@@ -751,29 +760,22 @@ static int prefill_impl(const float* qn, const float* qg, const void* kcache, co
   if (int rc = prefill_setup(ctx)) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   const int tiles = (M + QT - 1) / QT;
-  const int ctas = tiles * nqh;
-  // Splits over the positions: enough CTAs for every SM, at least 2048 positions per split
-  // (the reference's rule, src/attn.cu:945-951, with this kernel's CTA count).
-  int nsplit = 1;
-  if (depth_hint >= 0) nsplit = std::max(1, std::min({8, (2 * ctx->n_sm + ctas - 1) / ctas, (depth_hint + M) / 2048}));
-  if (const char* e = getenv("Q27_ATTN_SPLIT")) {  // same switch as the reference (src/attn.cu:952)
-    const int f = atoi(e);
-    if (f > 0) nsplit = std::min(f, 64);
-  }
+  const SplitPlan sp = plan_prefill_split(tiles, nqh, ctx->n_sm, M, depth_hint, false);
+  const int nsplit = sp.ns, Ms = std::min(M, sp.ts * QT);
   if (nsplit > 1)
-    if (int rc = ensure_part(ctx, (size_t)nsplit * M * nqh * PROW)) return rc;
+    if (int rc = ensure_part(ctx, (size_t)nsplit * Ms * nqh * PROW)) return rc;
   const CUtensorMap *kv, *ks, *vv, *vs;
   if (int rc = get_tmaps(kcache, nkvh, n_ctx, &kv, &ks)) return rc;
   if (int rc = get_tmaps(vcache, nkvh, n_ctx, &vv, &vs)) return rc;
   PrefillParams p = {};
   p.qn = qn; p.qg = qg; p.o = o; p.xq = xq; p.xd = xd; p.part = nsplit > 1 ? ctx->part : nullptr; p.pos0 = pos0; p.status = ctx->status;
-  p.M = M; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nsplit = nsplit; p.kq_scale = kq_scale;
+  p.M = M; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.ts = sp.ts; p.nsplit = nsplit; p.kq_scale = kq_scale;
   p.tile_major = depth_hint >= 0 && depth_hint < 4 * M;  // short prefix: the causal part dominates
-  prefill_i8_kernel<<<dim3(tiles * nqh, 1, nsplit), PF_THREADS, PF_SMEM_BYTES, s>>>(*kv, *ks, *vv, *vs, p);
+  prefill_i8_kernel<<<(tiles - sp.ts) * nqh + sp.ts * nqh * nsplit, PF_THREADS, PF_SMEM_BYTES, s>>>(*kv, *ks, *vv, *vs, p);
   Q27B_CK(cudaGetLastError());
-  if (nsplit > 1) {
+  if (nsplit > 1) {  // the split tokens are rows [0, Ms * nqh) of every array
     MergeParams mp = {};
-    mp.part = ctx->part; mp.nparts = nsplit; mp.part_stride = (int64_t)M * nqh * PROW; mp.rows = (int64_t)M * nqh;
+    mp.part = ctx->part; mp.nparts = nsplit; mp.part_stride = (int64_t)Ms * nqh * PROW; mp.rows = (int64_t)Ms * nqh;
     mp.qg = qg; mp.o = o; mp.xq = xq; mp.xd = xd;
     return launch_merge(mp, false, s);
   }

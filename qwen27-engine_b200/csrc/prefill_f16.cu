@@ -52,10 +52,11 @@ struct F16Params {
   const float* qn;   // [M][nqh][256]
   const float* qg;   // [M][nqh][512]
   float* o;          // [M][nqh][256]
-  float* part;       // [nsplit][M][nqh][258] when nsplit > 1
+  float* part;       // [nsplit][Ms][nqh][258], Ms = min(M, 128 ts): the tokens whose positions are split
   const int* pos0;
   int* status;
-  int M, nqh, nkvh, n_ctx, nsplit;
+  int M, nqh, nkvh, n_ctx;
+  int ts, nsplit;    // query tiles [0, ts) are split nsplit ways over their positions, the others are not
   float kq_scale;
 };
 
@@ -86,12 +87,21 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   volatile int* abort_flag = (volatile int*)(sgen + OFF_MISC + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // CTA order: head by head, the query tiles with the most positions first (src/attn.cu:567)
-  const int n_tiles = (p.M + QT - 1) / QT;
-  const int L = (int)blockIdx.x;
-  const int h = L / n_tiles, kh = h / GQA;
-  const int t0 = (n_tiles - 1 - L % n_tiles) * QT;
-  const int z = blockIdx.z, nsplit = p.nsplit;
+  // CTA order: the unsplit CTAs (tiles >= ts) first, then the pieces of the split tiles, split index
+  // slowest; within each class head by head, the query tiles with the most positions first
+  // (src/attn.cu:567)
+  int L = (int)blockIdx.x, z = 0, nsplit = 1, ntl = (p.M + QT - 1) / QT - p.ts, tile_base = p.ts;
+  if (L >= ntl * p.nqh) {
+    L -= ntl * p.nqh;
+    ntl = p.ts;
+    tile_base = 0;
+    nsplit = p.nsplit;
+    z = L / (ntl * p.nqh);
+    L -= z * ntl * p.nqh;
+  }
+  const int h = L / ntl, kh = h / GQA;
+  const int t0 = (tile_base + ntl - 1 - L % ntl) * QT;
+  const int Ms = min(p.M, p.ts * QT);
   const int pos0 = *p.pos0;
   const int n_end = min(pos0 + min(t0 + QT, p.M), p.n_ctx);
   const int ntot = (n_end + PT - 1) / PT;
@@ -101,7 +111,7 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
   if (nt <= 0) {  // nothing in this split: neutral partials
     if (nsplit > 1 && tid < QT && t0 + tid < p.M) {
-      float* po = p.part + (((size_t)z * p.M + t0 + tid) * p.nqh + h) * PROW;
+      float* po = p.part + (((size_t)z * Ms + t0 + tid) * p.nqh + h) * PROW;
       po[0] = M_INIT;
       po[1] = 0.f;
       for (int d = 0; d < AD; d++) po[2 + d] = 0.f;
@@ -275,7 +285,7 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     mbar_wait(&bar[B_ODONE], 0, abort_flag, p.status);
     tc_fence_after();
     const float inv_l = 1.0f / l;
-    float* po = nsplit > 1 ? p.part + (((size_t)z * p.M + t) * p.nqh + h) * PROW : nullptr;
+    float* po = nsplit > 1 ? p.part + (((size_t)z * Ms + t) * p.nqh + h) * PROW : nullptr;
     if (live && po && wg == 0) {
       po[0] = m_ref;
       po[1] = l;
@@ -415,29 +425,23 @@ int launch_prefill_f16(DeviceCtx* ctx, const float* qn, const float* qg, const v
     attr[ctx->dev] = true;
   }
   const int tiles = (M + QT - 1) / QT;
-  const int ctas = tiles * nqh;
-  // splits over the positions as for the q8_0 kernel (the reference's rule, src/attn.cu:945-951); the
-  // q8_1 output is written by the merge kernel, so it needs the split path (at least one merge)
-  int nsplit = 1;
-  if (depth_hint >= 0) nsplit = std::max(1, std::min({8, (2 * ctx->n_sm + ctas - 1) / ctas, (depth_hint + M) / 2048}));
-  if (const char* e = getenv("Q27_ATTN_SPLIT")) {
-    const int f = atoi(e);
-    if (f > 0) nsplit = std::min(f, 64);
-  }
-  if (xq && nsplit < 2) nsplit = 2;
+  // splits over the positions as for the q8_0 kernel; the q8_1 output is written by the merge kernel,
+  // so it needs every tile on the split path (at least one merge)
+  const SplitPlan sp = plan_prefill_split(tiles, nqh, ctx->n_sm, M, depth_hint, xq != nullptr);
+  const int nsplit = sp.ns, Ms = std::min(M, sp.ts * QT);
   if (nsplit > 1)
-    if (int rc = ensure_part(ctx, (size_t)nsplit * M * nqh * PROW)) return rc;
+    if (int rc = ensure_part(ctx, (size_t)nsplit * Ms * nqh * PROW)) return rc;
   const CUtensorMap *tk, *tv;
   if (int rc = get_tmap(kcache, nkvh, n_ctx, &tk)) return rc;
   if (int rc = get_tmap(vcache, nkvh, n_ctx, &tv)) return rc;
   F16Params p = {};
   p.qn = qn; p.qg = qg; p.o = o; p.part = nsplit > 1 ? ctx->part : nullptr; p.pos0 = pos0; p.status = ctx->status;
-  p.M = M; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nsplit = nsplit; p.kq_scale = kq_scale;
-  prefill_f16_kernel<<<dim3(tiles * nqh, 1, nsplit), F16_THREADS, F16_SMEM_BYTES, s>>>(*tk, *tv, p);
+  p.M = M; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.ts = sp.ts; p.nsplit = nsplit; p.kq_scale = kq_scale;
+  prefill_f16_kernel<<<(tiles - sp.ts) * nqh + sp.ts * nqh * nsplit, F16_THREADS, F16_SMEM_BYTES, s>>>(*tk, *tv, p);
   Q27B_CK(cudaGetLastError());
-  if (nsplit > 1) {
+  if (nsplit > 1) {  // the split tokens are rows [0, Ms * nqh) of every array
     MergeParams mp = {};
-    mp.part = ctx->part; mp.nparts = nsplit; mp.part_stride = (int64_t)M * nqh * PROW; mp.rows = (int64_t)M * nqh;
+    mp.part = ctx->part; mp.nparts = nsplit; mp.part_stride = (int64_t)Ms * nqh * PROW; mp.rows = (int64_t)Ms * nqh;
     mp.qg = qg; mp.o = o; mp.xq = xq; mp.xd = xd;
     return launch_merge(mp, false, s);
   }

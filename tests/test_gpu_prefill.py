@@ -222,3 +222,39 @@ def test_prefill_sharded_over_ranks(q27, orc, world, q8):
         orc.attn_ref(qn, qg, kc, vc, pos0, SCALE, nkvh, n_ctx, q8=False)
     assert_close(out, ref, "prefill over %d ranks" % world)
     assert q27.device_status() == 0
+
+
+@pytest.mark.parametrize("q8", [True, False])
+def test_prefill_tail_split(q27, orc, q8):
+    """More CTAs than SMs on a deep prefix: only the earliest query tile(s) are split over their
+    positions and merged, the others write their result directly. Checked on the token ranges around
+    the boundary between the two kinds and at the end of the chunk; the q8_1 form of the same call."""
+    from qwen27_engine_b200 import synth
+    nkvh, pos0, M = 4, 3600, 896      # 7 tiles x 24 heads = 168 CTAs, prefix >= 4 M
+    nqh, n = nkvh * GQA, pos0 + M
+    n_ctx = n + 9
+    qn = synth.normal(synth.SEED_Q, (M, nqh, AD))
+    qg = np.zeros((M, nqh, 512), np.float32)
+    qg[..., 256:] = synth.normal(synth.SEED_GATE, (M, nqh, AD))
+    kc_ref, vc_ref = orc.fill_cache(synth.normal(synth.SEED_K, (nkvh, n, AD)), synth.normal(synth.SEED_V, (nkvh, n, AD)),
+                                    n_ctx, q8=q8)
+    kc, vc = dev(kc_ref), dev(vc_ref)
+    o = torch.full((M, nqh, AD), float("nan"), device="cuda")
+    q27.attn_prefill(dev(qn), dev(qg), kc, vc, o, pos_tensor(pos0), M, SCALE, nqh, nkvh, n_ctx, q8, pos0)
+    torch.cuda.synchronize()
+    got = o.cpu().numpy()
+    assert np.isfinite(got).all()
+    for a, b in [(0, 8), (100, 160), (880, 896)]:
+        if q8:
+            ref = orc.attn_prefill_i8(qn, qg, kc_ref, vc_ref, pos0, SCALE, nkvh, n_ctx, a, b)[a:b]
+        else:
+            ref = orc.attn_ref(qn[a:b], qg[a:b], kc_ref, vc_ref, pos0 + a, SCALE, nkvh, n_ctx, q8=False)
+        assert_close(got[a:b], ref, "tail split tokens %d..%d" % (a, b))
+    if q8:  # unsplit tiles quantise in the kernel's epilogue, split tiles in the merge kernel
+        xq = torch.zeros((M, nqh, AD), dtype=torch.int8, device="cuda")
+        xd = torch.zeros((M * nqh * 8,), dtype=torch.float32, device="cuda")
+        q27.attn_prefill_q8_1(dev(qn), dev(qg), kc, vc, xq, xd, pos_tensor(pos0), M, SCALE, nqh, nkvh, n_ctx, q8, pos0)
+        torch.cuda.synchronize()
+        rq, rd = orc.q8_1(got.reshape(-1))
+        assert np.array_equal(xq.cpu().numpy().reshape(-1), rq) and np.array_equal(xd.cpu().numpy(), rd)
+    assert q27.device_status() == 0
