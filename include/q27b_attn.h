@@ -170,6 +170,14 @@ int q27b_lse_merge_wait(void* xbuf, int nz, int64_t rows, const float* qg, float
  * has one kernel). */
 int q27b_set_decode_kernel(int which);
 
+/* Which kernel q27b_attn_prefill* uses for q8_0 caches: 0 = default, 1 = int8 Q K^T
+ * (attn_prefill_i8_kernel, src/attn.cu:557-801; the reference's default), 2 = f16 Q K^T on K and V
+ * dequantised to f16 on the way to the tensor core (attn_prefill_kernel<PT, true>,
+ * src/attn.cu:338-528; the reference's Q27_ATTN_I8=0). Process-wide; the environment variable
+ * Q27_ATTN_I8=0 sets the initial value to 2, as in the reference (src/attn.cu:933). f16 caches
+ * always use the f16 kernel. */
+int q27b_set_prefill_kernel(int which);
+
 /* Test hook for the failure path, no counterpart in the reference: launches one warp that waits on
  * a barrier nobody arrives at, with the bounded wait every kernel of this library uses. After the
  * limit (about two seconds) the wait gives up, the kernel returns normally and

@@ -740,11 +740,32 @@ int prefill_setup(DeviceCtx* ctx) {
 }
 
 }  // namespace
+
+int get_q8_tmaps(const void* cache, int nkvh, int n_ctx, const CUtensorMap** vals, const CUtensorMap** scales) {
+  return get_tmaps(cache, nkvh, n_ctx, vals, scales);
+}
 }  // namespace q27b
 
 using namespace q27b;
 
+// Which kernel serves a q8_0 cache: int8 Q K^T (default, as the reference since its Q27_ATTN_I8
+// default) or the f16-QK kernel on dequantised K and V (the reference's Q27_ATTN_I8=0).
+static int g_prefill_choice = -1;  // -1: not read yet; 0 default, 1 int8 Q K^T, 2 f16 Q K^T
+static bool use_f16_qk() {
+  if (g_prefill_choice < 0) {
+    const char* e = getenv("Q27_ATTN_I8");
+    g_prefill_choice = e && e[0] == '0' ? 2 : 0;
+  }
+  return g_prefill_choice == 2;
+}
+
 extern "C" {
+
+int q27b_set_prefill_kernel(int which) {
+  if (which < 0 || which > 2) return fail(Q27B_BAD_SHAPE, "set_prefill_kernel: 0 auto, 1 int8 QK, 2 f16 QK");
+  g_prefill_choice = which;
+  return Q27B_OK;
+}
 
 static int prefill_impl(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o, int8_t* xq,
                         float* xd, const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, int q8,
@@ -754,9 +775,9 @@ static int prefill_impl(const float* qn, const float* qg, const void* kcache, co
     return fail(Q27B_BAD_SHAPE, "attn_prefill: null pointer");
   DeviceCtx* ctx;
   if (int rc = device_ctx(&ctx)) return rc;
-  if (!q8)  // f16 cache: the f16-QK kernel (the reference's attn_prefill_kernel<PT, false>, src/attn.cu:338-528)
-    return launch_prefill_f16(ctx, qn, qg, kcache, vcache, o, xq, xd, pos0, M, kq_scale, nqh, nkvh, n_ctx, depth_hint,
-                              (cudaStream_t)stream);
+  if (!q8 || use_f16_qk())  // the f16-QK kernel (the reference's attn_prefill_kernel<PT, Q8>, src/attn.cu:338-528)
+    return launch_prefill_f16(ctx, qn, qg, kcache, vcache, o, xq, xd, pos0, M, kq_scale, nqh, nkvh, n_ctx, q8 != 0,
+                              depth_hint, (cudaStream_t)stream);
   if (int rc = prefill_setup(ctx)) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   const int tiles = (M + QT - 1) / QT;

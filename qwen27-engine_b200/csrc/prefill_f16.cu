@@ -12,6 +12,12 @@
 // Warps 0-7 softmax (two warpgroups, 32 columns of a tile each), warp 8 TMA producer, warp 9 MMA
 // issuer: per tile 16 x (128x64x16) into one of two S buffers, then 4 x (128x256x16) into O.
 // TMEM: columns 0-255 O (f32), 256-383 two S buffers of 64 columns (f32).
+//
+// Q8 = true: the same on a q8_0 cache, the reference's path with Q27_ATTN_I8=0
+// (attn_prefill_kernel<PT, true>, src/attn.cu:338-528): K and V are dequantised to f16 (q * d rounded
+// once, cvt_q8_16 src/attn.cu:59-76) on their way to the tensor core. TMA brings the int8 tiles and
+// their scales into raw stages, warps 10-13 turn K and warps 14-17 turn V into the f16 operand
+// layout above (one f16 buffer each, two raw stages each).
 #include "combine.h"
 #include "common.cuh"
 #include "prefill_f16.h"
@@ -29,20 +35,30 @@ constexpr int SEGQ = QT * 128;   // one 64-dim segment of the Q tile: [128 rows]
 constexpr int SEGK = PT * 128;   // one 64-dim segment of a K or V tile: [64 positions][128 B]
 constexpr int KV_BYTES = 4 * SEGK;          // 32 KB
 constexpr int P_BYTES = QT * 128;           // f16 P: [128][64 positions]
-constexpr int OFF_Q = 0;                    // 64 KB
-constexpr int OFF_K = OFF_Q + 4 * SEGQ;     // two stages
-constexpr int OFF_V = OFF_K + 2 * KV_BYTES; // two stages
-constexpr int OFF_P = OFF_V + 2 * KV_BYTES; // one buffer
-constexpr int OFF_XCH = OFF_P + P_BYTES;    // [tile parity][2 warpgroups][128] f32
-constexpr int OFF_BAR = OFF_XCH + 2 * 2 * QT * 4;
-enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_SEMPTY = 11, B_PFULL = 13, B_PEMPTY = 14, B_ODONE = 15, NBAR = 16 };
-constexpr int OFF_MISC = OFF_BAR + NBAR * 8;
-constexpr int F16_SMEM_BYTES = OFF_MISC + 16 + 1024;
-static_assert(OFF_K % 1024 == 0 && OFF_V % 1024 == 0 && OFF_P % 1024 == 0, "swizzled tiles need 1024-byte alignment");
-static_assert(F16_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+constexpr int RAW_BYTES = 2 * PT * 128 + PT * 16;  // q8_0 tile: two 128-dim int8 segments [64][128 B], then [64][8] f16 scales
+// Shared memory. f16 cache: two K and two V stages, filled by TMA. q8_0 cache: one f16 K and one f16 V
+// buffer, filled by the converter warps from two raw stages each.
+template <bool Q8>
+struct Lay {
+  static constexpr int NKF = Q8 ? 1 : 2;
+  static constexpr int OFF_Q = 0;                          // 64 KB
+  static constexpr int OFF_K = OFF_Q + 4 * SEGQ;
+  static constexpr int OFF_V = OFF_K + NKF * KV_BYTES;
+  static constexpr int OFF_P = OFF_V + NKF * KV_BYTES;     // one buffer
+  static constexpr int OFF_RAW = OFF_P + P_BYTES;          // q8_0: K stage 0, 1, V stage 0, 1
+  static constexpr int OFF_XCH = OFF_RAW + (Q8 ? 4 * RAW_BYTES : 0);  // [tile parity][2 warpgroups][128] f32
+  static constexpr int OFF_BAR = OFF_XCH + 2 * 2 * QT * 4;
+  static constexpr int OFF_MISC = OFF_BAR + 24 * 8;
+  static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;
+  static constexpr int THREADS = (Q8 ? 18 : 10) * 32;
+  static_assert(OFF_K % 1024 == 0 && OFF_V % 1024 == 0 && OFF_P % 1024 == 0 && OFF_RAW % 1024 == 0 && RAW_BYTES % 1024 == 0,
+                "swizzled tiles need 1024-byte alignment");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+};
+enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_SEMPTY = 11, B_PFULL = 13, B_PEMPTY = 14, B_ODONE = 15,
+       B_RKFULL = 16, B_RKEMPTY = 18, B_RVFULL = 20, B_RVEMPTY = 22, NBAR = 24 };
 
-constexpr int N_SOFTMAX_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9;
-constexpr int F16_THREADS = 10 * 32;
+constexpr int N_SOFTMAX_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9, KCONV_WARP0 = 10, VCONV_WARP0 = 14, N_CONV_WARPS = 4;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_O = 0, TM_S = 256;
 constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, QT, PT);   // f32 += f16 * f16, both K-major, M128 N64
@@ -75,8 +91,55 @@ __device__ __noinline__ void rescale_o_f16(uint32_t taddr, float f) {
   }
 }
 
-__global__ void __launch_bounds__(F16_THREADS, 1)
-prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const F16Params p) {
+// One tile of a q8_0 cache, raw stage -> f16 operand buffer. 128 threads; item = (row, 16-dim chunk);
+// eight neighbouring lanes take 4 chunks of rows rho and rho ^ 5, which keeps both the swizzled
+// 16-byte loads and the swizzled 16-byte stores free of bank conflicts. Rows >= zero_from are cleared
+// (rows past the sequence may hold anything: P is 0 there, V must be too).
+__device__ __forceinline__ void convert_q8_tile(const uint8_t* raw, uint8_t* dst_tile, int ct, int zero_from) {
+#pragma unroll 1
+  for (int k0 = 0; k0 < 8; k0 += 4) {
+    // loads of four items first: a shared-memory load is never moved above an earlier store
+    uint4 x[4];
+    __half d[4];
+    int row[4], c16[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const int item = ct + 128 * (k0 + k);
+      row[k] = (2 * (item >> 5)) ^ (5 * ((item >> 2) & 1));
+      c16[k] = (item & 3) + 4 * ((item >> 3) & 3);
+      x[k] = *(const uint4*)(raw + (c16[k] >> 3) * (PT * 128) + swz128(row[k], c16[k] & 7));
+      d[k] = *(const __half*)(raw + 2 * PT * 128 + row[k] * 16 + (c16[k] >> 1) * 2);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const __half2 dd = __half2half2(d[k]);
+      const uint32_t xw[4] = {x[k].x ^ 0x80808080u, x[k].y ^ 0x80808080u, x[k].z ^ 0x80808080u, x[k].w ^ 0x80808080u};
+      uint32_t o[8];
+#pragma unroll
+      for (int w = 0; w < 4; w++) {
+        o[2 * w] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4140), dd);
+        o[2 * w + 1] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4342), dd);
+      }
+      if (row[k] >= zero_from) {
+#pragma unroll
+        for (int w = 0; w < 8; w++) o[w] = 0;
+      }
+      uint8_t* dst = dst_tile + (c16[k] >> 2) * SEGK;
+      const uint32_t cc = 2 * (c16[k] & 3);
+      *(uint4*)(dst + swz128(row[k], cc)) = make_uint4(o[0], o[1], o[2], o[3]);
+      *(uint4*)(dst + swz128(row[k], cc + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+  }
+}
+
+// tm_k, tm_v: f16 cache rows (f16 cache) or the int8 values (q8_0 cache); tm_ks, tm_vs: the q8_0 scales.
+template <bool Q8>
+__global__ void __launch_bounds__(Lay<Q8>::THREADS, 1)
+prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                   const __grid_constant__ CUtensorMap tm_ks, const __grid_constant__ CUtensorMap tm_vs, const F16Params p) {
+  using LY = Lay<Q8>;
+  constexpr int OFF_Q = LY::OFF_Q, OFF_K = LY::OFF_K, OFF_V = LY::OFF_V, OFF_P = LY::OFF_P, OFF_RAW = LY::OFF_RAW,
+                OFF_XCH = LY::OFF_XCH, OFF_BAR = LY::OFF_BAR, OFF_MISC = LY::OFF_MISC;
   pdl_wait();
   pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
@@ -122,12 +185,16 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   if (tid == 0) {
     mbar_init(&bar[B_QFULL], N_SOFTMAX_WARPS);
     for (int s = 0; s < 2; s++) {
-      mbar_init(&bar[B_KFULL + s], 1);
+      mbar_init(&bar[B_KFULL + s], Q8 ? N_CONV_WARPS : 1);  // q8_0: the converter warps fill buffer 0
       mbar_init(&bar[B_KEMPTY + s], 1);
-      mbar_init(&bar[B_VFULL + s], 1);
+      mbar_init(&bar[B_VFULL + s], Q8 ? N_CONV_WARPS : 1);
       mbar_init(&bar[B_VEMPTY + s], 1);
       mbar_init(&bar[B_SFULL + s], 1);
       mbar_init(&bar[B_SEMPTY + s], N_SOFTMAX_WARPS);
+      mbar_init(&bar[B_RKFULL + s], 1);
+      mbar_init(&bar[B_RKEMPTY + s], N_CONV_WARPS);
+      mbar_init(&bar[B_RVFULL + s], 1);
+      mbar_init(&bar[B_RVEMPTY + s], N_CONV_WARPS);
     }
     mbar_init(&bar[B_PFULL], N_SOFTMAX_WARPS);
     mbar_init(&bar[B_PEMPTY], 1);
@@ -257,7 +324,7 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
         *(uint4*)(sP + swz128(r, 4 * wg + c)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      if (p_tile + PT > n_end) {
+      if (!Q8 && p_tile + PT > n_end) {
         // The last tile reaches past the sequence: those cache rows hold whatever was there before
         // (possibly NaN or Inf, and 0 * NaN = NaN in the P V product), so the V rows past the end are
         // cleared in shared memory. Thread = (segment, position); a row of a segment is 128 bytes,
@@ -322,29 +389,69 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     if (lane == 0) {
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
+      if (Q8) {
+        tma_prefetch_desc(&tm_ks);
+        tma_prefetch_desc(&tm_vs);
+      }
 #pragma unroll 1
       for (int j = 0; j < nt; j++) {
         const int st = j & 1, ph = (j >> 1) & 1;
         const int row = kh * p.n_ctx + (it0 + j) * PT;
-        uint8_t* ks = sgen + OFF_K + st * KV_BYTES;
-        uint8_t* vs = sgen + OFF_V + st * KV_BYTES;
-        mbar_wait(&bar[B_KEMPTY + st], ph ^ 1, abort_flag, p.status);
-        mbar_expect_tx(&bar[B_KFULL + st], KV_BYTES);
+        if constexpr (Q8) {
+          uint8_t* kr = sgen + OFF_RAW + st * RAW_BYTES;
+          uint8_t* vr = sgen + OFF_RAW + (2 + st) * RAW_BYTES;
+          mbar_wait(&bar[B_RKEMPTY + st], ph ^ 1, abort_flag, p.status);
+          mbar_expect_tx(&bar[B_RKFULL + st], RAW_BYTES);
+          tma_load_2d(kr, &tm_k, 0, row, &bar[B_RKFULL + st]);
+          tma_load_2d(kr + PT * 128, &tm_k, 128, row, &bar[B_RKFULL + st]);
+          tma_load_2d(kr + 2 * PT * 128, &tm_ks, 0, row, &bar[B_RKFULL + st]);
+          mbar_wait(&bar[B_RVEMPTY + st], ph ^ 1, abort_flag, p.status);
+          mbar_expect_tx(&bar[B_RVFULL + st], RAW_BYTES);
+          tma_load_2d(vr, &tm_v, 0, row, &bar[B_RVFULL + st]);
+          tma_load_2d(vr + PT * 128, &tm_v, 128, row, &bar[B_RVFULL + st]);
+          tma_load_2d(vr + 2 * PT * 128, &tm_vs, 0, row, &bar[B_RVFULL + st]);
+        } else {
+          uint8_t* ks = sgen + OFF_K + st * KV_BYTES;
+          uint8_t* vs = sgen + OFF_V + st * KV_BYTES;
+          mbar_wait(&bar[B_KEMPTY + st], ph ^ 1, abort_flag, p.status);
+          mbar_expect_tx(&bar[B_KFULL + st], KV_BYTES);
 #pragma unroll
-        for (int sg = 0; sg < 4; sg++) tma_load_2d(ks + sg * SEGK, &tm_k, sg * 128, row, &bar[B_KFULL + st]);
-        mbar_wait(&bar[B_VEMPTY + st], ph ^ 1, abort_flag, p.status);
-        mbar_expect_tx(&bar[B_VFULL + st], KV_BYTES);
+          for (int sg = 0; sg < 4; sg++) tma_load_2d(ks + sg * SEGK, &tm_k, sg * 128, row, &bar[B_KFULL + st]);
+          mbar_wait(&bar[B_VEMPTY + st], ph ^ 1, abort_flag, p.status);
+          mbar_expect_tx(&bar[B_VFULL + st], KV_BYTES);
 #pragma unroll
-        for (int sg = 0; sg < 4; sg++) tma_load_2d(vs + sg * SEGK, &tm_v, sg * 128, row, &bar[B_VFULL + st]);
+          for (int sg = 0; sg < 4; sg++) tma_load_2d(vs + sg * SEGK, &tm_v, sg * 128, row, &bar[B_VFULL + st]);
+        }
       }
     }
-  } else {
+  } else if (Q8 && warp >= KCONV_WARP0) {
+    // ================================================================ converter warps (q8_0 cache)
+    const bool is_v = warp >= VCONV_WARP0;
+    const int ct = tid - (is_v ? VCONV_WARP0 : KCONV_WARP0) * 32;
+    uint8_t* dst = sgen + (is_v ? OFF_V : OFF_K);
+    const int b_rfull = is_v ? B_RVFULL : B_RKFULL, b_rempty = is_v ? B_RVEMPTY : B_RKEMPTY;
+    const int b_full = is_v ? B_VFULL : B_KFULL, b_empty = is_v ? B_VEMPTY : B_KEMPTY;
+#pragma unroll 1
+    for (int j = 0; j < nt; j++) {
+      const int st = j & 1;
+      mbar_wait(&bar[b_rfull + st], (j >> 1) & 1, abort_flag, p.status);
+      mbar_wait(&bar[b_empty], (j & 1) ^ 1, abort_flag, p.status);  // the MMAs of tile j-1 have read the buffer
+      convert_q8_tile(sgen + OFF_RAW + ((is_v ? 2 : 0) + st) * RAW_BYTES, dst, ct, is_v ? n_end - (it0 + j) * PT : PT);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bar[b_full]);
+        mbar_arrive(&bar[b_rempty + st]);
+      }
+    }
+  } else if (warp == MMA_WARP) {
     // ================================================================ MMA issuer
     if (lane == 0) {
       mbar_wait(&bar[B_QFULL], 0, abort_flag, p.status);
       tc_fence_after();
+      // operand buffer and phase of tile j: two TMA stages (f16 cache) or the one converted buffer (q8_0)
       auto issue_pv = [&](int jj) {
-        const int st = jj & 1, ph = (jj >> 1) & 1;
+        const int st = Q8 ? 0 : jj & 1, ph = Q8 ? jj & 1 : (jj >> 1) & 1;
         mbar_wait(&bar[B_PFULL], jj & 1, abort_flag, p.status);
         mbar_wait(&bar[B_VFULL + st], ph, abort_flag, p.status);
         tc_fence_after();
@@ -359,17 +466,18 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       };
 #pragma unroll 1
       for (int j = 0; j < nt; j++) {
-        const int st = j & 1, ph = (j >> 1) & 1;
+        const int ss = j & 1, sph = (j >> 1) & 1;                         // S buffer
+        const int st = Q8 ? 0 : j & 1, ph = Q8 ? j & 1 : (j >> 1) & 1;   // K buffer
         mbar_wait(&bar[B_KFULL + st], ph, abort_flag, p.status);
-        mbar_wait(&bar[B_SEMPTY + st], ph ^ 1, abort_flag, p.status);
+        mbar_wait(&bar[B_SEMPTY + ss], sph ^ 1, abort_flag, p.status);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < AD / 16; kk++) {
           const uint64_t da = umma_desc_sw128(sbase + OFF_Q + (kk >> 2) * SEGQ + (kk & 3) * 32, 16, 1024);
           const uint64_t db = umma_desc_sw128(sbase + OFF_K + st * KV_BYTES + (kk >> 2) * SEGK + (kk & 3) * 32, 16, 1024);
-          tc_mma_f16(tmem + TM_S + st * PT, da, db, IDESC_QK, kk > 0 ? 1u : 0u);
+          tc_mma_f16(tmem + TM_S + ss * PT, da, db, IDESC_QK, kk > 0 ? 1u : 0u);
         }
-        tc_commit(&bar[B_SFULL + st]);
+        tc_commit(&bar[B_SFULL + ss]);
         tc_commit(&bar[B_KEMPTY + st]);
         if (j >= 1) issue_pv(j - 1);
       }
@@ -417,27 +525,39 @@ int get_tmap(const void* cache, int nkvh, int n_ctx, const CUtensorMap** out) {
 }  // namespace
 
 int launch_prefill_f16(DeviceCtx* ctx, const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
-                       int8_t* xq, float* xd, const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx,
+                       int8_t* xq, float* xd, const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, bool q8,
                        int depth_hint, cudaStream_t s) {
   static bool attr[64] = {};
   if (!attr[ctx->dev]) {
-    Q27B_CK(cudaFuncSetAttribute(prefill_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F16_SMEM_BYTES));
+    Q27B_CK(cudaFuncSetAttribute(prefill_f16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<false>::SMEM_BYTES));
+    Q27B_CK(cudaFuncSetAttribute(prefill_f16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<true>::SMEM_BYTES));
     attr[ctx->dev] = true;
   }
   const int tiles = (M + QT - 1) / QT;
-  // splits over the positions as for the q8_0 kernel; the q8_1 output is written by the merge kernel,
+  // splits over the positions as for the int8 kernel; the q8_1 output is written by the merge kernel,
   // so it needs every tile on the split path (at least one merge)
   const SplitPlan sp = plan_prefill_split(tiles, nqh, ctx->n_sm, M, depth_hint, xq != nullptr);
   const int nsplit = sp.ns, Ms = std::min(M, sp.ts * QT);
   if (nsplit > 1)
     if (int rc = ensure_part(ctx, (size_t)nsplit * Ms * nqh * PROW)) return rc;
-  const CUtensorMap *tk, *tv;
-  if (int rc = get_tmap(kcache, nkvh, n_ctx, &tk)) return rc;
-  if (int rc = get_tmap(vcache, nkvh, n_ctx, &tv)) return rc;
+  const CUtensorMap *tk, *tv, *tks, *tvs;
+  if (q8) {
+    if (int rc = get_q8_tmaps(kcache, nkvh, n_ctx, &tk, &tks)) return rc;
+    if (int rc = get_q8_tmaps(vcache, nkvh, n_ctx, &tv, &tvs)) return rc;
+  } else {
+    if (int rc = get_tmap(kcache, nkvh, n_ctx, &tk)) return rc;
+    if (int rc = get_tmap(vcache, nkvh, n_ctx, &tv)) return rc;
+    tks = tk;  // not read
+    tvs = tv;
+  }
   F16Params p = {};
   p.qn = qn; p.qg = qg; p.o = o; p.part = nsplit > 1 ? ctx->part : nullptr; p.pos0 = pos0; p.status = ctx->status;
   p.M = M; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.ts = sp.ts; p.nsplit = nsplit; p.kq_scale = kq_scale;
-  prefill_f16_kernel<<<(tiles - sp.ts) * nqh + sp.ts * nqh * nsplit, F16_THREADS, F16_SMEM_BYTES, s>>>(*tk, *tv, p);
+  const int grid = (tiles - sp.ts) * nqh + sp.ts * nqh * nsplit;
+  if (q8)
+    prefill_f16_kernel<true><<<grid, Lay<true>::THREADS, Lay<true>::SMEM_BYTES, s>>>(*tk, *tv, *tks, *tvs, p);
+  else
+    prefill_f16_kernel<false><<<grid, Lay<false>::THREADS, Lay<false>::SMEM_BYTES, s>>>(*tk, *tv, *tks, *tvs, p);
   Q27B_CK(cudaGetLastError());
   if (nsplit > 1) {  // the split tokens are rows [0, Ms * nqh) of every array
     MergeParams mp = {};

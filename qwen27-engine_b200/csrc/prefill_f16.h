@@ -48,10 +48,15 @@ inline SplitPlan plan_prefill_split(int tiles, int nqh, int n_sm, int M, int dep
   return best_ns > 1 ? SplitPlan{ts, best_ns} : SplitPlan{0, 1};
 }
 
-// o (f32) or xq/xd (q8_1, written by the merge kernel of the split path). Same contract as the q8_0
-// path of q27b_attn_prefill.
+// The f16-QK kernel: on an f16 cache (q8 = false), or on a q8_0 cache whose K and V it dequantises to
+// f16 on the way (q8 = true; the reference's Q27_ATTN_I8=0 path). o (f32) or xq/xd (q8_1, written by
+// the merge kernel of the split path). Same contract as q27b_attn_prefill.
 int launch_prefill_f16(DeviceCtx* ctx, const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
-                       int8_t* xq, float* xd, const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx,
+                       int8_t* xq, float* xd, const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, bool q8,
                        int depth_hint, cudaStream_t s);
+
+// Tensor maps of a q8_0 cache (prefill.cu): the int8 values in boxes of 128 bytes x 64 rows with the
+// 128-byte swizzle, the f16 scales in boxes of 16 bytes x 64 rows.
+int get_q8_tmaps(const void* cache, int nkvh, int n_ctx, const CUtensorMap** vals, const CUtensorMap** scales);
 
 }  // namespace q27b

@@ -63,6 +63,16 @@ def test_decode_kernel_selection_is_checked(q27):
         assert b"set_decode_kernel" in lib.q27b_last_error()
 
 
+def test_prefill_kernel_selection_is_checked(q27):
+    lib = ctypes.CDLL(q27.LIB_PATH)
+    lib.q27b_last_error.restype = ctypes.c_char_p
+    for which in (0, 1, 2, 0):
+        assert lib.q27b_set_prefill_kernel(which) == 0
+    for which in (-1, 3):
+        assert lib.q27b_set_prefill_kernel(which) == q27.BAD_SHAPE
+        assert b"set_prefill_kernel" in lib.q27b_last_error()
+
+
 def test_python_mirror_raises(q27):
     with pytest.raises(RuntimeError):
         q27.kv_append(None, None, None, None, None, 1, 4, 16)

@@ -258,3 +258,26 @@ def test_prefill_tail_split(q27, orc, q8):
         rq, rd = orc.q8_1(got.reshape(-1))
         assert np.array_equal(xq.cpu().numpy().reshape(-1), rq) and np.array_equal(xd.cpu().numpy(), rd)
     assert q27.device_status() == 0
+
+
+@pytest.mark.parametrize("pos0,M,depth_hint", [(0, 37, -1), (0, 128, -1), (1000, 64, -1), (5000, 128, 8000), (63, 2, -1),
+                                               (300, 200, -1), (129, 257, 4096)])
+def test_prefill_f16_qk_on_q8_cache(q27, orc, pos0, M, depth_hint):
+    """q8_0 cache served by the f16-QK kernel (the reference's Q27_ATTN_I8=0, attn_prefill_kernel<PT, true>,
+    src/attn.cu:338-528): K and V dequantised to f16 (q * d, one rounding), Q * scale in f16. Cache rows
+    past the sequence are poisoned (NaN scales)."""
+    nkvh = 2
+    nqh = nkvh * GQA
+    qn, qg, kc_ref, vc_ref, n, n_ctx = make_case(orc, M, pos0, nkvh)
+    o = torch.full((M, nqh, AD), float("nan"), device="cuda")
+    q27.set_prefill_kernel(2)
+    try:
+        q27.attn_prefill(dev(qn), dev(qg), poisoned_cache(q27, kc_ref, nkvh, n_ctx, n),
+                         poisoned_cache(q27, vc_ref, nkvh, n_ctx, n), o, pos_tensor(pos0), M, SCALE, nqh, nkvh, n_ctx, True,
+                         depth_hint)
+        torch.cuda.synchronize()
+    finally:
+        q27.set_prefill_kernel(0)
+    ref = orc.attn_ref(qn, qg, kc_ref, vc_ref, pos0, SCALE, nkvh, n_ctx, q8=True)
+    assert_close(o.cpu().numpy(), ref, "f16-QK prefill on q8_0 pos0=%d M=%d" % (pos0, M))
+    assert q27.device_status() == 0
