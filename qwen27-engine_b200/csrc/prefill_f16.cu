@@ -9,8 +9,9 @@
 // K-major for K, read MN-major for V): no converter warps, no per-block scale arithmetic.
 //
 // One CTA = 128 query tokens of one query head (TMEM lane = token) x one split of the positions.
-// Warps 0-7 softmax (two warpgroups, 32 columns of a tile each), warp 8 TMA producer, warp 9 MMA
-// issuer: per tile 16 x (128x64x16) into one of two S buffers, then 4 x (128x256x16) into O.
+// Warps 0-7 softmax (two warpgroups, 32 columns of a tile each), warp 8 TMA producer, warp 9 issues
+// the Q K^T MMAs (per tile 16 x (128x64x16) into one of two S buffers), warp 10 the P V MMAs
+// (4 x (128x256x16) into O).
 // TMEM: columns 0-255 O (f32), 256-383 two S buffers of 64 columns (f32).
 //
 // Q8 = true: the same on a q8_0 cache, the reference's path with Q27_ATTN_I8=0
@@ -38,19 +39,25 @@ constexpr int P_BYTES = QT * 128;           // f16 P: [128][64 positions]
 constexpr int RAW_BYTES = 2 * PT * 128 + PT * 16;  // q8_0 tile: two 128-dim int8 segments [64][128 B], then [64][8] f16 scales
 // Shared memory. f16 cache: two K and two V stages, filled by TMA. q8_0 cache: one f16 K and one f16 V
 // buffer, filled by the converter warps from two raw stages each.
-template <bool Q8>
+template <bool Q8, int NWG>
 struct Lay {
   static constexpr int NKF = Q8 ? 1 : 2;
+  static constexpr int NSW = 4 * NWG;                      // softmax warps: NWG threads per query row
+  // f16 cache: the P V MMAs have an issuing thread of their own (measured +10 %); with the converter
+  // warps of the q8_0 variant on the same shared memory that lost 11 %, so there one thread issues both
+  static constexpr bool SPLIT_ISSUE = !Q8;
+  static constexpr int TMA_WARP = NSW, MMA_WARP = NSW + 1, PV_WARP = SPLIT_ISSUE ? NSW + 2 : -1;
+  static constexpr int KCONV_WARP0 = NSW + 2 + SPLIT_ISSUE, VCONV_WARP0 = KCONV_WARP0 + 4;
   static constexpr int OFF_Q = 0;                          // 64 KB
   static constexpr int OFF_K = OFF_Q + 4 * SEGQ;
   static constexpr int OFF_V = OFF_K + NKF * KV_BYTES;
   static constexpr int OFF_P = OFF_V + NKF * KV_BYTES;     // one buffer
   static constexpr int OFF_RAW = OFF_P + P_BYTES;          // q8_0: K stage 0, 1, V stage 0, 1
-  static constexpr int OFF_XCH = OFF_RAW + (Q8 ? 4 * RAW_BYTES : 0);  // [tile parity][2 warpgroups][128] f32
-  static constexpr int OFF_BAR = OFF_XCH + 2 * 2 * QT * 4;
+  static constexpr int OFF_XCH = OFF_RAW + (Q8 ? 4 * RAW_BYTES : 0);  // [tile parity][NWG][128] f32
+  static constexpr int OFF_BAR = OFF_XCH + 2 * NWG * QT * 4;
   static constexpr int OFF_MISC = OFF_BAR + 24 * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;
-  static constexpr int THREADS = (Q8 ? 18 : 10) * 32;
+  static constexpr int THREADS = (NSW + 2 + SPLIT_ISSUE + (Q8 ? 8 : 0)) * 32;
   static_assert(OFF_K % 1024 == 0 && OFF_V % 1024 == 0 && OFF_P % 1024 == 0 && OFF_RAW % 1024 == 0 && RAW_BYTES % 1024 == 0,
                 "swizzled tiles need 1024-byte alignment");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
@@ -58,7 +65,7 @@ struct Lay {
 enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_SEMPTY = 11, B_PFULL = 13, B_PEMPTY = 14, B_ODONE = 15,
        B_RKFULL = 16, B_RKEMPTY = 18, B_RVFULL = 20, B_RVEMPTY = 22, NBAR = 24 };
 
-constexpr int N_SOFTMAX_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9, KCONV_WARP0 = 10, VCONV_WARP0 = 14, N_CONV_WARPS = 4;
+constexpr int N_CONV_WARPS = 4;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_O = 0, TM_S = 256;
 constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, QT, PT);   // f32 += f16 * f16, both K-major, M128 N64
@@ -76,12 +83,14 @@ struct F16Params {
   float kq_scale;
 };
 
-__device__ __forceinline__ void pair_sync(int q) { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); }
+// the NWG threads of a query row sit in warp q of every softmax warpgroup
+template <int NWG>
+__device__ __forceinline__ void row_sync(int q) { asm volatile("bar.sync %0, %1;" ::"r"(1 + q), "n"(32 * NWG) : "memory"); }
 
 // Rare, and kept out of line: inlined, its 32 registers of payload would sit on the loop's state.
-__device__ __noinline__ void rescale_o_f16(uint32_t taddr, float f) {
+__device__ __noinline__ void rescale_o_f16(uint32_t taddr, float f, int chunks) {
 #pragma unroll 1
-  for (int c = 0; c < 4; c++) {
+  for (int c = 0; c < chunks; c++) {
     uint32_t v[32];
     tmem_ld32(taddr + c * 32, v);
     tc_wait_ld();
@@ -133,11 +142,16 @@ __device__ __forceinline__ void convert_q8_tile(const uint8_t* raw, uint8_t* dst
 }
 
 // tm_k, tm_v: f16 cache rows (f16 cache) or the int8 values (q8_0 cache); tm_ks, tm_vs: the q8_0 scales.
-template <bool Q8>
-__global__ void __launch_bounds__(Lay<Q8>::THREADS, 1)
+template <bool Q8, int NWG>
+__global__ void __launch_bounds__(Lay<Q8, NWG>::THREADS, 1)
 prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const __grid_constant__ CUtensorMap tm_ks, const __grid_constant__ CUtensorMap tm_vs, const F16Params p) {
-  using LY = Lay<Q8>;
+  using LY = Lay<Q8, NWG>;
+  constexpr int N_SOFTMAX_WARPS = LY::NSW, TMA_WARP = LY::TMA_WARP, MMA_WARP = LY::MMA_WARP, PV_WARP = LY::PV_WARP,
+                KCONV_WARP0 = LY::KCONV_WARP0, VCONV_WARP0 = LY::VCONV_WARP0;
+  (void)VCONV_WARP0;
+  constexpr int CW = PT / NWG;    // columns (positions) of a tile per softmax thread
+  constexpr int OW = AD / NWG;    // columns of O per softmax thread (rescale, epilogue)
   constexpr int OFF_Q = LY::OFF_Q, OFF_K = LY::OFF_K, OFF_V = LY::OFF_V, OFF_P = LY::OFF_P, OFF_RAW = LY::OFF_RAW,
                 OFF_XCH = LY::OFF_XCH, OFF_BAR = LY::OFF_BAR, OFF_MISC = LY::OFF_MISC;
   pdl_wait();
@@ -219,12 +233,12 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     const bool live = t < p.M;
     float* xch = (float*)(sgen + OFF_XCH);
     {
-      // Q tile: this thread writes dims 128 wg .. 128 wg + 127 of its row (segments 2wg, 2wg + 1),
+      // Q tile: this thread writes dims OW wg .. OW wg + OW - 1 of its row (whole 64-dim segments),
       // scaled, f16, K-major with the 128-byte swizzle; rows past M are zero
-      const float* src = live ? p.qn + ((size_t)t * p.nqh + h) * AD + 128 * wg : nullptr;
+      const float* src = live ? p.qn + ((size_t)t * p.nqh + h) * AD + OW * wg : nullptr;
 #pragma unroll
-      for (int sg = 0; sg < 2; sg++) {
-        uint8_t* dst = sgen + OFF_Q + (2 * wg + sg) * SEGQ;
+      for (int sg = 0; sg < OW / 64; sg++) {
+        uint8_t* dst = sgen + OFF_Q + (OW / 64 * wg + sg) * SEGQ;
 #pragma unroll
         for (int c = 0; c < 8; c++) {
           uint32_t w[4] = {0, 0, 0, 0};
@@ -245,7 +259,7 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
     const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
     const int limit = pos0 + t + 1;    // positions < limit are visible
-    const int col0 = wg * 32;          // this thread's positions of a tile
+    const int col0 = wg * CW;          // this thread's positions of a tile
     float m_run = M_INIT, m_ref = M_INIT;
     uint64_t l2 = pack2(0.f, 0.f);
     const uint64_t log2e2 = pack2(LOG2E, LOG2E);
@@ -256,13 +270,13 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       const int p_tile = (it0 + j) * PT;
       mbar_wait(&bar[B_SFULL + slot], (j >> 1) & 1, abort_flag, p.status);
       tc_fence_after();
-      float s[32];
+      float s[CW];
       {
-        uint32_t v[32];
-        tmem_ld32(tlane + TM_S + slot * PT + col0, v);
+        uint32_t v[CW];
+        tmem_ld(tlane + TM_S + slot * PT + col0, v);
         tc_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; i++) s[i] = __uint_as_float(v[i]);
+        for (int i = 0; i < CW; i++) s[i] = __uint_as_float(v[i]);
       }
       tc_fence_before();
       __syncwarp();
@@ -271,26 +285,27 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       // causal mask (only tiles that reach past the first row's limit need it) and this thread's max
       if (p_tile + PT > pos0 + t0 + 1) {
 #pragma unroll
-        for (int i = 0; i < 32; i++)
+        for (int i = 0; i < CW; i++)
           if (p_tile + col0 + i >= limit) s[i] = -INFINITY;
       }
       float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) {
+      for (int i = 0; i < CW; i += 4) {
         mq[0] = fmaxf(mq[0], s[i]);
         mq[1] = fmaxf(mq[1], s[i + 1]);
         mq[2] = fmaxf(mq[2], s[i + 2]);
         mq[3] = fmaxf(mq[3], s[i + 3]);
       }
       float mt = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
-      // row maximum over the two threads of the row; the buffer alternates with the tile
-      xch[(slot * 2 + wg) * QT + r] = mt;
-      pair_sync(q);
-      mt = fmaxf(mt, xch[(slot * 2 + (wg ^ 1)) * QT + r]);
+      // row maximum over the NWG threads of the row; the buffer alternates with the tile
+      xch[(slot * NWG + wg) * QT + r] = mt;
+      row_sync<NWG>(q);
+#pragma unroll
+      for (int o = 1; o < NWG; o++) mt = fmaxf(mt, xch[(slot * NWG + ((wg + o) % NWG)) * QT + r]);
       m_run = fmaxf(m_run, mt);
 
-      // Move the reference max when the true max has run away from it (and on the first tile). Both
-      // threads of a row hold the same m_run and m_ref, so both warps of a pair take the same branch.
+      // Move the reference max when the true max has run away from it (and on the first tile). The
+      // threads of a row hold the same m_run and m_ref, so their warps take the same branch.
       const bool want = m_run > m_ref + TAU;
       if (__any_sync(0xffffffffu, want)) {
         const float f = ex2((m_ref - m_run) * LOG2E);  // 0 on the first move (m_ref = -1e30)
@@ -300,19 +315,19 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           // O holds the sum of tiles < j once the P V of tile j-1 has completed
           mbar_wait(&bar[B_PEMPTY], (j - 1) & 1, abort_flag, p.status);
           tc_fence_after();
-          rescale_o_f16(tlane + TM_O + wg * 128, f);
+          rescale_o_f16(tlane + TM_O + wg * OW, f, OW / 32);
           tc_wait_st();
           tc_fence_before();
         }
       }
 
-      // P = exp(s - m_ref): f32 row sum, f16 half-tile for the P V MMA (chunks 4wg .. 4wg+3 of the row)
+      // P = exp(s - m_ref): f32 row sum, f16 for the P V MMA (16-byte chunks CW/8 wg .. of the row)
       mbar_wait(&bar[B_PEMPTY], (j & 1) ^ 1, abort_flag, p.status);  // P V of tile j-1 has read the buffer
       uint8_t* sP = sgen + OFF_P;
       const float nmb = -m_ref * LOG2E;
       const uint64_t nmb2 = pack2(nmb, nmb);
 #pragma unroll
-      for (int c = 0; c < 4; c++) {
+      for (int c = 0; c < CW / 8; c++) {
         uint32_t w[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
@@ -322,7 +337,7 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           l2 = add2(l2, pack2(e0, e1));
           w[k] = pack_h2(e0, e1);
         }
-        *(uint4*)(sP + swz128(r, 4 * wg + c)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *(uint4*)(sP + swz128(r, CW / 8 * wg + c)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
       if (!Q8 && p_tile + PT > n_end) {
         // The last tile reaches past the sequence: those cache rows hold whatever was there before
@@ -330,11 +345,13 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         // cleared in shared memory. Thread = (segment, position); a row of a segment is 128 bytes,
         // and the swizzle only permutes within it.
         mbar_wait(&bar[B_VFULL + slot], (j >> 1) & 1, abort_flag, p.status);
-        const int sg = tid >> 6, row = tid & 63;
-        if (p_tile + row >= n_end) {
-          uint4* vrow = (uint4*)(sgen + OFF_V + slot * KV_BYTES + sg * SEGK + row * 128);
+        for (int u = tid; u < 4 * PT; u += 32 * N_SOFTMAX_WARPS) {
+          const int sg = u >> 6, row = u & 63;
+          if (p_tile + row >= n_end) {
+            uint4* vrow = (uint4*)(sgen + OFF_V + slot * KV_BYTES + sg * SEGK + row * 128);
 #pragma unroll
-          for (int c = 0; c < 8; c++) vrow[c] = make_uint4(0, 0, 0, 0);
+            for (int c = 0; c < 8; c++) vrow[c] = make_uint4(0, 0, 0, 0);
+          }
         }
       }
       fence_proxy_async();
@@ -346,9 +363,10 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     float la, lb;
     unpack2(l2, la, lb);
     float l = la + lb;
-    xch[((nt & 1) * 2 + wg) * QT + r] = l;
-    pair_sync(q);
-    l += xch[((nt & 1) * 2 + (wg ^ 1)) * QT + r];
+    xch[((nt & 1) * NWG + wg) * QT + r] = l;
+    row_sync<NWG>(q);
+#pragma unroll
+    for (int o = 1; o < NWG; o++) l += xch[((nt & 1) * NWG + ((wg + o) % NWG)) * QT + r];
     mbar_wait(&bar[B_ODONE], 0, abort_flag, p.status);
     tc_fence_after();
     const float inv_l = 1.0f / l;
@@ -358,8 +376,8 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       po[1] = l;
     }
 #pragma unroll 1
-    for (int c = 0; c < 4; c++) {
-      const int d0 = wg * 128 + c * 32;
+    for (int c = 0; c < OW / 32; c++) {
+      const int d0 = wg * OW + c * 32;
       uint32_t v[32];
       tmem_ld32(tlane + TM_O + d0, v);
       tc_wait_ld();
@@ -444,26 +462,34 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         mbar_arrive(&bar[b_rempty + st]);
       }
     }
-  } else if (warp == MMA_WARP) {
-    // ================================================================ MMA issuer
-    if (lane == 0) {
+  } else if (warp == MMA_WARP || warp == PV_WARP) {
+    // ================================================================ MMA issuers
+    // Operand buffer and phase of tile j: two TMA stages (f16 cache) or the one converted buffer (q8_0).
+    auto issue_pv = [&](int jj) {
+      const int st = Q8 ? 0 : jj & 1, ph = Q8 ? jj & 1 : (jj >> 1) & 1;
+      mbar_wait(&bar[B_PFULL], jj & 1, abort_flag, p.status);
+      mbar_wait(&bar[B_VFULL + st], ph, abort_flag, p.status);
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < PT / 16; kk++) {
+        const uint64_t da = umma_desc_sw128(sbase + OFF_P + kk * 32, 16, 1024);
+        const uint64_t db = umma_desc_sw128(sbase + OFF_V + st * KV_BYTES + kk * 2048, SEGK, 1024);
+        tc_mma_f16(tmem + TM_O, da, db, IDESC_PV, (jj > 0 || kk > 0) ? 1u : 0u);
+      }
+      tc_commit(&bar[B_PEMPTY]);
+      tc_commit(&bar[B_VEMPTY + st]);
+    };
+    if (LY::SPLIT_ISSUE && warp == PV_WARP) {
+      // P V from a thread of its own: a single thread issues the 128x64x16 MMAs of Q K^T at about
+      // half the rate the tensor pipe could run them, and the P V MMAs of the previous tile fill the gaps
+      if (lane == 0) {
+#pragma unroll 1
+        for (int jj = 0; jj < nt; jj++) issue_pv(jj);
+        tc_commit(&bar[B_ODONE]);
+      }
+    } else if (lane == 0) {
       mbar_wait(&bar[B_QFULL], 0, abort_flag, p.status);
       tc_fence_after();
-      // operand buffer and phase of tile j: two TMA stages (f16 cache) or the one converted buffer (q8_0)
-      auto issue_pv = [&](int jj) {
-        const int st = Q8 ? 0 : jj & 1, ph = Q8 ? jj & 1 : (jj >> 1) & 1;
-        mbar_wait(&bar[B_PFULL], jj & 1, abort_flag, p.status);
-        mbar_wait(&bar[B_VFULL + st], ph, abort_flag, p.status);
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < PT / 16; kk++) {
-          const uint64_t da = umma_desc_sw128(sbase + OFF_P + kk * 32, 16, 1024);
-          const uint64_t db = umma_desc_sw128(sbase + OFF_V + st * KV_BYTES + kk * 2048, SEGK, 1024);
-          tc_mma_f16(tmem + TM_O, da, db, IDESC_PV, (jj > 0 || kk > 0) ? 1u : 0u);
-        }
-        tc_commit(&bar[B_PEMPTY]);
-        tc_commit(&bar[B_VEMPTY + st]);
-      };
 #pragma unroll 1
       for (int j = 0; j < nt; j++) {
         const int ss = j & 1, sph = (j >> 1) & 1;                         // S buffer
@@ -479,10 +505,12 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
         tc_commit(&bar[B_SFULL + ss]);
         tc_commit(&bar[B_KEMPTY + st]);
-        if (j >= 1) issue_pv(j - 1);
+        if (!LY::SPLIT_ISSUE && j >= 1) issue_pv(j - 1);
       }
-      issue_pv(nt - 1);
-      tc_commit(&bar[B_ODONE]);
+      if (!LY::SPLIT_ISSUE) {
+        issue_pv(nt - 1);
+        tc_commit(&bar[B_ODONE]);
+      }
     }
   }
 
@@ -529,10 +557,12 @@ int launch_prefill_f16(DeviceCtx* ctx, const float* qn, const float* qg, const v
                        int depth_hint, cudaStream_t s) {
   static bool attr[64] = {};
   if (!attr[ctx->dev]) {
-    Q27B_CK(cudaFuncSetAttribute(prefill_f16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<false>::SMEM_BYTES));
-    Q27B_CK(cudaFuncSetAttribute(prefill_f16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<true>::SMEM_BYTES));
+    Q27B_CK(cudaFuncSetAttribute(prefill_f16_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<false, 2>::SMEM_BYTES));
+    Q27B_CK(cudaFuncSetAttribute(prefill_f16_kernel<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<false, 4>::SMEM_BYTES));
+    Q27B_CK(cudaFuncSetAttribute(prefill_f16_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<true, 2>::SMEM_BYTES));
     attr[ctx->dev] = true;
   }
+  static const int nwg_f16 = [] { const char* e = getenv("Q27B_PF16_NWG"); return e && e[0] == '4' ? 4 : 2; }();
   const int tiles = (M + QT - 1) / QT;
   // splits over the positions as for the int8 kernel; the q8_1 output is written by the merge kernel,
   // so it needs every tile on the split path (at least one merge)
@@ -555,9 +585,11 @@ int launch_prefill_f16(DeviceCtx* ctx, const float* qn, const float* qg, const v
   p.M = M; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.ts = sp.ts; p.nsplit = nsplit; p.kq_scale = kq_scale;
   const int grid = (tiles - sp.ts) * nqh + sp.ts * nqh * nsplit;
   if (q8)
-    prefill_f16_kernel<true><<<grid, Lay<true>::THREADS, Lay<true>::SMEM_BYTES, s>>>(*tk, *tv, *tks, *tvs, p);
+    prefill_f16_kernel<true, 2><<<grid, Lay<true, 2>::THREADS, Lay<true, 2>::SMEM_BYTES, s>>>(*tk, *tv, *tks, *tvs, p);
+  else if (nwg_f16 == 4)
+    prefill_f16_kernel<false, 4><<<grid, Lay<false, 4>::THREADS, Lay<false, 4>::SMEM_BYTES, s>>>(*tk, *tv, *tks, *tvs, p);
   else
-    prefill_f16_kernel<false><<<grid, Lay<false>::THREADS, Lay<false>::SMEM_BYTES, s>>>(*tk, *tv, *tks, *tvs, p);
+    prefill_f16_kernel<false, 2><<<grid, Lay<false, 2>::THREADS, Lay<false, 2>::SMEM_BYTES, s>>>(*tk, *tv, *tks, *tvs, p);
   Q27B_CK(cudaGetLastError());
   if (nsplit > 1) {  // the split tokens are rows [0, Ms * nqh) of every array
     MergeParams mp = {};
