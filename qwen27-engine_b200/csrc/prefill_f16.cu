@@ -32,42 +32,40 @@ namespace {
 constexpr int QT = 128;          // query tokens per CTA
 constexpr int PT = 64;           // positions per tile
 constexpr float TAU = 5.0f;
-constexpr int SEGQ = QT * 128;   // one 64-dim segment of the Q tile: [128 rows][128 B]
 constexpr int SEGK = PT * 128;   // one 64-dim segment of a K or V tile: [64 positions][128 B]
 constexpr int KV_BYTES = 4 * SEGK;          // 32 KB
 constexpr int P_BYTES = QT * 128;           // f16 P: [128][64 positions]
 constexpr int RAW_BYTES = 2 * PT * 128 + PT * 16;  // q8_0 tile: two 128-dim int8 segments [64][128 B], then [64][8] f16 scales
-// Shared memory. f16 cache: two K and two V stages, filled by TMA. q8_0 cache: one f16 K and one f16 V
-// buffer, filled by the converter warps from two raw stages each.
+enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 4, B_VFULL = 7, B_VEMPTY = 10, B_SFULL = 13, B_SEMPTY = 15, B_PFULL = 17, B_PEMPTY = 18, B_ODONE = 19,
+       B_RKFULL = 20, B_RKEMPTY = 22, B_RVFULL = 24, B_RVEMPTY = 26, NBAR = 28 };
+// Shared memory. f16 cache: three K and three V stages, filled by TMA. q8_0 cache: two f16 K and two
+// f16 V buffers, filled by the converter warps from two raw stages each. (The Q tile is in TMEM.)
 template <bool Q8, int NWG>
 struct Lay {
-  static constexpr int NKF = Q8 ? 1 : 2;
+  static constexpr int NKF = Q8 ? 2 : 3;                   // f16 K buffers, and as many f16 V buffers
   static constexpr int NSW = 4 * NWG;                      // softmax warps: NWG threads per query row
   // f16 cache: the P V MMAs have an issuing thread of their own (measured +10 %); with the converter
   // warps of the q8_0 variant on the same shared memory that lost 11 %, so there one thread issues both
   static constexpr bool SPLIT_ISSUE = !Q8;
   static constexpr int TMA_WARP = NSW, MMA_WARP = NSW + 1, PV_WARP = SPLIT_ISSUE ? NSW + 2 : -1;
   static constexpr int KCONV_WARP0 = NSW + 2 + SPLIT_ISSUE, VCONV_WARP0 = KCONV_WARP0 + 4;
-  static constexpr int OFF_Q = 0;                          // 64 KB
-  static constexpr int OFF_K = OFF_Q + 4 * SEGQ;
+  static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + NKF * KV_BYTES;
   static constexpr int OFF_P = OFF_V + NKF * KV_BYTES;     // one buffer
   static constexpr int OFF_RAW = OFF_P + P_BYTES;          // q8_0: K stage 0, 1, V stage 0, 1
   static constexpr int OFF_XCH = OFF_RAW + (Q8 ? 4 * RAW_BYTES : 0);  // [tile parity][NWG][128] f32
   static constexpr int OFF_BAR = OFF_XCH + 2 * NWG * QT * 4;
-  static constexpr int OFF_MISC = OFF_BAR + 24 * 8;
+  static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;
   static constexpr int THREADS = (NSW + 2 + SPLIT_ISSUE + (Q8 ? 8 : 0)) * 32;
   static_assert(OFF_K % 1024 == 0 && OFF_V % 1024 == 0 && OFF_P % 1024 == 0 && OFF_RAW % 1024 == 0 && RAW_BYTES % 1024 == 0,
                 "swizzled tiles need 1024-byte alignment");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 };
-enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_SEMPTY = 11, B_PFULL = 13, B_PEMPTY = 14, B_ODONE = 15,
-       B_RKFULL = 16, B_RKEMPTY = 18, B_RVFULL = 20, B_RVEMPTY = 22, NBAR = 24 };
 
 constexpr int N_CONV_WARPS = 4;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TM_O = 0, TM_S = 256;
+constexpr uint32_t TM_O = 0, TM_S = 256, TM_Q = 384;  // O f32 256 columns, S 2 x 64 f32, Q 128 columns of f16 pairs
 constexpr uint32_t IDESC_QK = umma_idesc(1, 0, 0, 0, 0, QT, PT);   // f32 += f16 * f16, both K-major, M128 N64
 constexpr uint32_t IDESC_PV = umma_idesc(1, 0, 0, 0, 1, QT, AD);   // B (V) MN-major, M128 N256
 
@@ -152,7 +150,7 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   (void)VCONV_WARP0;
   constexpr int CW = PT / NWG;    // columns (positions) of a tile per softmax thread
   constexpr int OW = AD / NWG;    // columns of O per softmax thread (rescale, epilogue)
-  constexpr int OFF_Q = LY::OFF_Q, OFF_K = LY::OFF_K, OFF_V = LY::OFF_V, OFF_P = LY::OFF_P, OFF_RAW = LY::OFF_RAW,
+  constexpr int NKF = LY::NKF, OFF_K = LY::OFF_K, OFF_V = LY::OFF_V, OFF_P = LY::OFF_P, OFF_RAW = LY::OFF_RAW,
                 OFF_XCH = LY::OFF_XCH, OFF_BAR = LY::OFF_BAR, OFF_MISC = LY::OFF_MISC;
   pdl_wait();
   pdl_trigger();
@@ -198,11 +196,13 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
   if (tid == 0) {
     mbar_init(&bar[B_QFULL], N_SOFTMAX_WARPS);
-    for (int s = 0; s < 2; s++) {
-      mbar_init(&bar[B_KFULL + s], Q8 ? N_CONV_WARPS : 1);  // q8_0: the converter warps fill buffer 0
+    for (int s = 0; s < 3; s++) {
+      mbar_init(&bar[B_KFULL + s], Q8 ? N_CONV_WARPS : 1);  // q8_0: the converter warps fill the buffers
       mbar_init(&bar[B_KEMPTY + s], 1);
       mbar_init(&bar[B_VFULL + s], Q8 ? N_CONV_WARPS : 1);
       mbar_init(&bar[B_VEMPTY + s], 1);
+    }
+    for (int s = 0; s < 2; s++) {
       mbar_init(&bar[B_SFULL + s], 1);
       mbar_init(&bar[B_SEMPTY + s], N_SOFTMAX_WARPS);
       mbar_init(&bar[B_RKFULL + s], 1);
@@ -232,32 +232,30 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     const int t = t0 + r;
     const bool live = t < p.M;
     float* xch = (float*)(sgen + OFF_XCH);
+    const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
     {
-      // Q tile: this thread writes dims OW wg .. OW wg + OW - 1 of its row (whole 64-dim segments),
-      // scaled, f16, K-major with the 128-byte swizzle; rows past M are zero
+      // Q tile -> tensor memory, the A operand of every Q K^T MMA of this CTA (lane = row, column c =
+      // dims 2c, 2c+1 as f16, even dim in the low half): it is read from there 16 times per tile
+      // without touching shared memory. This thread writes dims OW wg .. OW wg + OW - 1 of its row,
+      // scaled and rounded to f16; rows past M are zero.
       const float* src = live ? p.qn + ((size_t)t * p.nqh + h) * AD + OW * wg : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < OW / 64; c++) {
+        uint32_t w[32];
 #pragma unroll
-      for (int sg = 0; sg < OW / 64; sg++) {
-        uint8_t* dst = sgen + OFF_Q + (OW / 64 * wg + sg) * SEGQ;
-#pragma unroll
-        for (int c = 0; c < 8; c++) {
-          uint32_t w[4] = {0, 0, 0, 0};
-          if (src) {
-            const float4 a = *(const float4*)(src + sg * 64 + c * 8), b = *(const float4*)(src + sg * 64 + c * 8 + 4);
-            w[0] = pack_h2(a.x * p.kq_scale, a.y * p.kq_scale);
-            w[1] = pack_h2(a.z * p.kq_scale, a.w * p.kq_scale);
-            w[2] = pack_h2(b.x * p.kq_scale, b.y * p.kq_scale);
-            w[3] = pack_h2(b.z * p.kq_scale, b.w * p.kq_scale);
-          }
-          *(uint4*)(dst + swz128(r, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int i = 0; i < 32; i += 2) {
+          const float4 a = src ? *(const float4*)(src + c * 64 + 2 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          w[i] = pack_h2(a.x * p.kq_scale, a.y * p.kq_scale);
+          w[i + 1] = pack_h2(a.z * p.kq_scale, a.w * p.kq_scale);
         }
+        tmem_st32(tlane + TM_Q + wg * (OW / 2) + c * 32, w);
       }
-      fence_proxy_async();
+      tc_wait_st();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[B_QFULL]);
     }
 
-    const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
     const int limit = pos0 + t + 1;    // positions < limit are visible
     const int col0 = wg * CW;          // this thread's positions of a tile
     float m_run = M_INIT, m_ref = M_INIT;
@@ -344,11 +342,12 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         // (possibly NaN or Inf, and 0 * NaN = NaN in the P V product), so the V rows past the end are
         // cleared in shared memory. Thread = (segment, position); a row of a segment is 128 bytes,
         // and the swizzle only permutes within it.
-        mbar_wait(&bar[B_VFULL + slot], (j >> 1) & 1, abort_flag, p.status);
+        const int vb = j % NKF;
+        mbar_wait(&bar[B_VFULL + vb], (j / NKF) & 1, abort_flag, p.status);
         for (int u = tid; u < 4 * PT; u += 32 * N_SOFTMAX_WARPS) {
           const int sg = u >> 6, row = u & 63;
           if (p_tile + row >= n_end) {
-            uint4* vrow = (uint4*)(sgen + OFF_V + slot * KV_BYTES + sg * SEGK + row * 128);
+            uint4* vrow = (uint4*)(sgen + OFF_V + vb * KV_BYTES + sg * SEGK + row * 128);
 #pragma unroll
             for (int c = 0; c < 8; c++) vrow[c] = make_uint4(0, 0, 0, 0);
           }
@@ -413,9 +412,9 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       }
 #pragma unroll 1
       for (int j = 0; j < nt; j++) {
-        const int st = j & 1, ph = (j >> 1) & 1;
         const int row = kh * p.n_ctx + (it0 + j) * PT;
         if constexpr (Q8) {
+          const int st = j & 1, ph = (j >> 1) & 1;  // raw stages
           uint8_t* kr = sgen + OFF_RAW + st * RAW_BYTES;
           uint8_t* vr = sgen + OFF_RAW + (2 + st) * RAW_BYTES;
           mbar_wait(&bar[B_RKEMPTY + st], ph ^ 1, abort_flag, p.status);
@@ -429,6 +428,7 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           tma_load_2d(vr + PT * 128, &tm_v, 128, row, &bar[B_RVFULL + st]);
           tma_load_2d(vr + 2 * PT * 128, &tm_vs, 0, row, &bar[B_RVFULL + st]);
         } else {
+          const int st = j % NKF, ph = (j / NKF) & 1;
           uint8_t* ks = sgen + OFF_K + st * KV_BYTES;
           uint8_t* vs = sgen + OFF_V + st * KV_BYTES;
           mbar_wait(&bar[B_KEMPTY + st], ph ^ 1, abort_flag, p.status);
@@ -446,27 +446,27 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     // ================================================================ converter warps (q8_0 cache)
     const bool is_v = warp >= VCONV_WARP0;
     const int ct = tid - (is_v ? VCONV_WARP0 : KCONV_WARP0) * 32;
-    uint8_t* dst = sgen + (is_v ? OFF_V : OFF_K);
     const int b_rfull = is_v ? B_RVFULL : B_RKFULL, b_rempty = is_v ? B_RVEMPTY : B_RKEMPTY;
     const int b_full = is_v ? B_VFULL : B_KFULL, b_empty = is_v ? B_VEMPTY : B_KEMPTY;
 #pragma unroll 1
     for (int j = 0; j < nt; j++) {
-      const int st = j & 1;
+      const int st = j & 1, fb = j % NKF;
       mbar_wait(&bar[b_rfull + st], (j >> 1) & 1, abort_flag, p.status);
-      mbar_wait(&bar[b_empty], (j & 1) ^ 1, abort_flag, p.status);  // the MMAs of tile j-1 have read the buffer
-      convert_q8_tile(sgen + OFF_RAW + ((is_v ? 2 : 0) + st) * RAW_BYTES, dst, ct, is_v ? n_end - (it0 + j) * PT : PT);
+      mbar_wait(&bar[b_empty + fb], ((j / NKF) & 1) ^ 1, abort_flag, p.status);  // the MMAs of tile j-NKF have read the buffer
+      convert_q8_tile(sgen + OFF_RAW + ((is_v ? 2 : 0) + st) * RAW_BYTES, sgen + (is_v ? OFF_V : OFF_K) + fb * KV_BYTES, ct,
+                      is_v ? n_end - (it0 + j) * PT : PT);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&bar[b_full]);
+        mbar_arrive(&bar[b_full + fb]);
         mbar_arrive(&bar[b_rempty + st]);
       }
     }
   } else if (warp == MMA_WARP || warp == PV_WARP) {
     // ================================================================ MMA issuers
-    // Operand buffer and phase of tile j: two TMA stages (f16 cache) or the one converted buffer (q8_0).
+    // Operand buffer and phase of tile j: ring of NKF TMA stages (f16 cache) or converted buffers (q8_0).
     auto issue_pv = [&](int jj) {
-      const int st = Q8 ? 0 : jj & 1, ph = Q8 ? jj & 1 : (jj >> 1) & 1;
+      const int st = jj % NKF, ph = (jj / NKF) & 1;
       mbar_wait(&bar[B_PFULL], jj & 1, abort_flag, p.status);
       mbar_wait(&bar[B_VFULL + st], ph, abort_flag, p.status);
       tc_fence_after();
@@ -493,15 +493,14 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll 1
       for (int j = 0; j < nt; j++) {
         const int ss = j & 1, sph = (j >> 1) & 1;                         // S buffer
-        const int st = Q8 ? 0 : j & 1, ph = Q8 ? j & 1 : (j >> 1) & 1;   // K buffer
+        const int st = j % NKF, ph = (j / NKF) & 1;                       // K buffer
         mbar_wait(&bar[B_KFULL + st], ph, abort_flag, p.status);
         mbar_wait(&bar[B_SEMPTY + ss], sph ^ 1, abort_flag, p.status);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < AD / 16; kk++) {
-          const uint64_t da = umma_desc_sw128(sbase + OFF_Q + (kk >> 2) * SEGQ + (kk & 3) * 32, 16, 1024);
           const uint64_t db = umma_desc_sw128(sbase + OFF_K + st * KV_BYTES + (kk >> 2) * SEGK + (kk & 3) * 32, 16, 1024);
-          tc_mma_f16(tmem + TM_S + ss * PT, da, db, IDESC_QK, kk > 0 ? 1u : 0u);
+          tc_mma_f16_ts(tmem + TM_S + ss * PT, tmem + TM_Q + kk * 8, db, IDESC_QK, kk > 0 ? 1u : 0u);
         }
         tc_commit(&bar[B_SFULL + ss]);
         tc_commit(&bar[B_KEMPTY + st]);
