@@ -6,19 +6,21 @@
 // src/attn.cu:323) is not needed; the reference max of a row moves only when the true max has
 // grown by more than TAU. The 64-position K and V tiles that TMA brings from the cache are the
 // operands of the tensor core as they land ([64-dim segment][position][128 B], 128-byte swizzle:
-// K-major for K, read MN-major for V): no converter warps, no per-block scale arithmetic.
+// K-major for K, read MN-major for V; ring of three stages each): no converter warps, no per-block
+// scale arithmetic.
 //
 // One CTA = 128 query tokens of one query head (TMEM lane = token) x one split of the positions.
 // Warps 0-7 softmax (two warpgroups, 32 columns of a tile each), warp 8 TMA producer, warp 9 issues
 // the Q K^T MMAs (per tile 16 x (128x64x16) into one of two S buffers), warp 10 the P V MMAs
 // (4 x (128x256x16) into O).
-// TMEM: columns 0-255 O (f32), 256-383 two S buffers of 64 columns (f32).
+// TMEM: columns 0-255 O (f32), 256-383 two S buffers of 64 columns (f32), 384-511 the Q tile (f16
+// pairs), the A operand of every Q K^T MMA (tcgen05.mma with A in tensor memory).
 //
 // Q8 = true: the same on a q8_0 cache, the reference's path with Q27_ATTN_I8=0
 // (attn_prefill_kernel<PT, true>, src/attn.cu:338-528): K and V are dequantised to f16 (q * d rounded
 // once, cvt_q8_16 src/attn.cu:59-76) on their way to the tensor core. TMA brings the int8 tiles and
-// their scales into raw stages, warps 10-13 turn K and warps 14-17 turn V into the f16 operand
-// layout above (one f16 buffer each, two raw stages each).
+// their scales into raw stages, warps 11-14 turn K and warps 15-18 turn V into the f16 operand
+// layout above (two f16 buffers and two raw stages per operand).
 #include "combine.h"
 #include "common.cuh"
 #include "prefill_f16.h"
@@ -44,9 +46,9 @@ template <bool Q8, int NWG>
 struct Lay {
   static constexpr int NKF = Q8 ? 2 : 3;                   // f16 K buffers, and as many f16 V buffers
   static constexpr int NSW = 4 * NWG;                      // softmax warps: NWG threads per query row
-  // f16 cache: the P V MMAs have an issuing thread of their own (measured +10 %); with the converter
-  // warps of the q8_0 variant on the same shared memory that lost 11 %, so there one thread issues both
-  static constexpr bool SPLIT_ISSUE = !Q8;
+  // The P V MMAs have an issuing thread of their own: measured +10 % on an f16 cache and +11-15 % on
+  // a q8_0 cache (with one f16 buffer per operand instead of two it had lost 11 % there).
+  static constexpr bool SPLIT_ISSUE = true;
   static constexpr int TMA_WARP = NSW, MMA_WARP = NSW + 1, PV_WARP = SPLIT_ISSUE ? NSW + 2 : -1;
   static constexpr int KCONV_WARP0 = NSW + 2 + SPLIT_ISSUE, VCONV_WARP0 = KCONV_WARP0 + 4;
   static constexpr int OFF_K = 0;
