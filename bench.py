@@ -577,17 +577,32 @@ def extras(q, caches, qn, qg, o, n_ctx):
             out["prefill"][str(P)] = {"ms": ms, "tops": ops / (ms * 1e-3) / 1e12}
         except Exception as e:  # report, do not hide
             out["prefill"][str(P)] = {"error": str(e)}
-    # the same chunk on an f16 KV cache (f16 Q K^T and P V, no per-block scale arithmetic)
+    # the same chunk and cache through the f16-QK kernel (the reference's Q27_ATTN_I8=0: K and V dequantised to f16)
+    out["prefill_f16_qk_on_q8_0"] = {}
     try:
-        P = 32768
-        f16c = fill_caches(q, NKVH, P + M, P + M + 64, 3002, q8=False)
-        pos.fill_(P)
-        ops = NQH * 1024.0 * (M * P + M * (M + 1) / 2)
-        ms = time_steps(lambda i: q.attn_prefill(pqn, pqg, f16c[0], f16c[1], po, pos, M, SCALE, NQH, NKVH, P + M + 64, False, P), 3, 3)
-        out["prefill_f16_cache"] = {str(P): {"ms": ms, "tflops": ops / (ms * 1e-3) / 1e12}}
+        q.set_prefill_kernel(2)
+        for P in (0, 32768, 148000):
+            pos.fill_(P)
+            ops = NQH * 1024.0 * (M * P + M * (M + 1) / 2)
+            ms = time_steps(lambda i: q.attn_prefill(pqn, pqg, kc, vc, po, pos, M, SCALE, NQH, NKVH, n_ctx, True, P), 3, 3)
+            out["prefill_f16_qk_on_q8_0"][str(P)] = {"ms": ms, "tops": ops / (ms * 1e-3) / 1e12}
+    except Exception as e:  # report, do not hide
+        out["prefill_f16_qk_on_q8_0"]["error"] = str(e)
+    finally:
+        q.set_prefill_kernel(0)
+    # the same chunk on an f16 KV cache (f16 Q K^T and P V, no per-block scale arithmetic)
+    out["prefill_f16_cache"] = {}
+    try:
+        Pmax = 148000
+        f16c = fill_caches(q, NKVH, Pmax + M, Pmax + M + 64, 3002, q8=False)
+        for P in (0, 32768, Pmax):
+            pos.fill_(P)
+            ops = NQH * 1024.0 * (M * P + M * (M + 1) / 2)
+            ms = time_steps(lambda i: q.attn_prefill(pqn, pqg, f16c[0], f16c[1], po, pos, M, SCALE, NQH, NKVH, Pmax + M + 64, False, P), 3, 3)
+            out["prefill_f16_cache"][str(P)] = {"ms": ms, "tflops": ops / (ms * 1e-3) / 1e12}
         del f16c
     except Exception as e:  # report, do not hide
-        out["prefill_f16_cache"] = {"error": str(e)}
+        out["prefill_f16_cache"]["error"] = str(e)
     out["device_status"] = q.device_status()
     try:
         out["batched_paged"] = batched_paged(q, 0, 1)
