@@ -689,6 +689,11 @@ def prefill_mode(q, args, steps, warmup, dist=None, rank=0, world=1):
         line["config"] = {"workload": "prefill chunk M=2048 on an f16 prefix of %d tokens" % P}
         line["roofline"] = {"bound": "tensor", "achieved": tops, "peak": f16, "unit": "TFLOP/s", "frac": tops / f16,
                             "peak_kind": "%s bf16 GEMM rate (sustained)" % pk_kind, "traffic": None}
+    if q8 and os.environ.get("Q27_ATTN_I8", "1")[:1] == "0":  # the library reads the same switch
+        line["metric"] = "f16-QK prefill-attn TOPS on a q8_0 prefix (Q27_ATTN_I8=0: K and V dequantised to f16; 2048-token chunk, 24q/4kv heads, head dim 256)"
+        line["dtype"] = "f16 -> f32 (QK and PV), q8_0 K/V dequantised on the way"
+        line["roofline"] = {"bound": "tensor", "achieved": tops, "peak": f16, "unit": "TFLOP/s", "frac": tops / f16,
+                            "peak_kind": "%s bf16 GEMM rate (sustained)" % pk_kind, "traffic": None}
     if world > 1:
         line["config"]["sharding"] = "KV-head groups x %d query-token slices per group, no exchange; rank 0: heads %d..%d, tokens %s" % (
             max(1, world // NKVH), plan.kv_head0, plan.kv_head0 + nkvh - 1, list(plan.ranges))
