@@ -178,6 +178,13 @@ int q27b_set_decode_kernel(int which);
  * always use the f16 kernel. */
 int q27b_set_prefill_kernel(int which);
 
+/* How a q27b_attn_prefill call of M tokens and nqh heads on a GPU of n_sm SMs splits its positions
+ * (host arithmetic only, no GPU needed): the first *split_tiles 128-token query tiles are cut into
+ * *pieces pieces each (partials + merge), the others are not split. Few CTAs: every tile is split by
+ * the reference's rule (src/attn.cu:945-951, also what Q27_ATTN_SPLIT forces); more CTAs than SMs on
+ * a deep prefix: only as many CTAs as do not fill a last full round are cut. 0 / 1 = no split. */
+int q27b_prefill_split_plan(int M, int nqh, int n_sm, int depth_hint, int* split_tiles, int* pieces);
+
 /* Test hook for the failure path, no counterpart in the reference: launches one warp that waits on
  * a barrier nobody arrives at, with the bounded wait every kernel of this library uses. After the
  * limit (about two seconds) the wait gives up, the kernel returns normally and

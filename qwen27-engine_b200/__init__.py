@@ -28,7 +28,7 @@ OK, BAD_SHAPE, CUDA_ERROR, UNSUPPORTED, DEVICE_STATUS = 0, 1, 2, 3, 4
 SYMBOLS = [
     "q27b_last_error", "q27b_device_status", "q27b_kv_cache_bytes", "q27b_attn_chunks", "q27b_kv_append",
     "q27b_attn_prep", "q27b_attn_decode", "q27b_attn_decode_partial", "q27b_lse_merge", "q27b_attn_decode_paged",
-    "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_set_decode_kernel", "q27b_set_prefill_kernel", "q27b_debug_expire_wait",
+    "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_set_decode_kernel", "q27b_set_prefill_kernel", "q27b_prefill_split_plan", "q27b_debug_expire_wait",
     "q27b_attn_prefill_q8_1", "q27b_xbuf_bytes", "q27b_attn_decode_partial_push", "q27b_lse_merge_wait",
     "q27b_xbuf_alloc", "q27b_xbuf_free", "q27b_ipc_export", "q27b_ipc_open", "q27b_ipc_close",
     "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
@@ -192,6 +192,14 @@ def lse_merge_wait(xbuf, nz, rows, qg, o):
 def set_decode_kernel(which):
     """0 automatic, 1 warp-MMA kernel, 2 tcgen05 kernel (q8_0 caches; see include/q27b_attn.h)."""
     _check(_lib.q27b_set_decode_kernel(int(which)))
+
+
+def prefill_split_plan(M, nqh, n_sm, depth_hint):
+    """(split_tiles, pieces) of an attn_prefill call: the first split_tiles query tiles are cut into
+    `pieces` pieces over their positions, the others are not (host arithmetic only)."""
+    ts, ns = ctypes.c_int(0), ctypes.c_int(0)
+    _check(_lib.q27b_prefill_split_plan(int(M), int(nqh), int(n_sm), int(depth_hint), ctypes.byref(ts), ctypes.byref(ns)))
+    return ts.value, ns.value
 
 
 def set_prefill_kernel(which):

@@ -761,6 +761,14 @@ static bool use_f16_qk() {
 
 extern "C" {
 
+int q27b_prefill_split_plan(int M, int nqh, int n_sm, int depth_hint, int* split_tiles, int* pieces) {
+  if (M < 1 || nqh < 1 || n_sm < 1 || !split_tiles || !pieces) return fail(Q27B_BAD_SHAPE, "prefill_split_plan: bad argument");
+  const SplitPlan sp = plan_prefill_split((M + QT - 1) / QT, nqh, n_sm, M, depth_hint, false);
+  *split_tiles = sp.ts;
+  *pieces = sp.ns;
+  return Q27B_OK;
+}
+
 int q27b_set_prefill_kernel(int which) {
   if (which < 0 || which > 2) return fail(Q27B_BAD_SHAPE, "set_prefill_kernel: 0 auto, 1 int8 QK, 2 f16 QK");
   g_prefill_choice = which;

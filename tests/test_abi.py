@@ -73,6 +73,32 @@ def test_prefill_kernel_selection_is_checked(q27):
         assert b"set_prefill_kernel" in lib.q27b_last_error()
 
 
+def test_prefill_split_plan(q27, monkeypatch):
+    """Host arithmetic of the prefill split: the reference's rule while the CTAs do not fill the GPU,
+    the tail split on a deep prefix, nothing on a short one."""
+    monkeypatch.delenv("Q27_ATTN_SPLIT", raising=False)
+    monkeypatch.delenv("Q27B_PREFILL_TAIL_SPLIT", raising=False)
+    assert q27.prefill_split_plan(2048, 24, 148, -1) == (0, 1)          # no hint: never split
+    assert q27.prefill_split_plan(2048, 24, 148, 0) == (0, 1)           # short prefix
+    ts, ns = q27.prefill_split_plan(2048, 24, 148, 32768)                # 384 CTAs = 2 rounds + 88
+    assert ts == 4 and 2 <= ns <= 8
+    ts2, ns2 = q27.prefill_split_plan(2048, 24, 148, 148000)
+    assert ts2 == 4 and ns2 >= ns                                        # pieces get cheaper with depth
+    assert q27.prefill_split_plan(70, 6, 148, 8000) == (1, 3)            # 6 CTAs: every tile, (8000 + 70) / 2048 pieces
+    assert q27.prefill_split_plan(128 * 37, 4, 148, 10 ** 6) == (37, 2)  # 148 CTAs: the reference's rule, two per SM
+    assert q27.prefill_split_plan(128 * 74, 4, 148, 10 ** 6) == (0, 1)   # 296 CTAs: two full rounds
+    for M, nqh, depth in [(896, 24, 3600), (2048, 12, 32768), (1024, 24, 65536), (4096, 24, 200000)]:
+        ts, ns = q27.prefill_split_plan(M, nqh, 148, depth)
+        tiles = (M + 127) // 128
+        assert 0 <= ts <= tiles and 1 <= ns <= 8 and (ts == 0) == (ns == 1)
+        if 0 < ts < tiles:  # tail split: the unsplit CTAs fit in full rounds
+            assert (tiles - ts) * nqh <= (tiles * nqh // 148) * 148
+    monkeypatch.setenv("Q27_ATTN_SPLIT", "3")
+    assert q27.prefill_split_plan(2048, 24, 148, 32768) == (16, 3)
+    monkeypatch.setenv("Q27_ATTN_SPLIT", "1")
+    assert q27.prefill_split_plan(2048, 24, 148, 32768) == (0, 1)
+
+
 def test_python_mirror_raises(q27):
     with pytest.raises(RuntimeError):
         q27.kv_append(None, None, None, None, None, 1, 4, 16)
