@@ -472,6 +472,11 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
   } else if (warp < TMA_WARP) {
     // ================================================================ converter warps
     const int ct = tid - CONV_WARP0 * 32;
+    static_assert(N_CONV_THREADS == 128, "the item mapping below is for 128 converter threads");
+    const int cv_row0 = (2 * (ct >> 5)) ^ (5 * ((ct >> 2) & 1)), cv_c16 = (ct & 3) + 4 * ((ct >> 3) & 3);
+    const uint32_t cv_src = (cv_c16 >> 3) * (PT * 128) + swz128(cv_row0, cv_c16 & 7);
+    const uint32_t cv_sc = 2 * PT * 128 + cv_row0 * 16 + (cv_c16 >> 1) * 2;
+    const uint32_t cv_dst = (cv_c16 >> 2) * (PT * 128) + swz128(cv_row0, 2 * (cv_c16 & 3));
     for (int j = 0; j < nt; j++) {
       const int pb = j & 1, ph = (j >> 1) & 1;
       mbar_wait(&bar[B_VFULL + pb], ph, abort_flag, p.status);
@@ -484,20 +489,18 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
       // V: 64 rows x 16 chunks of 16 int8 -> 16 f16 (one rounding of q * d, as src/attn.cu:59-76).
       // Item = (row, 16-dim chunk); eight neighbouring lanes take 4 chunks of rows rho and rho ^ 5,
       // which keeps both the swizzled 16-byte loads and the swizzled 16-byte stores conflict-free.
+      // A thread owns the same chunk of rows row0, row0 + 8, ..: rows 8 apart share their swizzle
+      // phase, so every address is a per-thread base (computed before the tile loop) plus a constant.
 #pragma unroll 1
       for (int k0 = 0; k0 < 1024 / N_CONV_THREADS; k0 += 4) {
         // Loads of four items first: a shared-memory load cannot be moved above an earlier store, so
         // load / convert / store per item would serialise the load latencies.
         uint4 x[4];
         __half d[4];
-        int row[4], c16[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-          const int item = ct + N_CONV_THREADS * (k0 + k);
-          row[k] = (2 * (item >> 5)) ^ (5 * ((item >> 2) & 1));
-          c16[k] = (item & 3) + 4 * ((item >> 3) & 3);
-          x[k] = *(const uint4*)(vst + (c16[k] >> 3) * (PT * 128) + swz128(row[k], c16[k] & 7));
-          d[k] = *(const __half*)(vst + 2 * PT * 128 + row[k] * 16 + (c16[k] >> 1) * 2);
+          x[k] = *(const uint4*)(vst + cv_src + (k0 + k) * 1024);
+          d[k] = *(const __half*)(vst + cv_sc + (k0 + k) * 128);
         }
 #pragma unroll
         for (int k = 0; k < 4; k++) {
@@ -509,14 +512,13 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
             o[2 * w] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4140), dd);
             o[2 * w + 1] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4342), dd);
           }
-          if ((it0 + j) * PT + row[k] >= n_end) {  // rows past the end may hold anything: P is 0 there, V must be too
+          if ((it0 + j) * PT + cv_row0 + 8 * (k0 + k) >= n_end) {  // rows past the end may hold anything: P is 0 there, V must be too
 #pragma unroll
             for (int w = 0; w < 8; w++) o[w] = 0;
           }
-          uint8_t* dst = vf + (c16[k] >> 2) * (PT * 128);
-          const uint32_t cc = 2 * (c16[k] & 3);
-          *(uint4*)(dst + swz128(row[k], cc)) = make_uint4(o[0], o[1], o[2], o[3]);
-          *(uint4*)(dst + swz128(row[k], cc + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+          uint8_t* dst = vf + (k0 + k) * 1024;
+          *(uint4*)(dst + cv_dst) = make_uint4(o[0], o[1], o[2], o[3]);
+          *(uint4*)(dst + (cv_dst ^ 16u)) = make_uint4(o[4], o[5], o[6], o[7]);
         }
       }
       // K scales f16 [64][8] -> f32 [8][64]

@@ -102,22 +102,35 @@ __device__ __noinline__ void rescale_o_f16(uint32_t taddr, float f, int chunks) 
 
 // One tile of a q8_0 cache, raw stage -> f16 operand buffer. 128 threads; item = (row, 16-dim chunk);
 // eight neighbouring lanes take 4 chunks of rows rho and rho ^ 5, which keeps both the swizzled
-// 16-byte loads and the swizzled 16-byte stores free of bank conflicts. Rows >= zero_from are cleared
-// (rows past the sequence may hold anything: P is 0 there, V must be too).
-__device__ __forceinline__ void convert_q8_tile(const uint8_t* raw, uint8_t* dst_tile, int ct, int zero_from) {
+// 16-byte loads and the swizzled 16-byte stores free of bank conflicts. Thread ct owns the same chunk
+// of rows row0, row0 + 8, .., row0 + 56: rows 8 apart share their swizzle phase, so every address is
+// a per-thread base (ConvAddr, computed once per kernel) plus a constant. Rows >= zero_from are
+// cleared (rows past the sequence may hold anything: P is 0 there, V must be too).
+struct ConvAddr {
+  int row0;       // first row of this thread
+  uint32_t src;   // byte offset of its 16 int8 values of row0 in the raw stage
+  uint32_t sc;    // ... of their f16 scale
+  uint32_t dst;   // ... of the first of its two 16-byte chunks in the f16 buffer
+};
+__device__ __forceinline__ ConvAddr conv_addr(int ct) {
+  ConvAddr a;
+  a.row0 = (2 * (ct >> 5)) ^ (5 * ((ct >> 2) & 1));
+  const int c16 = (ct & 3) + 4 * ((ct >> 3) & 3);
+  a.src = (c16 >> 3) * (PT * 128) + swz128(a.row0, c16 & 7);
+  a.sc = 2 * PT * 128 + a.row0 * 16 + (c16 >> 1) * 2;
+  a.dst = (c16 >> 2) * SEGK + swz128(a.row0, 2 * (c16 & 3));
+  return a;
+}
+__device__ __forceinline__ void convert_q8_tile(const uint8_t* raw, uint8_t* dst_tile, const ConvAddr& a, int zero_from) {
 #pragma unroll 1
   for (int k0 = 0; k0 < 8; k0 += 4) {
     // loads of four items first: a shared-memory load is never moved above an earlier store
     uint4 x[4];
     __half d[4];
-    int row[4], c16[4];
 #pragma unroll
     for (int k = 0; k < 4; k++) {
-      const int item = ct + 128 * (k0 + k);
-      row[k] = (2 * (item >> 5)) ^ (5 * ((item >> 2) & 1));
-      c16[k] = (item & 3) + 4 * ((item >> 3) & 3);
-      x[k] = *(const uint4*)(raw + (c16[k] >> 3) * (PT * 128) + swz128(row[k], c16[k] & 7));
-      d[k] = *(const __half*)(raw + 2 * PT * 128 + row[k] * 16 + (c16[k] >> 1) * 2);
+      x[k] = *(const uint4*)(raw + a.src + (k0 + k) * 1024);
+      d[k] = *(const __half*)(raw + a.sc + (k0 + k) * 128);
     }
 #pragma unroll
     for (int k = 0; k < 4; k++) {
@@ -129,14 +142,13 @@ __device__ __forceinline__ void convert_q8_tile(const uint8_t* raw, uint8_t* dst
         o[2 * w] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4140), dd);
         o[2 * w + 1] = dq_pair(__byte_perm(xw[w], 0x64646464u, 0x4342), dd);
       }
-      if (row[k] >= zero_from) {
+      if (a.row0 + 8 * (k0 + k) >= zero_from) {
 #pragma unroll
         for (int w = 0; w < 8; w++) o[w] = 0;
       }
-      uint8_t* dst = dst_tile + (c16[k] >> 2) * SEGK;
-      const uint32_t cc = 2 * (c16[k] & 3);
-      *(uint4*)(dst + swz128(row[k], cc)) = make_uint4(o[0], o[1], o[2], o[3]);
-      *(uint4*)(dst + swz128(row[k], cc + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+      uint8_t* dst = dst_tile + (k0 + k) * 1024;
+      *(uint4*)(dst + a.dst) = make_uint4(o[0], o[1], o[2], o[3]);
+      *(uint4*)(dst + (a.dst ^ 16u)) = make_uint4(o[4], o[5], o[6], o[7]);
     }
   }
 }
@@ -450,12 +462,13 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     const int ct = tid - (is_v ? VCONV_WARP0 : KCONV_WARP0) * 32;
     const int b_rfull = is_v ? B_RVFULL : B_RKFULL, b_rempty = is_v ? B_RVEMPTY : B_RKEMPTY;
     const int b_full = is_v ? B_VFULL : B_KFULL, b_empty = is_v ? B_VEMPTY : B_KEMPTY;
+    const ConvAddr ca = conv_addr(ct);
 #pragma unroll 1
     for (int j = 0; j < nt; j++) {
       const int st = j & 1, fb = j % NKF;
       mbar_wait(&bar[b_rfull + st], (j >> 1) & 1, abort_flag, p.status);
       mbar_wait(&bar[b_empty + fb], ((j / NKF) & 1) ^ 1, abort_flag, p.status);  // the MMAs of tile j-NKF have read the buffer
-      convert_q8_tile(sgen + OFF_RAW + ((is_v ? 2 : 0) + st) * RAW_BYTES, sgen + (is_v ? OFF_V : OFF_K) + fb * KV_BYTES, ct,
+      convert_q8_tile(sgen + OFF_RAW + ((is_v ? 2 : 0) + st) * RAW_BYTES, sgen + (is_v ? OFF_V : OFF_K) + fb * KV_BYTES, ca,
                       is_v ? n_end - (it0 + j) * PT : PT);
       fence_proxy_async();
       __syncwarp();
