@@ -162,6 +162,30 @@ int q27b_attn_decode_partial_push(const float* qn, const void* kcache, const voi
                                   void* const* peer_xbuf, int my_z, int nz, void* stream);
 int q27b_lse_merge_wait(void* xbuf, int nz, int64_t rows, const float* qg, float* o, void* stream);
 
+/* The step after the attention output projection (row f4 of the path's neighbours): x [rows][n] +=
+ * the sum over the GPUs of their partial rows, then RMSNorm(x) * w -> h (f32, may be null) and q8_1
+ * (xq int8 [rows][n], xd f32 [rows * n / 32] = f32(f16(amax / 127)); xq may be null). Replaces
+ * q27::sum_norm_q8 (src/ops.h:101-104; kernel src/ops.cu:129-260 with norm_q8_row :89-107; call
+ * sites src/model.cu:652-692). n a multiple of 32 up to 16384 (the model has n = 5120).
+ *  - q27b_sum_norm_q8: one GPU, or partials already summed (the reference's ar == null branch).
+ *  - q27b_sum_push + q27b_sum_norm_q8_wait: `world` GPUs on one NVLink switch. Every rank owns an
+ *    exchange buffer of q27b_sum_xbuf_bytes(world, rows, n) bytes (q27b_xbuf_alloc_bytes: zeroed,
+ *    an allocation of its own for CUDA IPC) and passes the buffers of all ranks, its own at index
+ *    `rank`, as mapped into its address space, in rank order. q27b_sum_push stores this rank's f32
+ *    rows into slot `rank` of every buffer and releases a flag; q27b_sum_norm_q8_wait waits (bounded:
+ *    a missing rank ends in Q27B status 4 / device status 1, not in a hang) for the flags of all ranks,
+ *    adds the slices in rank order - every rank gets the same bits - and normalises. The reference's
+ *    two PCIe cards exchange through mapped host memory in a bf16 or q8 wire format
+ *    (src/ops.cu:151-243); over NVLink the f32 rows go as they are. A buffer serves one call site
+ *    per step (its header counts steps); rows and n must not change between steps. */
+uint64_t q27b_sum_xbuf_bytes(int world, int rows, int n);
+int q27b_xbuf_alloc_bytes(uint64_t bytes, void** out);
+int q27b_sum_norm_q8(float* x, const float* partial, int n, int rows, const float* w, float eps, float* h, int8_t* xq,
+                     float* xd, void* stream);
+int q27b_sum_push(const float* partial, int n, int rows, int rank, int world, void* const* xbufs, void* stream);
+int q27b_sum_norm_q8_wait(float* x, void* xbuf, int world, int n, int rows, const float* w, float eps, float* h, int8_t* xq,
+                          float* xd, void* stream);
+
 /* Which split-K kernel q27b_attn_decode* uses for q8_0 caches: 0 = default (the warp-MMA kernel),
  * 1 = warp-MMA kernel, 2 = tcgen05 kernel (both contractions on the 5th-generation tensor cores;
  * faster at long contexts in its best builds, less predictable: see csrc/decode.cu). Both compute

@@ -90,6 +90,22 @@ def q8_1(y):
     return xq, xd
 
 
+def sum_norm(x, partials, w, eps):
+    """The reference's sum_norm_q8 (src/ops.cu:129-260, non-exchange branch, and norm_q8_row :89-107) for
+    a list of per-rank partials: x_new = x + (p0 + p1 + ..) in f32 in rank order, scale =
+    1 / sqrt(mean(x_new^2) + eps) with the mean taken in f64 (the kernel's f32 tree may differ in the last
+    bit), h = scale * x_new * w in f32. Returns (x_new, h); the q8_1 form is q8_1(h)."""
+    x = _c(x, np.float32)
+    s = _c(partials[0], np.float32).copy()
+    for p in partials[1:]:
+        s = s + _c(p, np.float32)
+    xn = x + s
+    t = (xn.astype(np.float64) ** 2).sum(axis=-1, keepdims=True)
+    scale = (1.0 / np.sqrt(t / xn.shape[-1] + np.float64(np.float32(eps)))).astype(np.float32)
+    h = (scale * xn) * _c(w, np.float32)
+    return xn, h.astype(np.float32)
+
+
 def attn_ref(qn, qg, kcache, vcache, pos0, kq_scale, nkvh, n_ctx, q8=True):
     """qn [T][nqh][256], qg [T][nqh][512] -> o [T][nqh][256] (decode numerics)."""
     qn = _c(qn, np.float32)

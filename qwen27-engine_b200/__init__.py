@@ -28,7 +28,8 @@ OK, BAD_SHAPE, CUDA_ERROR, UNSUPPORTED, DEVICE_STATUS = 0, 1, 2, 3, 4
 SYMBOLS = [
     "q27b_last_error", "q27b_device_status", "q27b_kv_cache_bytes", "q27b_attn_chunks", "q27b_kv_append",
     "q27b_attn_prep", "q27b_attn_decode", "q27b_attn_decode_partial", "q27b_lse_merge", "q27b_attn_decode_paged",
-    "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_set_decode_kernel", "q27b_set_prefill_kernel", "q27b_prefill_split_plan", "q27b_debug_expire_wait",
+    "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_set_decode_kernel", "q27b_set_prefill_kernel", "q27b_prefill_split_plan", "q27b_sum_xbuf_bytes", "q27b_xbuf_alloc_bytes",
+    "q27b_sum_norm_q8", "q27b_sum_push", "q27b_sum_norm_q8_wait", "q27b_debug_expire_wait",
     "q27b_attn_prefill_q8_1", "q27b_xbuf_bytes", "q27b_attn_decode_partial_push", "q27b_lse_merge_wait",
     "q27b_xbuf_alloc", "q27b_xbuf_free", "q27b_ipc_export", "q27b_ipc_open", "q27b_ipc_close",
     "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
@@ -46,6 +47,7 @@ def _load():
     lib.q27b_kv_pool_bytes.restype = ctypes.c_uint64
     lib.q27b_kv_wire_bytes.restype = ctypes.c_uint64
     lib.q27b_xbuf_bytes.restype = ctypes.c_uint64
+    lib.q27b_sum_xbuf_bytes.restype = ctypes.c_uint64
     return lib
 
 
@@ -187,6 +189,40 @@ def lse_merge_wait(xbuf, nz, rows, qg, o):
     """Waits for the nz slices of this step in this rank's exchange buffer, merges them, applies the gate."""
     _check(_lib.q27b_lse_merge_wait(_ptr(xbuf), int(nz), ctypes.c_int64(int(rows)),
                                     _ptr(qg, torch.float32) if qg is not None else None, _ptr(o, torch.float32), _stream()))
+
+
+def sum_xbuf_bytes(world, rows, n):
+    return int(_lib.q27b_sum_xbuf_bytes(int(world), int(rows), int(n)))
+
+
+def xbuf_alloc_bytes(nbytes):
+    """Device address of a new zeroed exchange buffer of nbytes (an allocation of its own, exportable over CUDA IPC)."""
+    out = ctypes.c_void_p(0)
+    _check(_lib.q27b_xbuf_alloc_bytes(ctypes.c_uint64(int(nbytes)), ctypes.byref(out)))
+    return int(out.value)
+
+
+def sum_norm_q8(x, partial, n, rows, w, eps, h=None, xq=None, xd=None):
+    """q27::sum_norm_q8 without an exchange (src/ops.h:101-104): x += partial, RMSNorm(x) * w -> h and q8_1."""
+    _check(_lib.q27b_sum_norm_q8(_ptr(x, torch.float32), _ptr(partial, torch.float32), int(n), int(rows), _ptr(w, torch.float32),
+                                 _f(eps), _ptr(h, torch.float32) if h is not None else None,
+                                 _ptr(xq, torch.int8) if xq is not None else None,
+                                 _ptr(xd, torch.float32) if xd is not None else None, _stream()))
+
+
+def sum_push(partial, n, rows, rank, xbufs):
+    """Stores this rank's partial rows into slot `rank` of the exchange buffers of all ranks (xbufs: their
+    device addresses as seen from here, in rank order, this rank's own at index rank)."""
+    arr = (ctypes.c_void_p * len(xbufs))(*[ctypes.c_void_p(int(x)) for x in xbufs])
+    _check(_lib.q27b_sum_push(_ptr(partial, torch.float32), int(n), int(rows), int(rank), len(xbufs), arr, _stream()))
+
+
+def sum_norm_q8_wait(x, xbuf, world, n, rows, w, eps, h=None, xq=None, xd=None):
+    """Waits for the partial rows of all ranks of this step, x += their sum in rank order, RMSNorm -> h and q8_1."""
+    _check(_lib.q27b_sum_norm_q8_wait(_ptr(x, torch.float32), _ptr(xbuf), int(world), int(n), int(rows), _ptr(w, torch.float32),
+                                      _f(eps), _ptr(h, torch.float32) if h is not None else None,
+                                      _ptr(xq, torch.int8) if xq is not None else None,
+                                      _ptr(xd, torch.float32) if xd is not None else None, _stream()))
 
 
 def set_decode_kernel(which):
