@@ -227,7 +227,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--ref-cpu", action="store_true", help="reference arm: time the CPU oracle instead of the reference's GPU kernels")
     ap.add_argument("--n", type=int, default=N_POS)
-    ap.add_argument("--mode", default="decode", help="decode (the headline) or prefill (second half of the metric)")
+    ap.add_argument("--mode", default="decode", help="decode (the headline), prefill (second half of the metric) or sum_norm (N > 1: the exchange after the output projection)")
     ap.add_argument("--prefix", type=int, default=32768, help="prefill mode: tokens already in the cache")
     ap.add_argument("--kv", default="q8", help="prefill mode: q8 (int8 Q K^T on the q8_0 cache) or f16 (f16 Q K^T on an f16 cache)")
     args = ap.parse_args()
@@ -253,6 +253,17 @@ def main():
     q = ge.load_package()
     if args.mode == "prefill":
         prefill_mode(q, args, steps, warmup, dist, rank, world)
+        return
+    if args.mode == "sum_norm":  # the exchange after the output projection alone (needs N > 1)
+        if dist is None:
+            raise SystemExit("--mode sum_norm needs torchrun with at least 2 ranks")
+        out = sum_norm_scaling(q, dist, rank, world, steps, warmup)
+        if rank == 0:
+            print(json.dumps({"metric": "sum_norm_q8 us/step (x[4][5120] += sum over GPUs, RMSNorm, q8_1)", "value": out["us_per_step"],
+                              "unit": "us", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": out["us_per_step"] / 1e3,
+                              "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                              "config": {"workload": out["what"]}, "gpu_launches": 2 * steps, "detail": out}))
+        dist.barrier()
         return
     line = {
         "metric": "q8_0 decode-attn HBM GB/s @150k ctx (4-token verify block, 24q/4kv heads, head dim 256)",
@@ -322,6 +333,10 @@ def main():
         del caches
         torch.cuda.empty_cache()
         line["batched_paged"] = batched_paged(q, rank, world, dist)
+        try:
+            line["sum_norm"] = sum_norm_scaling(q, dist, rank, world, steps, warmup)
+        except Exception as e:  # report, do not hide (every rank raises or none: the set-up agrees on errors)
+            line["sum_norm"] = {"error": str(e)}
     if rank == 0 and world == 1 and not args.no_extras:
         line["extras"] = extras(q, caches, qn, qg, o, n_ctx)
     if rank == 0:
@@ -462,6 +477,52 @@ def strong_scaling(q, dist, rank, world, n, steps, warmup):
                                           "+ waiting LSE merge (nccl_us_per_step: the same with an NCCL all-gather)")
         out["p2p_equals_nccl_bitwise"] = same
     return out
+
+
+def sum_norm_scaling(q, dist, rank, world, steps, warmup):
+    """The step after the attention output projection: x [4][5120] += the sum of the ranks' partial rows,
+    RMSNorm, q8_1 (the reference's sum_norm_q8 with its two-card exchange). Peer-memory form (each rank
+    stores its rows into every rank's exchange buffer, the norm kernel waits for the flags) against an
+    NCCL all-reduce followed by the single-GPU kernel."""
+    from qwen27_engine_b200 import shard
+    rows, n, eps = T, 5120, 1e-6
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4242)
+    x0 = torch.randn((rows, n), generator=g, device="cuda")
+    w = 1.0 + 0.1 * torch.randn((n,), generator=g, device="cuda")
+    g.manual_seed(4243 + rank)
+    partial = 0.3 * torch.randn((rows, n), generator=g, device="cuda")
+    x = x0.clone()
+    buf = torch.empty_like(partial)
+    xq = torch.zeros((rows, n), dtype=torch.int8, device="cuda")
+    xd = torch.zeros((rows * n // 32,), dtype=torch.float32, device="cuda")
+
+    def step_nccl(i):
+        buf.copy_(partial)
+        dist.all_reduce(buf)
+        q.sum_norm_q8(x, buf, n, rows, w, eps, None, xq, xd)
+
+    ms_nccl = time_steps(step_nccl, steps, warmup, dist)
+    x.copy_(x0)
+    step_nccl(0)
+    x_ref = x.clone()
+    own, peers = shard.make_sum_exchange(q, rank, world, rows, n)
+    xq2, xd2 = torch.zeros_like(xq), torch.zeros_like(xd)
+
+    def step_p2p(i):
+        q.sum_push(partial, n, rows, rank, peers)
+        q.sum_norm_q8_wait(x, own, world, n, rows, w, eps, None, xq2, xd2)
+
+    x.copy_(x0)
+    step_p2p(0)
+    torch.cuda.synchronize()
+    diff = float((x - x_ref).abs().max().item())
+    ms = time_steps(step_p2p, steps, warmup, dist)
+    assert q.device_status() == 0, "a kernel reported a device-side problem"
+    return {"what": "x[4][5120] += sum over %d GPUs of their partial rows, RMSNorm, q8_1: rows stored into every rank's exchange "
+                    "buffer over NVLink + waiting norm kernel (nccl_us_per_step: NCCL all-reduce + the single-GPU kernel)" % world,
+            "us_per_step": ms * 1e3, "nccl_us_per_step": ms_nccl * 1e3, "max_abs_diff_vs_nccl_sum": diff,
+            "bytes_pushed_per_rank": rows * n * 4 * world}
 
 
 def batched_paged(q, rank, world, dist=None):

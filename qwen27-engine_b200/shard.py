@@ -158,22 +158,33 @@ def make_exchange(q, shard, group, rows):
     CUDA IPC handle to the group and maps the peers' handles with ITS OWN device current. Returns
     (address of the own buffer, [address of rank k's buffer as seen from this GPU, k in group order]).
     If any rank of the group fails, every rank raises (the ranks agree before they return)."""
+    return _exchange_buffers(q, lambda: q.xbuf_alloc(shard.nz, rows), shard.z, shard.nz, group)
+
+
+def make_sum_exchange(q, rank, world, rows, n, group=None):
+    """The same for the sum over all ranks that follows the attention output projection
+    (q27b_sum_push / q27b_sum_norm_q8_wait): one buffer per rank for `rows` rows of n floats from each of
+    `world` ranks. Returns (own address, [addresses in rank order as seen from this GPU])."""
+    return _exchange_buffers(q, lambda: q.xbuf_alloc_bytes(q.sum_xbuf_bytes(world, rows, n)), rank, world, group)
+
+
+def _exchange_buffers(q, alloc, me, count, group):
     err, own, peers = None, 0, []
     try:
-        own = q.xbuf_alloc(shard.nz, rows)
+        own = alloc()
         mine = q.ipc_export(own)
     except Exception as e:  # still take part in the collectives below
         err, mine = str(e), None
-    handles = [None] * shard.nz
+    handles = [None] * count
     dist.all_gather_object(handles, mine, group=group)
     if err is None and all(h is not None for h in handles):
         try:
-            peers = [own if k == shard.z else q.ipc_open(h) for k, h in enumerate(handles)]
+            peers = [own if k == me else q.ipc_open(h) for k, h in enumerate(handles)]
         except Exception as e:
             err = str(e)
     elif err is None:
         err = "a peer could not export its buffer"
-    errs = [None] * shard.nz
+    errs = [None] * count
     dist.all_gather_object(errs, err, group=group)
     bad = [e for e in errs if e]
     if bad:
