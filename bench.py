@@ -516,6 +516,10 @@ def sum_norm_scaling(q, dist, rank, world, steps, warmup):
     x.copy_(x0)
     step_p2p(0)
     torch.cuda.synchronize()
+    bad = torch.tensor([float(q.device_status())], device="cuda")
+    dist.all_reduce(bad, op=dist.ReduceOp.MAX)  # every rank takes the same path
+    if bad.item() != 0:  # e.g. a wait that ran out: do not time hundreds of bounded waits
+        return {"error": "device status %d after the first peer-memory step" % int(bad.item()), "nccl_us_per_step": ms_nccl * 1e3}
     diff = float((x - x_ref).abs().max().item())
     ms = time_steps(step_p2p, steps, warmup, dist)
     assert q.device_status() == 0, "a kernel reported a device-side problem"
