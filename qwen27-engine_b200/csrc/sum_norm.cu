@@ -140,21 +140,20 @@ struct SumPushParams {
   int rows, n, rank, world;
 };
 
-// One CTA per row: the row goes into slot `rank` of every rank's buffer; the last CTA releases the flags.
+// One CTA per (row, destination rank): the row goes into slot `rank` of that rank's buffer; the last
+// CTA of the grid releases the flags.
 __global__ void __launch_bounds__(256) sum_push_kernel(const SumPushParams p) {
   pdl_wait();
   pdl_trigger();
-  const int row = blockIdx.x, n = p.n;
+  const int row = blockIdx.x, k = blockIdx.y, n = p.n;
   const int epoch = *(volatile int*)p.xbuf;
   const float4* src = (const float4*)(p.partial + (size_t)row * n);
-  for (int k = 0; k < p.world; k++) {
-    float4* dst = (float4*)((float*)((uint8_t*)p.peer[k] + XBUF_HEADER_BYTES) +
-                            (((size_t)(epoch & 1) * p.world + p.rank) * p.rows + row) * n);
-    for (int i = threadIdx.x; i < n / 4; i += blockDim.x) dst[i] = src[i];
-  }
+  float4* dst = (float4*)((float*)((uint8_t*)p.peer[k] + XBUF_HEADER_BYTES) +
+                          (((size_t)(epoch & 1) * p.world + p.rank) * p.rows + row) * n);
+  for (int i = threadIdx.x; i < n / 4; i += blockDim.x) dst[i] = src[i];
   __threadfence_system();  // the rows are visible to the peers before the flag below can be
   __syncthreads();
-  if (threadIdx.x == 0 && atomicAdd(p.xbuf + 1, 1) == p.rows - 1) {
+  if (threadIdx.x == 0 && atomicAdd(p.xbuf + 1, 1) == p.rows * p.world - 1) {
     p.xbuf[1] = 0;
     __threadfence_system();
     for (int k = 0; k < p.world; k++) {
@@ -217,7 +216,7 @@ int q27b_sum_push(const float* partial, int n, int rows, int rank, int world, vo
     p.peer[k] = xbufs[k];
   }
   p.xbuf = (int*)xbufs[rank];
-  Q27B_CK(launch_pdl(sum_push_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, p));
+  Q27B_CK(launch_pdl(sum_push_kernel, dim3(rows, world), dim3(256), 0, (cudaStream_t)stream, p));
   return Q27B_OK;
 }
 
