@@ -118,3 +118,48 @@ def test_kv_length_split_over_two_gloo_ranks(q27, tmp_path):
     b = np.load(tmp_path / "r1.npy")
     assert np.array_equal(a[0], b[0])  # both ranks end with the same merged output
     assert_close(a[0], a[1], "2-rank merge", abs_tol=2e-4, rel_tol=2e-3)
+
+
+def _prefill_rank_main(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import __graft_entry__ as ge
+    ge.load_package()
+    import oracle
+    from qwen27_engine_b200 import shard, synth
+    # one chunk over two ranks that share ONE KV head (the 8-GPU layout with nkvh = 1): query-token ranges
+    pos0, M, nkvh, nqh = 300, 400, 1, 6
+    n, n_ctx = pos0 + M, pos0 + M + 8
+    qn = synth.normal(synth.SEED_Q, (M, nqh, 256))
+    qg = np.zeros((M, nqh, 512), np.float32)
+    qg[..., 256:] = synth.normal(synth.SEED_GATE, (M, nqh, 256))
+    kc, vc = oracle.fill_cache(synth.normal(synth.SEED_K, (nkvh, n, 256)), synth.normal(synth.SEED_V, (nkvh, n, 256)), n_ctx)
+    plan = shard.plan_prefill(rank, world, M, pos0, nkvh)
+    assert plan.n_kv_heads == 1 and plan.kv_head0 == 0
+    mine = np.zeros((M, nqh, 256), np.float32)
+    mask = np.zeros((M,), np.float32)
+    for a, b in plan.ranges:  # one attn_prefill call per range at pos0 + a, the oracle standing in for the kernel
+        mine[a:b] = oracle.attn_prefill_i8(qn[a:b], qg[a:b], kc, vc, pos0 + a, 1 / 16, nkvh, n_ctx)
+        mask[a:b] = 1
+    o = torch.from_numpy(mine)
+    m = torch.from_numpy(mask)
+    dist.all_reduce(o)   # disjoint slices: the sum is the concatenation
+    dist.all_reduce(m)
+    if rank == 0:
+        whole = oracle.attn_prefill_i8(qn, qg, kc, vc, pos0, 1 / 16, nkvh, n_ctx)
+        np.save(os.path.join(out_dir, "pf.npy"), np.stack([o.numpy(), whole]))
+        np.save(os.path.join(out_dir, "mask.npy"), m.numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_prefill_query_ranges_over_two_gloo_ranks(q27, tmp_path):
+    """plan_prefill's query-token ranges on two ranks: every token computed exactly once, and a range
+    computed as its own call at pos0 + a gives the rows of the whole-chunk call bit for bit."""
+    port = _free_port()
+    mp.spawn(_prefill_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    got, whole = np.load(tmp_path / "pf.npy")
+    assert np.array_equal(np.load(tmp_path / "mask.npy"), np.ones(400, np.float32))
+    assert np.array_equal(got, whole)
