@@ -99,6 +99,26 @@ def test_prefill_split_plan(q27, monkeypatch):
     assert q27.prefill_split_plan(2048, 24, 148, 32768) == (0, 1)
 
 
+def test_sum_norm_entry_points_check_their_arguments(q27):
+    """Argument checks of the sum_norm family come before any CUDA call."""
+    lib = ctypes.CDLL(q27.LIB_PATH)
+    lib.q27b_last_error.restype = ctypes.c_char_p
+    lib.q27b_sum_xbuf_bytes.restype = ctypes.c_uint64
+    assert lib.q27b_sum_xbuf_bytes(8, 4, 5120) == 256 + 2 * 8 * 4 * 5120 * 4
+    assert lib.q27b_sum_xbuf_bytes(0, 4, 5120) == 0
+    null, one = ctypes.c_void_p(0), ctypes.c_void_p(16)
+    f = ctypes.c_float(1e-6)
+    assert lib.q27b_sum_norm_q8(null, one, 5120, 4, one, f, null, null, null, null) == q27.BAD_SHAPE
+    assert lib.q27b_sum_norm_q8(one, one, 5100, 4, one, f, null, null, null, null) == q27.BAD_SHAPE   # n % 32
+    assert lib.q27b_sum_norm_q8(one, one, 32768, 4, one, f, null, null, null, null) == q27.BAD_SHAPE  # n > 16384
+    assert lib.q27b_sum_norm_q8(one, one, 5120, 4, one, f, null, one, null, null) == q27.BAD_SHAPE    # xq without xd
+    assert lib.q27b_sum_push(one, 5120, 4, 2, 2, one, null) == q27.BAD_SHAPE                         # rank >= world
+    assert lib.q27b_sum_push(one, 5120, 4, 0, 9, one, null) == q27.BAD_SHAPE                         # more than 8 ranks
+    assert lib.q27b_sum_norm_q8_wait(one, null, 2, 5120, 4, one, f, null, null, null, null) == q27.BAD_SHAPE
+    assert b"sum_norm_q8_wait" in lib.q27b_last_error()
+    assert lib.q27b_xbuf_alloc_bytes(ctypes.c_uint64(8), ctypes.byref(ctypes.c_void_p(0))) == q27.BAD_SHAPE
+
+
 def test_python_mirror_raises(q27):
     with pytest.raises(RuntimeError):
         q27.kv_append(None, None, None, None, None, 1, 4, 16)
