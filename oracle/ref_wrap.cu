@@ -71,4 +71,11 @@ int ref_attn_decode_ref(const float* qn, const float* qg, const void* kcache, co
   });
 }
 
+// sum_norm_q8 without an exchange (ar == nullptr, src/ops.h:101-104), for the fixture that pins the
+// oracle's statement of it.
+int ref_sum_norm_q8(float* x, const float* partial, int n, int rows, const float* w, float eps, float* h, int8_t* xq,
+                    float* xd, void* stream) {
+  return guard([&] { q27::sum_norm_q8(x, partial, n, rows, nullptr, w, eps, h, xq, xd, (cudaStream_t)stream); });
+}
+
 }  // extern "C"

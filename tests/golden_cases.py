@@ -48,3 +48,16 @@ def case_inputs(name):
     qg[..., 256:] = synth.normal(synth.SEED_GATE, (M, nqh, AD), start=tag)
     return dict(qn=qn, qg=qg, k=synth.normal(synth.SEED_K, (nkvh, n, AD), start=tag),
                 v=synth.normal(synth.SEED_V, (nkvh, n, AD), start=tag))
+
+
+SUM_NORM_EPS = 1e-6
+
+
+def sum_norm_inputs():
+    """x [4][5120], partial [4][5120], w [5120] of the sum_norm_q8 fixture (the reference's kernel takes n = 5120 only)."""
+    from qwen27_engine_b200 import synth
+    rows, n = 4, 5120
+    x = synth.normal(synth.SEED_Q, (rows, n), start=7 << 20)
+    part = (0.3 * synth.normal(synth.SEED_K, (rows, n), start=7 << 20)).astype(np.float32)
+    w = (1.0 + 0.1 * synth.normal(synth.SEED_GATE, (n,), start=7 << 20)).astype(np.float32)
+    return x, part, w

@@ -124,3 +124,19 @@ def test_new_prefill_kernel_against_reference_outputs(gold, q27, orc, name):
                      c["nkvh"], c["n_ctx"])
     torch.cuda.synchronize()
     assert_close(o.cpu().numpy(), gold[name + "/i8"], name + ": new kernel vs the reference's int8 kernel")
+
+
+def test_sum_norm_oracle_reproduces_the_reference_kernel(q27, orc):
+    """The reference's sum_norm_q8 kernel (no exchange) on a B200, from tests/golden/make_golden_sum_norm.py:
+    the sum is exact, the normalised row agrees to the last bits (the block sum's tree and the fast-math
+    rsqrt are the reference's), and q8_1 of the reference's own row gives its bytes and scales."""
+    from golden_cases import SUM_NORM_EPS, sum_norm_inputs
+    g = np.load(os.path.join(ROOT, "tests", "golden", "ref_sum_norm_b200.npz"))
+    x, part, w = sum_norm_inputs()
+    xn, h = orc.sum_norm(x, [part], w, SUM_NORM_EPS)
+    assert np.array_equal(xn, g["x"])
+    np.testing.assert_allclose(h, g["h"], rtol=2e-6, atol=1e-7)
+    rq, rd = orc.q8_1(g["h"].reshape(-1))
+    off = rq.astype(np.int32) - g["xq"].reshape(-1).astype(np.int32)
+    assert np.abs(off).max() <= 1 and (off != 0).mean() <= 1e-4  # the reference divides with fast-math
+    assert np.array_equal(rd, g["xd"])
