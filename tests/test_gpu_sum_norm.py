@@ -91,3 +91,24 @@ def test_sum_norm_wait_reports_a_missing_rank(q27):
     finally:
         for b in bufs:
             q27.xbuf_free(b)
+
+
+def test_sum_norm_q8_against_the_reference_kernel_fixture(q27):
+    """The library's kernel against the outputs of the reference's own sum_norm_q8 kernel (B200 fixture)."""
+    import os
+    from conftest import ROOT
+    from golden_cases import SUM_NORM_EPS, sum_norm_inputs
+    g = np.load(os.path.join(ROOT, "tests", "golden", "ref_sum_norm_b200.npz"))
+    x, part, w = sum_norm_inputs()
+    rows, n = x.shape
+    dx = dev(x)
+    h = torch.empty((rows, n), device="cuda")
+    xq = torch.zeros((rows, n), dtype=torch.int8, device="cuda")
+    xd = torch.zeros((rows * n // 32,), dtype=torch.float32, device="cuda")
+    q27.sum_norm_q8(dx, dev(part), n, rows, dev(w), SUM_NORM_EPS, h, xq, xd)
+    torch.cuda.synchronize()
+    assert np.array_equal(dx.cpu().numpy(), g["x"])
+    np.testing.assert_allclose(h.cpu().numpy(), g["h"], rtol=2e-6, atol=1e-7)
+    off = xq.cpu().numpy().astype(np.int32) - g["xq"].astype(np.int32)
+    assert np.abs(off).max() <= 1 and (off != 0).mean() <= 1e-3
+    np.testing.assert_allclose(xd.cpu().numpy(), g["xd"], rtol=1e-3)
