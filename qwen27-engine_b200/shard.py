@@ -168,6 +168,9 @@ def make_sum_exchange(q, rank, world, rows, n, group=None):
     return _exchange_buffers(q, lambda: q.xbuf_alloc_bytes(q.sum_xbuf_bytes(world, rows, n)), rank, world, group)
 
 
+_PEER_FAILED = "a peer could not export its buffer"
+
+
 def _exchange_buffers(q, alloc, me, count, group):
     err, own, peers = None, 0, []
     try:
@@ -183,10 +186,11 @@ def _exchange_buffers(q, alloc, me, count, group):
         except Exception as e:
             err = str(e)
     elif err is None:
-        err = "a peer could not export its buffer"
+        err = _PEER_FAILED
     errs = [None] * count
     dist.all_gather_object(errs, err, group=group)
     bad = [e for e in errs if e]
-    if bad:
-        raise RuntimeError("peer-memory exchange not available: " + bad[0])
+    if bad:  # every rank reports the same cause: the failing rank's own message where there is one
+        own_msgs = [e for e in bad if e != _PEER_FAILED]
+        raise RuntimeError("peer-memory exchange not available: " + (own_msgs or bad)[0])
     return own, peers

@@ -163,3 +163,64 @@ def test_prefill_query_ranges_over_two_gloo_ranks(q27, tmp_path):
     got, whole = np.load(tmp_path / "pf.npy")
     assert np.array_equal(np.load(tmp_path / "mask.npy"), np.ones(400, np.float32))
     assert np.array_equal(got, whole)
+
+
+class _FakeLib:
+    """Stands in for the library in the set-up of the exchange buffers: 'device addresses' are small
+    integers, a handle is the address plus an offset, rank `bad` fails where told to."""
+
+    def __init__(self, rank, bad=None, where=None):
+        self.rank, self.bad, self.where = rank, bad, where
+
+    def _maybe(self, where):
+        if self.rank == self.bad and self.where == where:
+            raise RuntimeError("injected failure in %s on rank %d" % (where, self.rank))
+
+    def sum_xbuf_bytes(self, world, rows, n):
+        return 256 + 2 * world * rows * n * 4
+
+    def xbuf_alloc_bytes(self, nbytes):
+        self._maybe("alloc")
+        return 1000 + self.rank
+
+    def ipc_export(self, ptr):
+        self._maybe("export")
+        return ptr + 100000
+
+    def ipc_open(self, handle):
+        self._maybe("open")
+        return handle - 100000 + 50  # the peer's buffer as mapped here
+
+
+def _exchange_rank_main(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import __graft_entry__ as ge
+    ge.load_package()
+    from qwen27_engine_b200 import shard
+    res = []
+    own, peers = shard.make_sum_exchange(_FakeLib(rank), rank, world, 4, 5120)
+    res.append(("ok", own, peers))
+    for where in ("alloc", "export", "open"):  # one rank fails: every rank raises, nobody is left in a collective
+        try:
+            shard.make_sum_exchange(_FakeLib(rank, bad=1, where=where), rank, world, 4, 5120)
+            res.append(("no error", where))
+        except RuntimeError as e:
+            res.append(("raised", where, str(e)))
+    dist.barrier()
+    with open(os.path.join(out_dir, "x%d.txt" % rank), "w") as f:
+        f.write(repr(res))
+    dist.destroy_process_group()
+
+
+def test_exchange_set_up_agrees_on_failures_over_two_gloo_ranks(q27, tmp_path):
+    port = _free_port()
+    mp.spawn(_exchange_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0 = eval((tmp_path / "x0.txt").read_text())
+    r1 = eval((tmp_path / "x1.txt").read_text())
+    assert r0[0] == ("ok", 1000, [1000, 1051]) and r1[0] == ("ok", 1001, [1050, 1001])  # own buffer as is, the peer's as mapped
+    for a, b in zip(r0[1:], r1[1:]):
+        assert a[0] == "raised" and b[0] == "raised" and a[1] == b[1]
+        assert "injected failure" in a[2] and "rank 1" in a[2] and a[2] == b[2]
