@@ -194,6 +194,14 @@ int q27b_sum_norm_q8_wait(float* x, void* xbuf, int world, int n, int rows, cons
  * has one kernel). */
 int q27b_set_decode_kernel(int which);
 
+/* How the warp-specialised split-K kernel shares out one sequence: pool != 0 (default): every CTA owns
+ * about four fifths of an equal share of the 64-position tiles and draws the rest one by one from a
+ * pool per KV head, so that CTAs on faster SMs take more (the result then depends on the order of
+ * f32 additions and may differ in the last bits from run to run); pool == 0: equal static shares, the
+ * same bits on every run. Process-wide; Q27B_DECODE_POOL=0 sets the initial value. No counterpart in
+ * the reference. */
+int q27b_set_decode_schedule(int pool);
+
 /* Which kernel q27b_attn_prefill* uses for q8_0 caches: 0 = default, 1 = int8 Q K^T
  * (attn_prefill_i8_kernel, src/attn.cu:557-801; the reference's default), 2 = f16 Q K^T on K and V
  * dequantised to f16 on the way to the tensor core (attn_prefill_kernel<PT, true>,
@@ -220,6 +228,15 @@ int q27b_debug_expire_wait(void* stream);
  * caller's stream between its split-K kernel and its merge kernel, so that a benchmark can time
  * the dominant kernel alone with CUDA events. NULL switches it off. */
 int q27b_debug_split_event(void* event);
+
+/* Measurement hook, no counterpart in the reference: while `stamps` (device memory, 8 x uint64 per
+ * CTA of the split-K grid, i.e. 8 * q27b_attn_chunks(nkvh) * nkvh values) is set, every CTA of the
+ * warp-specialised split-K kernel of q27b_attn_decode / _partial on the current device writes
+ * %globaltimer values (ns) there: [0] kernel entry, [1] barriers initialised and the position known,
+ * [2] first K tile landed, [3] / [4] Q K^T loop of group 0 / 1 finished, [5] first P tile handed
+ * over, [6] P V loop of group 0 finished, [7] partial written. A benchmark reads from them how a
+ * launch divides into ramp-up, streaming and drain. NULL switches it off. */
+int q27b_debug_decode_trace(unsigned long long* stamps);
 
 /* The reference's host ("wire") layout of rows [p0, p1) of one cache, used for its RAM swap of idle
  * slots and its prompt-cache checkpoints (Decoder::kv_copy, src/model.cu:1809-1830): the values

@@ -28,7 +28,7 @@ OK, BAD_SHAPE, CUDA_ERROR, UNSUPPORTED, DEVICE_STATUS = 0, 1, 2, 3, 4
 SYMBOLS = [
     "q27b_last_error", "q27b_device_status", "q27b_kv_cache_bytes", "q27b_attn_chunks", "q27b_kv_append",
     "q27b_attn_prep", "q27b_attn_decode", "q27b_attn_decode_partial", "q27b_lse_merge", "q27b_attn_decode_paged",
-    "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_set_decode_kernel", "q27b_set_prefill_kernel", "q27b_prefill_split_plan", "q27b_sum_xbuf_bytes", "q27b_xbuf_alloc_bytes",
+    "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_debug_decode_trace", "q27b_set_decode_kernel", "q27b_set_decode_schedule", "q27b_set_prefill_kernel", "q27b_prefill_split_plan", "q27b_sum_xbuf_bytes", "q27b_xbuf_alloc_bytes",
     "q27b_sum_norm_q8", "q27b_sum_push", "q27b_sum_norm_q8_wait", "q27b_debug_expire_wait",
     "q27b_attn_prefill_q8_1", "q27b_xbuf_bytes", "q27b_attn_decode_partial_push", "q27b_lse_merge_wait",
     "q27b_xbuf_alloc", "q27b_xbuf_free", "q27b_ipc_export", "q27b_ipc_open", "q27b_ipc_close",
@@ -247,6 +247,16 @@ def set_prefill_kernel(which):
 def debug_split_event(event):
     """event: a recorded-at-least-once torch.cuda.Event (timing enabled) or None."""
     _check(_lib.q27b_debug_split_event(ctypes.c_void_p(event.cuda_event if event is not None else 0)))
+
+
+def set_decode_schedule(pool):
+    """True: CTAs share a pool of tiles (default, faster); False: equal static shares (same bits every run)."""
+    _check(_lib.q27b_set_decode_schedule(int(bool(pool))))
+
+
+def debug_decode_trace(stamps):
+    """stamps: int64 CUDA tensor of 8 values per CTA of the split-K grid, or None (see the header)."""
+    _check(_lib.q27b_debug_decode_trace(_ptr(stamps, torch.int64, optional=True)))
 
 
 def new_cache(nkvh, n_ctx, q8=True, device="cuda", fill=0):

@@ -638,13 +638,28 @@ int launch_decode_t(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensor
 // differently specialised warp roles per SM with a serial hand-off chain between them and is that
 // sensitive to code layout; it also starts 1.5 us later (13.2 us against 11.7 us at 64 positions).
 // So the warp-MMA kernel is the default. f16 caches always use it.
-int g_kernel_choice = -1;  // -1: not read yet; 0 default, 1 warp-MMA, 2 tcgen05
-bool use_tc_kernel() {
+// Whether the CTAs of the warp-specialised kernel share a pool of tiles (see decode_ws.cu) or keep to
+// equal static shares (Q27B_DECODE_POOL=0, q27b_set_decode_schedule(0)): the static form gives the
+// same bits on every run, the pool form ends earlier.
+bool g_pool_schedule = [] {
+  const char* e = getenv("Q27B_DECODE_POOL");
+  return !(e && e[0] == '0');
+}();
+int g_kernel_choice = -1;  // -1: not read yet; 0 default, 1 warp-MMA, 2 tcgen05, 3 warp-specialised
+int kernel_choice() {
   if (g_kernel_choice < 0) {
     const char* e = getenv("Q27B_DECODE_KERNEL");
-    g_kernel_choice = !e ? 0 : e[0] == 'm' ? 1 : e[0] == 't' ? 2 : 0;
+    g_kernel_choice = !e ? 0 : e[0] == 'm' ? 1 : e[0] == 't' ? 2 : e[0] == 'w' ? 3 : 0;
   }
-  return g_kernel_choice == 2;
+  return g_kernel_choice;
+}
+// Launches the split-K kernel chosen for a q8_0 cache.
+int launch_q8(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
+              const DecodeParams& p, bool paged, int nseq, cudaStream_t s) {
+  const int k = kernel_choice();
+  if (k == 2) return launch_decode_tc(kv, ks, vv, vs, p, paged, nseq, s);
+  if (k == 3) return launch_decode_ws(kv, ks, vv, vs, p, paged, nseq, s);
+  return paged ? launch_decode_t<true, true>(kv, ks, vv, vs, p, nseq, s) : launch_decode_t<false, true>(kv, ks, vv, vs, p, nseq, s);
 }
 
 // Split-K pass of one sequence into ctx->part [nkvh][nch][24][258].
@@ -659,11 +674,10 @@ int decode_split(DeviceCtx* ctx, const float* qn, const void* kcache, const void
   DecodeParams p = {};
   p.qn = qn; p.part = ctx->part; p.pos0 = pos0; p.status = ctx->status;
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nch = nch; p.kq_scale = kq_scale;
-  p.base_pos = base_pos; p.n_local = n_local;
+  p.base_pos = base_pos; p.n_local = n_local; p.trace = ctx->trace;
+  p.sched = (g_pool_schedule && nkvh <= 32) ? ctx->status + 16 : nullptr;
   *nch_out = nch;
-  if (int rc = !q8             ? launch_decode_t<false, false>(kv, ks, vv, vs, p, 1, s)
-               : use_tc_kernel() ? launch_decode_tc(kv, ks, vv, vs, p, false, 1, s)
-                                 : launch_decode_t<false, true>(kv, ks, vv, vs, p, 1, s))
+  if (int rc = !q8 ? launch_decode_t<false, false>(kv, ks, vv, vs, p, 1, s) : launch_q8(kv, ks, vv, vs, p, false, 1, s))
     return rc;
   if (ctx->split_event) Q27B_CK(cudaEventRecord(ctx->split_event, s));
   return Q27B_OK;
@@ -820,8 +834,13 @@ int q27b_attn_decode_noalloc(const float* qn, const float* qg, const void* kcach
 }
 
 int q27b_set_decode_kernel(int which) {
-  if (which < 0 || which > 2) return fail(Q27B_BAD_SHAPE, "set_decode_kernel: 0 auto, 1 warp-MMA, 2 tcgen05");
+  if (which < 0 || which > 3) return fail(Q27B_BAD_SHAPE, "set_decode_kernel: 0 auto, 1 warp-MMA, 2 tcgen05, 3 warp-specialised");
   g_kernel_choice = which;
+  return Q27B_OK;
+}
+
+int q27b_set_decode_schedule(int pool) {
+  g_pool_schedule = pool != 0;
   return Q27B_OK;
 }
 
@@ -829,6 +848,13 @@ int q27b_debug_split_event(void* event) {
   DeviceCtx* ctx;
   if (int rc = device_ctx(&ctx)) return rc;
   ctx->split_event = (cudaEvent_t)event;
+  return Q27B_OK;
+}
+
+int q27b_debug_decode_trace(unsigned long long* stamps) {
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  ctx->trace = stamps;
   return Q27B_OK;
 }
 
@@ -859,9 +885,7 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = max_pages * Q27B_PAGE; p.nch = nch; p.kq_scale = kq_scale;
   p.base_pos = 0; p.n_local = -1;
   p.page_table = page_table; p.seq_len = seq_len; p.max_pages = max_pages; p.n_pages = n_pages; p.chunk_len = chunk;
-  if (int rc = use_tc_kernel() ? launch_decode_tc(kv, ks, vv, vs, p, true, B, (cudaStream_t)stream)
-                               : launch_decode_t<true, true>(kv, ks, vv, vs, p, B, (cudaStream_t)stream))
-    return rc;
+  if (int rc = launch_q8(kv, ks, vv, vs, p, true, B, (cudaStream_t)stream)) return rc;
   MergeParams mp = {};
   mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)B * T * nqh; mp.qg = qg; mp.o = o; mp.T = T; mp.nqh = nqh;
   mp.seq_len = seq_len; mp.chunk_len = chunk;

@@ -18,11 +18,22 @@ struct DecodeParams {
   const int* page_table;  // [B][max_pages]
   const int* seq_len;     // [B], counts the T new tokens
   int max_pages, n_pages, chunk_len;
+  // Tile pool of the warp-specialised kernel (one sequence only): [KV head] tiles drawn so far,
+  // [32] CTAs that are done; all zero between launches. Null: every CTA keeps to its own share.
+  int* sched;
+  // measurement hook (null in normal use): [CTA][8] globaltimer stamps of the warp-specialised kernel
+  unsigned long long* trace;
 };
 
 // Split-K decode over a q8_0 cache on the tcgen05 path (decode_tc.cu). Same grid, same partial
 // layout and same tensor maps as the warp-MMA kernel. paged: rows through the page table.
 int launch_decode_tc(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
                      const DecodeParams& p, bool paged, int nseq, cudaStream_t s);
+
+// The warp-specialised split-K kernel (decode_ws.cu): same grid, partial layout and tensor maps again.
+int launch_decode_ws(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
+                     const DecodeParams& p, bool paged, int nseq, cudaStream_t s);
+// Opts the kernels of decode_ws.cu into their shared-memory size on the current device.
+int decode_ws_setup();
 
 }  // namespace q27b

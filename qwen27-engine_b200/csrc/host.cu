@@ -110,7 +110,7 @@ int q27b_device_status(int* status_out) {
   int st = 0;
   Q27B_CK(cudaDeviceSynchronize());
   Q27B_CK(cudaMemcpy(&st, ctx->status, sizeof(int), cudaMemcpyDeviceToHost));
-  if (st) Q27B_CK(cudaMemset(ctx->status, 0, sizeof(int)));
+  if (st) Q27B_CK(cudaMemset(ctx->status, 0, 256));  // the word, and the tile counters an aborted kernel may have left behind
   if (status_out) *status_out = st;
   return st ? fail(Q27B_DEVICE_STATUS, "device status word = " + std::to_string(st)) : Q27B_OK;
 }

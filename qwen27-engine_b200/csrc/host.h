@@ -35,6 +35,7 @@ struct DeviceCtx {
   size_t work_ints = 0;
   bool decode_attr = false, prefill_attr = false;
   cudaEvent_t split_event = nullptr;  // measurement hook: recorded after the split kernel of a decode call
+  unsigned long long* trace = nullptr;  // measurement hook: per-CTA time stamps of the split kernel
 };
 
 // Context of the current device, created on first use (allocates the status word).

@@ -11,9 +11,9 @@ AD, GQA = 256, 6
 SCALE = 1.0 / 16.0
 
 
-@pytest.fixture(autouse=True, params=[1, 2], ids=["mma", "tc"])
+@pytest.fixture(autouse=True, params=[1, 2, 3], ids=["mma", "tc", "ws"])
 def decode_kernel(request, q27):
-    """Every test of this module runs on both split-K kernels (warp-MMA and tcgen05)."""
+    """Every test of this module runs on every split-K kernel (warp-MMA, tcgen05, warp-specialised)."""
     q27.set_decode_kernel(request.param)
     yield request.param
     q27.set_decode_kernel(0)
