@@ -186,12 +186,12 @@ int q27b_sum_push(const float* partial, int n, int rows, int rank, int world, vo
 int q27b_sum_norm_q8_wait(float* x, void* xbuf, int world, int n, int rows, const float* w, float eps, float* h, int8_t* xq,
                           float* xd, void* stream);
 
-/* Which split-K kernel q27b_attn_decode* uses for q8_0 caches: 0 = default (the warp-MMA kernel),
- * 1 = warp-MMA kernel, 2 = tcgen05 kernel (both contractions on the 5th-generation tensor cores;
- * faster at long contexts in its best builds, less predictable: see csrc/decode.cu). Both compute
- * the same operator with the same roundings (src/attn.cu:95-292). Process-wide; the environment
- * variable Q27B_DECODE_KERNEL=mma|tc sets the initial value. No counterpart in the reference (it
- * has one kernel). */
+/* Which split-K kernel q27b_attn_decode* uses for q8_0 caches: 0 = default (the warp-specialised
+ * kernel), 1 = the single-role warp-MMA kernel (every warp runs both contractions), 2 = the tcgen05
+ * kernel (both contractions on the 5th-generation tensor cores), 3 = the warp-specialised kernel
+ * (Q K^T warps and P V warps, csrc/decode_ws.cu). All compute the same operator with the same roundings
+ * (src/attn.cu:95-292). Process-wide; the environment variable Q27B_DECODE_KERNEL=mma|tc|ws sets the
+ * initial value. No counterpart in the reference (it has one kernel). */
 int q27b_set_decode_kernel(int which);
 
 /* How the warp-specialised split-K kernel shares out one sequence: pool != 0 (default): every CTA owns

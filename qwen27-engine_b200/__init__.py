@@ -226,7 +226,7 @@ def sum_norm_q8_wait(x, xbuf, world, n, rows, w, eps, h=None, xq=None, xd=None):
 
 
 def set_decode_kernel(which):
-    """0 automatic, 1 warp-MMA kernel, 2 tcgen05 kernel (q8_0 caches; see include/q27b_attn.h)."""
+    """0 default (= 3), 1 single-role warp-MMA kernel, 2 tcgen05 kernel, 3 warp-specialised kernel (q8_0 caches; see include/q27b_attn.h)."""
     _check(_lib.q27b_set_decode_kernel(int(which)))
 
 

@@ -630,14 +630,12 @@ int launch_decode_t(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensor
   return launch_decode<3, PAGED, Q8>(kv, ks, vv, vs, p, nseq, s);
 }
 
-// Which split-K kernel serves a q8_0 cache: the warp-MMA kernel of this file unless
-// Q27B_DECODE_KERNEL=tc or q27b_set_decode_kernel(2) asks for the tcgen05 kernel (decode_tc.cu).
-// Measured on B200 (same call, CUDA-graph timing, 150k positions): builds of the tcgen05 kernel that
-// differ only in immaterial details (an extra loop condition, a helper moved out of line) ran at
-// 73.7, 75.7 and 80.8 us; the warp-MMA kernel stays within 76.5-77.7 us. The tcgen05 kernel runs eight
-// differently specialised warp roles per SM with a serial hand-off chain between them and is that
-// sensitive to code layout; it also starts 1.5 us later (13.2 us against 11.7 us at 64 positions).
-// So the warp-MMA kernel is the default. f16 caches always use it.
+// Which split-K kernel serves a q8_0 cache: the warp-specialised kernel of decode_ws.cu unless
+// Q27B_DECODE_KERNEL=mma|tc or q27b_set_decode_kernel(1|2) asks for the single-role warp-MMA kernel of
+// this file or the tcgen05 kernel (decode_tc.cu). Measured on B200 (same call, 20 calls in a CUDA
+// graph, 150k positions, T = 4): warp-specialised 69.7 us per call, single-role 75.7 us, tcgen05
+// 73.7-80.8 us depending on the build (eight differently specialised warp roles with a serial hand-off
+// chain: sensitive to code layout). f16 caches always use the kernel of this file.
 // Whether the CTAs of the warp-specialised kernel share a pool of tiles (see decode_ws.cu) or keep to
 // equal static shares (Q27B_DECODE_POOL=0, q27b_set_decode_schedule(0)): the static form gives the
 // same bits on every run, the pool form ends earlier.
@@ -645,7 +643,7 @@ bool g_pool_schedule = [] {
   const char* e = getenv("Q27B_DECODE_POOL");
   return !(e && e[0] == '0');
 }();
-int g_kernel_choice = -1;  // -1: not read yet; 0 default, 1 warp-MMA, 2 tcgen05, 3 warp-specialised
+int g_kernel_choice = -1;  // -1: not read yet; 0 default (= 3), 1 single-role warp-MMA, 2 tcgen05, 3 warp-specialised
 int kernel_choice() {
   if (g_kernel_choice < 0) {
     const char* e = getenv("Q27B_DECODE_KERNEL");
@@ -658,7 +656,7 @@ int launch_q8(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* v
               const DecodeParams& p, bool paged, int nseq, cudaStream_t s) {
   const int k = kernel_choice();
   if (k == 2) return launch_decode_tc(kv, ks, vv, vs, p, paged, nseq, s);
-  if (k == 3) return launch_decode_ws(kv, ks, vv, vs, p, paged, nseq, s);
+  if (k == 0 || k == 3) return launch_decode_ws(kv, ks, vv, vs, p, paged, nseq, s);
   return paged ? launch_decode_t<true, true>(kv, ks, vv, vs, p, nseq, s) : launch_decode_t<false, true>(kv, ks, vv, vs, p, nseq, s);
 }
 
