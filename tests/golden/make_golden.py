@@ -6,6 +6,8 @@ golden vectors for this path, so these outputs are what pins the CPU oracle: tes
 recomputes every case with the oracle from the same seeds.
 
 Usage (GPU box): python tests/golden/make_golden.py [--out tests/golden/ref_b200.npz]
+                 python tests/golden/make_golden.py --deep [--out tests/golden/ref_b200_deep.npz]
+--deep runs the cases at depth (DEEP_CASES of tests/golden_cases.py) and keeps only the rows the tests compare.
 """
 import argparse
 import ctypes
@@ -21,15 +23,18 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 import __graft_entry__ as ge  # noqa: E402
 import oracle  # noqa: E402
-from golden_cases import CASES, case_inputs  # noqa: E402
+from golden_cases import CASES, DEEP_CASES, case_inputs  # noqa: E402
 
 AD = 256
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden", "ref_b200.npz"))
+    ap.add_argument("--out", default=None)
+    ap.add_argument("--deep", action="store_true")
     args = ap.parse_args()
+    cases = DEEP_CASES if args.deep else CASES
+    args.out = args.out or os.path.join(ROOT, "tests", "golden", "ref_b200_deep.npz" if args.deep else "ref_b200.npz")
     ge.load_package()
     ref = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libq27ref.so"))
     ref.ref_last_error.restype = ctypes.c_char_p
@@ -44,7 +49,7 @@ def main():
     d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     f = ctypes.c_float
     out = {}
-    for name, c in CASES.items():
+    for name, c in cases.items():
         x = case_inputs(name)
         kind = c["kind"]
         if kind == "prep":
@@ -55,14 +60,22 @@ def main():
             vc = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
             pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
             keep = [d(x[k]) for k in ("qg", "k", "v", "q_norm", "k_norm")]  # stay alive until the kernel has run
+            rope3 = d(np.array(c["rope3"], np.int32)) if c.get("rope3") else None
             ck(ref.ref_attn_prep(p(keep[0]), p(keep[1]), p(keep[2]), p(keep[3]), p(keep[4]), p(qn),
                                  p(kc), p(vc), p(pos), T, f(c["eps"]), f(c["theta_scale"]), nqh, nkvh, n_ctx, int(q8),
-                                 None, None, None))
+                                 None, p(rope3), None))
             torch.cuda.synchronize()
             if T <= 8:
                 out[name + "/qn"] = qn.cpu().numpy()
-            out[name + "/kcache"] = kc.cpu().numpy()
-            out[name + "/vcache"] = vc.cpu().numpy()
+            if c.get("rows_only"):  # the rows just written: values [nkvh][T][256] and scales [nkvh][T][8]
+                for key, cache in (("k", kc), ("v", vc)):
+                    vals = cache[: nkvh * n_ctx * AD].view(nkvh, n_ctx, AD)[:, pos0:pos0 + T]
+                    sc = cache[nkvh * n_ctx * AD:].view(torch.float16).view(nkvh, n_ctx, 8)[:, pos0:pos0 + T]
+                    out[name + "/%srows" % key] = vals.cpu().numpy()
+                    out[name + "/%sscales" % key] = sc.cpu().numpy()
+            else:
+                out[name + "/kcache"] = kc.cpu().numpy()
+                out[name + "/vcache"] = vc.cpu().numpy()
         elif kind == "decode":
             T, nkvh, n, n_ctx, q8 = c["T"], c["nkvh"], c["n"], c["n_ctx"], c["q8"]
             nqh = nkvh * 6
@@ -96,6 +109,10 @@ def main():
             ck(ref.ref_attn_prefill(p(qn), p(qg), p(kcd), p(vcd), p(o), p(pos), M, f(c["scale"]), nqh,
                                     nkvh, n_ctx, 1, None, -1))
             torch.cuda.synchronize()
+            if c.get("keep"):  # sampled token ranges only
+                for a, b in c["keep"]:
+                    out[name + "/i8_%d_%d" % (a, b)] = o[a:b].cpu().numpy()
+                continue
             out[name + "/i8"] = o.cpu().numpy()
             o2 = torch.zeros((M, nqh, AD), device="cuda")
             ck(ref.ref_attn_decode_ref(p(qn), p(qg), p(kcd), p(vcd), p(o2), p(pos), M, f(c["scale"]),

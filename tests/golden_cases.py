@@ -22,10 +22,30 @@ CASES = {
 }
 
 
+# Cases at depth, in a fixture of their own (tests/golden/ref_b200_deep.npz), which keeps only what the
+# tests compare: query rows and the cache rows just written (prep), the output (decode), sampled token
+# ranges of the output (prefill). Inputs are regenerated from the seeds.
+DEEP_CASES = {
+    # attn_prep at the depth the metric is quoted at: the rotation angle of dim 0 is ~1.5e5 rad, where the
+    # fast sine / cosine of the reference's build (-use_fast_math) are far from the exact ones
+    "prep_q8_deep": dict(kind="prep", T=4, nqh=12, nkvh=2, n_ctx=150016, pos0=150000, q8=True, eps=1e-6,
+                         theta_scale=float(10000000.0 ** (-2.0 / 64)), rows_only=True),
+    # IMRoPE sections with large time / height / width positions
+    "prep_q8_rope3": dict(kind="prep", T=4, nqh=12, nkvh=2, n_ctx=64, pos0=20, q8=True, eps=1e-6,
+                          theta_scale=float(10000000.0 ** (-2.0 / 64)), rows_only=True,
+                          rope3=[[120000, 300, 77], [120001, 300, 78], [120002, 301, 77], [149999, 2047, 2047]]),
+    "decode_deep": dict(kind="decode", T=4, nkvh=2, n=40000, n_ctx=40000, q8=True, scale=1 / 16),
+    "prefill_deep": dict(kind="prefill", M=256, nkvh=1, pos0=8192, n_ctx=8448, scale=1 / 16,
+                         keep=[(0, 8), (124, 132), (248, 256)]),
+}
+CASES_ALL = dict(CASES, **DEEP_CASES)
+
+
 def case_inputs(name):
     from qwen27_engine_b200 import synth
-    c = CASES[name]
-    tag = (sorted(CASES).index(name) + 1) << 26  # disjoint slices of the streams per case
+    c = CASES_ALL[name]
+    # disjoint slices of the streams per case
+    tag = (sorted(CASES).index(name) + 1 if name in CASES else 17 + sorted(DEEP_CASES).index(name)) << 26
     if c["kind"] == "prep":
         T, nqh, nkvh = c["T"], c["nqh"], c["nkvh"]
         return dict(qg=synth.normal(synth.SEED_Q, (T, nqh, 512), start=tag),

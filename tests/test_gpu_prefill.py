@@ -97,6 +97,47 @@ def test_prefill_chunk_2048_rows_sampled(q27, orc):
     assert q27.device_status() == 0
 
 
+_cfg4 = {}
+
+
+def _config4_case(orc, pos0):
+    """The prefill configuration of the metric (M = 2048, 24 Q / 4 KV heads) on a prefix of pos0 tokens;
+    built once per prefix (150,048 positions x 4 heads of N(0,1) rows take a while on the host)."""
+    if pos0 not in _cfg4:
+        _cfg4.clear()  # one prefix at a time: a case is 1.2 GB of host memory
+        _cfg4[pos0] = make_case(orc, 2048, pos0, 4, n_ctx=pos0 + 2048)
+    return _cfg4[pos0]
+
+
+@pytest.mark.parametrize("kernel", [1, 2], ids=["int8", "f16qk"])
+@pytest.mark.parametrize("pos0", [0, 148000])
+def test_prefill_config4_at_both_ends(q27, orc, pos0, kernel):
+    """The metric's prefill chunk at the two depths that the 32,768 test above leaves out: no prefix at
+    all (causal only, tiles of 1..16 K/V tiles) and 148,000 tokens (the depth the TOPS figure is quoted
+    at, where the tail split cuts the first query tiles into 5 pieces). Both kernels; the oracle checks
+    token ranges at the start, around tile and split boundaries, and at the end."""
+    M, nkvh = 2048, 4
+    nqh = nkvh * GQA
+    qn, qg, kc_ref, vc_ref, n, n_ctx = _config4_case(orc, pos0)
+    o = torch.full((M, nqh, AD), float("nan"), device="cuda")
+    q27.set_prefill_kernel(kernel)
+    try:
+        q27.attn_prefill(dev(qn), dev(qg), dev(kc_ref), dev(vc_ref), o, pos_tensor(pos0), M, SCALE, nqh, nkvh, n_ctx,
+                         True, pos0)
+        torch.cuda.synchronize()
+    finally:
+        q27.set_prefill_kernel(0)
+    out = o.cpu().numpy()
+    assert np.isfinite(out).all()
+    for lo in (0, 126, 510, 1022, 2044):
+        if kernel == 1:
+            ref = orc.attn_prefill_i8(qn, qg, kc_ref, vc_ref, pos0, SCALE, nkvh, n_ctx, lo, lo + 4)[lo:lo + 4]
+        else:
+            ref = orc.attn_ref(qn[lo:lo + 4], qg[lo:lo + 4], kc_ref, vc_ref, pos0 + lo, SCALE, nkvh, n_ctx, q8=True)
+        assert_close(out[lo:lo + 4], ref, "prefix %d, tokens %d..%d" % (pos0, lo, lo + 3))
+    assert q27.device_status() == 0
+
+
 def test_prefill_agrees_with_decode(q27, orc):
     """The last 4 tokens of a prefill chunk and a 4-token decode over the same cache differ only by
     the int8 rounding of Q (bounded well inside the path's tolerance)."""
