@@ -14,9 +14,15 @@ keys, one sequence sharded over the ranks by KV-head group and then KV length wi
 gather + log-sum-exp merge ("strong"), the other context depths, the prefill TOPS and the
 reference's own kernels on the same GPU.
 
+Timing: `value` is taken the way the reference times this operator (tools/bench_attn.cu:131-147): the
+steps are captured in CUDA graphs of 20 calls and replayed, so that host launch time does not count;
+the call-by-call figure is kept beside it (eager_*). The split-K kernel alone (roofline) is timed with
+CUDA events recorded inside such a graph, on the launching stream, around each launch of the kernel.
+
 --impl reference runs the reference's kernels (oracle/_ref/libq27ref.so: its src/attn.cu compiled
-for sm_100a, called through its own q27::attn_decode) on the same workload; the reference has no
-CPU implementation of this path. If that library is missing, the CPU oracle is timed instead.
+for sm_100a, called through its own q27::attn_decode) on the same workload, timed the same way; that
+process loads nothing of this repository's library (the caches are written with torch). The reference
+has no CPU implementation of this path. If that library is missing, the CPU oracle is timed instead.
 """
 import argparse
 import ctypes
@@ -116,21 +122,37 @@ def graph_us(fn, calls=20, replays=5):
     return e0.elapsed_time(e1) * 1e3 / (calls * replays)
 
 
-def fill_caches(q, nkvh, n, n_ctx, seed, q8=True):
-    """K and V caches of n positions, written by the library's own append kernel from N(0,1) rows."""
-    g = torch.Generator(device="cuda")
-    g.manual_seed(seed)
-    kc, vc = q.new_cache(nkvh, n_ctx, q8), q.new_cache(nkvh, n_ctx, q8)
-    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
-    step = 8192
+def torch_q8_cache(nkvh, n, n_ctx, gen):
+    """One q8_0 cache in the reference's layout (int8 values [nkvh][n_ctx][256], then f16 scales
+    [nkvh][n_ctx][8]) holding n positions of N(0,1) rows, quantised with torch operations (d = amax / 127
+    per 32 values, q = round(x / d)): synthetic data of the metric's distribution that neither arm's
+    library has touched."""
+    buf = torch.zeros(nkvh * n_ctx * 272, dtype=torch.uint8, device="cuda")
+    vals = buf[: nkvh * n_ctx * AD].view(torch.int8).view(nkvh, n_ctx, AD)
+    sc = buf[nkvh * n_ctx * AD:].view(torch.float16).view(nkvh, n_ctx, 8)
+    step = 16384
     for p0 in range(0, n, step):
         m = min(step, n - p0)
-        k = torch.randn((m, nkvh, AD), generator=g, device="cuda")
-        v = torch.randn((m, nkvh, AD), generator=g, device="cuda")
-        pos.fill_(p0)
-        q.kv_append(k, v, kc, vc, pos, m, nkvh, n_ctx, q8)
-    torch.cuda.synchronize()
-    return kc, vc
+        x = torch.randn((nkvh, m, 8, 32), generator=gen, device="cuda")
+        d = x.abs().amax(-1, keepdim=True) / 127.0
+        vals[:, p0:p0 + m] = (x / d).round_().clamp_(-127, 127).to(torch.int8).view(nkvh, m, AD)
+        sc[:, p0:p0 + m] = d.squeeze(-1).to(torch.float16)
+    return buf
+
+
+def torch_caches(nkvh, n, n_ctx, seed, q8=True):
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    if q8:
+        return torch_q8_cache(nkvh, n, n_ctx, g), torch_q8_cache(nkvh, n, n_ctx, g)
+
+    def f16():  # f16 cache [nkvh][n_ctx][256] halves
+        c = torch.zeros((nkvh, n_ctx, AD), dtype=torch.float16, device="cuda")
+        for p0 in range(0, n, 16384):
+            m = min(16384, n - p0)
+            c[:, p0:p0 + m] = torch.randn((nkvh, m, AD), generator=g, device="cuda").to(torch.float16)
+        return c.view(torch.uint8).view(-1)
+    return f16(), f16()
 
 
 def kv_bytes(nkvh, n):
@@ -150,6 +172,39 @@ def time_steps(fn, steps, warmup, dist=None):
     e0.record()
     for i in range(steps):
         fn(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        ms = float(t.item())
+    return ms
+
+
+def time_graph_steps(fn, steps, warmup, dist=None, calls=20):
+    """The same contract with the steps captured in CUDA graphs: W untimed calls issued one by one, then
+    graphs of `calls` steps (one graph of all K steps when K is not a multiple of it), one untimed replay,
+    then exactly K steps of replays between two events; returns ms per step (max over ranks)."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if steps % calls != 0:
+        calls = steps
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(calls):
+            fn(warmup + i)
+    g.replay()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps // calls):
+        g.replay()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
@@ -250,7 +305,10 @@ def main():
     else:
         torch.cuda.set_device(local)
 
-    q = ge.load_package()
+    if args.impl == "reference":
+        q = None  # the reference arm loads nothing of this repository's library
+    else:
+        q = ge.load_package()
     if args.mode == "prefill":
         prefill_mode(q, args, steps, warmup, dist, rank, world)
         return
@@ -272,11 +330,13 @@ def main():
         "config": {"workload": "verify-decode T=4, 24 Q / 4 KV heads, head_dim 256, q8_0 KV length %d" % n,
                    "per_gpu": "one sequence per GPU (batched decode sharded by sequence, no exchange)",
                    "bytes_per_step_per_gpu": kv_bytes(NKVH, n),
-                   "l2": "%.0f MB of KV per step, %d caches in rotation: inputs larger than L2" % (kv_bytes(NKVH, n) / 1e6, NBUF)},
+                   "l2": "%.0f MB of KV per step, %d caches in rotation: inputs larger than L2" % (kv_bytes(NKVH, n) / 1e6, NBUF),
+                   "timing": "steps captured in CUDA graphs of 20 calls and replayed (tools/bench_attn.cu:131-147); "
+                             "eager_* = the same calls issued one by one"},
     }
 
-    # ---- inputs resident in HBM
-    caches = [fill_caches(q, NKVH, n, n_ctx, 1002 + 10 * rank + i) for i in range(NBUF)]
+    # ---- inputs resident in HBM: q8_0 caches of N(0,1) rows written with torch (the same for both arms)
+    caches = [torch_caches(NKVH, n, n_ctx, 1002 + 10 * rank + i) for i in range(NBUF)]
     g = torch.Generator(device="cuda")
     g.manual_seed(1001 + rank)
     qn = torch.randn((T, NQH, AD), generator=g, device="cuda")
@@ -285,7 +345,7 @@ def main():
     pos = torch.tensor([n - T], dtype=torch.int32, device="cuda")
 
     if args.impl == "reference":
-        run_reference(args, line, q, caches, qn, qg, o, pos, n, n_ctx, steps, warmup)
+        run_reference(args, line, caches, qn, qg, o, pos, n, n_ctx, steps, warmup)
         return
 
     def step(i):
@@ -294,34 +354,21 @@ def main():
 
     sampler = ClockSampler(local)
     sampler.start()
-    ms = time_steps(step, steps, warmup, dist)
+    ms = time_graph_steps(step, steps, warmup, dist)
     clocks = sampler.stop()
     assert q.device_status() == 0, "a kernel reported a device-side problem"
+    ms_eager = time_steps(step, steps, warmup, dist)
     line["value"] = world * kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9
     line["ms_per_step"] = ms
     line["us_per_step"] = ms * 1e3
+    line["eager_ms_per_step"] = ms_eager
+    line["eager_value"] = world * kv_bytes(NKVH, n) / (ms_eager * 1e-3) / 1e9
     line["gpu_launches"] = 2 * steps
     line["clocks"] = clocks
 
-    # ---- the dominant kernel alone (split-K decode kernel), CUDA events on the launching stream
-    ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-    ev1 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-    for e in ev1:
-        e.record()
-    torch.cuda.synchronize()
-    for i in range(steps):
-        q.debug_split_event(ev1[i])
-        ev0[i].record()
-        step(i)
-    q.debug_split_event(None)
-    torch.cuda.synchronize()
-    kms = statistics.mean(a.elapsed_time(b) for a, b in zip(ev0, ev1))
-    pk, pk_kind = peaks()
-    ach = kv_bytes(NKVH, n) / (kms * 1e-3) / 1e9
-    line["roofline"] = {"bound": "hbm", "kernel": "decode_kernel<3,false,true> (q8_0, T=4)", "achieved": ach, "peak": pk["hbm_gbs"],
-                        "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "peak_kind": pk_kind + " copy bandwidth (burst)",
-                        "frac_of_8TBs_nominal": ach / 8000.0, "kernel_us": kms * 1e3,
-                        "traffic": env_float("Q27B_NCU_TRAFFIC_BYTES")}
+    # ---- the dominant kernel alone (split-K decode kernel): CUDA events recorded on the launching stream
+    # around every launch of it, inside a replayed graph of 20 calls (event nodes of the graph)
+    line["roofline"] = split_kernel_roofline(q, step, n)
 
     # ---- end to end through the C ABI with host buffers
     line["e2e"] = e2e(q, caches, n, n_ctx, steps, warmup, dist, world)
@@ -339,6 +386,8 @@ def main():
             line["sum_norm"] = {"error": str(e)}
     if rank == 0 and world == 1 and not args.no_extras:
         line["extras"] = extras(q, caches, qn, qg, o, n_ctx)
+        # the second half of the metric, last in the line: int8 prefill TOPS of a 2048-token chunk per prefix depth
+        line["prefill_int8_tops"] = {k: round(v["tops"], 1) for k, v in line["extras"]["prefill"].items() if "tops" in v}
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:
@@ -346,15 +395,51 @@ def main():
         dist.destroy_process_group()
 
 
+def split_kernel_roofline(q, step, n, calls=20, replays=5):
+    """Average duration of one launch of the split-K kernel: a CUDA graph of `calls` decode calls that stop
+    after the split-K kernel (q27b_debug_split_only), replayed between two CUDA events on the launching
+    stream; against the measured copy peak. (With event nodes around every launch inside the graph the
+    figure comes out 3-5 us higher than the whole two-kernel step: event_nodes_us, kept for the record.)"""
+    step(0)
+    torch.cuda.synchronize()
+    q.debug_split_only(True)
+    try:
+        kus = graph_us(step, calls, replays)
+    finally:
+        q.debug_split_only(False)
+    ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(calls)]
+    ev1 = [torch.cuda.Event(enable_timing=True) for _ in range(calls)]
+    for e in ev0 + ev1:
+        e.record()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(calls):
+            q.debug_split_events(ev0[i], ev1[i])
+            step(i)
+    q.debug_split_events(None, None)
+    g.replay()
+    torch.cuda.synchronize()
+    g.replay()
+    torch.cuda.synchronize()
+    ev_us = sum(a.elapsed_time(b) for a, b in zip(ev0, ev1)) / calls * 1e3
+    pk, pk_kind = peaks()
+    ach = kv_bytes(NKVH, n) / (kus * 1e-6) / 1e9
+    return {"bound": "hbm", "kernel": "decode_ws_kernel<3,false> (q8_0, T=4)", "achieved": ach, "peak": pk["hbm_gbs"],
+            "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "peak_kind": pk_kind + " copy bandwidth (burst)",
+            "frac_of_8TBs_nominal": ach / 8000.0, "kernel_us": kus, "launches_timed": calls * replays,
+            "event_nodes_us": ev_us, "traffic": env_float("Q27B_NCU_TRAFFIC_BYTES")}
+
+
 def env_float(name):
     v = os.environ.get(name)
     return float(v) if v else NCU_TRAFFIC_BYTES
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel at the bench
-# workload, from the ncu capture summarised under profiles/ (captured at 60,000 positions and scaled:
-# the reads grow in proportion to the positions, the writes are the partials and do not).
-NCU_TRAFFIC_BYTES = 333.5e6  # 130.82 MB read at 60,000 positions scaled by 2.5, plus 6.46 MB written (profiles/decode_q8_60k.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel at the bench workload,
+# from an ncu capture at 60,000 positions scaled to 150,000: the reads (130.82 MB) grow in proportion to
+# the positions, the writes (3.62 MB: the partials) do not.
+NCU_TRAFFIC_BYTES = 330.7e6
 
 
 def e2e(q, caches, n, n_ctx, steps, warmup, dist, world):
@@ -423,7 +508,7 @@ def strong_scaling(q, dist, rank, world, n, steps, warmup):
     lo, hi = shard.kv_slice(n, sh.z, sh.nz)
     nk, nq = sh.n_kv_heads, sh.n_kv_heads * GQA
     n_ctx = hi - lo + 64
-    caches = [fill_caches(q, nk, hi - lo, n_ctx, 5000 + 10 * rank + i) for i in range(NBUF)]
+    caches = [torch_caches(nk, hi - lo, n_ctx, 5000 + 10 * rank + i) for i in range(NBUF)]
     g = torch.Generator(device="cuda")
     g.manual_seed(77 + sh.kv_head0)
     qn = torch.randn((T, nq, AD), generator=g, device="cuda")
@@ -441,10 +526,15 @@ def strong_scaling(q, dist, rank, world, n, steps, warmup):
             allp = shard.gather_partials(part, sh, group)
             q.lse_merge(allp, sh.nz, T * nq * 258, T * nq, qg, o)
 
-    ms = time_steps(step, steps, warmup, dist)
+    # no exchange: graph-timed like the headline; with the NCCL all-gather the steps are issued one by one
+    ms = time_graph_steps(step, steps, warmup, dist) if sh.nz == 1 else time_steps(step, steps, warmup, dist)
     out = {"what": "one 150k sequence sharded over %d GPUs: %d KV head(s) per GPU x %d KV-length slice(s)%s" % (
                world, nk, sh.nz, ", NCCL all-gather of partials + LSE merge" if sh.nz > 1 else ", no exchange"),
-           "us_per_step": ms * 1e3, "value": kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong"}
+           "us_per_step": ms * 1e3, "value": kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong",
+           "timing": "CUDA graphs of 20 steps" if sh.nz == 1 else "steps issued one by one"}
+    if sh.nz == 1:
+        ms_e = time_steps(step, steps, warmup, dist)
+        out["eager_us_per_step"] = ms_e * 1e3
     if sh.nz > 1 and os.environ.get("Q27B_P2P_MERGE", "1") != "0":
         # the same exchange over peer memory: the merge kernel of each slice stores its rows into every
         # rank's exchange buffer and raises a flag; the final merge waits for the flags of its own buffer
@@ -467,9 +557,12 @@ def strong_scaling(q, dist, rank, world, n, steps, warmup):
         step_p2p(0)
         torch.cuda.synchronize()
         same = bool(torch.equal(o, o2))
-        ms2 = time_steps(step_p2p, steps, warmup, dist)
+        ms2_e = time_steps(step_p2p, steps, warmup, dist)
+        ms2 = time_graph_steps(step_p2p, steps, warmup, dist)  # the whole step of every rank replayed from a CUDA graph
         assert q.device_status() == 0, "a kernel reported a device-side problem"
         out["nccl_us_per_step"] = out["us_per_step"]
+        out["eager_us_per_step"] = ms2_e * 1e3
+        out["timing"] = "CUDA graphs of 20 steps per rank (nccl_us_per_step: steps issued one by one)"
         out["us_per_step"] = ms2 * 1e3
         out["value"] = kv_bytes(NKVH, n) / (ms2 * 1e-3) / 1e9
         out["what"] = out["what"].replace("NCCL all-gather of partials + LSE merge",
@@ -521,9 +614,12 @@ def sum_norm_scaling(q, dist, rank, world, steps, warmup):
     if bad.item() != 0:  # e.g. a wait that ran out: do not time hundreds of bounded waits
         return {"error": "device status %d after the first peer-memory step" % int(bad.item()), "nccl_us_per_step": ms_nccl * 1e3}
     diff = float((x - x_ref).abs().max().item())
-    ms = time_steps(step_p2p, steps, warmup, dist)
+    ms_e = time_steps(step_p2p, steps, warmup, dist)
+    ms = time_graph_steps(step_p2p, steps, warmup, dist)
     assert q.device_status() == 0, "a kernel reported a device-side problem"
-    return {"what": "x[4][5120] += sum over %d GPUs of their partial rows, RMSNorm, q8_1: rows stored into every rank's exchange "
+    return {"timing": "CUDA graphs of 20 steps per rank (eager_us_per_step, nccl_us_per_step: issued one by one)",
+            "eager_us_per_step": ms_e * 1e3,
+            "what": "x[4][5120] += sum over %d GPUs of their partial rows, RMSNorm, q8_1: rows stored into every rank's exchange "
                     "buffer over NVLink + waiting norm kernel (nccl_us_per_step: NCCL all-reduce + the single-GPU kernel)" % world,
             "us_per_step": ms * 1e3, "nccl_us_per_step": ms_nccl * 1e3, "max_abs_diff_vs_nccl_sum": diff,
             "bytes_pushed_per_rank": rows * n * 4 * world}
@@ -570,12 +666,14 @@ def batched_paged(q, rank, world, dist=None):
 
     def step(i):
         q.attn_decode_paged(qn, qg, kpool, vpool, d_table, d_len, o, B, T, SCALE, NQH, NKVH, n_pages, max_pages, max(lens))
-    ms = time_steps(step, 10, 3, dist)
+    ms_e = time_steps(step, 10, 3, dist)
+    ms = time_graph_steps(step, 10, 3, dist, calls=10)
     assert q.device_status() == 0, "a kernel reported a device-side problem"
     total = float(sum(2.0 * NKVH * int(n) * 272 for n in lengths))
     return {"what": "64 sequences x 4 query tokens, lengths U{1024..131072} (seed 1005), 256-token pages, random page "
                     "table; %d sequence(s) on rank 0 of %d" % (B, world),
-            "positions_total": int(lengths.sum()), "kv_bytes_total": total, "ms_per_step": ms,
+            "positions_total": int(lengths.sum()), "kv_bytes_total": total, "ms_per_step": ms, "eager_ms_per_step": ms_e,
+            "timing": "one CUDA graph of 10 steps",
             "value": total / (ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong (sequences sharded by KV length)"}
 
 
@@ -618,7 +716,7 @@ def extras(q, caches, qn, qg, o, n_ctx):
     # spec-verify decode at 32,768 positions with the q8_0 and with the f16 KV cache
     n2 = 32768
     pos.fill_(n2 - T)
-    f16c = [fill_caches(q, NKVH, n2, n2 + 64, 2002 + i, q8=False) for i in range(NBUF)]
+    f16c = [torch_caches(NKVH, n2, n2 + 64, 2002 + i, q8=False) for i in range(NBUF)]
     us_q8 = graph_us(lambda i: q.attn_decode(qn, qg, caches[i % NBUF][0], caches[i % NBUF][1], o, None, None, pos, T,
                                              SCALE, NQH, NKVH, n_ctx))
     us_f16 = graph_us(lambda i: q.attn_decode(qn, qg, f16c[i % NBUF][0], f16c[i % NBUF][1], o, None, None, pos, T,
@@ -659,7 +757,7 @@ def extras(q, caches, qn, qg, o, n_ctx):
     out["prefill_f16_cache"] = {}
     try:
         Pmax = 148000
-        f16c = fill_caches(q, NKVH, Pmax + M, Pmax + M + 64, 3002, q8=False)
+        f16c = torch_caches(NKVH, Pmax + M, Pmax + M + 64, 3002, q8=False)
         for P in (0, 32768, Pmax):
             pos.fill_(P)
             ops = NQH * 1024.0 * (M * P + M * (M + 1) / 2)
@@ -708,10 +806,14 @@ def prefill_mode(q, args, steps, warmup, dist=None, rank=0, world=1):
     ref = RefLib() if use_ref else None
     # N > 1: the one chunk is shared out (strong scaling): KV-head groups, then query-token ranges within a
     # group (shard.plan_prefill); every rank holds the K and V rows of its heads, nothing is exchanged
-    from qwen27_engine_b200 import shard
-    plan = shard.plan_prefill(rank, world, M, P, NKVH)
+    if use_ref:  # one GPU, the whole chunk in one call
+        import collections
+        plan = collections.namedtuple("Plan", "kv_head0 n_kv_heads ranges")(0, NKVH, [(0, M)])
+    else:
+        from qwen27_engine_b200 import shard
+        plan = shard.plan_prefill(rank, world, M, P, NKVH)
     nkvh, nqh = plan.n_kv_heads, plan.n_kv_heads * GQA
-    kc, vc = fill_caches(q, nkvh, P + M, n_ctx, 1002 + plan.kv_head0, q8=q8)
+    kc, vc = torch_caches(nkvh, P + M, n_ctx, 1002 + plan.kv_head0, q8=q8)
     g = torch.Generator(device="cuda")
     g.manual_seed(3 + plan.kv_head0)
     qn = torch.randn((M, nqh, AD), generator=g, device="cuda")
@@ -772,7 +874,7 @@ def prefill_mode(q, args, steps, warmup, dist=None, rank=0, world=1):
     print(json.dumps(line))
 
 
-def run_reference(args, line, q, caches, qn, qg, o, pos, n, n_ctx, steps, warmup):
+def run_reference(args, line, caches, qn, qg, o, pos, n, n_ctx, steps, warmup):
     line["impl"] = "reference"
     use_cpu = args.ref_cpu
     ref = None
@@ -795,13 +897,16 @@ def run_reference(args, line, q, caches, qn, qg, o, pos, n, n_ctx, steps, warmup
 
     sampler = ClockSampler(env_int("LOCAL_RANK", 0))
     sampler.start()
-    ms = time_steps(step, steps, warmup)
+    ms = time_graph_steps(step, steps, warmup)
     line["clocks"] = sampler.stop()
+    ms_eager = time_steps(step, steps, warmup)
     v = kv_bytes(NKVH, n) / (ms * 1e-3) / 1e9
     line.update({"value": v, "ms_per_step": ms, "us_per_step": ms * 1e3, "gpu_launches": 2 * steps,
+                 "eager_ms_per_step": ms_eager, "eager_value": kv_bytes(NKVH, n) / (ms_eager * 1e-3) / 1e9,
                  "reference_arm": "the reference's own CUDA kernels (src/attn.cu, mma.sync + cp.async) compiled for "
-                                  "sm_100a and called through q27::attn_decode on the same GPU; the reference has no "
-                                  "CPU implementation of this path",
+                                  "sm_100a and called through q27::attn_decode on the same GPU, timed the same way "
+                                  "(CUDA graphs of 20 calls); the reference has no CPU implementation of this path; "
+                                  "this process loads oracle/_ref/libq27ref.so only",
                  "cpu_baseline": {"value": v, "unit": "GB/s", "cores": 0, "kind": "reference",
                                   "sample": "%d full steps on the GPU (not host cores)" % steps},
                  "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})

@@ -12,11 +12,17 @@
  * Fixed model constants (reference src/attn.cu:22-28): head dim 256, 6 query heads per KV
  * head, at most 4 query tokens per decode call.
  *
- * Memory: the caller owns every buffer that it passes. The library keeps one lazily allocated
- * workspace per device (split partials, a status word), grown only when a call needs more than
- * any earlier call on that device did; run every shape class once before capturing a CUDA
- * graph (the reference's Decoder::warmup does the same, src/model.cu:910-931).
- * Threading: one caller thread per device at a time (as the reference, src/attn.cu:869-879).
+ * Memory: the caller owns every buffer that it passes. The library keeps a workspace per device
+ * (see q27b_attn_workspace_*): a status word, the decode partials (fixed size, allocated by the
+ * first decode call), the prefill partials (allocated once, by the first prefill call that splits,
+ * at a fixed cap - a later, deeper call splits less instead of reallocating, as the reference's
+ * fixed buffer, src/attn.cu:954-959) and the partials of the batched paged decode (grow with the
+ * batch). Run every shape class once before capturing a CUDA graph (the reference's
+ * Decoder::warmup does the same, src/model.cu:910-931), or fix everything up front with
+ * q27b_attn_workspace_init.
+ * Threading: one caller thread per device at a time (as the reference, src/attn.cu:869-879);
+ * different devices may be driven from different threads (the process-wide state - tensor-map
+ * cache, kernel choices, one-time set-up - is synchronised).
  */
 #ifndef Q27B_ATTN_H_
 #define Q27B_ATTN_H_
@@ -46,6 +52,21 @@ const char* q27b_last_error(void);
 /* Reads (and clears) the device status word of the current device. Synchronises the device:
  * call it after your own synchronisation point. 0 = no kernel reported a problem. */
 int q27b_device_status(int* status_out);
+
+/* The per-device workspace (the counterpart of the reference's static AttnWs ws[16] and pbuf[16],
+ * src/attn.cu:869-879,954-959), for callers that want control. All three act on the current device.
+ *  - query: bytes currently held for the decode partials, the prefill partials and the paged-decode
+ *    partials (0 = not allocated yet), and whether the workspace has been fixed.
+ *  - init: allocates everything now - the decode partials, the prefill partials at prefill_bytes
+ *    (0: the default cap of 128 MiB) and paged_bytes for the batched paged decode (0: none) - and
+ *    fixes it: afterwards no entry point allocates or frees device memory (q27b_attn_decode_ref
+ *    and the exchange-buffer helpers excepted); a call that would need more splits less (prefill) or
+ *    fails with Q27B_UNSUPPORTED and says how much it needs (paged decode).
+ *  - destroy: synchronises the device, frees the workspace and lifts the fix. Graphs captured
+ *    before must not be replayed afterwards. */
+int q27b_attn_workspace_query(uint64_t* decode_bytes, uint64_t* prefill_bytes, uint64_t* paged_bytes, int* fixed);
+int q27b_attn_workspace_init(uint64_t prefill_bytes, uint64_t paged_bytes);
+int q27b_attn_workspace_destroy(void);
 
 /* Bytes of the K (or V) cache of one layer. q8_0 (q8 != 0): int8 values [nkvh][n_ctx][256]
  * followed by f16 scales [nkvh][n_ctx][8]; else f16 [nkvh][n_ctx][256].
@@ -80,6 +101,13 @@ int q27b_attn_decode(const float* qn, const float* qg, const void* kcache, const
                      float* xd, const int* pos0, int T, float kq_scale, int nqh, int nkvh, int n_ctx, int q8,
                      void* stream);
 
+/* The same result with a simple slow kernel, for checks (plain f32 softmax over all visible
+ * positions, roundings of the definition); T may be any size up to 65535. Its score scratch
+ * (T * nqh * n_ctx floats) is allocated on demand. Replaces q27::attn_decode_ref (src/ops.h:73-75;
+ * src/attn.cu:824-867,976-987), which tools/bench_attn.cu compares the fast kernels with. */
+int q27b_attn_decode_ref(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
+                         const int* pos0, int T, float kq_scale, int nqh, int nkvh, int n_ctx, int q8, void* stream);
+
 /* q27b_attn_decode for callers that must not allocate device memory. It has no counterpart in
  * the reference, whose attn_decode allocates its partial buffer on first use
  * (src/attn.cu:898-900). Same arguments, same result as q27b_attn_decode (q8_0 cache only).
@@ -93,8 +121,9 @@ int q27b_attn_decode(const float* qn, const float* qg, const void* kcache, const
  * that loads the library, held until the process exits), and the result goes to the caller's
  * own buffers.
  *
- * Limit: nkvh * q27b_attn_chunks(nkvh) <= 160 chunk partials, i.e. any KV-head count on GPUs of up
- * to 160 SMs; beyond that the call returns Q27B_BAD_SHAPE and says so.
+ * Limit: nkvh * floor(SMs / nkvh) <= 160 chunk partials, i.e. any KV-head count on GPUs of up to
+ * 160 SMs; beyond that the call returns Q27B_BAD_SHAPE and says so. A bounded wait that ran out in
+ * these kernels shows in q27b_device_status like any other.
  * The first call on a device looks up the array's device address and opts the kernels into their
  * shared-memory size; make that first call before any stream capture starts.
  * Every call on a device uses the same array and leaves its partials there; nothing in it has to
@@ -228,6 +257,16 @@ int q27b_debug_expire_wait(void* stream);
  * caller's stream between its split-K kernel and its merge kernel, so that a benchmark can time
  * the dominant kernel alone with CUDA events. NULL switches it off. */
 int q27b_debug_split_event(void* event);
+/* The same with an event before the split-K kernel as well. Inside a stream capture both records
+ * become event nodes of the graph (cudaEventRecordExternal) and are taken at every replay, so the
+ * kernel can be timed alone, on the launching stream, inside the replayed graph: set a pair of events
+ * before each captured call. NULL, NULL switches it off. */
+int q27b_debug_split_events(void* begin, void* end);
+/* While on, q27b_attn_decode on the current device launches its split-K kernel only (the partials stay
+ * in the workspace, the output is not written): a benchmark captures a graph of such calls and times
+ * the dominant kernel alone, back to back, with events around the replay (event nodes between the
+ * kernels of a graph cost a few microseconds each and distort a 65 us kernel). */
+int q27b_debug_split_only(int on);
 
 /* Measurement hook, no counterpart in the reference: while `stamps` (device memory, 8 x uint64 per
  * CTA of the split-K grid, i.e. 8 * q27b_attn_chunks(nkvh) * nkvh values) is set, every CTA of the

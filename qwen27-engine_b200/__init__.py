@@ -28,12 +28,13 @@ OK, BAD_SHAPE, CUDA_ERROR, UNSUPPORTED, DEVICE_STATUS = 0, 1, 2, 3, 4
 SYMBOLS = [
     "q27b_last_error", "q27b_device_status", "q27b_kv_cache_bytes", "q27b_attn_chunks", "q27b_kv_append",
     "q27b_attn_prep", "q27b_attn_decode", "q27b_attn_decode_partial", "q27b_lse_merge", "q27b_attn_decode_paged",
-    "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_debug_decode_trace", "q27b_set_decode_kernel", "q27b_set_decode_schedule", "q27b_set_prefill_kernel", "q27b_prefill_split_plan", "q27b_sum_xbuf_bytes", "q27b_xbuf_alloc_bytes",
+    "q27b_kv_pool_bytes", "q27b_attn_prefill", "q27b_prefill_qk_debug", "q27b_debug_split_event", "q27b_debug_split_events", "q27b_debug_split_only", "q27b_debug_decode_trace", "q27b_set_decode_kernel", "q27b_set_decode_schedule", "q27b_set_prefill_kernel", "q27b_prefill_split_plan", "q27b_sum_xbuf_bytes", "q27b_xbuf_alloc_bytes",
     "q27b_sum_norm_q8", "q27b_sum_push", "q27b_sum_norm_q8_wait", "q27b_debug_expire_wait",
     "q27b_attn_prefill_q8_1", "q27b_xbuf_bytes", "q27b_attn_decode_partial_push", "q27b_lse_merge_wait",
     "q27b_xbuf_alloc", "q27b_xbuf_free", "q27b_ipc_export", "q27b_ipc_open", "q27b_ipc_close",
     "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
-    "q27b_attn_decode_noalloc",
+    "q27b_attn_decode_noalloc", "q27b_attn_decode_ref", "q27b_attn_workspace_query", "q27b_attn_workspace_init",
+    "q27b_attn_workspace_destroy",
 ]
 
 
@@ -249,6 +250,29 @@ def debug_split_event(event):
     _check(_lib.q27b_debug_split_event(ctypes.c_void_p(event.cuda_event if event is not None else 0)))
 
 
+def attn_decode_ref(qn, qg, kcache, vcache, o, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8=True):
+    """q27::attn_decode_ref (src/ops.h:73-75): the simple slow kernel, for checks."""
+    _check(_lib.q27b_attn_decode_ref(_ptr(qn, torch.float32), _ptr(qg, torch.float32), _ptr(kcache), _ptr(vcache),
+                                     _ptr(o, torch.float32), _ptr(pos0, torch.int32), int(T), _f(kq_scale), int(nqh),
+                                     int(nkvh), int(n_ctx), int(bool(q8)), _stream()))
+
+
+def workspace_query():
+    """(decode_bytes, prefill_bytes, paged_bytes, fixed) of the current device's workspace."""
+    a, b, c, f = ctypes.c_uint64(0), ctypes.c_uint64(0), ctypes.c_uint64(0), ctypes.c_int(0)
+    _check(_lib.q27b_attn_workspace_query(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), ctypes.byref(f)))
+    return a.value, b.value, c.value, bool(f.value)
+
+
+def workspace_init(prefill_bytes=0, paged_bytes=0):
+    """Allocates the whole workspace now and fixes it: no later call allocates or frees."""
+    _check(_lib.q27b_attn_workspace_init(ctypes.c_uint64(int(prefill_bytes)), ctypes.c_uint64(int(paged_bytes))))
+
+
+def workspace_destroy():
+    _check(_lib.q27b_attn_workspace_destroy())
+
+
 def set_decode_schedule(pool):
     """True: CTAs share a pool of tiles (default, faster); False: equal static shares (same bits every run)."""
     _check(_lib.q27b_set_decode_schedule(int(bool(pool))))
@@ -257,6 +281,17 @@ def set_decode_schedule(pool):
 def debug_decode_trace(stamps):
     """stamps: int64 CUDA tensor of 8 values per CTA of the split-K grid, or None (see the header)."""
     _check(_lib.q27b_debug_decode_trace(_ptr(stamps, torch.int64, optional=True)))
+
+
+def debug_split_only(on):
+    """True: attn_decode launches its split-K kernel only (benchmarks time that kernel alone)."""
+    _check(_lib.q27b_debug_split_only(int(bool(on))))
+
+
+def debug_split_events(begin, end):
+    """begin, end: torch.cuda.Event objects (timing enabled, each recorded at least once) or None, None."""
+    h = lambda e: ctypes.c_void_p(e.cuda_event if e is not None else 0)
+    _check(_lib.q27b_debug_split_events(h(begin), h(end)))
 
 
 def new_cache(nkvh, n_ctx, q8=True, device="cuda", fill=0):

@@ -32,7 +32,9 @@
 #include "decode_params.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
+#include <mutex>
 
 namespace q27b {
 namespace {
@@ -569,43 +571,17 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__
   }
 }
 
-struct TmapKey {
-  const void* base;
-  int nkvh, n_ctx, q8;
-  CUtensorMap vals, scales;
-};
-// Small cache of tensor maps per (cache pointer, shape): the reference's caches never move
-// (src/model.cu:464-472), so a decode step re-encodes nothing.
-constexpr int TMAP_CACHE = 64;
-TmapKey g_tmaps[TMAP_CACHE];
-int g_tmap_next = 0;
-
-int get_tmaps(const void* cache, int nkvh, int n_ctx, bool q8, const CUtensorMap** vals, const CUtensorMap** scales) {
-  for (int i = 0; i < TMAP_CACHE; i++)
-    if (g_tmaps[i].base == cache && g_tmaps[i].nkvh == nkvh && g_tmaps[i].n_ctx == n_ctx && g_tmaps[i].q8 == (int)q8) {
-      *vals = &g_tmaps[i].vals;
-      *scales = &g_tmaps[i].scales;
-      return Q27B_OK;
-    }
-  TmapKey& k = g_tmaps[g_tmap_next];
-  g_tmap_next = (g_tmap_next + 1) % TMAP_CACHE;
-  k.base = nullptr;
+// Tensor maps of one cache (values and, for q8_0, scales), by value, from the process-wide cache.
+int get_tmaps(const void* cache, int nkvh, int n_ctx, bool q8, CUtensorMap* vals, CUtensorMap* scales) {
   const uint64_t rows = (uint64_t)nkvh * n_ctx;
-  const uint32_t rowb = q8 ? AD : 2 * AD;
-  if (int rc = make_tmap_2d(&k.vals, cache, rows, rowb, rowb, 128, TILE, true)) return rc;
-  if (q8) {
-    if (int rc = make_tmap_2d(&k.scales, (const uint8_t*)cache + rows * AD, rows, 16, 16, 16, TILE, false)) return rc;
-  } else {
-    k.scales = k.vals;  // unused by the f16 kernel
-  }
-  k.base = cache;
-  k.nkvh = nkvh;
-  k.n_ctx = n_ctx;
-  k.q8 = q8;
-  *vals = &k.vals;
-  *scales = &k.scales;
+  if (q8) return q8_tmaps(cache, rows, vals, scales);
+  if (int rc = cached_tmap_2d(vals, cache, rows, 2 * AD, 2 * AD, 128, TILE, true)) return rc;
+  *scales = *vals;  // unused by the f16 kernel
   return Q27B_OK;
 }
+
+// Per-device one-time set-up flags of this file's kernels (attribute opt-ins), safe from several threads.
+std::mutex g_setup_mu;
 
 template <int NT, bool PAGED, bool Q8>
 int launch_decode(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
@@ -613,9 +589,12 @@ int launch_decode(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMa
   static bool attr[64] = {};
   int dev;
   Q27B_CK(cudaGetDevice(&dev));
-  if (!attr[dev]) {
-    Q27B_CK(cudaFuncSetAttribute(decode_kernel<NT, PAGED, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    attr[dev] = true;
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mu);
+    if (!attr[dev]) {
+      Q27B_CK(cudaFuncSetAttribute(decode_kernel<NT, PAGED, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      attr[dev] = true;
+    }
   }
   Q27B_CK(launch_pdl(decode_kernel<NT, PAGED, Q8>, dim3(p.nch, p.nkvh, nseq), dim3(N_THREADS), SMEM_BYTES, s, *kv, *ks, *vv,
                      *vs, p));
@@ -639,17 +618,20 @@ int launch_decode_t(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensor
 // Whether the CTAs of the warp-specialised kernel share a pool of tiles (see decode_ws.cu) or keep to
 // equal static shares (Q27B_DECODE_POOL=0, q27b_set_decode_schedule(0)): the static form gives the
 // same bits on every run, the pool form ends earlier.
-bool g_pool_schedule = [] {
+std::atomic<bool> g_pool_schedule{[] {
   const char* e = getenv("Q27B_DECODE_POOL");
   return !(e && e[0] == '0');
-}();
-int g_kernel_choice = -1;  // -1: not read yet; 0 default (= 3), 1 single-role warp-MMA, 2 tcgen05, 3 warp-specialised
+}()};
+std::atomic<int> g_kernel_choice{-1};  // -1: not read yet; 0 default (= 3), 1 single-role warp-MMA, 2 tcgen05, 3 warp-specialised
 int kernel_choice() {
-  if (g_kernel_choice < 0) {
+  int k = g_kernel_choice.load(std::memory_order_relaxed);
+  if (k < 0) {
     const char* e = getenv("Q27B_DECODE_KERNEL");
-    g_kernel_choice = !e ? 0 : e[0] == 'm' ? 1 : e[0] == 't' ? 2 : e[0] == 'w' ? 3 : 0;
+    k = !e ? 0 : e[0] == 'm' ? 1 : e[0] == 't' ? 2 : e[0] == 'w' ? 3 : 0;
+    int expected = -1;
+    if (!g_kernel_choice.compare_exchange_strong(expected, k)) k = expected;
   }
-  return g_kernel_choice;
+  return k;
 }
 // Launches the split-K kernel chosen for a q8_0 cache.
 int launch_q8(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
@@ -660,30 +642,46 @@ int launch_q8(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* v
   return paged ? launch_decode_t<true, true>(kv, ks, vv, vs, p, nseq, s) : launch_decode_t<false, true>(kv, ks, vv, vs, p, nseq, s);
 }
 
-// Split-K pass of one sequence into ctx->part [nkvh][nch][24][258].
+// Records a measurement event on s; in a stream that is being captured the record becomes an event
+// node of the graph (cudaEventRecordExternal), so that it is taken again at every replay.
+int record_hook(cudaEvent_t ev, cudaStream_t s) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  Q27B_CK(cudaStreamIsCapturing(s, &st));
+  Q27B_CK(cudaEventRecordWithFlags(ev, s, st == cudaStreamCaptureStatusActive ? cudaEventRecordExternal : cudaEventRecordDefault));
+  return Q27B_OK;
+}
+
+// Split-K pass of one sequence into the decode workspace [nkvh][nch][24][258].
 int decode_split(DeviceCtx* ctx, const float* qn, const void* kcache, const void* vcache, const int* pos0, int T,
                  float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos, int n_local, int* nch_out,
                  cudaStream_t s) {
+  if (nkvh > ctx->n_sm) return fail(Q27B_BAD_SHAPE, "attn_decode: more KV heads than SMs");
   const int nch = std::max(1, ctx->n_sm / nkvh);
-  if (int rc = ensure_part(ctx, (size_t)nkvh * nch * MAXR * PROW)) return rc;
-  const CUtensorMap *kv, *ks, *vv, *vs;
-  if (int rc = get_tmaps(kcache, nkvh, n_ctx, q8 != 0, &kv, &ks)) return rc;
-  if (int rc = get_tmaps(vcache, nkvh, n_ctx, q8 != 0, &vv, &vs)) return rc;
+  float* part;
+  if (int rc = decode_ws(ctx, &part)) return rc;
+  CUtensorMap kvm, ksm, vvm, vsm;
+  if (int rc = get_tmaps(kcache, nkvh, n_ctx, q8 != 0, &kvm, &ksm)) return rc;
+  if (int rc = get_tmaps(vcache, nkvh, n_ctx, q8 != 0, &vvm, &vsm)) return rc;
+  const CUtensorMap *kv = &kvm, *ks = &ksm, *vv = &vvm, *vs = &vsm;
   DecodeParams p = {};
-  p.qn = qn; p.part = ctx->part; p.pos0 = pos0; p.status = ctx->status;
+  p.qn = qn; p.part = part; p.pos0 = pos0; p.status = ctx->status;
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nch = nch; p.kq_scale = kq_scale;
   p.base_pos = base_pos; p.n_local = n_local; p.trace = ctx->trace;
-  p.sched = (g_pool_schedule && nkvh <= 32) ? ctx->status + 16 : nullptr;
+  p.sched = (g_pool_schedule.load(std::memory_order_relaxed) && nkvh <= 32) ? ctx->status + 16 : nullptr;
   *nch_out = nch;
+  if (ctx->split_begin)
+    if (int rc = record_hook(ctx->split_begin, s)) return rc;
   if (int rc = !q8 ? launch_decode_t<false, false>(kv, ks, vv, vs, p, 1, s) : launch_q8(kv, ks, vv, vs, p, false, 1, s))
     return rc;
-  if (ctx->split_event) Q27B_CK(cudaEventRecord(ctx->split_event, s));
+  if (ctx->split_event)
+    if (int rc = record_hook(ctx->split_event, s)) return rc;
   return Q27B_OK;
 }
 
 // ---------------------------------------------------------------- decode without any allocation
 // Scratch of q27b_attn_decode_noalloc: the split partials [chunk slots][24 rows][258 floats] and a
-// status word, reserved in the library image itself. NOALLOC_SLOTS chunk slots = nkvh * chunks per
+// status word (followed, from int 16 on, by the tile counters of the pool schedule, which every launch
+// leaves at zero), reserved in the library image itself. NOALLOC_SLOTS chunk slots = nkvh * chunks per
 // KV head, which on a GPU with up to 160 SMs is at most 160 (3.96 MB). Every GPU that loads the
 // library carries this array until the process exits.
 constexpr int NOALLOC_SLOTS = 160;
@@ -697,21 +695,35 @@ float* g_noalloc_part_ptr[64] = {};
 int* g_noalloc_status_ptr[64] = {};
 
 int noalloc_setup(int dev) {
+  std::lock_guard<std::mutex> lock(g_setup_mu);
   if (g_noalloc_part_ptr[dev]) return Q27B_OK;
   float* part = nullptr;
   int* status = nullptr;
   Q27B_CK(cudaGetSymbolAddress((void**)&part, g_noalloc_part));
   Q27B_CK(cudaGetSymbolAddress((void**)&status, g_noalloc_status));
   // the kernels' shared-memory opt-in, done here so that later calls only launch
-  Q27B_CK(cudaFuncSetAttribute(decode_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-  Q27B_CK(cudaFuncSetAttribute(decode_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-  Q27B_CK(cudaFuncSetAttribute(decode_kernel<3, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  if (int rc = decode_ws_setup()) return rc;
   g_noalloc_status_ptr[dev] = status;
   g_noalloc_part_ptr[dev] = part;
   return Q27B_OK;
 }
 
 }  // namespace
+
+// Reads (and clears) the status word that the no-allocation entry point's kernels report into; 0 when
+// that entry point has not run on this device. Copies from the library's own device array: allocates nothing.
+int noalloc_status(int dev, int* out) {
+  *out = 0;
+  int* ptr;
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mu);
+    ptr = (dev >= 0 && dev < 64) ? g_noalloc_status_ptr[dev] : nullptr;
+  }
+  if (!ptr) return Q27B_OK;
+  Q27B_CK(cudaMemcpy(out, ptr, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*out) Q27B_CK(cudaMemset(ptr, 0, sizeof(int)));
+  return Q27B_OK;
+}
 }  // namespace q27b
 
 using namespace q27b;
@@ -731,8 +743,9 @@ int q27b_attn_decode(const float* qn, const float* qg, const void* kcache, const
   if (int rc = decode_split(ctx, qn, kcache, vcache, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8, 0, -1, &nch,
                             (cudaStream_t)stream))
     return rc;
+  if (ctx->split_only) return Q27B_OK;
   MergeParams mp = {};
-  mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.qg = qg; mp.o = o; mp.xq = xq; mp.xd = xd;
+  mp.part = ctx->dec.p; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.qg = qg; mp.o = o; mp.xq = xq; mp.xd = xd;
   mp.T = T; mp.nqh = nqh;
   return launch_merge(mp, true, (cudaStream_t)stream);
 }
@@ -751,7 +764,7 @@ int q27b_attn_decode_partial(const float* qn, const void* kcache, const void* vc
                             (cudaStream_t)stream))
     return rc;
   MergeParams mp = {};
-  mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.part_out = part; mp.T = T; mp.nqh = nqh;
+  mp.part = ctx->dec.p; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.part_out = part; mp.T = T; mp.nqh = nqh;
   return launch_merge(mp, true, (cudaStream_t)stream);
 }
 
@@ -769,31 +782,14 @@ int q27b_attn_decode_partial_push(const float* qn, const void* kcache, const voi
   // Every buffer must be device memory that kernels of this GPU may store into: a peer's buffer needs
   // peer access from this device to the peer's, which is enabled here (once per pointer) rather than
   // left to whoever mapped the memory. Anything else is refused before a kernel can touch it.
-  static const void* checked[64] = {};
-  static int n_checked = 0;
-  for (int k = 0; k < nz; k++) {
-    bool seen = false;
-    for (int i = 0; i < n_checked; i++) seen |= checked[i] == peer_xbuf[k];
-    if (seen) continue;
-    cudaPointerAttributes a;
-    Q27B_CK(cudaPointerGetAttributes(&a, peer_xbuf[k]));
-    if (a.type != cudaMemoryTypeDevice) return fail(Q27B_BAD_SHAPE, "attn_decode_partial_push: exchange buffer is not device memory");
-    if (a.device != ctx->dev) {
-      int can = 0;
-      Q27B_CK(cudaDeviceCanAccessPeer(&can, ctx->dev, a.device));
-      if (!can) return fail(Q27B_UNSUPPORTED, "attn_decode_partial_push: no peer access to the device of an exchange buffer");
-      const cudaError_t e = cudaDeviceEnablePeerAccess(a.device, 0);
-      if (e == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError();
-      else Q27B_CK(e);
-    }
-    if (n_checked < 64) checked[n_checked++] = peer_xbuf[k];
-  }
+  for (int k = 0; k < nz; k++)
+    if (int rc = check_peer_buffer(peer_xbuf[k], "attn_decode_partial_push")) return rc;
   int nch;
   if (int rc = decode_split(ctx, qn, kcache, vcache, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8, base_pos, n_local, &nch,
                             (cudaStream_t)stream))
     return rc;
   MergeParams mp = {};
-  mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.T = T; mp.nqh = nqh;
+  mp.part = ctx->dec.p; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.T = T; mp.nqh = nqh;
   for (int k = 0; k < nz; k++) mp.push_buf[k] = peer_xbuf[k];
   mp.push_n = nz; mp.push_z = my_z; mp.xbuf = (int*)peer_xbuf[my_z]; mp.status = ctx->status;
   return launch_merge(mp, true, (cudaStream_t)stream);
@@ -817,14 +813,17 @@ int q27b_attn_decode_noalloc(const float* qn, const float* qg, const void* kcach
                                     " chunk partials, the built-in scratch holds " + std::to_string(NOALLOC_SLOTS) +
                                     " (use q27b_attn_decode, which allocates)");
   if (int rc = noalloc_setup(dev)) return rc;
-  const CUtensorMap *kv, *ks, *vv, *vs;
-  if (int rc = get_tmaps(kcache, nkvh, n_ctx, true, &kv, &ks)) return rc;
-  if (int rc = get_tmaps(vcache, nkvh, n_ctx, true, &vv, &vs)) return rc;
+  CUtensorMap kvm, ksm, vvm, vsm;  // (the tensor-map cache lives in host memory)
+  if (int rc = get_tmaps(kcache, nkvh, n_ctx, true, &kvm, &ksm)) return rc;
+  if (int rc = get_tmaps(vcache, nkvh, n_ctx, true, &vvm, &vsm)) return rc;
+  const CUtensorMap *kv = &kvm, *ks = &ksm, *vv = &vvm, *vs = &vsm;
   DecodeParams p = {};
   p.qn = qn; p.part = g_noalloc_part_ptr[dev]; p.pos0 = pos0; p.status = g_noalloc_status_ptr[dev];
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.nch = nch; p.kq_scale = kq_scale;
   p.base_pos = 0; p.n_local = -1;
-  if (int rc = launch_decode_t<false, true>(kv, ks, vv, vs, p, 1, (cudaStream_t)stream)) return rc;
+  // the tile counters of the pool schedule sit behind the status word, as in the allocated workspace
+  p.sched = (g_pool_schedule.load(std::memory_order_relaxed) && nkvh <= 32) ? g_noalloc_status_ptr[dev] + 16 : nullptr;
+  if (int rc = launch_decode_ws(kv, ks, vv, vs, p, false, 1, (cudaStream_t)stream)) return rc;
   MergeParams mp = {};
   mp.part = g_noalloc_part_ptr[dev]; mp.nparts = nch; mp.rows = (int64_t)T * nqh; mp.qg = qg; mp.o = o; mp.xq = xq;
   mp.xd = xd; mp.T = T; mp.nqh = nqh;
@@ -833,12 +832,12 @@ int q27b_attn_decode_noalloc(const float* qn, const float* qg, const void* kcach
 
 int q27b_set_decode_kernel(int which) {
   if (which < 0 || which > 3) return fail(Q27B_BAD_SHAPE, "set_decode_kernel: 0 auto, 1 warp-MMA, 2 tcgen05, 3 warp-specialised");
-  g_kernel_choice = which;
+  g_kernel_choice.store(which);
   return Q27B_OK;
 }
 
 int q27b_set_decode_schedule(int pool) {
-  g_pool_schedule = pool != 0;
+  g_pool_schedule.store(pool != 0);
   return Q27B_OK;
 }
 
@@ -846,6 +845,22 @@ int q27b_debug_split_event(void* event) {
   DeviceCtx* ctx;
   if (int rc = device_ctx(&ctx)) return rc;
   ctx->split_event = (cudaEvent_t)event;
+  ctx->split_begin = nullptr;
+  return Q27B_OK;
+}
+
+int q27b_debug_split_only(int on) {
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  ctx->split_only = on != 0;
+  return Q27B_OK;
+}
+
+int q27b_debug_split_events(void* begin, void* end) {
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  ctx->split_begin = (cudaEvent_t)begin;
+  ctx->split_event = (cudaEvent_t)end;
   return Q27B_OK;
 }
 
@@ -872,20 +887,22 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
   int chunk = (int)std::min<int64_t>(8192, std::max<int64_t>(1024, total / (8 * (int64_t)ctx->n_sm)));
   chunk = (chunk + Q27B_PAGE - 1) / Q27B_PAGE * Q27B_PAGE;
   const int nch = (max_seq_len + chunk - 1) / chunk;
-  if (int rc = ensure_part(ctx, (size_t)B * nkvh * nch * MAXR * PROW)) return rc;
+  float* part;
+  if (int rc = paged_ws(ctx, (size_t)B * nkvh * nch * MAXR * PROW, &part)) return rc;
   // One pool = n_pages * nkvh pages of 256 rows: the same row tensor as a cache of that many rows.
   const int pool_rows_per_head = n_pages * Q27B_PAGE;
-  const CUtensorMap *kv, *ks, *vv, *vs;
-  if (int rc = get_tmaps(kpool, nkvh, pool_rows_per_head, true, &kv, &ks)) return rc;
-  if (int rc = get_tmaps(vpool, nkvh, pool_rows_per_head, true, &vv, &vs)) return rc;
+  CUtensorMap kvm, ksm, vvm, vsm;
+  if (int rc = get_tmaps(kpool, nkvh, pool_rows_per_head, true, &kvm, &ksm)) return rc;
+  if (int rc = get_tmaps(vpool, nkvh, pool_rows_per_head, true, &vvm, &vsm)) return rc;
+  const CUtensorMap *kv = &kvm, *ks = &ksm, *vv = &vvm, *vs = &vsm;
   DecodeParams p = {};
-  p.qn = qn; p.part = ctx->part; p.status = ctx->status;
+  p.qn = qn; p.part = part; p.status = ctx->status;
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = max_pages * Q27B_PAGE; p.nch = nch; p.kq_scale = kq_scale;
   p.base_pos = 0; p.n_local = -1;
   p.page_table = page_table; p.seq_len = seq_len; p.max_pages = max_pages; p.n_pages = n_pages; p.chunk_len = chunk;
   if (int rc = launch_q8(kv, ks, vv, vs, p, true, B, (cudaStream_t)stream)) return rc;
   MergeParams mp = {};
-  mp.part = ctx->part; mp.nparts = nch; mp.rows = (int64_t)B * T * nqh; mp.qg = qg; mp.o = o; mp.T = T; mp.nqh = nqh;
+  mp.part = part; mp.nparts = nch; mp.rows = (int64_t)B * T * nqh; mp.qg = qg; mp.o = o; mp.T = T; mp.nqh = nqh;
   mp.seq_len = seq_len; mp.chunk_len = chunk;
   return launch_merge(mp, true, (cudaStream_t)stream);
 }

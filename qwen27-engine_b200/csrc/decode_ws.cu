@@ -31,6 +31,8 @@
 #include "common.cuh"
 #include "decode_params.h"
 
+#include <mutex>
+
 namespace q27b {
 namespace {
 
@@ -748,11 +750,15 @@ int decode_ws_setup() {
 int launch_decode_ws(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
                      const DecodeParams& p, bool paged, int nseq, cudaStream_t s) {
   static bool attr[64] = {};
+  static std::mutex attr_mu;
   int dev;
   Q27B_CK(cudaGetDevice(&dev));
-  if (!attr[dev]) {
-    if (int rc = decode_ws_setup()) return rc;
-    attr[dev] = true;
+  {
+    std::lock_guard<std::mutex> lock(attr_mu);
+    if (!attr[dev]) {
+      if (int rc = decode_ws_setup()) return rc;
+      attr[dev] = true;
+    }
   }
   const int nt = (GQA * p.T + 7) / 8;
   if (nt == 1) return launch_ws_nt<1>(kv, ks, vv, vs, p, paged, nseq, s);

@@ -6,6 +6,9 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
 
 namespace q27b {
 
@@ -54,23 +57,68 @@ int device_ctx(DeviceCtx** out) {
   return Q27B_OK;
 }
 
-int ensure_part(DeviceCtx* ctx, size_t floats) {
-  if (floats <= ctx->part_floats) return Q27B_OK;
-  if (ctx->part) Q27B_CK(cudaFree(ctx->part));
-  ctx->part = nullptr;
-  ctx->part_floats = 0;
-  Q27B_CK(cudaMalloc(&ctx->part, floats * sizeof(float)));
-  ctx->part_floats = floats;
+namespace {
+// Default cap of the prefill partial buffer: 128 MiB. The metric's chunk (2048 tokens, 24 heads) on a
+// 148,000-token prefix cuts 4 query tiles into 5 pieces = 63 MB; a chunk whose q8_1 output needs every
+// tile on the split path, 2 x 2048 x 24 rows = 101 MB. (The reference fixes 24 MB on a 16 GB card.)
+constexpr size_t PF_CAP_DEFAULT_FLOATS = (128ull << 20) / sizeof(float);
+
+int alloc_ws(DeviceCtx* ctx, WsBuf* b, size_t floats, const char* what) {
+  if (ctx->frozen)
+    return fail(Q27B_UNSUPPORTED, std::string(what) + ": the workspace was fixed by q27b_attn_workspace_init and holds " +
+                                      std::to_string(b->floats * sizeof(float)) + " bytes, this call needs " +
+                                      std::to_string(floats * sizeof(float)));
+  if (b->p) Q27B_CK(cudaFree(b->p));
+  b->p = nullptr;
+  b->floats = 0;
+  Q27B_CK(cudaMalloc(&b->p, floats * sizeof(float)));
+  b->floats = floats;
+  return Q27B_OK;
+}
+}  // namespace
+
+int decode_ws(DeviceCtx* ctx, float** out) {
+  const size_t need = (size_t)ctx->n_sm * MAXR * PROW;
+  if (ctx->dec.floats < need)
+    if (int rc = alloc_ws(ctx, &ctx->dec, need, "attn_decode")) return rc;
+  *out = ctx->dec.p;
   return Q27B_OK;
 }
 
-int ensure_work(DeviceCtx* ctx, size_t ints) {
-  if (ints <= ctx->work_ints) return Q27B_OK;
-  if (ctx->work) Q27B_CK(cudaFree(ctx->work));
-  ctx->work = nullptr;
-  ctx->work_ints = 0;
-  Q27B_CK(cudaMalloc(&ctx->work, ints * sizeof(int)));
-  ctx->work_ints = ints;
+int prefill_ws(DeviceCtx* ctx, float** out, size_t* max_floats) {
+  if (!ctx->pf.p) {
+    const size_t cap = ctx->pf_cap_floats ? ctx->pf_cap_floats : PF_CAP_DEFAULT_FLOATS;
+    if (int rc = alloc_ws(ctx, &ctx->pf, cap, "attn_prefill")) return rc;
+  }
+  *out = ctx->pf.p;
+  *max_floats = ctx->pf.floats;
+  return Q27B_OK;
+}
+
+int paged_ws(DeviceCtx* ctx, size_t floats, float** out) {
+  if (ctx->paged.floats < floats)
+    if (int rc = alloc_ws(ctx, &ctx->paged, floats, "attn_decode_paged")) return rc;
+  *out = ctx->paged.p;
+  return Q27B_OK;
+}
+
+int fit_prefill_split(DeviceCtx* ctx, int* ts, int* ns, int M, int nqh, bool must_merge, float** part) {
+  *part = nullptr;
+  if (*ns <= 1) return Q27B_OK;
+  size_t cap = 0;
+  if (int rc = prefill_ws(ctx, part, &cap)) return rc;
+  const size_t per_piece = (size_t)std::min(M, *ts * 128) * nqh * PROW;
+  const int fit = (int)std::min<size_t>(64, cap / per_piece);
+  if (*ns > fit) *ns = fit;
+  if (*ns < 2) {
+    if (must_merge)
+      return fail(Q27B_UNSUPPORTED, "attn_prefill: the prefill workspace (" + std::to_string(cap * sizeof(float)) +
+                                        " bytes) is too small for two partials of this call (" +
+                                        std::to_string(2 * per_piece * sizeof(float)) + " bytes)");
+    *ns = 1;
+    *ts = 0;
+    *part = nullptr;
+  }
   return Q27B_OK;
 }
 
@@ -96,6 +144,86 @@ int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint32_t row
   return Q27B_OK;
 }
 
+namespace {
+struct TmapKey {
+  const void* base;
+  uint64_t rows, pitch;
+  uint32_t row_bytes, box_bytes, box_rows;
+  int swz, dev;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && pitch == o.pitch && row_bytes == o.row_bytes && box_bytes == o.box_bytes &&
+           box_rows == o.box_rows && swz == o.swz && dev == o.dev;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = (uint64_t)(uintptr_t)k.base * 0x9E3779B97F4A7C15ull;
+    h ^= (k.rows + 0x7F4A7C15ull) * 0xBF58476D1CE4E5B9ull;
+    h ^= ((uint64_t)k.row_bytes << 40) ^ ((uint64_t)k.box_bytes << 24) ^ ((uint64_t)k.box_rows << 8) ^ (uint64_t)(k.swz * 2 + k.dev * 4);
+    return (size_t)(h ^ (h >> 29));
+  }
+};
+std::mutex g_tmap_mu;
+std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
+constexpr size_t TMAP_CACHE_MAX = 4096;  // far above what an engine holds (the reference: 17 layers x K, V x 2 cards)
+
+std::mutex g_peer_mu;
+std::vector<std::pair<int, const void*>> g_peer_ok;  // (storing device, buffer) pairs already checked
+}  // namespace
+
+int cached_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint32_t row_bytes, uint64_t pitch_bytes,
+                   uint32_t box_bytes, uint32_t box_rows, bool swizzle128) {
+  int dev = 0;
+  Q27B_CK(cudaGetDevice(&dev));
+  const TmapKey key = {base, rows, pitch_bytes, row_bytes, box_bytes, box_rows, swizzle128 ? 1 : 0, dev};
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mu);
+    auto it = g_tmap_cache.find(key);
+    if (it != g_tmap_cache.end()) {
+      *out = it->second;
+      return Q27B_OK;
+    }
+  }
+  if (int rc = make_tmap_2d(out, base, rows, row_bytes, pitch_bytes, box_bytes, box_rows, swizzle128)) return rc;
+  std::lock_guard<std::mutex> lock(g_tmap_mu);
+  if (g_tmap_cache.size() >= TMAP_CACHE_MAX) g_tmap_cache.clear();  // nobody holds references into it
+  g_tmap_cache.emplace(key, *out);
+  return Q27B_OK;
+}
+
+int q8_tmaps(const void* cache, uint64_t rows, CUtensorMap* vals, CUtensorMap* scales) {
+  if (int rc = cached_tmap_2d(vals, cache, rows, AD, AD, 128, 64, true)) return rc;
+  return cached_tmap_2d(scales, (const uint8_t*)cache + rows * AD, rows, 16, 16, 16, 64, false);
+}
+
+int check_peer_buffer(const void* p, const char* who) {
+  int dev = 0;
+  Q27B_CK(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(g_peer_mu);
+    for (auto& e : g_peer_ok)
+      if (e.first == dev && e.second == p) return Q27B_OK;
+  }
+  cudaPointerAttributes a;
+  const cudaError_t pe = cudaPointerGetAttributes(&a, p);
+  if (pe != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(Q27B_BAD_SHAPE, std::string(who) + ": exchange buffer is not a CUDA pointer (" + cudaGetErrorString(pe) + ")");
+  }
+  if (a.type != cudaMemoryTypeDevice) return fail(Q27B_BAD_SHAPE, std::string(who) + ": exchange buffer is not device memory");
+  if (a.device != dev) {
+    int can = 0;
+    Q27B_CK(cudaDeviceCanAccessPeer(&can, dev, a.device));
+    if (!can) return fail(Q27B_UNSUPPORTED, std::string(who) + ": no peer access to the device of an exchange buffer");
+    const cudaError_t e = cudaDeviceEnablePeerAccess(a.device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError();
+    else Q27B_CK(e);
+  }
+  std::lock_guard<std::mutex> lock(g_peer_mu);
+  if (g_peer_ok.size() < 4096) g_peer_ok.emplace_back(dev, p);
+  return Q27B_OK;
+}
+
 }  // namespace q27b
 
 using namespace q27b;
@@ -104,6 +232,50 @@ extern "C" {
 
 const char* q27b_last_error(void) { return g_err_text(); }
 
+int q27b_attn_workspace_query(uint64_t* decode_bytes, uint64_t* prefill_bytes, uint64_t* paged_bytes, int* fixed) {
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  if (decode_bytes) *decode_bytes = ctx->dec.floats * sizeof(float);
+  if (prefill_bytes) *prefill_bytes = ctx->pf.floats * sizeof(float);
+  if (paged_bytes) *paged_bytes = ctx->paged.floats * sizeof(float);
+  if (fixed) *fixed = ctx->frozen ? 1 : 0;
+  return Q27B_OK;
+}
+
+int q27b_attn_workspace_init(uint64_t prefill_bytes, uint64_t paged_bytes) {
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  if (ctx->frozen) return fail(Q27B_UNSUPPORTED, "attn_workspace_init: already fixed on this device (destroy it first)");
+  if (ctx->pf.p && prefill_bytes && prefill_bytes / sizeof(float) != ctx->pf.floats)
+    return fail(Q27B_UNSUPPORTED, "attn_workspace_init: the prefill workspace is already allocated at another size");
+  if (prefill_bytes) ctx->pf_cap_floats = (size_t)(prefill_bytes / sizeof(float));
+  float* dummy;
+  size_t cap;
+  if (int rc = decode_ws(ctx, &dummy)) return rc;
+  if (int rc = prefill_ws(ctx, &dummy, &cap)) return rc;
+  if (paged_bytes)
+    if (int rc = paged_ws(ctx, (size_t)((paged_bytes + sizeof(float) - 1) / sizeof(float)), &dummy)) return rc;
+  ctx->frozen = true;
+  return Q27B_OK;
+}
+
+int q27b_attn_workspace_destroy(void) {
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  Q27B_CK(cudaDeviceSynchronize());
+  for (WsBuf* b : {&ctx->dec, &ctx->pf, &ctx->paged}) {
+    if (b->p) Q27B_CK(cudaFree(b->p));
+    b->p = nullptr;
+    b->floats = 0;
+  }
+  if (ctx->ref_scores) Q27B_CK(cudaFree(ctx->ref_scores));
+  ctx->ref_scores = nullptr;
+  ctx->ref_scores_floats = 0;
+  ctx->pf_cap_floats = 0;
+  ctx->frozen = false;
+  return Q27B_OK;
+}
+
 int q27b_device_status(int* status_out) {
   DeviceCtx* ctx;
   if (int rc = device_ctx(&ctx)) return rc;
@@ -111,6 +283,9 @@ int q27b_device_status(int* status_out) {
   Q27B_CK(cudaDeviceSynchronize());
   Q27B_CK(cudaMemcpy(&st, ctx->status, sizeof(int), cudaMemcpyDeviceToHost));
   if (st) Q27B_CK(cudaMemset(ctx->status, 0, 256));  // the word, and the tile counters an aborted kernel may have left behind
+  int st2 = 0;  // kernels of the no-allocation entry point report into a word of their own
+  if (int rc = noalloc_status(ctx->dev, &st2)) return rc;
+  st |= st2;
   if (status_out) *status_out = st;
   return st ? fail(Q27B_DEVICE_STATUS, "device status word = " + std::to_string(st)) : Q27B_OK;
 }

@@ -29,6 +29,7 @@
 #include "prefill_f16.h"
 
 #include <algorithm>
+#include <atomic>
 
 namespace q27b {
 namespace {
@@ -702,36 +703,6 @@ prefill_qk_debug_kernel(const __grid_constant__ CUtensorMap tm_kv, const QkDebug
   }
 }
 
-struct TmapPair {
-  const void* base;
-  int nkvh, n_ctx;
-  CUtensorMap vals, scales;
-};
-constexpr int TMAP_CACHE = 64;
-TmapPair g_tmaps[TMAP_CACHE];
-int g_tmap_next = 0;
-
-int get_tmaps(const void* cache, int nkvh, int n_ctx, const CUtensorMap** vals, const CUtensorMap** scales) {
-  for (int i = 0; i < TMAP_CACHE; i++)
-    if (g_tmaps[i].base == cache && g_tmaps[i].nkvh == nkvh && g_tmaps[i].n_ctx == n_ctx) {
-      *vals = &g_tmaps[i].vals;
-      *scales = &g_tmaps[i].scales;
-      return Q27B_OK;
-    }
-  TmapPair& k = g_tmaps[g_tmap_next];
-  g_tmap_next = (g_tmap_next + 1) % TMAP_CACHE;
-  k.base = nullptr;
-  const uint64_t rows = (uint64_t)nkvh * n_ctx;
-  if (int rc = make_tmap_2d(&k.vals, cache, rows, AD, AD, 128, PT, true)) return rc;
-  if (int rc = make_tmap_2d(&k.scales, (const uint8_t*)cache + rows * AD, rows, 16, 16, 16, PT, false)) return rc;
-  k.base = cache;
-  k.nkvh = nkvh;
-  k.n_ctx = n_ctx;
-  *vals = &k.vals;
-  *scales = &k.scales;
-  return Q27B_OK;
-}
-
 int prefill_setup(DeviceCtx* ctx) {
   if (!ctx->prefill_attr) {
     Q27B_CK(cudaFuncSetAttribute(prefill_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_BYTES));
@@ -743,22 +714,22 @@ int prefill_setup(DeviceCtx* ctx) {
 
 }  // namespace
 
-int get_q8_tmaps(const void* cache, int nkvh, int n_ctx, const CUtensorMap** vals, const CUtensorMap** scales) {
-  return get_tmaps(cache, nkvh, n_ctx, vals, scales);
-}
 }  // namespace q27b
 
 using namespace q27b;
 
 // Which kernel serves a q8_0 cache: int8 Q K^T (default, as the reference since its Q27_ATTN_I8
 // default) or the f16-QK kernel on dequantised K and V (the reference's Q27_ATTN_I8=0).
-static int g_prefill_choice = -1;  // -1: not read yet; 0 default, 1 int8 Q K^T, 2 f16 Q K^T
+static std::atomic<int> g_prefill_choice{-1};  // -1: not read yet; 0 default, 1 int8 Q K^T, 2 f16 Q K^T
 static bool use_f16_qk() {
-  if (g_prefill_choice < 0) {
+  int k = g_prefill_choice.load(std::memory_order_relaxed);
+  if (k < 0) {
     const char* e = getenv("Q27_ATTN_I8");
-    g_prefill_choice = e && e[0] == '0' ? 2 : 0;
+    k = e && e[0] == '0' ? 2 : 0;
+    int expected = -1;
+    if (!g_prefill_choice.compare_exchange_strong(expected, k)) k = expected;
   }
-  return g_prefill_choice == 2;
+  return k == 2;
 }
 
 extern "C" {
@@ -773,7 +744,7 @@ int q27b_prefill_split_plan(int M, int nqh, int n_sm, int depth_hint, int* split
 
 int q27b_set_prefill_kernel(int which) {
   if (which < 0 || which > 2) return fail(Q27B_BAD_SHAPE, "set_prefill_kernel: 0 auto, 1 int8 QK, 2 f16 QK");
-  g_prefill_choice = which;
+  g_prefill_choice.store(which);
   return Q27B_OK;
 }
 
@@ -791,22 +762,23 @@ static int prefill_impl(const float* qn, const float* qg, const void* kcache, co
   if (int rc = prefill_setup(ctx)) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   const int tiles = (M + QT - 1) / QT;
-  const SplitPlan sp = plan_prefill_split(tiles, nqh, ctx->n_sm, M, depth_hint, false);
+  SplitPlan sp = plan_prefill_split(tiles, nqh, ctx->n_sm, M, depth_hint, false);
+  float* part;  // the fixed prefill workspace; the plan is cut to what it holds
+  if (int rc = fit_prefill_split(ctx, &sp.ts, &sp.ns, M, nqh, false, &part)) return rc;
   const int nsplit = sp.ns, Ms = std::min(M, sp.ts * QT);
-  if (nsplit > 1)
-    if (int rc = ensure_part(ctx, (size_t)nsplit * Ms * nqh * PROW)) return rc;
-  const CUtensorMap *kv, *ks, *vv, *vs;
-  if (int rc = get_tmaps(kcache, nkvh, n_ctx, &kv, &ks)) return rc;
-  if (int rc = get_tmaps(vcache, nkvh, n_ctx, &vv, &vs)) return rc;
+  CUtensorMap kvm, ksm, vvm, vsm;
+  if (int rc = q8_tmaps(kcache, (uint64_t)nkvh * n_ctx, &kvm, &ksm)) return rc;
+  if (int rc = q8_tmaps(vcache, (uint64_t)nkvh * n_ctx, &vvm, &vsm)) return rc;
+  const CUtensorMap *kv = &kvm, *ks = &ksm, *vv = &vvm, *vs = &vsm;
   PrefillParams p = {};
-  p.qn = qn; p.qg = qg; p.o = o; p.xq = xq; p.xd = xd; p.part = nsplit > 1 ? ctx->part : nullptr; p.pos0 = pos0; p.status = ctx->status;
+  p.qn = qn; p.qg = qg; p.o = o; p.xq = xq; p.xd = xd; p.part = nsplit > 1 ? part : nullptr; p.pos0 = pos0; p.status = ctx->status;
   p.M = M; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.ts = sp.ts; p.nsplit = nsplit; p.kq_scale = kq_scale;
   p.tile_major = depth_hint >= 0 && depth_hint < 4 * M;  // short prefix: the causal part dominates
   prefill_i8_kernel<<<(tiles - sp.ts) * nqh + sp.ts * nqh * nsplit, PF_THREADS, PF_SMEM_BYTES, s>>>(*kv, *ks, *vv, *vs, p);
   Q27B_CK(cudaGetLastError());
   if (nsplit > 1) {  // the split tokens are rows [0, Ms * nqh) of every array
     MergeParams mp = {};
-    mp.part = ctx->part; mp.nparts = nsplit; mp.part_stride = (int64_t)Ms * nqh * PROW; mp.rows = (int64_t)Ms * nqh;
+    mp.part = part; mp.nparts = nsplit; mp.part_stride = (int64_t)Ms * nqh * PROW; mp.rows = (int64_t)Ms * nqh;
     mp.qg = qg; mp.o = o; mp.xq = xq; mp.xd = xd;
     return launch_merge(mp, false, s);
   }
@@ -835,8 +807,9 @@ int q27b_prefill_qk_debug(const float* x, int rows, float kq_scale, const void* 
   DeviceCtx* ctx;
   if (int rc = device_ctx(&ctx)) return rc;
   if (int rc = prefill_setup(ctx)) return rc;
-  const CUtensorMap *kv, *ks;
-  if (int rc = get_tmaps(kcache, nkvh, n_ctx, &kv, &ks)) return rc;
+  CUtensorMap kvm, ksm;
+  if (int rc = q8_tmaps(kcache, (uint64_t)nkvh * n_ctx, &kvm, &ksm)) return rc;
+  const CUtensorMap* kv = &kvm;
   QkDebugParams p = {x, rows, kq_scale, kh * n_ctx + p0, npos, q_i8, q_scale, acc, ctx->status};
   prefill_qk_debug_kernel<<<1, 128, DBG_SMEM, (cudaStream_t)stream>>>(*kv, p);
   Q27B_CK(cudaGetLastError());

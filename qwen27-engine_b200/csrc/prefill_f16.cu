@@ -25,6 +25,8 @@
 #include "common.cuh"
 #include "prefill_f16.h"
 
+#include <mutex>
+
 #include <algorithm>
 #include <cstdlib>
 
@@ -537,39 +539,14 @@ prefill_f16_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   }
 }
 
-struct TmapF16 {
-  const void* base;
-  int nkvh, n_ctx;
-  CUtensorMap map;
-};
-constexpr int TMAP_CACHE = 64;
-TmapF16 g_tmaps[TMAP_CACHE];
-int g_tmap_next = 0;
-
-int get_tmap(const void* cache, int nkvh, int n_ctx, const CUtensorMap** out) {
-  for (int i = 0; i < TMAP_CACHE; i++)
-    if (g_tmaps[i].base == cache && g_tmaps[i].nkvh == nkvh && g_tmaps[i].n_ctx == n_ctx) {
-      *out = &g_tmaps[i].map;
-      return Q27B_OK;
-    }
-  TmapF16& k = g_tmaps[g_tmap_next];
-  g_tmap_next = (g_tmap_next + 1) % TMAP_CACHE;
-  k.base = nullptr;
-  // rows of 512 bytes (256 halves), fetched as 128-byte wide, 64-row boxes with the 128-byte swizzle
-  if (int rc = make_tmap_2d(&k.map, cache, (uint64_t)nkvh * n_ctx, 2 * AD, 2 * AD, 128, PT, true)) return rc;
-  k.base = cache;
-  k.nkvh = nkvh;
-  k.n_ctx = n_ctx;
-  *out = &k.map;
-  return Q27B_OK;
-}
-
 }  // namespace
 
 int launch_prefill_f16(DeviceCtx* ctx, const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
                        int8_t* xq, float* xd, const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, bool q8,
                        int depth_hint, cudaStream_t s) {
   static bool attr[64] = {};
+  static std::mutex attr_mu;
+  std::lock_guard<std::mutex> attr_lock(attr_mu);
   if (!attr[ctx->dev]) {
     Q27B_CK(cudaFuncSetAttribute(prefill_f16_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<false, 2>::SMEM_BYTES));
     Q27B_CK(cudaFuncSetAttribute(prefill_f16_kernel<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<false, 4>::SMEM_BYTES));
@@ -580,22 +557,25 @@ int launch_prefill_f16(DeviceCtx* ctx, const float* qn, const float* qg, const v
   const int tiles = (M + QT - 1) / QT;
   // splits over the positions as for the int8 kernel; the q8_1 output is written by the merge kernel,
   // so it needs every tile on the split path (at least one merge)
-  const SplitPlan sp = plan_prefill_split(tiles, nqh, ctx->n_sm, M, depth_hint, xq != nullptr);
+  SplitPlan sp = plan_prefill_split(tiles, nqh, ctx->n_sm, M, depth_hint, xq != nullptr);
+  float* part;  // the fixed prefill workspace; the plan is cut to what it holds
+  if (int rc = fit_prefill_split(ctx, &sp.ts, &sp.ns, M, nqh, xq != nullptr, &part)) return rc;
   const int nsplit = sp.ns, Ms = std::min(M, sp.ts * QT);
-  if (nsplit > 1)
-    if (int rc = ensure_part(ctx, (size_t)nsplit * Ms * nqh * PROW)) return rc;
-  const CUtensorMap *tk, *tv, *tks, *tvs;
+  CUtensorMap tkm, tvm, tksm, tvsm;
+  const uint64_t rows = (uint64_t)nkvh * n_ctx;
   if (q8) {
-    if (int rc = get_q8_tmaps(kcache, nkvh, n_ctx, &tk, &tks)) return rc;
-    if (int rc = get_q8_tmaps(vcache, nkvh, n_ctx, &tv, &tvs)) return rc;
+    if (int rc = q8_tmaps(kcache, rows, &tkm, &tksm)) return rc;
+    if (int rc = q8_tmaps(vcache, rows, &tvm, &tvsm)) return rc;
   } else {
-    if (int rc = get_tmap(kcache, nkvh, n_ctx, &tk)) return rc;
-    if (int rc = get_tmap(vcache, nkvh, n_ctx, &tv)) return rc;
-    tks = tk;  // not read
-    tvs = tv;
+    // rows of 512 bytes (256 halves), fetched as 128-byte wide, 64-row boxes with the 128-byte swizzle
+    if (int rc = cached_tmap_2d(&tkm, kcache, rows, 2 * AD, 2 * AD, 128, PT, true)) return rc;
+    if (int rc = cached_tmap_2d(&tvm, vcache, rows, 2 * AD, 2 * AD, 128, PT, true)) return rc;
+    tksm = tkm;  // not read
+    tvsm = tvm;
   }
+  const CUtensorMap *tk = &tkm, *tv = &tvm, *tks = &tksm, *tvs = &tvsm;
   F16Params p = {};
-  p.qn = qn; p.qg = qg; p.o = o; p.part = nsplit > 1 ? ctx->part : nullptr; p.pos0 = pos0; p.status = ctx->status;
+  p.qn = qn; p.qg = qg; p.o = o; p.part = nsplit > 1 ? part : nullptr; p.pos0 = pos0; p.status = ctx->status;
   p.M = M; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.ts = sp.ts; p.nsplit = nsplit; p.kq_scale = kq_scale;
   const int grid = (tiles - sp.ts) * nqh + sp.ts * nqh * nsplit;
   if (q8)
@@ -607,7 +587,7 @@ int launch_prefill_f16(DeviceCtx* ctx, const float* qn, const float* qg, const v
   Q27B_CK(cudaGetLastError());
   if (nsplit > 1) {  // the split tokens are rows [0, Ms * nqh) of every array
     MergeParams mp = {};
-    mp.part = ctx->part; mp.nparts = nsplit; mp.part_stride = (int64_t)Ms * nqh * PROW; mp.rows = (int64_t)Ms * nqh;
+    mp.part = part; mp.nparts = nsplit; mp.part_stride = (int64_t)Ms * nqh * PROW; mp.rows = (int64_t)Ms * nqh;
     mp.qg = qg; mp.o = o; mp.xq = xq; mp.xd = xd;
     return launch_merge(mp, false, s);
   }

@@ -55,8 +55,4 @@ int launch_prefill_f16(DeviceCtx* ctx, const float* qn, const float* qg, const v
                        int8_t* xq, float* xd, const int* pos0, int M, float kq_scale, int nqh, int nkvh, int n_ctx, bool q8,
                        int depth_hint, cudaStream_t s);
 
-// Tensor maps of a q8_0 cache (prefill.cu): the int8 values in boxes of 128 bytes x 64 rows with the
-// 128-byte swizzle, the f16 scales in boxes of 16 bytes x 64 rows.
-int get_q8_tmaps(const void* cache, int nkvh, int n_ctx, const CUtensorMap** vals, const CUtensorMap** scales);
-
 }  // namespace q27b

@@ -204,15 +204,14 @@ int q27b_sum_push(const float* partial, int n, int rows, int rank, int world, vo
   if (!partial || !xbufs) return fail(Q27B_BAD_SHAPE, "sum_push: null pointer");
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(Q27B_BAD_SHAPE, "sum_push: bad rank/world");
   if (int rc = check_shape(rows, n, "sum_push: rows >= 1, n a multiple of 32 up to 16384")) return rc;
-  int dev;
-  Q27B_CK(cudaGetDevice(&dev));
   SumPushParams p = {};
   p.partial = partial; p.rows = rows; p.n = n; p.rank = rank; p.world = world;
-  for (int k = 0; k < world; k++) {
+  for (int k = 0; k < world; k++)
     if (!xbufs[k]) return fail(Q27B_BAD_SHAPE, "sum_push: null exchange buffer");
-    cudaPointerAttributes a;
-    Q27B_CK(cudaPointerGetAttributes(&a, xbufs[k]));
-    if (a.type != cudaMemoryTypeDevice) return fail(Q27B_BAD_SHAPE, "sum_push: exchange buffer is not device memory");
+  // Every buffer must be device memory that kernels of this GPU may store into (its own, or a peer's
+  // with peer access, enabled here once per pointer); anything else is refused before the launch.
+  for (int k = 0; k < world; k++) {
+    if (int rc = check_peer_buffer(xbufs[k], "sum_push")) return rc;
     p.peer[k] = xbufs[k];
   }
   p.xbuf = (int*)xbufs[rank];

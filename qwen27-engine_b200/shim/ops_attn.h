@@ -1,9 +1,8 @@
 // Drop-in C++ shim: the attention operators of the reference (namespace q27, src/ops.h:50-77) with
 // their exact signatures, forwarding to the q27b_attn C ABI. A non-zero status becomes the
 // std::runtime_error that the reference's own implementation throws (CK() and the shape checks,
-// src/common.cuh:12-13, src/attn.cu:906,929), so src/model.cu and tools/bench_attn.cu compile and
-// behave unchanged when src/attn.cu and the attn_prep part of src/ops.cu are replaced by this
-// header plus libq27b_attn.so.
+// src/common.cuh:12-13, src/attn.cu:906,929). The reference's check-and-bench tool tools/bench_attn.cu
+// compiles unchanged against this directory (its "ops.h" and "common.cuh" here) and libq27b_attn.so.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -49,6 +48,12 @@ inline void attn_prefill(const float* qn, const float* qg, const void* kcache, c
                          int depth_hint = -1) {
   q27b_detail::check(q27b_attn_prefill(qn, qg, kcache, vcache, o, pos0, M, kq_scale, nqh, nkvh, n_ctx, q8 ? 1 : 0,
                                        (void*)s, depth_hint));
+}
+
+inline void attn_decode_ref(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
+                            const int* pos0, int T, float kq_scale, int nqh, int nkvh, int n_ctx, bool q8, cudaStream_t s) {
+  q27b_detail::check(q27b_attn_decode_ref(qn, qg, kcache, vcache, o, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8 ? 1 : 0,
+                                          (void*)s));
 }
 
 }  // namespace q27
