@@ -5,7 +5,9 @@
 // A = sum O_c e^(m_c - M), y = (A / L) * sigmoid(gate); partials are added in index order, so
 // the result does not depend on scheduling. One CTA per output row, one thread per dim; the
 // factors e^(m_c - M) are computed once per CTA into shared memory, then every thread streams
-// its column of the partials with independent loads. Built without fast-math: the q8_1 epilogue
+// its column of the partials with independent loads. With many partials (one KV head per GPU puts all
+// SMs of the GPU on that head: 148 partials per row, and only 24 rows) the CTA has four thread groups
+// that each take a quarter of the partials and are added up in group order at the end. Built without fast-math: the q8_1 epilogue
 // (q8_store, src/common.cuh:72-81) is specified in IEEE operations.
 #include "combine.h"
 
@@ -36,14 +38,20 @@ __device__ __forceinline__ RowMap map_decode(const MergeParams& p, int64_t row) 
 }
 
 // XCHG: the peer-memory exchange modes (push_n / wait_n of MergeParams) are compiled in.
-template <bool DECODE_LAYOUT, bool XCHG>
-__global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
+constexpr int MAX_GROUPS = 4;
+
+// NGRP: thread groups of 256 (1, or MAX_GROUPS for many partials).
+template <bool DECODE_LAYOUT, bool XCHG, int NGRP>
+__global__ void __launch_bounds__(AD * NGRP) merge_kernel(const MergeParams p) {
   pdl_wait();
   pdl_trigger();
   __shared__ float sf[MAX_PARTS];
-  __shared__ float sred[2][8];
+  __shared__ float sred[32];
+  __shared__ float sgl[NGRP], sga[NGRP > 1 ? NGRP - 1 : 1][AD];
   const int64_t row = blockIdx.x;
-  const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
+  constexpr int ngrp = NGRP, nthr = AD * NGRP;
+  const int tid = threadIdx.x, grp = tid / AD;
+  const int d = tid % AD, lane = tid & 31, warp = tid >> 5;
   RowMap rm = DECODE_LAYOUT ? map_decode(p, row) : map_generic(p, row);
   int np = p.nparts;
   int epoch = 0;
@@ -84,47 +92,62 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
 
   // The first PRE partials of this thread's column (and their sums l) are requested before the
   // maxima are reduced, so that the kernel makes one trip to L2 instead of two.
-  constexpr int PRE = 48;
+  constexpr int PRE = NGRP == 1 ? 48 : 16;  // (four groups leave 64 registers per thread)
+  // this group's partials [c_lo, c_hi)
+  const int per = (np + ngrp - 1) / ngrp, c_lo = min(np, grp * per), c_hi = min(np, c_lo + per);
   const float* col = rm.first + 2 + d;
   float av[PRE], lv[PRE];
 #pragma unroll
   for (int c = 0; c < PRE; c++)
-    if (c < np) {
-      av[c] = col[c * rm.stride];
-      lv[c] = rm.first[c * rm.stride + 1];
+    if (c_lo + c < c_hi) {
+      av[c] = col[(size_t)(c_lo + c) * rm.stride];
+      lv[c] = rm.first[(size_t)(c_lo + c) * rm.stride + 1];
     }
   const float gate = rm.gate ? rm.gate[d] : 0.f;
 
   // M and the factors
   float mx = M_INIT;
-  for (int c = d; c < np; c += AD) mx = fmaxf(mx, rm.first[c * rm.stride]);
+  for (int c = tid; c < np; c += nthr) mx = fmaxf(mx, rm.first[c * rm.stride]);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if (lane == 0) sred[0][warp] = mx;
+  if (lane == 0) sred[warp] = mx;
   __syncthreads();
-  float M = sred[0][0];
-#pragma unroll
-  for (int i = 1; i < 8; i++) M = fmaxf(M, sred[0][i]);
-  for (int c = d; c < np; c += AD) sf[c] = expf(rm.first[c * rm.stride] - M);
+  float M = sred[0];
+  for (int i = 1; i < nthr / 32; i++) M = fmaxf(M, sred[i]);
+  for (int c = tid; c < np; c += nthr) sf[c] = expf(rm.first[c * rm.stride] - M);
   __syncthreads();
 
   float L = 0.f, A = 0.f;
 #pragma unroll
   for (int c = 0; c < PRE; c++)
-    if (c < np) {
-      const float f = sf[c];
+    if (c_lo + c < c_hi) {
+      const float f = sf[c_lo + c];
       L += lv[c] * f;
       A += av[c] * f;
     }
 #pragma unroll 8
-  for (int c = PRE; c < np; c++) {
+  for (int c = c_lo + PRE; c < c_hi; c++) {
     const float f = sf[c];
     L += rm.first[c * rm.stride + 1] * f;
     A += col[c * rm.stride] * f;
   }
+  if constexpr (NGRP > 1) {  // add the groups up in group order (group 0 carries on alone)
+    if (grp > 0) {
+      sga[grp - 1][d] = A;
+      if (d == 0) sgl[grp] = L;
+    }
+    __syncthreads();
+    if (grp == 0)
+      for (int k = 1; k < ngrp; k++) {
+        A += sga[k - 1][d];
+        L += sgl[k];
+      }
+  }
+  // Group 0 writes the result; the other groups only keep the CTA's barriers and counters company.
+  const bool lead = NGRP == 1 || grp == 0;
 
   const size_t oi = (size_t)row * AD + d;
-  if (XCHG && !DECODE_LAYOUT && p.wait_n > 0 && d == 0) {
+  if (XCHG && !DECODE_LAYOUT && p.wait_n > 0 && tid == 0) {
     // the last CTA of the step advances the epoch (nobody reads it again before the next launch)
     __threadfence();
     if (atomicAdd(p.xbuf + 2, 1) == (int)p.rows - 1) {
@@ -133,7 +156,7 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
     }
   }
   if (XCHG && p.push_n > 0) {  // merged, not normalised, into slot push_z of every rank's exchange buffer
-    for (int k = 0; k < p.push_n; k++) {
+    for (int k = 0; lead && k < p.push_n; k++) {
       float* po = (float*)((uint8_t*)p.push_buf[k] + XBUF_HEADER_BYTES) +
                   (((size_t)(epoch & 1) * p.push_n + p.push_z) * p.rows + row) * PROW;
       po[2 + d] = A;
@@ -144,7 +167,7 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
     }
     __threadfence_system();  // the rows are visible to the peers before the flag below can be
     __syncthreads();
-    if (d == 0 && atomicAdd(p.xbuf + 1, 1) == (int)p.rows - 1) {
+    if (tid == 0 && atomicAdd(p.xbuf + 1, 1) == (int)p.rows - 1) {
       p.xbuf[1] = 0;
       __threadfence_system();
       for (int k = 0; k < p.push_n; k++) {
@@ -154,6 +177,7 @@ __global__ void __launch_bounds__(AD) merge_kernel(const MergeParams p) {
     }
     return;
   }
+  if (!lead) return;
   if (p.part_out) {  // merged but not normalised: (M, L, A) for a later merge
     float* po = p.part_out + (size_t)row * PROW;
     po[2 + d] = A;
@@ -184,10 +208,16 @@ int launch_merge(const MergeParams& p, bool decode_layout, cudaStream_t s) {
   if (p.rows < 1) return Q27B_OK;
   const bool xchg = p.push_n > 0 || p.wait_n > 0;
   const dim3 grid((unsigned)p.rows);
-  if (decode_layout && xchg) Q27B_CK(launch_pdl(merge_kernel<true, true>, grid, dim3(AD), 0, s, p));
-  else if (decode_layout) Q27B_CK(launch_pdl(merge_kernel<true, false>, grid, dim3(AD), 0, s, p));
-  else if (xchg) Q27B_CK(launch_pdl(merge_kernel<false, true>, grid, dim3(AD), 0, s, p));
-  else Q27B_CK(launch_pdl(merge_kernel<false, false>, grid, dim3(AD), 0, s, p));
+  // four thread groups once a row has more partials than a 4-head decode call gives it (37 on 148 SMs)
+  // (the waiting merge of an exchange has at most 8 partials; the pushing one is a decode-layout merge)
+  const bool wide = p.wait_n == 0 && p.nparts > 64;
+  if (decode_layout && xchg && wide) Q27B_CK(launch_pdl(merge_kernel<true, true, MAX_GROUPS>, grid, dim3(AD * MAX_GROUPS), 0, s, p));
+  else if (decode_layout && xchg) Q27B_CK(launch_pdl(merge_kernel<true, true, 1>, grid, dim3(AD), 0, s, p));
+  else if (decode_layout && wide) Q27B_CK(launch_pdl(merge_kernel<true, false, MAX_GROUPS>, grid, dim3(AD * MAX_GROUPS), 0, s, p));
+  else if (decode_layout) Q27B_CK(launch_pdl(merge_kernel<true, false, 1>, grid, dim3(AD), 0, s, p));
+  else if (xchg) Q27B_CK(launch_pdl(merge_kernel<false, true, 1>, grid, dim3(AD), 0, s, p));
+  else if (wide) Q27B_CK(launch_pdl(merge_kernel<false, false, MAX_GROUPS>, grid, dim3(AD * MAX_GROUPS), 0, s, p));
+  else Q27B_CK(launch_pdl(merge_kernel<false, false, 1>, grid, dim3(AD), 0, s, p));
   return Q27B_OK;
 }
 
