@@ -266,6 +266,23 @@ def cpu_baseline(n=N_POS):
             "ms_per_step": dt * 1e3}
 
 
+def measure_mma_peak(q, kind, iters=4000, reps=3):
+    """TOPS (kind 0: tcgen05.mma kind::i8) or TFLOP/s (kind 1: kind::f16) of the library's tensor-core peak
+    microbenchmark: back-to-back 128 x 256 tiles from operands resident in shared memory, one CTA per SM,
+    timed with CUDA events around the launch; best of `reps`."""
+    q.debug_mma_peak(kind, 200)
+    torch.cuda.synchronize()
+    best = 0.0
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops = q.debug_mma_peak(kind, iters)
+        e1.record()
+        torch.cuda.synchronize()
+        best = max(best, ops / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return best
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -388,6 +405,11 @@ def main():
         line["extras"] = extras(q, caches, qn, qg, o, n_ctx)
         # the second half of the metric, last in the line: int8 prefill TOPS of a 2048-token chunk per prefix depth
         line["prefill_int8_tops"] = {k: round(v["tops"], 1) for k, v in line["extras"]["prefill"].items() if "tops" in v}
+        i8 = line["extras"].get("mma_peak", {}).get("int8_tops")
+        if i8:
+            line["prefill_int8_tops"]["int8_peak_measured"] = round(i8, 1)
+            line["prefill_int8_tops"]["frac_of_int8_peak"] = {k: round(v / i8, 3) for k, v in line["prefill_int8_tops"].items()
+                                                              if k.isdigit()}
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:
@@ -767,6 +789,11 @@ def extras(q, caches, qn, qg, o, n_ctx):
     except Exception as e:  # report, do not hide
         out["prefill_f16_cache"]["error"] = str(e)
     out["device_status"] = q.device_status()
+    try:  # the tensor-pipe denominators, measured in this run
+        out["mma_peak"] = {"int8_tops": measure_mma_peak(q, 0), "f16_tflops": measure_mma_peak(q, 1),
+                           "what": "tcgen05.mma kind::i8 / kind::f16, 128 x 256 tiles back to back from shared memory, one CTA per SM"}
+    except Exception as e:  # report, do not hide
+        out["mma_peak"] = {"error": str(e)}
     try:
         out["batched_paged"] = batched_paged(q, 0, 1)
     except Exception as e:  # report, do not hide
@@ -838,40 +865,106 @@ def prefill_mode(q, args, steps, warmup, dist=None, rank=0, world=1):
     tops = ops / (ms * 1e-3) / 1e12
     pk, pk_kind = peaks()
     f16 = pk["bf16_tflops_sustained"]
-    # half of the ops run on the int8 pipe (taken as twice the measured 16-bit rate), half on the f16 pipe
-    t_min_ms = (ops / 2 / (2 * f16 * 1e12) + ops / 2 / (f16 * 1e12)) * 1e3
+    sm_mhz = clocks.get("sm_mhz") or 1965.0
     line = {"metric": "int8 prefill-attn TOPS (2048-token chunk, 24q/4kv heads, head dim 256, q8_0 prefix)",
             "value": tops, "unit": "TOPS", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
             "dtype": "s8 x s8 -> s32 (QK), f16 -> f32 (PV)",
             "data": "synthetic", "config": {"workload": "prefill chunk M=2048 on a q8_0 prefix of %d tokens" % P},
-            "gpu_launches": steps * len(calls), "clocks": clocks,
-            "roofline": {"bound": "tensor", "achieved": tops, "peak": 2 * f16, "unit": "TOP/s",
-                         "frac": tops / (2 * f16), "peak_kind": "2 x %s bf16 GEMM rate (sustained) as the int8 peak" % pk_kind,
-                         "frac_of_mixed_int8_f16_bound": t_min_ms / ms, "traffic": None}}
+            "gpu_launches": steps * len(calls), "clocks": clocks}
+    if use_ref:
+        i8_peak, f16_peak, peak_kind = 2 * f16, f16, "2 x %s bf16 GEMM rate (sustained) as the int8 peak" % pk_kind
+    else:
+        # the denominators measured on this GPU, in this process: tcgen05.mma kind::i8 and kind::f16 back to back
+        i8_peak, f16_peak = measure_mma_peak(q, 0), measure_mma_peak(q, 1)
+        peak_kind = "tcgen05.mma kind::i8 microbenchmark of this run (kind::f16: %.0f TFLOP/s; %s bf16 GEMM: %.0f sustained)" % (
+            f16_peak, pk_kind, f16)
+    # half of the ops run on the int8 pipe, half on the f16 pipe
+    t_min_ms = (ops / 2 / (i8_peak * 1e12) + ops / 2 / (f16_peak * 1e12)) * 1e3
+    # the exact per-block numerics cost ~22 SIMT instructions per score (8 blocks x (int -> float, scale
+    # product, FMA) + softmax): what 128 lanes per SM can issue at the sampled clock, as TOPS of the same ops
+    alu_bound_tops = 1024.0 * 128 * n_sm_of_device() * sm_mhz * 1e6 / 22.0 / 1e12 * world
+    line["roofline"] = {"bound": "tensor", "achieved": tops, "peak": i8_peak * world, "unit": "TOP/s",
+                        "frac": tops / (i8_peak * world), "peak_kind": peak_kind, "int8_tops_measured": i8_peak,
+                        "f16_tflops_measured": f16_peak, "frac_of_mixed_int8_f16_bound": t_min_ms / ms / world,
+                        "fp32_alu_bound_tops": alu_bound_tops, "frac_of_fp32_alu_bound": tops / alu_bound_tops,
+                        "traffic": None}
+    if not use_ref and world == 1:
+        line["e2e"] = prefill_e2e(q, kc, vc, M, P, n_ctx, q8, steps, warmup)
+        if q8:
+            line["cpu_baseline"] = prefill_cpu_baseline(kc, vc, qn, qg, M, P, n_ctx)
     if not q8:  # all of the ops on the f16 pipe
         line["metric"] = "f16 prefill-attn TFLOPS (2048-token chunk, 24q/4kv heads, head dim 256, f16 prefix)"
         line["unit"] = "TFLOP/s"
         line["dtype"] = "f16 -> f32 (QK and PV)"
         line["config"] = {"workload": "prefill chunk M=2048 on an f16 prefix of %d tokens" % P}
-        line["roofline"] = {"bound": "tensor", "achieved": tops, "peak": f16, "unit": "TFLOP/s", "frac": tops / f16,
-                            "peak_kind": "%s bf16 GEMM rate (sustained)" % pk_kind, "traffic": None}
+        line["roofline"] = {"bound": "tensor", "achieved": tops, "peak": f16_peak * world, "unit": "TFLOP/s",
+                            "frac": tops / (f16_peak * world), "peak_kind": peak_kind, "traffic": None}
     if q8 and os.environ.get("Q27_ATTN_I8", "1")[:1] == "0":  # the library reads the same switch
         line["metric"] = "f16-QK prefill-attn TOPS on a q8_0 prefix (Q27_ATTN_I8=0: K and V dequantised to f16; 2048-token chunk, 24q/4kv heads, head dim 256)"
         line["dtype"] = "f16 -> f32 (QK and PV), q8_0 K/V dequantised on the way"
-        line["roofline"] = {"bound": "tensor", "achieved": tops, "peak": f16, "unit": "TFLOP/s", "frac": tops / f16,
-                            "peak_kind": "%s bf16 GEMM rate (sustained)" % pk_kind, "traffic": None}
+        line["roofline"] = {"bound": "tensor", "achieved": tops, "peak": f16_peak * world, "unit": "TFLOP/s",
+                            "frac": tops / (f16_peak * world), "peak_kind": peak_kind, "traffic": None}
     if world > 1:
         line["config"]["sharding"] = "KV-head groups x %d query-token slices per group, no exchange; rank 0: heads %d..%d, tokens %s" % (
             max(1, world // NKVH), plan.kv_head0, plan.kv_head0 + nkvh - 1, list(plan.ranges))
-        line["roofline"]["peak"] *= world
-        line["roofline"]["frac"] /= world
-        line["roofline"].pop("frac_of_mixed_int8_f16_bound", None)
     if use_ref:
         line["impl"] = "reference"
     if not use_ref:
         assert q.device_status() == 0
     print(json.dumps(line))
+
+
+def n_sm_of_device():
+    return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+
+
+def prefill_e2e(q, kc, vc, M, P, n_ctx, q8, steps, warmup):
+    """The prefill chunk through the operator API with host buffers: every step copies the chunk's query +
+    gate rows and its new K and V rows from pinned host memory, appends the rows to the cache, runs
+    attn_prefill and copies the result back to pinned host memory."""
+    sizes = [M * NQH * AD, M * NQH * 512, M * NKVH * AD, M * NKVH * AD]
+    h_in = torch.randn((sum(sizes),)).pin_memory()
+    d_in = torch.empty((sum(sizes),), device="cuda")
+    o0, o1, o2 = sizes[0], sizes[0] + sizes[1], sizes[0] + sizes[1] + sizes[2]
+    d_qn, d_qg = d_in[:o0].view(M, NQH, AD), d_in[o0:o1].view(M, NQH, 512)
+    d_k, d_v = d_in[o1:o2].view(M, NKVH, AD), d_in[o2:].view(M, NKVH, AD)
+    h_o = torch.empty((M, NQH, AD)).pin_memory()
+    d_o = torch.empty((M, NQH, AD), device="cuda")
+    pos = torch.tensor([P], dtype=torch.int32, device="cuda")
+
+    def step(i):
+        d_in.copy_(h_in, non_blocking=True)
+        q.kv_append(d_k, d_v, kc, vc, pos, M, NKVH, n_ctx, q8)
+        q.attn_prefill(d_qn, d_qg, kc, vc, d_o, pos, M, SCALE, NQH, NKVH, n_ctx, q8, P)
+        h_o.copy_(d_o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    ms = time_steps(step, steps, warmup)
+    ops = NQH * 1024.0 * (M * P + M * (M + 1) / 2)
+    return {"value": ops / (ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": ms, "h2d_bytes_per_step": h_in.numel() * 4,
+            "d2h_bytes_per_step": h_o.numel() * 4,
+            "what": "every step: pinned host q|gate and new K, V rows of the chunk -> device, kv_append, attn_prefill, "
+                    "result -> pinned host, synchronise"}
+
+
+def prefill_cpu_baseline(kc, vc, qn, qg, M, P, n_ctx):
+    """The CPU oracle's int8-QK prefill on a subset of the chunk's query tokens (the first, a middle and the
+    last 8 tokens, all 24 heads, their whole causal range), timed on the host cores; the rate is per op of
+    what it computed, as for the GPU figure."""
+    import oracle
+    hk, hv = kc.cpu().numpy(), vc.cpu().numpy()
+    hq, hg = qn.cpu().numpy(), qg.cpu().numpy()
+    ranges = [(0, 8), (M // 2 - 4, M // 2 + 4), (M - 8, M)]
+    oracle.attn_prefill_i8(hq, hg, hk, hv, P, SCALE, NKVH, n_ctx, 0, 1)  # warm
+    t0 = time.perf_counter()
+    for a, b in ranges:
+        oracle.attn_prefill_i8(hq, hg, hk, hv, P, SCALE, NKVH, n_ctx, a, b)
+    dt = time.perf_counter() - t0
+    ops = sum(NQH * 1024.0 * (P + t + 1) for a, b in ranges for t in range(a, b))
+    return {"value": ops / dt / 1e12, "unit": "TOPS", "cores": oracle.num_threads(), "kind": "port",
+            "sample": "%d of the %d query tokens (tokens %s, all heads, whole causal range): %.2f s on the host cores; "
+                      "the whole chunk would take %.0f s at that rate" % (
+                          sum(b - a for a, b in ranges), M, ranges, dt, NQH * 1024.0 * (M * P + M * (M + 1) / 2) / (ops / dt))}
 
 
 def run_reference(args, line, caches, qn, qg, o, pos, n, n_ctx, steps, warmup):

@@ -277,6 +277,15 @@ int q27b_debug_split_only(int on);
  * launch divides into ramp-up, streaming and drain. NULL switches it off. */
 int q27b_debug_decode_trace(unsigned long long* stamps);
 
+/* Measurement hook, no counterpart in the reference: launches the tensor-core peak microbenchmark on
+ * the current device (one CTA per SM issuing `iters` x 4 back-to-back tcgen05.mma 128 x 256 tiles from
+ * operands resident in shared memory into tensor memory): kind 0 = kind::i8 (s8 x s8 -> s32, K = 32 per
+ * instruction), kind 1 = kind::f16 (f16 x f16 -> f32, K = 16). *ops_per_launch = the multiply-adds x 2
+ * of one launch; time the launch with events to get the int8 TOPS / f16 TFLOPS that the prefill
+ * kernels' tensor-pipe fractions are quoted against (the reference quotes its kernel against its card's
+ * tensor peak, docs/PERFORMANCE.md:214). */
+int q27b_debug_mma_peak(int kind, int iters, void* stream, double* ops_per_launch);
+
 /* The reference's host ("wire") layout of rows [p0, p1) of one cache, used for its RAM swap of idle
  * slots and its prompt-cache checkpoints (Decoder::kv_copy, src/model.cu:1809-1830): the values
  * [nkvh][p1-p0][256 B], then the scales [nkvh][p1-p0][16 B]; q27b_kv_wire_bytes gives its size

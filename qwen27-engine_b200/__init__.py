@@ -34,7 +34,7 @@ SYMBOLS = [
     "q27b_xbuf_alloc", "q27b_xbuf_free", "q27b_ipc_export", "q27b_ipc_open", "q27b_ipc_close",
     "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
     "q27b_attn_decode_noalloc", "q27b_attn_decode_ref", "q27b_attn_workspace_query", "q27b_attn_workspace_init",
-    "q27b_attn_workspace_destroy",
+    "q27b_attn_workspace_destroy", "q27b_debug_mma_peak",
 ]
 
 
@@ -271,6 +271,13 @@ def workspace_init(prefill_bytes=0, paged_bytes=0):
 
 def workspace_destroy():
     _check(_lib.q27b_attn_workspace_destroy())
+
+
+def debug_mma_peak(kind, iters):
+    """Launches the tensor-core peak microbenchmark (kind 0: int8, 1: f16); returns the ops of the launch."""
+    ops = ctypes.c_double(0)
+    _check(_lib.q27b_debug_mma_peak(int(kind), int(iters), _stream(), ctypes.byref(ops)))
+    return ops.value
 
 
 def set_decode_schedule(pool):
