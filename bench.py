@@ -492,7 +492,9 @@ def e2e(q, caches, n, n_ctx, steps, warmup, dist, world):
 
     # The same step the way the reference's engine issues a decode step: captured once in a CUDA graph
     # (src/model.cu:910-955), one graph per cache of the rotation; a step is one replay plus the
-    # synchronise before the host reads the result. The copies are memcpy nodes of the graph.
+    # synchronise before the host reads the result. The copies are memcpy nodes of the graph. (A graph with
+    # the gate's 196 KB on a branch of its own, joined before the merge kernel, was measured too: 130 us
+    # against 107 us per step - three copy nodes and a join cost more than the overlap returns.)
     def body(i):
         kc, vc = caches[i % NBUF]
         d_in.copy_(h_in, non_blocking=True)

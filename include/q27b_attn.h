@@ -183,6 +183,13 @@ uint64_t q27b_xbuf_bytes(int nz, int64_t rows);
  * whose kernels will store into it (a handle opened under another device is not reachable). */
 int q27b_xbuf_alloc(int nz, int64_t rows, void** out);
 int q27b_xbuf_free(void* xbuf);
+/* After a step that ended in device status 1 (a peer's slice or rows never arrived: the waiting kernel
+ * gave up, and its CTAs did not finish the step's bookkeeping) an exchange buffer is out of step with
+ * its peers. Before the group uses its buffers again EVERY rank of the group zeroes the header of its
+ * own buffer with this call (epoch, arrival counters, flags; 256 bytes, on `stream`), and the ranks meet
+ * on the host (a barrier of whatever they use to talk) between the resets and the next push. Applies to
+ * the buffers of both exchanges (q27b_lse_merge_wait and q27b_sum_norm_q8_wait). */
+int q27b_xbuf_reset(void* xbuf, void* stream);
 int q27b_ipc_export(const void* ptr, unsigned char handle[64]);
 int q27b_ipc_open(const unsigned char handle[64], void** out);
 int q27b_ipc_close(void* mapped);

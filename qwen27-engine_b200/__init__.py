@@ -34,7 +34,7 @@ SYMBOLS = [
     "q27b_xbuf_alloc", "q27b_xbuf_free", "q27b_ipc_export", "q27b_ipc_open", "q27b_ipc_close",
     "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
     "q27b_attn_decode_noalloc", "q27b_attn_decode_ref", "q27b_attn_workspace_query", "q27b_attn_workspace_init",
-    "q27b_attn_workspace_destroy", "q27b_debug_mma_peak",
+    "q27b_attn_workspace_destroy", "q27b_debug_mma_peak", "q27b_xbuf_reset",
 ]
 
 
@@ -271,6 +271,11 @@ def workspace_init(prefill_bytes=0, paged_bytes=0):
 
 def workspace_destroy():
     _check(_lib.q27b_attn_workspace_destroy())
+
+
+def xbuf_reset(xbuf):
+    """Zeroes the header of an exchange buffer (every rank of the group, after a step that reported status 1)."""
+    _check(_lib.q27b_xbuf_reset(_ptr(xbuf), _stream()))
 
 
 def debug_mma_peak(kind, iters):

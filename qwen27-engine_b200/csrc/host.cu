@@ -326,6 +326,12 @@ int q27b_xbuf_alloc(int nz, int64_t rows, void** out) {
   return Q27B_OK;
 }
 
+int q27b_xbuf_reset(void* xbuf, void* stream) {
+  if (!xbuf) return fail(Q27B_BAD_SHAPE, "xbuf_reset: null pointer");
+  Q27B_CK(cudaMemsetAsync(xbuf, 0, 256, (cudaStream_t)stream));  // epoch, arrival counters, flags
+  return Q27B_OK;
+}
+
 int q27b_xbuf_free(void* p) {
   if (p) Q27B_CK(cudaFree(p));
   return Q27B_OK;

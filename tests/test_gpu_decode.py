@@ -233,3 +233,18 @@ def test_peer_memory_merge_reports_a_missing_slice(q27):
     q27.lse_merge_wait(buf, nz, rows, None, o)
     assert q27.device_status() & 1
     assert bool((o == 7.0).all())
+    # the buffer is out of step now (its CTAs left without the step's bookkeeping): after a reset of the
+    # header a complete step on the same buffer works again
+    q27.xbuf_reset(buf)
+    parts = torch.randn((nz, rows, 258), device="cuda")
+    parts[..., 1] = parts[..., 1].abs() + 0.5
+    data = buf[256:].view(torch.float32)[: nz * rows * 258].view(nz, rows, 258)  # parity 0 of epoch 0
+    data.copy_(parts)
+    buf[64:72] = torch.tensor([1, 0, 0, 0, 1, 0, 0, 0], dtype=torch.uint8, device="cuda")  # both flags = epoch + 1
+    q27.lse_merge_wait(buf, nz, rows, None, o)
+    want = torch.empty((rows, AD), device="cuda")
+    q27.lse_merge(parts.contiguous(), nz, rows * 258, rows, None, want)
+    torch.cuda.synchronize()
+    assert q27.device_status() == 0
+    assert torch.equal(o, want)
+    assert int(buf[:4].view(torch.int32).item()) == 1  # the step counter advanced from zero
