@@ -627,7 +627,7 @@ int kernel_choice() {
   int k = g_kernel_choice.load(std::memory_order_relaxed);
   if (k < 0) {
     const char* e = getenv("Q27B_DECODE_KERNEL");
-    k = !e ? 0 : e[0] == 'm' ? 1 : e[0] == 't' ? 2 : e[0] == 'w' ? 3 : 0;
+    k = !e ? 0 : e[0] == 'm' ? 1 : e[0] == 't' ? 2 : (e[0] == 'w' && e[1] == 't') ? 4 : e[0] == 'w' ? 3 : 0;
     int expected = -1;
     if (!g_kernel_choice.compare_exchange_strong(expected, k)) k = expected;
   }
@@ -639,6 +639,7 @@ int launch_q8(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* v
   const int k = kernel_choice();
   if (k == 2) return launch_decode_tc(kv, ks, vv, vs, p, paged, nseq, s);
   if (k == 0 || k == 3) return launch_decode_ws(kv, ks, vv, vs, p, paged, nseq, s);
+  if (k == 4) return launch_decode_wt(kv, ks, vv, vs, p, paged, nseq, s);
   return paged ? launch_decode_t<true, true>(kv, ks, vv, vs, p, nseq, s) : launch_decode_t<false, true>(kv, ks, vv, vs, p, nseq, s);
 }
 
@@ -831,7 +832,8 @@ int q27b_attn_decode_noalloc(const float* qn, const float* qg, const void* kcach
 }
 
 int q27b_set_decode_kernel(int which) {
-  if (which < 0 || which > 3) return fail(Q27B_BAD_SHAPE, "set_decode_kernel: 0 auto, 1 warp-MMA, 2 tcgen05, 3 warp-specialised");
+  if (which < 0 || which > 4)
+    return fail(Q27B_BAD_SHAPE, "set_decode_kernel: 0 auto, 1 warp-MMA, 2 tcgen05, 3 warp-specialised, 4 warp-specialised with P V on tcgen05");
   g_kernel_choice.store(which);
   return Q27B_OK;
 }

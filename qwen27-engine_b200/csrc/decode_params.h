@@ -33,6 +33,9 @@ int launch_decode_tc(const CUtensorMap* kv, const CUtensorMap* ks, const CUtenso
 // The warp-specialised split-K kernel (decode_ws.cu): same grid, partial layout and tensor maps again.
 int launch_decode_ws(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
                      const DecodeParams& p, bool paged, int nseq, cudaStream_t s);
+// The same with the P V contraction on tcgen05 (decode_wt.cu).
+int launch_decode_wt(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
+                     const DecodeParams& p, bool paged, int nseq, cudaStream_t s);
 // Opts the kernels of decode_ws.cu into their shared-memory size on the current device.
 int decode_ws_setup();
 

@@ -56,9 +56,9 @@ def test_bad_shapes_are_rejected_on_the_host(q27):
 def test_decode_kernel_selection_is_checked(q27):
     lib = ctypes.CDLL(q27.LIB_PATH)
     lib.q27b_last_error.restype = ctypes.c_char_p
-    for which in (0, 1, 2, 3, 0):
+    for which in (0, 1, 2, 3, 4, 0):
         assert lib.q27b_set_decode_kernel(which) == 0
-    for which in (-1, 4):
+    for which in (-1, 5):
         assert lib.q27b_set_decode_kernel(which) == q27.BAD_SHAPE
         assert b"set_decode_kernel" in lib.q27b_last_error()
 

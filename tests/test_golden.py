@@ -220,7 +220,7 @@ def test_decode_oracle_at_depth_against_reference_kernels(deep, orc):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("kernel", [1, 2, 3], ids=["mma", "tc", "ws"])
+@pytest.mark.parametrize("kernel", [1, 2, 3, 4], ids=["mma", "tc", "ws", "wt"])
 def test_new_decode_kernels_at_depth_against_reference_outputs(deep, q27, orc, kernel):
     """40,000 positions: every split-K kernel of the library against what the reference's slow and fast
     decode kernels gave for the same seeded inputs."""

@@ -11,9 +11,9 @@ AD, GQA, PAGE = 256, 6, 256
 SCALE = 1.0 / 16.0
 
 
-@pytest.fixture(autouse=True, params=[1, 2, 3], ids=["mma", "tc", "ws"])
+@pytest.fixture(autouse=True, params=[1, 2, 3, 4], ids=["mma", "tc", "ws", "wt"])
 def decode_kernel(request, q27):
-    """Every test of this module runs on every split-K kernel (warp-MMA, tcgen05, warp-specialised)."""
+    """Every test of this module runs on every split-K kernel (warp-MMA, tcgen05, warp-specialised, warp-specialised with P V on tcgen05)."""
     q27.set_decode_kernel(request.param)
     yield request.param
     q27.set_decode_kernel(0)
