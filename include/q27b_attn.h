@@ -198,6 +198,20 @@ int q27b_attn_decode_partial_push(const float* qn, const void* kcache, const voi
                                   void* const* peer_xbuf, int my_z, int nz, void* stream);
 int q27b_lse_merge_wait(void* xbuf, int nz, int64_t rows, const float* qg, float* o, void* stream);
 
+/* How the path is shared out over the GPUs of one box, as host arithmetic (no GPU needed), for hosts that do
+ * not go through the Python helpers (qwen27-engine_b200/shard.py gives the same answers). The reference splits
+ * by KV head only (2 KV heads + their 12 query heads per card, src/model.cu:161-164).
+ *  - plan_single_sequence: up to nkvh ranks, rank r owns KV heads [kv_head0, kv_head0 + n_kv_heads) and there is
+ *    no exchange (nz = 1); beyond, a head belongs to nz = world / nkvh ranks, rank r holding KV-length slice z of it.
+ *  - kv_slice: positions [lo, hi) of slice z of nz of a sequence of n positions (boundaries on 64-position tiles).
+ *  - plan_prefill: one chunk of M tokens at pos0: KV-head groups first, then up to two query-token ranges
+ *    [ranges[2i], ranges[2i+1]) per rank (an early and a late block of equal causal cost, whole 128-token tiles);
+ *    each range is one q27b_attn_prefill call at pos0 + ranges[2i]. ranges must hold 4 ints. */
+int q27b_plan_single_sequence(int rank, int world, int nkvh, int* kv_head0, int* n_kv_heads, int* z, int* nz);
+int q27b_kv_slice(int n, int z, int nz, int* lo, int* hi);
+int q27b_plan_prefill(int rank, int world, int M, int pos0, int nkvh, int* kv_head0, int* n_kv_heads, int* ranges,
+                      int* n_ranges);
+
 /* The step after the attention output projection (row f4 of the path's neighbours): x [rows][n] +=
  * the sum over the GPUs of their partial rows, then RMSNorm(x) * w -> h (f32, may be null) and q8_1
  * (xq int8 [rows][n], xd f32 [rows * n / 32] = f32(f16(amax / 127)); xq may be null). Replaces

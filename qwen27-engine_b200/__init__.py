@@ -34,7 +34,7 @@ SYMBOLS = [
     "q27b_xbuf_alloc", "q27b_xbuf_free", "q27b_ipc_export", "q27b_ipc_open", "q27b_ipc_close",
     "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
     "q27b_attn_decode_noalloc", "q27b_attn_decode_ref", "q27b_attn_workspace_query", "q27b_attn_workspace_init",
-    "q27b_attn_workspace_destroy", "q27b_debug_mma_peak", "q27b_xbuf_reset",
+    "q27b_attn_workspace_destroy", "q27b_debug_mma_peak", "q27b_xbuf_reset", "q27b_plan_single_sequence", "q27b_kv_slice", "q27b_plan_prefill",
 ]
 
 

@@ -364,6 +364,96 @@ int q27b_ipc_close(void* p) {
   return Q27B_OK;
 }
 
+// ---- how one sequence / one prefill chunk is shared out over the GPUs of a box (host arithmetic only)
+int q27b_plan_single_sequence(int rank, int world, int nkvh, int* kv_head0, int* n_kv_heads, int* z, int* nz) {
+  if (world < 1 || rank < 0 || rank >= world || nkvh < 1 || !kv_head0 || !n_kv_heads || !z || !nz)
+    return fail(Q27B_BAD_SHAPE, "plan_single_sequence: bad rank / world");
+  if (world <= nkvh) {
+    if (nkvh % world) return fail(Q27B_BAD_SHAPE, "plan_single_sequence: world must divide the KV heads");
+    *n_kv_heads = nkvh / world;
+    *kv_head0 = rank * *n_kv_heads;
+    *z = 0;
+    *nz = 1;
+    return Q27B_OK;
+  }
+  if (world % nkvh) return fail(Q27B_BAD_SHAPE, "plan_single_sequence: world must be a multiple of the KV heads");
+  *nz = world / nkvh;
+  *kv_head0 = rank / *nz;
+  *n_kv_heads = 1;
+  *z = rank % *nz;
+  return Q27B_OK;
+}
+
+int q27b_kv_slice(int n, int z, int nz, int* lo, int* hi) {
+  if (n < 0 || nz < 1 || z < 0 || z >= nz || !lo || !hi) return fail(Q27B_BAD_SHAPE, "kv_slice: bad argument");
+  int per = (n + nz - 1) / nz;
+  per = (per + 63) / 64 * 64;  // slice boundaries are multiples of the 64-position tile
+  *lo = std::min(n, z * per);
+  *hi = std::min(n, *lo + per);
+  return Q27B_OK;
+}
+
+int q27b_plan_prefill(int rank, int world, int M, int pos0, int nkvh, int* kv_head0, int* n_kv_heads, int* ranges,
+                      int* n_ranges) {
+  if (world < 1 || rank < 0 || rank >= world || M < 1 || nkvh < 1 || pos0 < 0 || !kv_head0 || !n_kv_heads || !ranges || !n_ranges)
+    return fail(Q27B_BAD_SHAPE, "plan_prefill: bad rank / world / M");
+  if (world <= nkvh) {
+    if (nkvh % world) return fail(Q27B_BAD_SHAPE, "plan_prefill: world must divide the KV heads");
+    *n_kv_heads = nkvh / world;
+    *kv_head0 = rank * *n_kv_heads;
+    ranges[0] = 0;
+    ranges[1] = M;
+    *n_ranges = 1;
+    return Q27B_OK;
+  }
+  if (world % nkvh) return fail(Q27B_BAD_SHAPE, "plan_prefill: world must be a multiple of the KV heads");
+  const int nq = world / nkvh, s = rank % nq, tiles = (M + 127) / 128, nb = 2 * nq;
+  *kv_head0 = rank / nq;
+  *n_kv_heads = 1;
+  // cost of tile i ~ positions it attends: pos0 + (i + 1) * 128; cuts at equal cumulative cost
+  double total = 0;
+  for (int i = 0; i < tiles; i++) total += pos0 + std::min(M, (i + 1) * 128);
+  std::vector<int> cuts(1, 0);
+  double acc = 0;
+  int k = 1;
+  for (int i = 0; i < tiles; i++) {
+    acc += pos0 + std::min(M, (i + 1) * 128);
+    while (k < nb && acc >= total * k / nb - 1e-9) {
+      cuts.push_back(i + 1);
+      k++;
+    }
+  }
+  while ((int)cuts.size() < nb + 1) cuts.push_back(tiles);
+  cuts[nb] = tiles;
+  auto block = [&](int b, int* a, int* e) {
+    *a = std::min(M, cuts[b] * 128);
+    *e = std::min(M, cuts[b + 1] * 128);
+  };
+  int a0, e0, a1, e1;
+  block(s, &a0, &e0);
+  block(nb - 1 - s, &a1, &e1);
+  if (a1 < a0 || (a1 == a0 && e1 < e0)) {
+    std::swap(a0, a1);
+    std::swap(e0, e1);
+  }
+  int cnt = 0;
+  if (e0 > a0) {
+    ranges[0] = a0;
+    ranges[1] = e0;
+    cnt = 1;
+  }
+  if (e1 > a1) {
+    if (cnt && ranges[1] == a1) ranges[1] = e1;
+    else {
+      ranges[2 * cnt] = a1;
+      ranges[2 * cnt + 1] = e1;
+      cnt++;
+    }
+  }
+  *n_ranges = cnt;
+  return Q27B_OK;
+}
+
 uint64_t q27b_kv_cache_bytes(int nkvh, int n_ctx, int q8) {
   return q8 ? (uint64_t)nkvh * n_ctx * (Q27B_HEAD_DIM + 16) : (uint64_t)nkvh * n_ctx * Q27B_HEAD_DIM * 2;
 }

@@ -224,3 +224,30 @@ def test_exchange_set_up_agrees_on_failures_over_two_gloo_ranks(q27, tmp_path):
     for a, b in zip(r0[1:], r1[1:]):
         assert a[0] == "raised" and b[0] == "raised" and a[1] == b[1]
         assert "injected failure" in a[2] and "rank 1" in a[2] and a[2] == b[2]
+
+
+def test_c_abi_plans_agree_with_the_python_plans(q27):
+    """q27b_plan_single_sequence / q27b_kv_slice / q27b_plan_prefill (host arithmetic behind the C ABI, for C++
+    hosts) give what shard.py gives."""
+    import ctypes
+    from qwen27_engine_b200 import shard
+    lib = ctypes.CDLL(q27.LIB_PATH)
+    i = ctypes.c_int
+    for world in (1, 2, 4, 8, 16):
+        for rank in range(world):
+            h0, nh, z, nz = i(), i(), i(), i()
+            assert lib.q27b_plan_single_sequence(rank, world, 4, ctypes.byref(h0), ctypes.byref(nh), ctypes.byref(z), ctypes.byref(nz)) == 0
+            s = shard.plan_single_sequence(rank, world, 4)
+            assert (h0.value, nh.value, z.value, nz.value) == (s.kv_head0, s.n_kv_heads, s.z, s.nz)
+            for n in (0, 1, 63, 64, 1000, 150000):
+                lo, hi = i(), i()
+                assert lib.q27b_kv_slice(n, s.z, s.nz, ctypes.byref(lo), ctypes.byref(hi)) == 0
+                assert (lo.value, hi.value) == shard.kv_slice(n, s.z, s.nz)
+            for M, pos0 in ((2048, 0), (2048, 32768), (300, 700), (128, 5), (1, 0), (2047, 148000)):
+                rng = (i * 4)()
+                nr = i()
+                assert lib.q27b_plan_prefill(rank, world, M, pos0, 4, ctypes.byref(h0), ctypes.byref(nh), rng, ctypes.byref(nr)) == 0
+                p = shard.plan_prefill(rank, world, M, pos0, 4)
+                assert (h0.value, nh.value) == (p.kv_head0, p.n_kv_heads)
+                assert tuple((rng[2 * k], rng[2 * k + 1]) for k in range(nr.value)) == tuple(p.ranges), (world, rank, M, pos0)
+    assert lib.q27b_plan_single_sequence(0, 3, 4, ctypes.byref(i()), ctypes.byref(i()), ctypes.byref(i()), ctypes.byref(i())) == q27.BAD_SHAPE
