@@ -12,21 +12,28 @@
 // stream (issue slots 39 % busy, DRAM 43 %). Here the two contractions belong to different warps:
 //
 //   warps 0-3, 4-7    "QK" groups 0 and 1: K tile -> S^T -> P (f16) into shared memory, the row
-//                     sums l and the reference maxima m. They own the Q fragments.
+//                     sums l and the reference maxima m.
 //   warps 8-11, 12-15 "PV" groups 0 and 1: V tile and P -> O^T. They own the O accumulators.
 //
-// Group g of either kind takes tiles g, g + 2, ...; QK group g hands its P tiles to PV group g
-// through two P buffers (named barriers: "ready" QK -> PV, "free" PV -> QK). setmaxnreg moves
-// registers from the PV warps (88) to the QK warps (168), so sixteen warps fit where eight did:
-// four warps per scheduler, twice the latency hiding for the same instruction count.
-// K halves and V halves of a ring stage have their own "full" barriers and are refilled by their
-// own consumers (one elected lane each) as soon as the group is provably done with them, so
-// there is no producer warp and no "empty" barrier.
+// QK group g hands its P tiles to PV group g through two P buffers (named barriers: "ready"
+// QK -> PV, "free" PV -> QK). Neither kind of warp needs more than 128 registers (the QK warps read
+// their Q fragments from shared memory instead of holding them), so sixteen warps fit where eight
+// did: four warps per scheduler, twice the latency hiding for the same instruction count.
+// K tiles and V tiles have their own rings (3 and 2 deep per group) with their own "full" barriers
+// and are refilled by their own consumers (one elected lane each) as soon as the group is provably
+// done with a slot, so there is no producer warp and no "empty" barrier.
 //
 // The query block is staged once per CTA: all threads load Q * kq_scale, round it to f16 and put
-// it in shared memory; the QK warps then pick their MMA fragments from there (each of the 8 QK
-// warps needs all 24 x 256 values; loading them from global memory per warp costs 48 16-byte
-// loads per thread before the first MMA).
+// it in shared memory; the QK warps then pick their MMA B fragments from there with two 16-byte
+// loads per (row half, position block) (each of the 8 QK warps needs all 24 x 256 values; holding
+// them costs 96 registers, loading them from global memory per warp 48 16-byte loads per thread
+// before the first MMA).
+//
+// Which tiles a group takes: a CTA owns the first part of its chunk outright (group g the g-th,
+// (g + 2)-th ... tile of it) and, when the launch passes pool counters (p.sched), draws the last
+// eighth or so of every chunk of its KV head from a shared pool with one atomicAdd per tile, one
+// tile ahead of its use; CTAs that started late or run on a slower SM then take fewer tiles and
+// the launch ends evenly. The last CTA to finish resets the counters for the next launch.
 #define Q27B_INLINE_WAITS
 #include "common.cuh"
 #include "decode_params.h"
