@@ -117,6 +117,27 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
   mbar_wait_slow(bar, parity, abort_flag, status);
 }
 
+// The same for a wait that is expected to be long while other warps of the scheduler have work: between
+// polls the warp sleeps, so that it is not eligible and takes no issue slots (a polling warp is always
+// eligible). Costs up to the sleep time in latency.
+static __device__ __forceinline__ void mbar_wait_sleeping(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                          uint32_t sleep_ns = 200) {
+  if (mbar_try_wait(bar, parity)) return;
+  unsigned long long t0 = 0;
+  for (uint32_t i = 1;; i++) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return;
+    if ((i & 63u) == 0) {
+      if (*abort_flag) return;
+      const unsigned long long t = global_ns();
+      if (t0 == 0) t0 = t;
+      else if (i >= (1u << 16) && (long long)(t - t0) > WAIT_LIMIT_NS) break;
+    }
+  }
+  *abort_flag = 1;
+  if (status) atomicOr(status, ST_WAIT_EXPIRED);
+}
+
 // After a wait has given up, a CTA drains to its end without synchronisation. Before it frees
 // tensor memory and exits it gives the copies and MMAs that it issued earlier time to land
 // (microseconds of work; this sleeps 100 us), so that nothing is still writing into shared or
@@ -132,6 +153,10 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
+}
+// The same box into L2 only: a later tma_load_2d of it then costs an L2 hit instead of the DRAM latency.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tmap, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");

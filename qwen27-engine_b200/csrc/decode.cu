@@ -887,6 +887,9 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
   // the longest length, between 1024 and 8192 positions.
   const int64_t total = (int64_t)B * nkvh * max_seq_len;
   int chunk = (int)std::min<int64_t>(8192, std::max<int64_t>(1024, total / (8 * (int64_t)ctx->n_sm)));
+  if (const char* e = getenv("Q27B_PAGED_CHUNK")) {  // tuning: chunk length in positions
+    if (atoi(e) >= Q27B_PAGE) chunk = atoi(e);
+  }
   chunk = (chunk + Q27B_PAGE - 1) / Q27B_PAGE * Q27B_PAGE;
   const int nch = (max_seq_len + chunk - 1) / chunk;
   float* part;
