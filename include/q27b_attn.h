@@ -164,6 +164,49 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
                            const int* page_table, const int* seq_len, float* o, int B, int T, float kq_scale, int nqh,
                            int nkvh, int n_pages, int max_pages, int max_seq_len, void* stream);
 
+/* q27::attn_prep for a batch over the page pool: B sequences, T new tokens each at positions
+ * seq_len[b] - T + t (seq_len counts them). qg [B][T][nqh][512], k / v [B][T][nkvh][256], qn [B][T][nqh][256];
+ * rope3 [B][T][3] or null, rdelta [B] or null. With q_norm == null it only appends K and V (no norm, no
+ * RoPE; qg, k_norm and qn are not used). The rows are written through page_table [B][max_pages] into the
+ * pools of q27b_attn_decode_paged; an entry outside [0, n_pages) sets device status bit 1 and the row is
+ * dropped. Same arithmetic as q27b_attn_prep (src/ops.cu:587-654) row by row. */
+int q27b_attn_prep_paged(const float* qg, const float* k, const float* v, const float* q_norm, const float* k_norm,
+                         float* qn, void* kpool, void* vpool, const int* page_table, const int* seq_len, int B, int T,
+                         float eps, float theta_scale, int nqh, int nkvh, int n_pages, int max_pages, void* stream,
+                         const int* rope3, const int* rdelta);
+
+/* Page bookkeeping for those pools (host only, thread-safe): which pages back which positions of which
+ * sequence. The reference has one contiguous cache per sequence; what its server relies on when it
+ * reuses a prompt prefix is that "KV rows below a position stay valid when the sequence is cut back to it"
+ * (src/model.h:177-180, Engine::prepare src/engine.cpp:228-291): q27b_pager_cut keeps the pages that hold
+ * rows below the new length and returns the others to the pool.
+ *  - create: a pool of n_pages pages, at most max_seqs sequences of at most max_pages_per_seq pages.
+ *  - open: a new empty sequence. extend: back positions below new_len (>= the current length) with pages;
+ *    Q27B_UNSUPPORTED, and nothing changed, when the pool has too few free pages. close: all pages back.
+ *  - fork: a new sequence that starts as the first prefix_len positions of `seq`: the full pages of the
+ *    prefix are shared (reference counts, no copy); if the prefix ends inside a page the new sequence gets a
+ *    page of its own for it and the call returns the pair to copy (q27b_kv_page_copy, K and V pools), else -1.
+ *    Only sequences whose last page is full or not shared can be extended; unshare gives a sequence whose
+ *    partly filled last page is shared (after a fork at a page boundary and a cut, say) a page of its own
+ *    and returns the pair to copy, or -1 when there was nothing to do.
+ *  - tables: page_table [B][max_pages_per_seq] (-1 where no page) and seq_len [B] of the given sequences,
+ *    into host memory, in the form the device operators read. */
+typedef struct q27b_pager q27b_pager;
+int q27b_pager_create(int n_pages, int max_seqs, int max_pages_per_seq, q27b_pager** out);
+void q27b_pager_destroy(q27b_pager* pager);
+int q27b_pager_open(q27b_pager* pager, int* seq);
+int q27b_pager_extend(q27b_pager* pager, int seq, int new_len);
+int q27b_pager_cut(q27b_pager* pager, int seq, int new_len);
+int q27b_pager_close(q27b_pager* pager, int seq);
+int q27b_pager_fork(q27b_pager* pager, int seq, int prefix_len, int* new_seq, int* copy_src_page, int* copy_dst_page,
+                    int* copy_rows);
+int q27b_pager_unshare(q27b_pager* pager, int seq, int* copy_src_page, int* copy_dst_page, int* copy_rows);
+int q27b_pager_free_pages(q27b_pager* pager); /* -1: null */
+int q27b_pager_len(q27b_pager* pager, int seq); /* -1: no such sequence */
+int q27b_pager_tables(q27b_pager* pager, const int* seqs, int B, int* page_table, int* seq_len);
+/* The first `rows` rows of page src_page into page dst_page, all heads, of one pool (K or V). */
+int q27b_kv_page_copy(void* pool, int src_page, int dst_page, int rows, int nkvh, int n_pages, void* stream);
+
 /* One sequence split by KV length over the nz GPUs of a head group, exchanged over peer memory
  * instead of a collective. Every rank owns an exchange buffer of q27b_xbuf_bytes(nz, T * nqh) bytes,
  * zeroed once, that its peers can store into (peer-mapped device memory; how it is mapped is the

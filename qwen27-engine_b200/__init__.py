@@ -35,6 +35,9 @@ SYMBOLS = [
     "q27b_kv_wire_bytes", "q27b_kv_pages_to_wire", "q27b_kv_wire_to_pages", "q27b_kv_cache_to_wire", "q27b_kv_wire_to_cache",
     "q27b_attn_decode_noalloc", "q27b_attn_decode_ref", "q27b_attn_workspace_query", "q27b_attn_workspace_init",
     "q27b_attn_workspace_destroy", "q27b_debug_mma_peak", "q27b_xbuf_reset", "q27b_plan_single_sequence", "q27b_kv_slice", "q27b_plan_prefill",
+    "q27b_attn_prep_paged", "q27b_pager_create", "q27b_pager_destroy", "q27b_pager_open", "q27b_pager_extend",
+    "q27b_pager_cut", "q27b_pager_close", "q27b_pager_fork", "q27b_pager_free_pages", "q27b_pager_len",
+    "q27b_pager_tables", "q27b_kv_page_copy", "q27b_pager_unshare",
 ]
 
 
@@ -49,6 +52,8 @@ def _load():
     lib.q27b_kv_wire_bytes.restype = ctypes.c_uint64
     lib.q27b_xbuf_bytes.restype = ctypes.c_uint64
     lib.q27b_sum_xbuf_bytes.restype = ctypes.c_uint64
+    lib.q27b_pager_destroy.restype = None
+    lib.q27b_pager_destroy.argtypes = [ctypes.c_void_p]
     return lib
 
 
@@ -369,6 +374,79 @@ def attn_decode_paged(qn, qg, kpool, vpool, page_table, seq_len, o, B, T, kq_sca
                                        _ptr(page_table, torch.int32), _ptr(seq_len, torch.int32),
                                        _ptr(o, torch.float32), int(B), int(T), _f(kq_scale), int(nqh), int(nkvh),
                                        int(n_pages), int(max_pages), int(max_seq_len), _stream()))
+
+
+def attn_prep_paged(qg, k, v, q_norm, k_norm, qn, kpool, vpool, page_table, seq_len, B, T, eps, theta_scale, nqh, nkvh,
+                    n_pages, max_pages, rope3=None, rdelta=None):
+    """q27::attn_prep for B sequences over the page pool; with q_norm None it only appends K and V."""
+    _check(_lib.q27b_attn_prep_paged(_ptr(qg, torch.float32, True), _ptr(k, torch.float32), _ptr(v, torch.float32),
+                                     _ptr(q_norm, torch.float32, True), _ptr(k_norm, torch.float32, True),
+                                     _ptr(qn, torch.float32, True), _ptr(kpool), _ptr(vpool),
+                                     _ptr(page_table, torch.int32), _ptr(seq_len, torch.int32), int(B), int(T),
+                                     _f(eps), _f(theta_scale), int(nqh), int(nkvh), int(n_pages), int(max_pages),
+                                     _stream(), _ptr(rope3, torch.int32, True), _ptr(rdelta, torch.int32, True)))
+
+
+def kv_page_copy(pool, src_page, dst_page, rows, nkvh, n_pages):
+    """The first `rows` rows of one page into another, all heads, of one pool."""
+    _check(_lib.q27b_kv_page_copy(_ptr(pool), int(src_page), int(dst_page), int(rows), int(nkvh), int(n_pages), _stream()))
+
+
+class Pager:
+    """Page bookkeeping of the paged cache (q27b_pager_*): host only, no device memory."""
+
+    def __init__(self, n_pages, max_seqs, max_pages_per_seq):
+        self._h = ctypes.c_void_p()
+        self.n_pages, self.max_seqs, self.max_pages = int(n_pages), int(max_seqs), int(max_pages_per_seq)
+        _check(_lib.q27b_pager_create(self.n_pages, self.max_seqs, self.max_pages, ctypes.byref(self._h)))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            _lib.q27b_pager_destroy(self._h)
+            self._h = None
+
+    def open(self):
+        s = ctypes.c_int()
+        _check(_lib.q27b_pager_open(self._h, ctypes.byref(s)))
+        return s.value
+
+    def extend(self, seq, new_len):
+        _check(_lib.q27b_pager_extend(self._h, int(seq), int(new_len)))
+
+    def cut(self, seq, new_len):
+        _check(_lib.q27b_pager_cut(self._h, int(seq), int(new_len)))
+
+    def close(self, seq):
+        _check(_lib.q27b_pager_close(self._h, int(seq)))
+
+    def fork(self, seq, prefix_len):
+        """-> (new sequence, (src page, dst page, rows) to copy in both pools, or None)."""
+        s, a, b, r = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        _check(_lib.q27b_pager_fork(self._h, int(seq), int(prefix_len), ctypes.byref(s), ctypes.byref(a), ctypes.byref(b),
+                                    ctypes.byref(r)))
+        return s.value, ((a.value, b.value, r.value) if r.value else None)
+
+    def unshare(self, seq):
+        """Gives the sequence its own copy of a shared, partly filled last page -> (src, dst, rows) to copy, or None."""
+        a, b, r = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        _check(_lib.q27b_pager_unshare(self._h, int(seq), ctypes.byref(a), ctypes.byref(b), ctypes.byref(r)))
+        return (a.value, b.value, r.value) if r.value else None
+
+    def free_pages(self):
+        return int(_lib.q27b_pager_free_pages(self._h))
+
+    def length(self, seq):
+        return int(_lib.q27b_pager_len(self._h, int(seq)))
+
+    def tables(self, seqs):
+        """-> (page_table int32 [B][max_pages], seq_len int32 [B]) as numpy arrays."""
+        import numpy as np
+        ids = (ctypes.c_int * len(seqs))(*[int(x) for x in seqs])
+        table = np.empty((len(seqs), self.max_pages), np.int32)
+        lens = np.empty((len(seqs),), np.int32)
+        _check(_lib.q27b_pager_tables(self._h, ids, len(seqs), table.ctypes.data_as(ctypes.c_void_p),
+                                      lens.ctypes.data_as(ctypes.c_void_p)))
+        return table, lens
 
 
 def attn_prefill(qn, qg, kcache, vcache, o, pos0, M, kq_scale, nqh, nkvh, n_ctx, q8=True, depth_hint=-1):

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libq27b_attn.so")
-SOURCES = ["host.cu", "kv_append.cu", "kv_wire.cu", "combine.cu", "decode.cu", "decode_tc.cu", "decode_ws.cu", "decode_wt.cu", "decode_ref.cu", "prefill.cu", "prefill_f16.cu", "sum_norm.cu", "peak_mma.cu"]
+SOURCES = ["host.cu", "kv_append.cu", "kv_wire.cu", "combine.cu", "decode.cu", "decode_tc.cu", "decode_ws.cu", "decode_wt.cu", "decode_ref.cu", "prefill.cu", "prefill_f16.cu", "sum_norm.cu", "peak_mma.cu", "pager.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr"]

@@ -27,6 +27,12 @@ struct PrepParams {
   const int* rdelta;  // or null
   int T, nqh, nkvh, n_ctx, q8;
   float eps, theta_scale;
+  // Batched form over a page pool (page_table != null): B sequences, T new tokens each at positions
+  // seq_len[b] - T + t; qg, k, v, qn carry a leading [B]; rope3 is [B][T][3], rdelta [B].
+  const int* page_table;  // [B][max_pages]
+  const int* seq_len;     // [B], the new tokens included
+  int B, max_pages, n_pages;
+  int* status;
 };
 
 __device__ __forceinline__ float warp_sum(float x) {
@@ -53,9 +59,9 @@ __device__ __forceinline__ uint32_t quant4(const float (&x)[4], float& d_out) {
   return w;
 }
 
-// Writes one row (two float4 halves per lane) to the cache at `row`.
+// Writes one row (two float4 halves per lane) to row `row` of a cache (or page pool) of `rows` rows.
 __device__ __forceinline__ void store_row(const float (&a)[4], const float (&b)[4], void* cache, size_t row, int lane,
-                                          int nkvh, int n_ctx, bool q8) {
+                                          size_t rows, bool q8) {
   if (!q8) {
     __half2* dst = (__half2*)((__half*)cache + row * AD);
     dst[2 * lane] = __floats2half2_rn(a[0], a[1]);
@@ -70,7 +76,7 @@ __device__ __forceinline__ void store_row(const float (&a)[4], const float (&b)[
   vals[lane] = wa;
   vals[32 + lane] = wb;
   if ((lane & 7) == 0) {
-    __half* sc = (__half*)((uint8_t*)cache + (size_t)nkvh * n_ctx * AD) + row * 8;
+    __half* sc = (__half*)((uint8_t*)cache + rows * AD) + row * 8;
     sc[lane >> 3] = __float2half_rn(da);
     sc[4 + (lane >> 3)] = __float2half_rn(db);
   }
@@ -85,10 +91,12 @@ __global__ void __launch_bounds__(256) prep_kernel(const PrepParams p) {
   const bool norm = p.q_norm != nullptr;
   const int per_tok = (norm ? p.nqh : 0) + 2 * p.nkvh;
   const int job = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (job >= p.T * per_tok) return;
-  const int tok = job / per_tok;
+  const bool paged = p.page_table != nullptr;
+  if (job >= (paged ? p.B : 1) * p.T * per_tok) return;
+  const int tok = job / per_tok;  // with pages: sequence * T + token
   int r = job % per_tok;
-  const int pos = *p.pos0 + tok;
+  const int seq = paged ? tok / p.T : 0;
+  const int pos = paged ? p.seq_len[seq] - p.T + tok % p.T : *p.pos0 + tok;
   if (pos < 0 || pos >= p.n_ctx) return;  // never write outside the cache
   const bool isq = norm && r < p.nqh;
   if (norm && !isq) r -= p.nqh;
@@ -120,7 +128,7 @@ __global__ void __launch_bounds__(256) prep_kernel(const PrepParams p) {
 #pragma unroll
     for (int i = 0; i < 4; i++) other[i] = __shfl_xor_sync(0xffffffffu, a[i], 8);
     if (lane < 16) {
-      const int rp_text = pos - (p.rdelta ? *p.rdelta : 0);
+      const int rp_text = pos - (p.rdelta ? p.rdelta[seq] : 0);
 #pragma unroll
       for (int i = 0; i < 4; i++) {
         const int j = (4 * lane + i) & 31;
@@ -138,12 +146,22 @@ __global__ void __launch_bounds__(256) prep_kernel(const PrepParams p) {
     *(float4*)(dst + 128 + 4 * lane) = make_float4(b[0], b[1], b[2], b[3]);
     return;
   }
-  store_row(a, b, isv ? p.vcache : p.kcache, (size_t)head * p.n_ctx + pos, lane, p.nkvh, p.n_ctx, p.q8 != 0);
+  if (!paged) {
+    store_row(a, b, isv ? p.vcache : p.kcache, (size_t)head * p.n_ctx + pos, lane, (size_t)p.nkvh * p.n_ctx, p.q8 != 0);
+    return;
+  }
+  const int pg = p.page_table[(size_t)seq * p.max_pages + pos / Q27B_PAGE];
+  if (pg < 0 || pg >= p.n_pages) {  // never write outside the pool: flag it and drop the row
+    if (lane == 0) atomicOr(p.status, ST_BAD_PAGE);
+    return;
+  }
+  store_row(a, b, isv ? p.vcache : p.kcache, ((size_t)pg * p.nkvh + head) * Q27B_PAGE + pos % Q27B_PAGE, lane,
+            (size_t)p.n_pages * p.nkvh * Q27B_PAGE, true);
 }
 
 int launch_prep(const PrepParams& p, cudaStream_t s) {
   const int per_tok = (p.q_norm ? p.nqh : 0) + 2 * p.nkvh;
-  const int jobs = p.T * per_tok;
+  const int jobs = (p.page_table ? p.B : 1) * p.T * per_tok;
   prep_kernel<<<(jobs + 7) / 8, 256, 0, s>>>(p);
   Q27B_CK(cudaGetLastError());
   return Q27B_OK;
@@ -180,6 +198,27 @@ int q27b_attn_prep(const float* qg, const float* k, const float* v, const float*
   p.qg = qg; p.k = k; p.v = v; p.q_norm = q_norm; p.k_norm = k_norm; p.qn = qn;
   p.kcache = kcache; p.vcache = vcache; p.pos0 = pos0; p.rope3 = rope3; p.rdelta = rdelta;
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = n_ctx; p.q8 = q8; p.eps = eps; p.theta_scale = theta_scale;
+  return launch_prep(p, (cudaStream_t)stream);
+}
+
+int q27b_attn_prep_paged(const float* qg, const float* k, const float* v, const float* q_norm, const float* k_norm,
+                         float* qn, void* kpool, void* vpool, const int* page_table, const int* seq_len, int B, int T,
+                         float eps, float theta_scale, int nqh, int nkvh, int n_pages, int max_pages, void* stream,
+                         const int* rope3, const int* rdelta) {
+  const bool norm = q_norm != nullptr;
+  if (!k || !v || !kpool || !vpool || !page_table || !seq_len || (norm && (!qg || !k_norm || !qn)))
+    return fail(Q27B_BAD_SHAPE, "attn_prep_paged: null pointer");
+  if (B < 1 || T < 1 || nkvh < 1 || n_pages < 1 || max_pages < 1 || (norm && nqh < 1) ||
+      (int64_t)B * T * (nqh + 2 * nkvh) > (int64_t)1 << 30)
+    return fail(Q27B_BAD_SHAPE, "attn_prep_paged: bad shape");
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  PrepParams p = {};
+  p.qg = qg; p.k = k; p.v = v; p.q_norm = q_norm; p.k_norm = norm ? k_norm : nullptr; p.qn = qn;
+  p.kcache = kpool; p.vcache = vpool; p.rope3 = rope3; p.rdelta = rdelta;
+  p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = max_pages * Q27B_PAGE; p.q8 = 1; p.eps = eps; p.theta_scale = theta_scale;
+  p.page_table = page_table; p.seq_len = seq_len; p.B = B; p.max_pages = max_pages; p.n_pages = n_pages;
+  p.status = ctx->status;
   return launch_prep(p, (cudaStream_t)stream);
 }
 
