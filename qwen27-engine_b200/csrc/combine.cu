@@ -6,12 +6,15 @@
 // the result does not depend on scheduling. One CTA per output row, one thread per dim; the
 // factors e^(m_c - M) are computed once per CTA into shared memory, then every thread streams
 // its column of the partials with independent loads. With many partials (one KV head per GPU puts all
-// SMs of the GPU on that head: 148 partials per row, and only 24 rows) the CTA has four thread groups
-// that each take a quarter of the partials and are added up in group order at the end. Built without fast-math: the q8_1 epilogue
+// SMs of the GPU on that head: 148 partials per row, and only 24 rows) a row is shared out over several
+// CTAs by columns and over thread groups by partials (merge_wide_kernel); where that would be more than one
+// wave of CTAs, one CTA of four thread groups that each take a quarter of the partials. Built without fast-math: the q8_1 epilogue
 // (q8_store, src/common.cuh:72-81) is specified in IEEE operations.
 #include "combine.h"
 
 #include "common.cuh"
+
+#include <cstdlib>
 
 namespace q27b {
 namespace {
@@ -201,6 +204,134 @@ __global__ void __launch_bounds__(AD * NGRP) merge_kernel(const MergeParams p) {
   if (lane == 0) p.xd[oi / 32] = __half2float(__float2half_rn(dd));
 }
 
+// Many partials per row (one or two KV heads on a whole GPU: 148 or 74 partials per row and few rows): a row is
+// shared out over WIDE_SLICES CTAs (4 of 64 dims, or 2 of 128), and inside a CTA of 1024 threads over
+// WIDE_GROUPS thread groups (16 or 8) that take every WIDE_GROUPS-th partial: a thread then has at most ten
+// loads, all in flight at once, where one CTA per row walks a chain of 37 per thread with a sixth of the SMs.
+// Sums are taken in a fixed order (a group's partials in index order, then the groups in order).
+constexpr int WIDE_PRE = 10;
+
+template <bool DECODE_LAYOUT, int WIDE_SLICES>
+__global__ void __launch_bounds__(1024) merge_wide_kernel(const MergeParams p) {
+  constexpr int WIDE_COLS = AD / WIDE_SLICES, WIDE_GROUPS = 1024 / WIDE_COLS;
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float sf[MAX_PARTS];
+  __shared__ float sred[32];
+  __shared__ float sgl[WIDE_GROUPS], sga[WIDE_GROUPS - 1][WIDE_COLS];
+  const int64_t row = blockIdx.x;
+  const int slice = blockIdx.y;
+  constexpr int nthr = WIDE_COLS * WIDE_GROUPS;
+  const int tid = threadIdx.x, grp = tid / WIDE_COLS, dl = tid % WIDE_COLS, d = slice * WIDE_COLS + dl;
+  const int lane = tid & 31, warp = tid >> 5;
+  const RowMap rm = DECODE_LAYOUT ? map_decode(p, row) : map_generic(p, row);
+  int np = p.nparts;
+  int epoch = 0;
+  if (p.push_n > 0) epoch = *(volatile int*)p.xbuf;
+  if (DECODE_LAYOUT && p.seq_len) {
+    const int64_t seq = row / ((int64_t)p.nqh * p.T);
+    np = min(np, max(1, (p.seq_len[seq] + p.chunk_len - 1) / p.chunk_len));
+  }
+  // this thread's partials grp, grp + WIDE_GROUPS, ...: the first WIDE_PRE are requested before the maxima
+  const float* col = rm.first + 2 + d;
+  float av[WIDE_PRE], lv[WIDE_PRE];
+#pragma unroll
+  for (int k = 0; k < WIDE_PRE; k++) {
+    const int c = grp + k * WIDE_GROUPS;
+    if (c < np) {
+      av[k] = col[(size_t)c * rm.stride];
+      lv[k] = rm.first[(size_t)c * rm.stride + 1];
+    }
+  }
+  const float gate = rm.gate ? rm.gate[d] : 0.f;
+
+  float mx = M_INIT;
+  for (int c = tid; c < np; c += nthr) mx = fmaxf(mx, rm.first[c * rm.stride]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) sred[warp] = mx;
+  __syncthreads();
+  float M = sred[0];
+#pragma unroll
+  for (int i = 1; i < nthr / 32; i++) M = fmaxf(M, sred[i]);
+  for (int c = tid; c < np; c += nthr) sf[c] = expf(rm.first[c * rm.stride] - M);
+  __syncthreads();
+
+  float L = 0.f, A = 0.f;
+#pragma unroll
+  for (int k = 0; k < WIDE_PRE; k++) {
+    const int c = grp + k * WIDE_GROUPS;
+    if (c < np) {
+      const float f = sf[c];
+      L += lv[k] * f;
+      A += av[k] * f;
+    }
+  }
+  for (int c = grp + WIDE_PRE * WIDE_GROUPS; c < np; c += WIDE_GROUPS) {
+    const float f = sf[c];
+    L += rm.first[c * rm.stride + 1] * f;
+    A += col[c * rm.stride] * f;
+  }
+  if (grp > 0) {
+    sga[grp - 1][dl] = A;
+    if (dl == 0) sgl[grp] = L;
+  }
+  __syncthreads();
+  const bool lead = grp == 0;
+  if (lead)
+#pragma unroll
+    for (int k = 1; k < WIDE_GROUPS; k++) {
+      A += sga[k - 1][dl];
+      L += sgl[k];
+    }
+
+  if (p.push_n > 0) {  // merged, not normalised, into slot push_z of every rank's exchange buffer
+    for (int k = 0; lead && k < p.push_n; k++) {
+      float* po = (float*)((uint8_t*)p.push_buf[k] + XBUF_HEADER_BYTES) +
+                  (((size_t)(epoch & 1) * p.push_n + p.push_z) * p.rows + row) * PROW;
+      po[2 + d] = A;
+      if (d == 0) {
+        po[0] = M;
+        po[1] = L;
+      }
+    }
+    __threadfence_system();  // the rows are visible to the peers before the flag below can be
+    __syncthreads();
+    if (tid == 0 && atomicAdd(p.xbuf + 1, 1) == (int)p.rows * WIDE_SLICES - 1) {
+      p.xbuf[1] = 0;
+      __threadfence_system();
+      for (int k = 0; k < p.push_n; k++) {
+        int* flag = (int*)p.push_buf[k] + 16 + p.push_z;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch + 1) : "memory");
+      }
+    }
+    return;
+  }
+  if (!lead) return;
+  if (p.part_out) {  // merged but not normalised: (M, L, A) for a later merge
+    float* po = p.part_out + (size_t)row * PROW;
+    po[2 + d] = A;
+    if (d == 0) {
+      po[0] = M;
+      po[1] = L;
+    }
+    return;
+  }
+  const size_t oi = (size_t)row * AD + d;
+  float y = A / L;
+  if (rm.gate) y *= 1.0f / (1.0f + expf(-gate));
+  if (!p.xq) {
+    p.o[oi] = y;
+    return;
+  }
+  float amax = fabsf(y);  // a warp of the leading group is one q8_1 block of 32 dims
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float dd = __fdiv_rn(amax, 127.0f);
+  p.xq[oi] = amax == 0.0f ? (int8_t)0 : (int8_t)roundf(__fdiv_rn(y, dd));
+  if (lane == 0) p.xd[oi / 32] = __half2float(__float2half_rn(dd));
+}
+
 }  // namespace
 
 int launch_merge(const MergeParams& p, bool decode_layout, cudaStream_t s) {
@@ -211,6 +342,21 @@ int launch_merge(const MergeParams& p, bool decode_layout, cudaStream_t s) {
   // four thread groups once a row has more partials than a 4-head decode call gives it (37 on 148 SMs)
   // (the waiting merge of an exchange has at most 8 partials; the pushing one is a decode-layout merge)
   const bool wide = p.wait_n == 0 && p.nparts > 64;
+  static const bool sliced = [] {  // Q27B_MERGE_SLICED=0: the one-CTA-per-row form for every shape
+    const char* e = getenv("Q27B_MERGE_SLICED");
+    return !(e && e[0] == '0');
+  }();
+  // as many slices as keep the CTAs (1024 threads) within one wave of a B200's 148 SMs (with the 96 rows of a
+  // 4-head call two slices were measured 3 us slower than one CTA per row, four 6 us)
+  const int slices = !(wide && sliced) ? 1 : (p.rows * 4 <= 160 ? 4 : (p.rows * 2 <= 160 ? 2 : 1));
+  if (slices > 1) {
+    const dim3 wgrid((unsigned)p.rows, slices);
+    if (decode_layout && slices == 4) Q27B_CK(launch_pdl(merge_wide_kernel<true, 4>, wgrid, dim3(1024), 0, s, p));
+    else if (decode_layout) Q27B_CK(launch_pdl(merge_wide_kernel<true, 2>, wgrid, dim3(1024), 0, s, p));
+    else if (slices == 4) Q27B_CK(launch_pdl(merge_wide_kernel<false, 4>, wgrid, dim3(1024), 0, s, p));
+    else Q27B_CK(launch_pdl(merge_wide_kernel<false, 2>, wgrid, dim3(1024), 0, s, p));
+    return Q27B_OK;
+  }
   if (decode_layout && xchg && wide) Q27B_CK(launch_pdl(merge_kernel<true, true, MAX_GROUPS>, grid, dim3(AD * MAX_GROUPS), 0, s, p));
   else if (decode_layout && xchg) Q27B_CK(launch_pdl(merge_kernel<true, true, 1>, grid, dim3(AD), 0, s, p));
   else if (decode_layout && wide) Q27B_CK(launch_pdl(merge_kernel<true, false, MAX_GROUPS>, grid, dim3(AD * MAX_GROUPS), 0, s, p));
