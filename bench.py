@@ -120,8 +120,8 @@ def graph_us(fn, calls=20, replays=5):
     with torch.cuda.graph(g):
         for i in range(calls):
             fn(i)
+    cool_down()
     g.replay()
-    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(replays):
@@ -720,7 +720,9 @@ def batched_paged(q, rank, world, dist=None):
 
     def step(i):
         q.attn_decode_paged(qn, qg, kpool, vpool, d_table, d_len, o, B, T, SCALE, NQH, NKVH, n_pages, max_pages, max(lens))
+    cool_down(1.0)
     ms_e = time_steps(step, 10, 3, dist)
+    cool_down(1.0)
     ms = time_graph_steps(step, 20, 3, dist, calls=5)
     assert q.device_status() == 0, "a kernel reported a device-side problem"
     total = float(sum(2.0 * NKVH * int(n) * 272 for n in lengths))
