@@ -635,10 +635,10 @@ int kernel_choice() {
 }
 // Launches the split-K kernel chosen for a q8_0 cache.
 int launch_q8(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
-              const DecodeParams& p, bool paged, int nseq, cudaStream_t s) {
+              const DecodeParams& p, bool paged, int nseq, cudaStream_t s, bool single_group = false) {
   const int k = kernel_choice();
   if (k == 2) return launch_decode_tc(kv, ks, vv, vs, p, paged, nseq, s);
-  if (k == 0 || k == 3) return launch_decode_ws(kv, ks, vv, vs, p, paged, nseq, s);
+  if (k == 0 || k == 3) return launch_decode_ws(kv, ks, vv, vs, p, paged, nseq, s, single_group);
   if (k == 4) return launch_decode_wt(kv, ks, vv, vs, p, paged, nseq, s);
   return paged ? launch_decode_t<true, true>(kv, ks, vv, vs, p, nseq, s) : launch_decode_t<false, true>(kv, ks, vv, vs, p, nseq, s);
 }
@@ -887,6 +887,16 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
   // the longest length, between 1024 and 8192 positions.
   const int64_t total = (int64_t)B * nkvh * max_seq_len;
   int chunk = (int)std::min<int64_t>(8192, std::max<int64_t>(1024, total / (8 * (int64_t)ctx->n_sm)));
+  // The default kernel runs a batch as CTAs of one tile group, two per SM (the prologue and epilogue of one
+  // overlap the streaming of the other), each with half the positions (Q27B_PAGED_GROUPS=2: one CTA of two
+  // groups per SM, as for a single sequence).
+  static const bool two_groups = [] {
+    const char* e = getenv("Q27B_PAGED_GROUPS");
+    return e && e[0] == '2';
+  }();
+  const int kc = kernel_choice();
+  const bool single_group = (kc == 0 || kc == 3) && !two_groups;
+  if (single_group) chunk = std::max(1024, chunk / 2);
   if (const char* e = getenv("Q27B_PAGED_CHUNK")) {  // tuning: chunk length in positions
     if (atoi(e) >= Q27B_PAGE) chunk = atoi(e);
   }
@@ -905,7 +915,7 @@ int q27b_attn_decode_paged(const float* qn, const float* qg, const void* kpool, 
   p.T = T; p.nqh = nqh; p.nkvh = nkvh; p.n_ctx = max_pages * Q27B_PAGE; p.nch = nch; p.kq_scale = kq_scale;
   p.base_pos = 0; p.n_local = -1;
   p.page_table = page_table; p.seq_len = seq_len; p.max_pages = max_pages; p.n_pages = n_pages; p.chunk_len = chunk;
-  if (int rc = launch_q8(kv, ks, vv, vs, p, true, B, (cudaStream_t)stream)) return rc;
+  if (int rc = launch_q8(kv, ks, vv, vs, p, true, B, (cudaStream_t)stream, single_group)) return rc;
   MergeParams mp = {};
   mp.part = part; mp.nparts = nch; mp.rows = (int64_t)B * T * nqh; mp.qg = qg; mp.o = o; mp.T = T; mp.nqh = nqh;
   mp.seq_len = seq_len; mp.chunk_len = chunk;

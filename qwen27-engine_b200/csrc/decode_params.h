@@ -31,8 +31,9 @@ int launch_decode_tc(const CUtensorMap* kv, const CUtensorMap* ks, const CUtenso
                      const DecodeParams& p, bool paged, int nseq, cudaStream_t s);
 
 // The warp-specialised split-K kernel (decode_ws.cu): same grid, partial layout and tensor maps again.
+// single_group (paged launches only): CTAs of 8 warps and one tile group, two per SM, instead of 16 warps and two.
 int launch_decode_ws(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
-                     const DecodeParams& p, bool paged, int nseq, cudaStream_t s);
+                     const DecodeParams& p, bool paged, int nseq, cudaStream_t s, bool single_group = false);
 // The same with the P V contraction on tcgen05 (decode_wt.cu).
 int launch_decode_wt(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
                      const DecodeParams& p, bool paged, int nseq, cudaStream_t s);

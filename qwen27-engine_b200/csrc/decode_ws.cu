@@ -34,6 +34,13 @@
 // eighth or so of every chunk of its KV head from a shared pool with one atomicAdd per tile, one
 // tile ahead of its use; CTAs that started late or run on a slower SM then take fewer tiles and
 // the launch ends evenly. The last CTA to finish resets the counters for the next launch.
+//
+// The batched decode over pages launches many short CTAs (a chunk of a sequence each, several waves). There
+// the kernel runs with ONE tile group per CTA (template parameter NG = 1: 8 warps, half the rings, 109 KB of
+// shared memory), two CTAs per SM: the prologue and epilogue of one CTA then overlap the streaming of the
+// other, which a single CTA per SM cannot do, and the tail of the launch is half as coarse (config 5 of the
+// metric: 2.10 -> 1.95 ms). For a single sequence (one wave of CTAs that start together) the same form was
+// measured slower: 296 partials instead of 148 cost the merge more than the split-K kernel gains.
 #define Q27B_INLINE_WAITS
 #include "common.cuh"
 #include "decode_params.h"
@@ -50,34 +57,42 @@ constexpr int SC_BYTES = TILE * 16;               // f16 scales of a tile (8 per
 constexpr int HALF_BYTES = VAL_BYTES + SC_BYTES;  // one K (or V) tile with its scales: 17408 = 17 * 1024
 constexpr int VDEPTH = 2;                         // V tiles in flight per group
 constexpr int KDEPTH = 3;                         // K tiles in flight per group
-constexpr int OFF_KRING = 0;                      // [KDEPTH][2 groups] K tiles
-constexpr int OFF_VRING = 2 * KDEPTH * HALF_BYTES;  // [VDEPTH][2 groups] V tiles
-constexpr int RING_BYTES = 2 * (KDEPTH + VDEPTH) * HALF_BYTES;
 constexpr int OFF_SC = VAL_BYTES;                 // scales inside a tile buffer
 constexpr int P_STRIDE = 36;                      // words per P row (32 position pairs + 4 padding: no bank conflicts)
 constexpr int P_WORDS = MAXR * P_STRIDE;
 constexpr int Q_STRIDE = 2 * AD + 16;             // bytes per staged Q row (f16; 16 bytes of padding: conflict-free 16-byte reads)
-constexpr int OFF_Q = RING_BYTES;                 // the staged Q block [24][Q_STRIDE], kept for the whole kernel
-constexpr int OFF_P = OFF_Q + MAXR * Q_STRIDE;    // [2 groups][2 buffers][24][36] words
-constexpr int OFF_MAX = OFF_P + 2 * 2 * P_WORDS * 4;  // [2 groups][2 buffers][4 warps][24] floats
-constexpr int OFF_F = OFF_MAX + 2 * 2 * 4 * MAXR * 4; // [2 groups][2 buffers][24] floats: rescale factors for the PV group
-constexpr int OFF_L = OFF_F + 2 * 2 * MAXR * 4;       // [2 groups][4 warps][24] floats: row sums at the end
-constexpr int OFF_M1 = OFF_L + 2 * 4 * MAXR * 4;      // [2 groups][24] floats: reference maxima at the end
-constexpr int OFF_BAR = OFF_M1 + 2 * MAXR * 4;        // fullK[2 * KDEPTH], fullV[2 * VDEPTH]
-constexpr int OFF_FLAG = OFF_BAR + 2 * (KDEPTH + VDEPTH) * 8;
-constexpr int OFF_TOK = OFF_FLAG + 16;                // [2 groups][2 buffers] words: "move the maxima" tokens (QK warps)
-constexpr int OFF_RTOK = OFF_TOK + 16;                // [2 groups][2 buffers] words: "rescale O" tokens (QK -> PV)
-constexpr int OFF_SEQ = OFF_RTOK + 16;                // [2 groups][8] ints: the groups' tile queues
-constexpr int SMEM_USED = OFF_SEQ + 64;
-constexpr int SCHED_DONE = 32;                        // p.sched: [KV head] pool counters, [32] CTAs that are done
-constexpr int WS_SMEM_BYTES = SMEM_USED + 1024;       // slack for the 1024-byte alignment of the ring
-constexpr float TAU = 8.0f;                           // a score may exceed the reference max by this much
-constexpr int O_STRIDE = AD + 4;                      // floats per row of the end-of-kernel O exchange
-static_assert(OFF_Q != OFF_P || MAXR * Q_STRIDE <= 2 * 2 * P_WORDS * 4, "the staged Q block must fit in the P buffers");
-static_assert(MAXR * O_STRIDE * 4 <= RING_BYTES, "O exchange must fit in the ring");
-static_assert(WS_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+constexpr int SCHED_DONE = 32;                    // p.sched: [KV head] pool counters, [32] CTAs that are done
+constexpr float TAU = 8.0f;                       // a score may exceed the reference max by this much
+constexpr int O_STRIDE = AD + 4;                  // floats per row of the end-of-kernel O exchange
 
-constexpr int WS_THREADS = 512;
+// Shared memory map of a CTA with NG tile groups (offsets from a 1024-byte aligned base). NG = 2: the
+// default, one CTA of 16 warps per SM. NG = 1: 8 warps and half the rings, two CTAs per SM, for launches of
+// many short CTAs (the batched decode over pages), where one CTA's prologue and epilogue then overlap the
+// other's streaming.
+template <int NG>
+struct Lay {
+  static constexpr int THREADS = 256 * NG;
+  static constexpr int OFF_KRING = 0;                                // [KDEPTH][NG groups] K tiles
+  static constexpr int OFF_VRING = NG * KDEPTH * HALF_BYTES;         // [VDEPTH][NG groups] V tiles
+  static constexpr int RING_BYTES = NG * (KDEPTH + VDEPTH) * HALF_BYTES;
+  static constexpr int OFF_Q = RING_BYTES;                           // the staged Q block [24][Q_STRIDE], kept for the whole kernel
+  static constexpr int OFF_P = OFF_Q + MAXR * Q_STRIDE;              // [NG groups][2 buffers][24][36] words
+  static constexpr int OFF_MAX = OFF_P + NG * 2 * P_WORDS * 4;       // [NG groups][2 buffers][4 warps][24] floats
+  static constexpr int OFF_F = OFF_MAX + NG * 2 * 4 * MAXR * 4;      // [NG groups][2 buffers][24] floats: rescale factors for the PV group
+  static constexpr int OFF_L = OFF_F + NG * 2 * MAXR * 4;            // [NG groups][4 warps][24] floats: row sums at the end
+  static constexpr int OFF_M1 = OFF_L + NG * 4 * MAXR * 4;           // [NG groups][24] floats: reference maxima at the end
+  static constexpr int OFF_BAR = OFF_M1 + NG * MAXR * 4;             // fullK[NG * KDEPTH], fullV[NG * VDEPTH]
+  static constexpr int OFF_FLAG = OFF_BAR + NG * (KDEPTH + VDEPTH) * 8;
+  static constexpr int OFF_TOK = OFF_FLAG + 16;                      // [2 groups][2 buffers] words: "move the maxima" tokens (QK warps)
+  static constexpr int OFF_RTOK = OFF_TOK + 16;                      // [2 groups][2 buffers] words: "rescale O" tokens (QK -> PV)
+  static constexpr int OFF_SEQ = OFF_RTOK + 16;                      // [2 groups][8] ints: the groups' tile queues
+  static constexpr int SMEM_USED = OFF_SEQ + 64;
+  static constexpr int SMEM_BYTES = SMEM_USED + 1024;                // slack for the 1024-byte alignment of the ring
+  static_assert(OFF_BAR % 8 == 0, "mbarriers are 8-byte aligned");
+  static_assert(NG == 1 || MAXR * O_STRIDE * 4 <= RING_BYTES, "O exchange must fit in the ring");
+  static_assert(SMEM_BYTES * (3 - NG) + (3 - NG) * 1024 <= 232448, "shared memory of one SM");
+};
+
 #ifdef Q27B_WS_PROFILE
 constexpr int TRACE_STRIDE = 16;
 #else
@@ -129,18 +144,24 @@ __device__ __forceinline__ int slot_row(int s) { return (s & 8) | ((s & 1) << 2)
 __device__ __forceinline__ int ks_dim0(int ks, int tg) { return 128 * (ks >> 3) + 64 * ((ks >> 2) & 1) + 16 * tg + 4 * (ks & 3); }
 
 // NT = 8-row groups of query rows (ceil(6 T / 8)). PAGED: batched decode over 256-position pages.
-template <int NT, bool PAGED>
-__global__ void __launch_bounds__(WS_THREADS, 1)
+template <int NT, bool PAGED, int NG>
+__global__ void __launch_bounds__(256 * NG, 3 - NG)
 decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_ks,
                  const __grid_constant__ CUtensorMap tm_vv, const __grid_constant__ CUtensorMap tm_vs,
                  const DecodeParams p) {
   pdl_wait();
   pdl_trigger();
+  using L = Lay<NG>;
+  constexpr int WS_THREADS = L::THREADS;
+  constexpr int OFF_KRING = L::OFF_KRING, OFF_VRING = L::OFF_VRING, OFF_Q = L::OFF_Q, OFF_P = L::OFF_P, OFF_MAX = L::OFF_MAX,
+                OFF_F = L::OFF_F, OFF_L = L::OFF_L, OFF_M1 = L::OFF_M1, OFF_BAR = L::OFF_BAR, OFF_FLAG = L::OFF_FLAG,
+                OFF_TOK = L::OFF_TOK, OFF_RTOK = L::OFF_RTOK, OFF_SEQ = L::OFF_SEQ;
+  constexpr int PV0 = 128 * NG;  // the first PV thread
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   uint64_t* fullK = (uint64_t*)(sgen + OFF_BAR);
-  uint64_t* fullV = fullK + 2 * KDEPTH;
+  uint64_t* fullV = fullK + NG * KDEPTH;
   volatile int* abort_flag = (volatile int*)(sgen + OFF_FLAG);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -163,10 +184,11 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   const float* qn = p.qn + (size_t)seq * T * p.nqh * AD;
   const int g = lane >> 2, tg = lane & 3;
 
-  // The query block: 64 float4 per row, three per thread, requested before anything else waits.
-  float4 qv[3];
+  // The query block: 64 float4 per row, three (six) per thread, requested before anything else waits.
+  constexpr int QV = MAXR * 64 / WS_THREADS;
+  float4 qv[QV];
 #pragma unroll
-  for (int j = 0; j < 3; j++) {
+  for (int j = 0; j < QV; j++) {
     const int i = tid + j * WS_THREADS, r = i >> 6, c4 = i & 63;
     qv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (r < R) qv[j] = *(const float4*)(qn + ((size_t)(r / GQA) * p.nqh + kh * GQA + r % GQA) * AD + 4 * c4);
@@ -210,7 +232,7 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   }
 
   if (tid == 0) {
-    for (int s = 0; s < 2 * (KDEPTH + VDEPTH); s++) mbar_init(&fullK[s], 1);
+    for (int s = 0; s < NG * (KDEPTH + VDEPTH); s++) mbar_init(&fullK[s], 1);
     *abort_flag = 0;
     for (int i = 0; i < 8; i++) ((volatile uint32_t*)(sgen + OFF_TOK))[i] = 0;
     mbar_fence_init();
@@ -232,10 +254,10 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
     }
     return row;
   };
-  const int grp = (warp >> 2) & 1, wq = warp & 3;
+  const int grp = NG == 2 ? (warp >> 2) & 1 : 0, wq = warp & 3;
   // Tile t into the K (V) buffer that serves the group's j-th tile: buffer 2 (j mod depth) + group.
   auto issue_k = [&](int t, int j) {  // one thread
-    const int s = 2 * (j % KDEPTH) + grp;
+    const int s = NG * (j % KDEPTH) + grp;
     uint8_t* st = sgen + OFF_KRING + (size_t)s * HALF_BYTES;
     const int row = tile_row(t);
     mbar_expect_tx(&fullK[s], HALF_BYTES);
@@ -244,7 +266,7 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
     tma_load_2d(st + OFF_SC, &tm_ks, 0, row, &fullK[s]);
   };
   auto issue_v = [&](int t, int j) {  // one thread
-    const int s = 2 * (j % VDEPTH) + grp;
+    const int s = NG * (j % VDEPTH) + grp;
     uint8_t* st = sgen + OFF_VRING + (size_t)s * HALF_BYTES;
     const int row = tile_row(t);
     mbar_expect_tx(&fullV[s], HALF_BYTES);
@@ -256,7 +278,7 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   // Only the loader of a QK group asks; everybody else reads the answer from the queue in shared
   // memory (8 entries per group, entry j mod 8), which the loader fills three tiles ahead.
   auto next_tile = [&](int j) {
-    const int i = grp + 2 * j;
+    const int i = grp + NG * j;
     if (i < n_static) return t_first + i;
     if (!has_pool) return -1;
     const int t = pool0 + atomicAdd(p.sched + kh, 1);
@@ -264,7 +286,7 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   };
   const uint32_t sSeq = sbase + OFF_SEQ + grp * 32;
 
-  const bool is_qk = warp < 8;
+  const bool is_qk = warp < 4 * NG;
   const bool loader = wq == 0 && lane == 0;  // refills this group's K (QK warps) or V (PV warps) halves
   // The ring is started in steps: a request for all six stages of 148 CTAs at once is 30 MB, and the
   // first tile of a CTA then arrives when most of that has been served (3 to 5 us). The first tile
@@ -288,7 +310,7 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
   {
     const uint32_t sQ = sbase + OFF_Q;
 #pragma unroll
-    for (int j = 0; j < 3; j++) {
+    for (int j = 0; j < QV; j++) {
       const int i = tid + j * WS_THREADS, r = i >> 6, c4 = i & 63;
       if (r < 8 * NT)
         sts64(sQ + r * Q_STRIDE + c4 * 8, pack_h2(qv[j].x * p.kq_scale, qv[j].y * p.kq_scale),
@@ -358,7 +380,7 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
     for (int jt = 0;; jt++) {
       const int tile = (int)lds32(sSeq + (jt & 7) * 4);
       if (tile < 0) break;
-      const int s = 2 * (jt % KDEPTH) + grp;
+      const int s = NG * (jt % KDEPTH) + grp;
       PROF_BEGIN();
       mbar_wait(&fullK[s], (jt / KDEPTH) & 1, abort_flag, p.status);
       PROF_END(w_full);
@@ -573,7 +595,7 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
     for (int jt = 0;; jt++) {
       const int tile = (int)lds32(sSeq + (jt & 7) * 4);
       if (tile < 0) break;
-      const int s = 2 * (jt % VDEPTH) + grp;
+      const int s = NG * (jt % VDEPTH) + grp;
       const int buf = jt & 1;
       const uint32_t token = (uint32_t)(jt + 1);
       const uint32_t st = sbase + OFF_VRING + s * HALF_BYTES;
@@ -597,7 +619,7 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       pv_wfull += t_c - t_b;
       pv_wready += clock64() - t_c;
 #endif
-      if (jt == 0 && tid == 256) stamp(5);
+      if (jt == 0 && tid == PV0) stamp(5);
       // Every PV warp of the group is past the previous tile: refill its V buffer with the group's
       // tile jt - 1 + VDEPTH (the queue entry was written before the QK group released tile jt - 1).
 #ifdef Q27B_WS_BURST
@@ -671,7 +693,7 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
       if ((int)lds32(sSeq + ((jt + 2) & 7) * 4) >= 0) bar_arrive(BAR_FREE + 2 * grp + buf, 256);
     }
   }
-  if (tid == 256) stamp(6);
+  if (tid == PV0) stamp(6);
 #ifdef Q27B_WS_PROFILE
   if (trace && lane == 0 && wq == 1 && grp == 0) {  // cycles this warp spent waiting: V tile, P tile; and in all
     trace[11] = (unsigned long long)pv_wfull;
@@ -681,6 +703,30 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
 #endif
   __syncthreads();  // every tile consumed: the ring is free for the O exchange; m and l are posted
 
+  if constexpr (NG == 1) {  // one group: its accumulators, maxima and sums are the chunk partial
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const int r = 8 * nt + 2 * tg + e;
+        if (r >= R) continue;
+        float* po = out + (size_t)r * PROW;
+#pragma unroll
+        for (int mt = 0; mt < 4; mt++) {
+          const int d = 64 * wq + 8 * g + 2 * mt;
+          *(float2*)(po + 2 + d) = make_float2(o[mt][nt][e], o[mt][nt][2 + e]);
+        }
+        if (wq == 0 && g == 0) {
+          float l0 = 0.f;
+#pragma unroll
+          for (int w = 0; w < 4; w++) l0 += ldsf(sbase + OFF_L + (w * MAXR + r) * 4);
+          po[0] = ldsf(sbase + OFF_M1 + r * 4);
+          po[1] = l0;
+        }
+      }
+    if (tid == PV0) stamp(7);
+    return;
+  }
   // ---- merge the two groups (log-sum-exp) and write the chunk partial
   const uint32_t sO = sbase;
   if (grp == 1) {
@@ -727,35 +773,46 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
           po[1] = l0 * f0 + l1 * f1;
         }
       }
-    if (tid == 256) stamp(7);
+    if (tid == PV0) stamp(7);
   }
 }
 
-template <int NT>
+template <int NT, int NG>
 int launch_ws_nt(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
                  const DecodeParams& p, bool paged, int nseq, cudaStream_t s) {
   const dim3 grid(p.nch, p.nkvh, nseq);
   if (paged)
-    Q27B_CK(launch_pdl(decode_ws_kernel<NT, true>, grid, dim3(WS_THREADS), WS_SMEM_BYTES, s, *kv, *ks, *vv, *vs, p));
+    Q27B_CK(launch_pdl(decode_ws_kernel<NT, true, NG>, grid, dim3(Lay<NG>::THREADS), Lay<NG>::SMEM_BYTES, s, *kv, *ks, *vv, *vs, p));
   else
-    Q27B_CK(launch_pdl(decode_ws_kernel<NT, false>, grid, dim3(WS_THREADS), WS_SMEM_BYTES, s, *kv, *ks, *vv, *vs, p));
+    Q27B_CK(launch_pdl(decode_ws_kernel<NT, false, NG>, grid, dim3(Lay<NG>::THREADS), Lay<NG>::SMEM_BYTES, s, *kv, *ks, *vv, *vs, p));
+  return Q27B_OK;
+}
+
+template <int NT, bool PAGED, int NG>
+int ws_attr() {
+  Q27B_CK(cudaFuncSetAttribute(decode_ws_kernel<NT, PAGED, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<NG>::SMEM_BYTES));
+  if (NG == 1)  // two CTAs per SM need the whole shared-memory carve-out
+    Q27B_CK(cudaFuncSetAttribute(decode_ws_kernel<NT, PAGED, NG>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
   return Q27B_OK;
 }
 
 }  // namespace
 
 int decode_ws_setup() {
-  Q27B_CK(cudaFuncSetAttribute(decode_ws_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM_BYTES));
-  Q27B_CK(cudaFuncSetAttribute(decode_ws_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM_BYTES));
-  Q27B_CK(cudaFuncSetAttribute(decode_ws_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM_BYTES));
-  Q27B_CK(cudaFuncSetAttribute(decode_ws_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM_BYTES));
-  Q27B_CK(cudaFuncSetAttribute(decode_ws_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM_BYTES));
-  Q27B_CK(cudaFuncSetAttribute(decode_ws_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM_BYTES));
+  if (int rc = ws_attr<1, false, 2>()) return rc;
+  if (int rc = ws_attr<2, false, 2>()) return rc;
+  if (int rc = ws_attr<3, false, 2>()) return rc;
+  if (int rc = ws_attr<1, true, 2>()) return rc;
+  if (int rc = ws_attr<2, true, 2>()) return rc;
+  if (int rc = ws_attr<3, true, 2>()) return rc;
+  if (int rc = ws_attr<1, true, 1>()) return rc;
+  if (int rc = ws_attr<2, true, 1>()) return rc;
+  if (int rc = ws_attr<3, true, 1>()) return rc;
   return Q27B_OK;
 }
 
 int launch_decode_ws(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensorMap* vv, const CUtensorMap* vs,
-                     const DecodeParams& p, bool paged, int nseq, cudaStream_t s) {
+                     const DecodeParams& p, bool paged, int nseq, cudaStream_t s, bool single_group) {
   static bool attr[64] = {};
   static std::mutex attr_mu;
   int dev;
@@ -768,9 +825,14 @@ int launch_decode_ws(const CUtensorMap* kv, const CUtensorMap* ks, const CUtenso
     }
   }
   const int nt = (GQA * p.T + 7) / 8;
-  if (nt == 1) return launch_ws_nt<1>(kv, ks, vv, vs, p, paged, nseq, s);
-  if (nt == 2) return launch_ws_nt<2>(kv, ks, vv, vs, p, paged, nseq, s);
-  return launch_ws_nt<3>(kv, ks, vv, vs, p, paged, nseq, s);
+  if (single_group && paged) {  // 8 warps, two CTAs per SM
+    if (nt == 1) return launch_ws_nt<1, 1>(kv, ks, vv, vs, p, true, nseq, s);
+    if (nt == 2) return launch_ws_nt<2, 1>(kv, ks, vv, vs, p, true, nseq, s);
+    return launch_ws_nt<3, 1>(kv, ks, vv, vs, p, true, nseq, s);
+  }
+  if (nt == 1) return launch_ws_nt<1, 2>(kv, ks, vv, vs, p, paged, nseq, s);
+  if (nt == 2) return launch_ws_nt<2, 2>(kv, ks, vv, vs, p, paged, nseq, s);
+  return launch_ws_nt<3, 2>(kv, ks, vv, vs, p, paged, nseq, s);
 }
 
 }  // namespace q27b
