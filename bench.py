@@ -308,8 +308,10 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--ref-cpu", action="store_true", help="reference arm: time the CPU oracle instead of the reference's GPU kernels")
     ap.add_argument("--n", type=int, default=N_POS)
-    ap.add_argument("--mode", default="decode", help="decode (the headline), prefill (second half of the metric) or sum_norm (N > 1: the exchange after the output projection)")
+    ap.add_argument("--mode", default="decode", help="decode (the headline), prefill (second half of the metric), paged (config 5: the batched decode over pages) or sum_norm (N > 1: the exchange after the output projection)")
     ap.add_argument("--prefix", type=int, default=32768, help="prefill mode: tokens already in the cache")
+    ap.add_argument("--seqs", type=int, default=64, help="paged mode: sequences in the batch")
+    ap.add_argument("--max-len", type=int, default=131072, help="paged mode: lengths are uniform in 1024 .. this")
     ap.add_argument("--kv", default="q8", help="prefill mode: q8 (int8 Q K^T on the q8_0 cache) or f16 (f16 Q K^T on an f16 cache)")
     args = ap.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
@@ -337,6 +339,20 @@ def main():
         q = ge.load_package()
     if args.mode == "prefill":
         prefill_mode(q, args, steps, warmup, dist, rank, world)
+        return
+    if args.mode == "paged":  # config 5 alone (or a smaller batch of the same kind: --seqs, --max-len)
+        out = batched_paged(q, rank, world, dist, args.seqs, args.max_len)
+        if rank == 0:
+            print(json.dumps({"metric": "batched paged q8_0 decode-attn HBM GB/s", "value": out["value"], "unit": "GB/s",
+                              "n_gpus": world, "steps": 20, "warmup": 3, "ms_per_step": out["ms_per_step"],
+                              "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+                              "data": "synthetic", "config": {"workload": out["what"]}, "gpu_launches": 40,
+                              "roofline": {"bound": "hbm", "achieved": out["value"] / world, "peak": peaks()[0]["hbm_gbs"],
+                                           "unit": "GB/s", "frac": out["value"] / world / peaks()[0]["hbm_gbs"],
+                                           "what": "the whole step (split-K kernel + merge) against the measured copy peak"},
+                              "detail": out}))
+        if dist is not None:
+            dist.barrier()
         return
     if args.mode == "sum_norm":  # the exchange after the output projection alone (needs N > 1)
         if dist is None:
@@ -679,19 +695,19 @@ def sum_norm_scaling(q, dist, rank, world, steps, warmup):
             "bytes_pushed_per_rank": rows * n * 4 * world}
 
 
-def batched_paged(q, rank, world, dist=None):
+def batched_paged(q, rank, world, dist=None, n_seqs=64, max_len=131072):
     """Config 5: 64 sequences, 4 query tokens each, lengths ~U{1,024..131,072} (seed 1005), q8_0 KV in
     256-token pages behind a random page table; sequences sharded over the ranks (greedy by length,
     no exchange). The pool holds random int8 values and scales of the size q8_0 gives N(0,1) rows:
     timing does not depend on the values. One step = one q27b_attn_decode_paged call per rank."""
     from qwen27_engine_b200 import shard
-    PAGE, B_ALL = 256, 64
+    PAGE, B_ALL = 256, n_seqs
     rng = np.random.default_rng(1005)
-    lengths = rng.integers(1024, 131072 + 1, size=B_ALL)
+    lengths = rng.integers(1024, max_len + 1, size=B_ALL)
     mine = shard.shard_sequences(lengths, world)[rank]
     lens = [int(lengths[i]) for i in mine]
     B = len(lens)
-    max_pages = (131072 + PAGE - 1) // PAGE
+    max_pages = (max_len + PAGE - 1) // PAGE
     need = [(n + PAGE - 1) // PAGE for n in lens]
     n_pages = sum(need)
     perm = rng.permutation(n_pages).astype(np.int32)
@@ -726,8 +742,8 @@ def batched_paged(q, rank, world, dist=None):
     ms = time_graph_steps(step, 20, 3, dist, calls=5)
     assert q.device_status() == 0, "a kernel reported a device-side problem"
     total = float(sum(2.0 * NKVH * int(n) * 272 for n in lengths))
-    return {"what": "64 sequences x 4 query tokens, lengths U{1024..131072} (seed 1005), 256-token pages, random page "
-                    "table; %d sequence(s) on rank 0 of %d" % (B, world),
+    return {"what": "%d sequences x 4 query tokens, lengths U{1024..%d} (seed 1005), 256-token pages, random page "
+                    "table; %d sequence(s) on rank 0 of %d" % (n_seqs, max_len, B, world),
             "positions_total": int(lengths.sum()), "kv_bytes_total": total, "ms_per_step": ms, "eager_ms_per_step": ms_e,
             "timing": "CUDA graphs of 5 steps, 4 replays timed",
             "value": total / (ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong (sequences sharded by KV length)"}
