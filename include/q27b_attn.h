@@ -213,12 +213,13 @@ int q27b_kv_page_copy(void* pool, int src_page, int dst_page, int rows, int nkvh
  * caller's business: CUDA IPC, symmetric memory, one process with several devices).
  * q27b_attn_decode_partial_push = q27b_attn_decode_partial whose merge kernel stores the slice's
  * (m, l, O) rows into slot my_z of all nz buffers (peer_xbuf[k] = buffer of rank k of the group, as
- * seen from this GPU; peer_xbuf[my_z] is this rank's own) and then raises flag my_z in each with a
- * system-scope release store. q27b_lse_merge_wait waits (bounded: about a second, then device status
- * bit 0) until the nz flags of its own buffer show the current step, merges the nz slices and applies
- * the gate. Steps are counted on the device, so the pair can sit in a CUDA graph; two parities of the
- * data area make it safe for a rank to run one step ahead of a peer. No counterpart in the reference
- * (its two cards split KV heads, never the KV length: src/model.cu:161-164). */
+ * seen from this GPU; peer_xbuf[my_z] is this rank's own). Every float travels as one 8-byte word
+ * {value, step tag}: an aligned 8-byte store arrives whole, so a word that carries the tag of the current
+ * step carries its value, and neither a fence nor a flag is needed. q27b_lse_merge_wait waits (bounded:
+ * about a second, then device status bit 0 and nothing is written) for the words of the nz slices in its
+ * own buffer, merges them and applies the gate. Steps are counted on the device, so the pair can sit in a
+ * CUDA graph; two parities of the data area make it safe for a rank to run one step ahead of a peer. No
+ * counterpart in the reference (its two cards split KV heads, never the KV length: src/model.cu:161-164). */
 uint64_t q27b_xbuf_bytes(int nz, int64_t rows);
 /* Helpers for one process per GPU: an exchange buffer as a cudaMalloc allocation of its own (zeroed),
  * its CUDA IPC handle (64 bytes, to be sent to the peers by any means), and the mapping of a peer's
@@ -227,12 +228,13 @@ uint64_t q27b_xbuf_bytes(int nz, int64_t rows);
 int q27b_xbuf_alloc(int nz, int64_t rows, void** out);
 int q27b_xbuf_free(void* xbuf);
 /* After a step that ended in device status 1 (a peer's slice or rows never arrived: the waiting kernel
- * gave up, and its CTAs did not finish the step's bookkeeping) an exchange buffer is out of step with
- * its peers. Before the group uses its buffers again EVERY rank of the group zeroes the header of its
- * own buffer with this call (epoch, arrival counters, flags; 256 bytes, on `stream`), and the ranks meet
- * on the host (a barrier of whatever they use to talk) between the resets and the next push. Applies to
- * the buffers of both exchanges (q27b_lse_merge_wait and q27b_sum_norm_q8_wait). */
-int q27b_xbuf_reset(void* xbuf, void* stream);
+ * gave up without finishing the step's bookkeeping) an exchange buffer is out of step with its peers.
+ * Before the group uses its buffers again EVERY rank of the group zeroes its own buffer with this call
+ * (`bytes` = the size it was allocated with: the header with the step counters, and the data area, whose
+ * words carry step tags that a restarted count would meet again; on `stream`), and the ranks meet on the
+ * host (a barrier of whatever they use to talk) between the resets and the next push. Applies to the
+ * buffers of both exchanges (q27b_lse_merge_wait and q27b_sum_norm_q8_wait). */
+int q27b_xbuf_reset(void* xbuf, uint64_t bytes, void* stream);
 int q27b_ipc_export(const void* ptr, unsigned char handle[64]);
 int q27b_ipc_open(const unsigned char handle[64], void** out);
 int q27b_ipc_close(void* mapped);
@@ -265,9 +267,10 @@ int q27b_plan_prefill(int rank, int world, int M, int pos0, int nkvh, int* kv_he
  *    exchange buffer of q27b_sum_xbuf_bytes(world, rows, n) bytes (q27b_xbuf_alloc_bytes: zeroed,
  *    an allocation of its own for CUDA IPC) and passes the buffers of all ranks, its own at index
  *    `rank`, as mapped into its address space, in rank order. q27b_sum_push stores this rank's f32
- *    rows into slot `rank` of every buffer and releases a flag; q27b_sum_norm_q8_wait waits (bounded:
- *    a missing rank ends in Q27B status 4 / device status 1, not in a hang) for the flags of all ranks,
- *    adds the slices in rank order - every rank gets the same bits - and normalises. The reference's
+ *    rows into slot `rank` of every buffer, one 8-byte word {value, step tag} per float (no fence, no
+ *    flag: a word with the tag of the current step carries its value); q27b_sum_norm_q8_wait waits
+ *    (bounded: a missing rank ends in Q27B status 4 / device status 1, not in a hang) for the words of all
+ *    ranks, adds the slices in rank order - every rank gets the same bits - and normalises. The reference's
  *    two PCIe cards exchange through mapped host memory in a bf16 or q8 wire format
  *    (src/ops.cu:151-243); over NVLink the f32 rows go as they are. A buffer serves one call site
  *    per step (its header counts steps); rows and n must not change between steps. */

@@ -278,9 +278,12 @@ def workspace_destroy():
     _check(_lib.q27b_attn_workspace_destroy())
 
 
-def xbuf_reset(xbuf):
-    """Zeroes the header of an exchange buffer (every rank of the group, after a step that reported status 1)."""
-    _check(_lib.q27b_xbuf_reset(_ptr(xbuf), _stream()))
+def xbuf_reset(xbuf, nbytes=None):
+    """Zeroes an exchange buffer (every rank of the group, after a step that reported status 1); nbytes is
+    needed when xbuf is a raw address."""
+    if nbytes is None:
+        nbytes = xbuf.numel() * xbuf.element_size()
+    _check(_lib.q27b_xbuf_reset(_ptr(xbuf), ctypes.c_uint64(int(nbytes)), _stream()))
 
 
 def debug_mma_peak(kind, iters):

@@ -40,7 +40,12 @@ __device__ __forceinline__ RowMap map_decode(const MergeParams& p, int64_t row) 
   return {first, (size_t)MAXR * PROW, p.qg ? p.qg + row * 512 + 256 : nullptr};
 }
 
-// XCHG: the peer-memory exchange modes (push_n / wait_n of MergeParams) are compiled in.
+// Row `row` of slice z in the data area of an exchange buffer (parity = step & 1).
+__device__ __forceinline__ uint64_t* xbuf_row(void* xbuf, int parity, int nz, int z, int64_t rows, int64_t row) {
+  return (uint64_t*)((uint8_t*)xbuf + XBUF_HEADER_BYTES) + (((size_t)parity * nz + z) * rows + row) * PROW;
+}
+
+// XCHG: the push mode of the peer-memory exchange (push_n of MergeParams) is compiled in.
 constexpr int MAX_GROUPS = 4;
 
 // NGRP: thread groups of 256 (1, or MAX_GROUPS for many partials).
@@ -58,36 +63,7 @@ __global__ void __launch_bounds__(AD * NGRP) merge_kernel(const MergeParams p) {
   RowMap rm = DECODE_LAYOUT ? map_decode(p, row) : map_generic(p, row);
   int np = p.nparts;
   int epoch = 0;
-  if (XCHG && (p.push_n > 0 || p.wait_n > 0)) epoch = *(volatile int*)p.xbuf;
-  if (XCHG && !DECODE_LAYOUT && p.wait_n > 0) {
-    // Slices of the other GPUs arrive by plain stores followed by a released flag: wait for the flags
-    // of this step (bounded; a lost peer ends in the status word, not in a hang), then read.
-    __shared__ int s_ok;
-    if (d == 0) {
-      bool ok = true;
-      for (int z = 0; z < p.wait_n && ok; z++) {
-        const int* flag = p.xbuf + 16 + z;
-        ok = false;
-        for (uint32_t i = 0; i < (1u << 22); i++) {  // about a second with the sleeps
-          int v;
-          asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-          if (v - (epoch + 1) >= 0) {
-            ok = true;
-            break;
-          }
-          if (i > 64) __nanosleep(200);
-        }
-      }
-      if (!ok && p.status) atomicOr(p.status, ST_WAIT_EXPIRED);
-      s_ok = ok;
-    }
-    __syncthreads();
-    if (!s_ok) return;
-    const float* data = (const float*)((const uint8_t*)p.xbuf + XBUF_HEADER_BYTES) + (size_t)(epoch & 1) * p.wait_n * p.rows * PROW;
-    rm.first = data + row * PROW;
-    rm.stride = (size_t)p.rows * PROW;
-    np = p.wait_n;
-  }
+  if (XCHG && p.push_n > 0) epoch = *(volatile int*)p.xbuf;
   if (DECODE_LAYOUT && p.seq_len) {
     const int64_t seq = row / ((int64_t)p.nqh * p.T);
     np = min(np, max(1, (p.seq_len[seq] + p.chunk_len - 1) / p.chunk_len));
@@ -150,32 +126,13 @@ __global__ void __launch_bounds__(AD * NGRP) merge_kernel(const MergeParams p) {
   const bool lead = NGRP == 1 || grp == 0;
 
   const size_t oi = (size_t)row * AD + d;
-  if (XCHG && !DECODE_LAYOUT && p.wait_n > 0 && tid == 0) {
-    // the last CTA of the step advances the epoch (nobody reads it again before the next launch)
-    __threadfence();
-    if (atomicAdd(p.xbuf + 2, 1) == (int)p.rows - 1) {
-      p.xbuf[2] = 0;
-      *(volatile int*)p.xbuf = epoch + 1;
-    }
-  }
   if (XCHG && p.push_n > 0) {  // merged, not normalised, into slot push_z of every rank's exchange buffer
     for (int k = 0; lead && k < p.push_n; k++) {
-      float* po = (float*)((uint8_t*)p.push_buf[k] + XBUF_HEADER_BYTES) +
-                  (((size_t)(epoch & 1) * p.push_n + p.push_z) * p.rows + row) * PROW;
-      po[2 + d] = A;
+      uint64_t* po = xbuf_row(p.push_buf[k], epoch & 1, p.push_n, p.push_z, p.rows, row);
+      ll_store(po + 2 + d, A, epoch + 1);
       if (d == 0) {
-        po[0] = M;
-        po[1] = L;
-      }
-    }
-    __threadfence_system();  // the rows are visible to the peers before the flag below can be
-    __syncthreads();
-    if (tid == 0 && atomicAdd(p.xbuf + 1, 1) == (int)p.rows - 1) {
-      p.xbuf[1] = 0;
-      __threadfence_system();
-      for (int k = 0; k < p.push_n; k++) {
-        int* flag = (int*)p.push_buf[k] + 16 + p.push_z;
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch + 1) : "memory");
+        ll_store(po, M, epoch + 1);
+        ll_store(po + 1, L, epoch + 1);
       }
     }
     return;
@@ -287,22 +244,11 @@ __global__ void __launch_bounds__(1024) merge_wide_kernel(const MergeParams p) {
 
   if (p.push_n > 0) {  // merged, not normalised, into slot push_z of every rank's exchange buffer
     for (int k = 0; lead && k < p.push_n; k++) {
-      float* po = (float*)((uint8_t*)p.push_buf[k] + XBUF_HEADER_BYTES) +
-                  (((size_t)(epoch & 1) * p.push_n + p.push_z) * p.rows + row) * PROW;
-      po[2 + d] = A;
+      uint64_t* po = xbuf_row(p.push_buf[k], epoch & 1, p.push_n, p.push_z, p.rows, row);
+      ll_store(po + 2 + d, A, epoch + 1);
       if (d == 0) {
-        po[0] = M;
-        po[1] = L;
-      }
-    }
-    __threadfence_system();  // the rows are visible to the peers before the flag below can be
-    __syncthreads();
-    if (tid == 0 && atomicAdd(p.xbuf + 1, 1) == (int)p.rows * WIDE_SLICES - 1) {
-      p.xbuf[1] = 0;
-      __threadfence_system();
-      for (int k = 0; k < p.push_n; k++) {
-        int* flag = (int*)p.push_buf[k] + 16 + p.push_z;
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch + 1) : "memory");
+        ll_store(po, M, epoch + 1);
+        ll_store(po + 1, L, epoch + 1);
       }
     }
     return;
@@ -332,16 +278,69 @@ __global__ void __launch_bounds__(1024) merge_wide_kernel(const MergeParams p) {
   if (lane == 0) p.xd[oi / 32] = __half2float(__float2half_rn(dd));
 }
 
+// The final merge of the peer-memory exchange: one CTA per output row merges the wait_n slices that the ranks
+// of the group pushed into this rank's own buffer, waiting (bounded) for each word of the current step; same
+// arithmetic, in the same order, as merge_kernel on the gathered partials. The last CTA advances the step.
+__global__ void __launch_bounds__(AD) merge_wait_kernel(const MergeParams p) {
+  pdl_wait();
+  pdl_trigger();
+  const int64_t row = blockIdx.x;
+  const int d = threadIdx.x, nz = p.wait_n;
+  const int epoch = *(volatile int*)p.xbuf;
+  bool ok = true;
+  float m[8], l[8], a[8];
+#pragma unroll
+  for (int z = 0; z < 8; z++)
+    if (z < nz) {
+      const uint64_t* pz = xbuf_row(p.xbuf, epoch & 1, nz, z, p.rows, row);
+      a[z] = ll_load(pz + 2 + d, epoch + 1, ok);
+      m[z] = ll_load(pz, epoch + 1, ok);
+      l[z] = ll_load(pz + 1, epoch + 1, ok);
+    }
+  const float gate = p.qg ? p.qg[row * 512 + 256 + d] : 0.f;
+  if (__syncthreads_or(!ok)) {  // a slice never arrived: the status word says so, nothing is written
+    if (d == 0 && p.status) atomicOr(p.status, ST_WAIT_EXPIRED);
+    return;
+  }
+  float M = M_INIT;
+#pragma unroll
+  for (int z = 0; z < 8; z++)
+    if (z < nz) M = fmaxf(M, m[z]);
+  float L = 0.f, A = 0.f;
+#pragma unroll
+  for (int z = 0; z < 8; z++)
+    if (z < nz) {
+      const float f = expf(m[z] - M);
+      L += l[z] * f;
+      A += a[z] * f;
+    }
+  float y = A / L;
+  if (p.qg) y *= 1.0f / (1.0f + expf(-gate));
+  p.o[(size_t)row * AD + d] = y;
+  if (d == 0) {  // the last CTA of the step advances the epoch (nobody reads it again before the next launch)
+    __threadfence();
+    if (atomicAdd(p.xbuf + 2, 1) == (int)p.rows - 1) {
+      p.xbuf[2] = 0;
+      *(volatile int*)p.xbuf = epoch + 1;
+    }
+  }
+}
+
 }  // namespace
 
 int launch_merge(const MergeParams& p, bool decode_layout, cudaStream_t s) {
   if (p.nparts < 1 || p.nparts > MAX_PARTS) return fail(Q27B_BAD_SHAPE, "lse_merge: 1..1024 partials");
   if (p.rows < 1) return Q27B_OK;
-  const bool xchg = p.push_n > 0 || p.wait_n > 0;
+  if (p.wait_n > 0) {
+    if (p.wait_n > 8 || !p.xbuf || !p.o) return fail(Q27B_BAD_SHAPE, "lse_merge_wait: bad arguments");
+    Q27B_CK(launch_pdl(merge_wait_kernel, dim3((unsigned)p.rows), dim3(AD), 0, s, p));
+    return Q27B_OK;
+  }
+  const bool xchg = p.push_n > 0;
   const dim3 grid((unsigned)p.rows);
   // four thread groups once a row has more partials than a 4-head decode call gives it (37 on 148 SMs)
   // (the waiting merge of an exchange has at most 8 partials; the pushing one is a decode-layout merge)
-  const bool wide = p.wait_n == 0 && p.nparts > 64;
+  const bool wide = p.nparts > 64;
   static const bool sliced = [] {  // Q27B_MERGE_SLICED=0: the one-CTA-per-row form for every shape
     const char* e = getenv("Q27B_MERGE_SLICED");
     return !(e && e[0] == '0');
@@ -372,7 +371,7 @@ int launch_merge(const MergeParams& p, bool decode_layout, cudaStream_t s) {
 using namespace q27b;
 
 extern "C" uint64_t q27b_xbuf_bytes(int nz, int64_t rows) {
-  return (uint64_t)XBUF_HEADER_BYTES + 2ull * (uint64_t)nz * (uint64_t)rows * PROW * sizeof(float);
+  return (uint64_t)XBUF_HEADER_BYTES + 2ull * (uint64_t)nz * (uint64_t)rows * PROW * sizeof(uint64_t);  // {value, tag} words
 }
 
 extern "C" int q27b_lse_merge_wait(void* xbuf, int nz, int64_t rows, const float* qg, float* o, void* stream) {

@@ -18,13 +18,12 @@ struct MergeParams {
   const int* seq_len;   // decode layout, batched: sequence s has ceil(seq_len[s] / chunk_len) partials
   int chunk_len;
   // Exchange over peer memory (KV-length slices of one sequence on several GPUs). An exchange buffer
-  // is [64 ints header][2 parities][nz slices][rows][258 floats]; header: [0] epoch, [1] and [2]
-  // arrival counters, [16 + z] flag of slice z (= epoch + 1 once slice z of that step has landed).
+  // is [64 ints header][2 parities][nz slices][rows][258 words of 8 bytes: {float value, int step tag}];
+  // header: [0] epoch (steps completed), [2] arrival counter of the waiting merge.
   // push_n > 0: the merged (M, L, A) rows go, instead of part_out, into slot push_z of the buffers of
-  // all push_n ranks of the group (plain stores, this rank's own buffer included), and the last CTA
-  // raises flag push_z in each of them. wait_n > 0: `part` is this rank's own buffer: the kernel waits
-  // (bounded) until all wait_n flags show the current epoch, merges those slices, and the last CTA
-  // advances the epoch.
+  // all push_n ranks of the group (one 8-byte store per float, tagged epoch + 1; this rank's own buffer
+  // included). wait_n > 0: `xbuf` is this rank's own buffer: the kernel waits (bounded) until the words of
+  // all wait_n slices carry the tag of the current step, merges them, and the last CTA advances the epoch.
   void* push_buf[8];
   int push_n, push_z;
   int* xbuf;            // this rank's own exchange buffer (push: epoch and counter; wait: everything)

@@ -138,6 +138,26 @@ static __device__ __forceinline__ void mbar_wait_sleeping(uint64_t* bar, uint32_
   if (status) atomicOr(status, ST_WAIT_EXPIRED);
 }
 
+// ---- exchange over peer memory: every float travels as one 8-byte word {value, tag}, tag = the step it belongs
+// to (epoch + 1). An aligned 8-byte store is one transaction, so a reader that finds the tag of the current
+// step has the value of the current step: no fence and no separate flag are needed (a system-scope fence, which
+// the flag form needs between the rows and the flag, was measured at 10 us and more per kernel on this GPU).
+__device__ __forceinline__ void ll_store(uint64_t* p, float v, int tag) {
+  const uint64_t w = ((uint64_t)(uint32_t)tag << 32) | (uint64_t)__float_as_uint(v);
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+// Waits (bounded: about a second with the sleeps, then ok = false) for the word to carry `tag`.
+__device__ __forceinline__ float ll_load(const uint64_t* p, int tag, bool& ok) {
+  for (uint32_t i = 0; i < (1u << 22); i++) {
+    uint64_t w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    if ((int)(uint32_t)(w >> 32) == tag) return __uint_as_float((uint32_t)w);
+    if (i > 64) __nanosleep(200);
+  }
+  ok = false;
+  return 0.f;
+}
+
 // After a wait has given up, a CTA drains to its end without synchronisation. Before it frees
 // tensor memory and exits it gives the copies and MMAs that it issued earlier time to land
 // (microseconds of work; this sleeps 100 us), so that nothing is still writing into shared or

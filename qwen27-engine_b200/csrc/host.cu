@@ -317,7 +317,7 @@ int q27b_debug_expire_wait(void* stream) {
 // ---- exchange buffers of the peer-memory merge, and their mapping between processes
 int q27b_xbuf_alloc(int nz, int64_t rows, void** out) {
   if (!out || nz < 1 || nz > 8 || rows < 1) return fail(Q27B_BAD_SHAPE, "xbuf_alloc: bad shape");
-  const size_t bytes = 256 + 2ull * (size_t)nz * (size_t)rows * (Q27B_HEAD_DIM + 2) * sizeof(float);
+  const size_t bytes = (size_t)q27b_xbuf_bytes(nz, rows);
   void* p = nullptr;
   Q27B_CK(cudaMalloc(&p, bytes));  // an allocation of its own: an IPC handle names whole allocations
   Q27B_CK(cudaMemset(p, 0, bytes));
@@ -326,9 +326,11 @@ int q27b_xbuf_alloc(int nz, int64_t rows, void** out) {
   return Q27B_OK;
 }
 
-int q27b_xbuf_reset(void* xbuf, void* stream) {
-  if (!xbuf) return fail(Q27B_BAD_SHAPE, "xbuf_reset: null pointer");
-  Q27B_CK(cudaMemsetAsync(xbuf, 0, 256, (cudaStream_t)stream));  // epoch, arrival counters, flags
+int q27b_xbuf_reset(void* xbuf, uint64_t bytes, void* stream) {
+  if (!xbuf || bytes < 256) return fail(Q27B_BAD_SHAPE, "xbuf_reset: null pointer or less than the header");
+  // the step counters of the header, and the data area: a word left over from the broken step carries the tag
+  // of a step that the restarted count will reach again
+  Q27B_CK(cudaMemsetAsync(xbuf, 0, bytes, (cudaStream_t)stream));
   return Q27B_OK;
 }
 

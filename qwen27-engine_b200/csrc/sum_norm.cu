@@ -5,10 +5,10 @@
 // from src/model.cu:652-692) has two cards on PCIe: the partials cross through mapped host memory in
 // a compressed wire format (bf16, or q8 with error feedback), one flag per row, a one-second bound
 // on the wait. Here the GPUs share an NVLink switch: every rank stores its f32 rows straight into
-// the exchange buffers of all ranks (plain peer stores, then a released flag), each rank adds the
-// slices in rank order - so every rank gets the same bits - and no wire format is needed. As in the
-// decode exchange (combine.cu) the remote rows land in the rank's own memory before anything reads
-// them, waits are bounded and end in the status word, and there are no multicast loads.
+// the exchange buffers of all ranks (peer stores of 8-byte words {value, step tag}: no fence, no flag, see
+// ll_store), each rank adds the slices in rank order - so every rank gets the same bits - and no wire
+// format is needed. As in the decode exchange (combine.cu) the remote rows land in the rank's own memory
+// before anything reads them, waits are bounded and end in the status word, and there are no multicast loads.
 //
 // Numerics of the reference's row kernel (norm_q8_row, src/ops.cu:89-107): t = sum v^2 in f32,
 // scale = rsqrtf(t / n + eps) with n a run-time divisor, y = scale * v * w, q8_1 per 32 values as
@@ -56,49 +56,37 @@ __global__ void __launch_bounds__(SN_THREADS) sum_norm_kernel(const SumNormParam
   pdl_wait();
   pdl_trigger();
   __shared__ float sred[32];
-  __shared__ int s_ok;
   const int row = blockIdx.x, tid = threadIdx.x, n = p.n;
   const int npt = n / SN_THREADS + (tid < n % SN_THREADS ? 1 : 0);  // n is a multiple of 32, not of 1024
   float v[SN_MAX_NPT];
   float* xr = p.x + (size_t)row * n;
   int epoch = 0;
+  if (WAIT) epoch = *(volatile int*)p.xbuf;
+  // WAIT: the ranks' rows of this step, words {value, tag} in this rank's own buffer
+  const uint64_t* data = WAIT ? (const uint64_t*)((const uint8_t*)p.xbuf + XBUF_HEADER_BYTES) + (size_t)(epoch & 1) * p.world * p.rows * n
+                              : nullptr;
+  float add[SN_MAX_NPT];
   if (WAIT) {
-    epoch = *(volatile int*)p.xbuf;
-    if (tid == 0) {
-      bool ok = true;
-      for (int z = 0; z < p.world && ok; z++) {
-        const int* flag = p.xbuf + 16 + z;
-        ok = false;
-        for (uint32_t i = 0; i < (1u << 22); i++) {  // about a second with the sleeps
-          int f;
-          asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(f) : "l"(flag) : "memory");
-          if (f - (epoch + 1) >= 0) {
-            ok = true;
-            break;
-          }
-          if (i > 64) __nanosleep(200);
-        }
+    bool ok = true;
+#pragma unroll
+    for (int k = 0; k < SN_MAX_NPT; k++)
+      if (k < npt) {
+        const int i = tid + k * SN_THREADS;
+        float sum = ll_load(data + (size_t)row * n + i, epoch + 1, ok);
+        for (int z = 1; z < p.world; z++) sum += ll_load(data + ((size_t)z * p.rows + row) * n + i, epoch + 1, ok);  // rank order on every rank
+        add[k] = sum;
       }
-      if (!ok && p.status) atomicOr(p.status, ST_WAIT_EXPIRED);
-      s_ok = ok;
+    if (__syncthreads_or(!ok)) {  // a rank's rows never arrived: the status word says so, nothing is written
+      if (tid == 0 && p.status) atomicOr(p.status, ST_WAIT_EXPIRED);
+      return;
     }
-    __syncthreads();
-    if (!s_ok) return;
   }
-  const float* data = WAIT ? (const float*)((const uint8_t*)p.xbuf + XBUF_HEADER_BYTES) + (size_t)(epoch & 1) * p.world * p.rows * n
-                           : nullptr;
   float t = 0.f;
 #pragma unroll
   for (int k = 0; k < SN_MAX_NPT; k++) {
     if (k < npt) {
       const int i = tid + k * SN_THREADS;
-      float s;
-      if (WAIT) {
-        s = data[(size_t)row * n + i];
-        for (int z = 1; z < p.world; z++) s += data[((size_t)z * p.rows + row) * n + i];  // rank order on every rank
-      } else {
-        s = p.partial[(size_t)row * n + i];
-      }
+      const float s = WAIT ? add[k] : p.partial[(size_t)row * n + i];
       v[k] = xr[i] + s;
       xr[i] = v[k];
       t += v[k] * v[k];
@@ -140,26 +128,22 @@ struct SumPushParams {
   int rows, n, rank, world;
 };
 
-// One CTA per (row, destination rank): the row goes into slot `rank` of that rank's buffer; the last
-// CTA of the grid releases the flags.
+// One CTA per (row, destination rank): the row goes into slot `rank` of that rank's buffer, one tagged 8-byte
+// word per value.
 __global__ void __launch_bounds__(256) sum_push_kernel(const SumPushParams p) {
   pdl_wait();
   pdl_trigger();
   const int row = blockIdx.x, k = blockIdx.y, n = p.n;
   const int epoch = *(volatile int*)p.xbuf;
   const float4* src = (const float4*)(p.partial + (size_t)row * n);
-  float4* dst = (float4*)((float*)((uint8_t*)p.peer[k] + XBUF_HEADER_BYTES) +
-                          (((size_t)(epoch & 1) * p.world + p.rank) * p.rows + row) * n);
-  for (int i = threadIdx.x; i < n / 4; i += blockDim.x) dst[i] = src[i];
-  __threadfence_system();  // the rows are visible to the peers before the flag below can be
-  __syncthreads();
-  if (threadIdx.x == 0 && atomicAdd(p.xbuf + 1, 1) == p.rows * p.world - 1) {
-    p.xbuf[1] = 0;
-    __threadfence_system();
-    for (int k = 0; k < p.world; k++) {
-      int* flag = (int*)p.peer[k] + 16 + p.rank;
-      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch + 1) : "memory");
-    }
+  uint64_t* dst = (uint64_t*)((uint8_t*)p.peer[k] + XBUF_HEADER_BYTES) +
+                  (((size_t)(epoch & 1) * p.world + p.rank) * p.rows + row) * n;
+  for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+    const float4 v = src[i];
+    ll_store(dst + 4 * i, v.x, epoch + 1);
+    ll_store(dst + 4 * i + 1, v.y, epoch + 1);
+    ll_store(dst + 4 * i + 2, v.z, epoch + 1);
+    ll_store(dst + 4 * i + 3, v.w, epoch + 1);
   }
 }
 
@@ -177,7 +161,7 @@ extern "C" {
 
 uint64_t q27b_sum_xbuf_bytes(int world, int rows, int n) {
   if (world < 1 || rows < 1 || n < 1) return 0;
-  return XBUF_HEADER_BYTES + 2ull * (uint64_t)world * (uint64_t)rows * (uint64_t)n * sizeof(float);
+  return XBUF_HEADER_BYTES + 2ull * (uint64_t)world * (uint64_t)rows * (uint64_t)n * sizeof(uint64_t);  // {value, tag} words
 }
 
 int q27b_xbuf_alloc_bytes(uint64_t bytes, void** out) {

@@ -223,24 +223,32 @@ def test_kv_length_slices_exchanged_over_peer_memory(q27, orc, n, cuts):
     assert q27.device_status() == 0
 
 
+def _tagged(parts, tag):
+    """float rows -> the exchange buffer's words: {value, step tag} as int32 pairs."""
+    w = torch.empty(parts.shape + (2,), dtype=torch.int32, device=parts.device)
+    w[..., 0] = parts.contiguous().view(torch.int32)
+    w[..., 1] = tag
+    return w
+
+
 def test_peer_memory_merge_reports_a_missing_slice(q27):
     """A slice that never arrives: the waiting merge gives up after its limit and says so in the status
     word (nothing hangs, nothing traps); the output is left alone."""
     nz, rows = 2, 6
     buf = torch.zeros(q27.xbuf_bytes(nz, rows), dtype=torch.uint8, device="cuda")
-    buf[64:68] = torch.tensor([1, 0, 0, 0], dtype=torch.uint8, device="cuda")  # flag of slice 0 set, slice 1 missing
+    words = buf[256:].view(torch.int32)[: 2 * nz * rows * 258 * 2].view(2, nz, rows, 258, 2)  # [parity][slice][row][word]
+    parts = torch.randn((nz, rows, 258), device="cuda")
+    parts[..., 1] = parts[..., 1].abs() + 0.5
+    words[0, 0] = _tagged(parts[0], 1)  # slice 0 of step 1 is there, slice 1 is missing
     o = torch.full((rows, AD), 7.0, device="cuda")
     q27.lse_merge_wait(buf, nz, rows, None, o)
     assert q27.device_status() & 1
     assert bool((o == 7.0).all())
-    # the buffer is out of step now (its CTAs left without the step's bookkeeping): after a reset of the
-    # header a complete step on the same buffer works again
+    # the buffer is out of step now (its CTAs left without the step's bookkeeping) and holds words of the
+    # broken step: after a reset a complete step on the same buffer works again
     q27.xbuf_reset(buf)
-    parts = torch.randn((nz, rows, 258), device="cuda")
-    parts[..., 1] = parts[..., 1].abs() + 0.5
-    data = buf[256:].view(torch.float32)[: nz * rows * 258].view(nz, rows, 258)  # parity 0 of epoch 0
-    data.copy_(parts)
-    buf[64:72] = torch.tensor([1, 0, 0, 0, 1, 0, 0, 0], dtype=torch.uint8, device="cuda")  # both flags = epoch + 1
+    assert int(buf.max().item()) == 0
+    words[0] = _tagged(parts, 1)  # parity 0 of step 1
     q27.lse_merge_wait(buf, nz, rows, None, o)
     want = torch.empty((rows, AD), device="cuda")
     q27.lse_merge(parts.contiguous(), nz, rows * 258, rows, None, want)
