@@ -102,6 +102,7 @@ constexpr int TRACE_STRIDE = 8;
 constexpr int BAR_QK = 1;      // + group: the four QK warps of a group
 constexpr int BAR_READY = 3;   // + 2 * group + buffer: P tile written (QK arrives, PV waits)
 constexpr int BAR_FREE = 7;    // + 2 * group + buffer: P tile consumed (PV arrives, QK waits)
+constexpr int BAR_QKALL = 11;  // all QK warps of the CTA, once, at their end
 
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
   uint32_t v;
@@ -556,10 +557,12 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
         if (g == 0) stsf(sbase + OFF_L + ((grp * 4 + wq) * MAXR + 8 * nt + 2 * tg + e) * 4, v);
         if (wq == 0 && g == 0) stsf(sbase + OFF_M1 + (grp * MAXR + 8 * nt + 2 * tg + e) * 4, m[nt][e]);
       }
-    __syncthreads();  // every tile consumed: the ring is free for the O exchange
+    // Both loaders of this CTA have drawn their last pool tile once both Q K^T groups are here. The last CTA
+    // of the grid to say so puts the counters back to zero for the next launch. This is done now, while the
+    // P V warps are still a tile behind: the fence and the atomic take more than a microsecond, and between
+    // the CTA's two barriers below the P V warps would wait for them.
+    if (NG == 2) bar_sync(BAR_QKALL, 256);
     if (has_pool && tid == 0) {
-      // Both loaders of this CTA have drawn their last pool tile. The last CTA of the grid to say so
-      // puts the counters back to zero for the next launch.
       __threadfence();
       const int total = gridDim.x * gridDim.y;
       if (atomicAdd(p.sched + SCHED_DONE, 1) == total - 1) {
@@ -568,7 +571,8 @@ decode_ws_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constan
         __threadfence();
       }
     }
-    __syncthreads();
+    __syncthreads();  // every tile consumed: the ring is free for the O exchange
+    if (NG == 2) __syncthreads();  // (the P V warps' barrier between the two halves of their exchange)
     return;
   }
 
