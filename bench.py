@@ -619,10 +619,9 @@ def strong_scaling(q, dist, rank, world, n, steps, warmup):
             return out
         o2 = torch.empty((T, nq, AD), device="cuda")
 
-        def step_p2p(i):
+        def step_p2p(i):  # split-K kernel, then one kernel that pushes this rank's slice and merges all of them
             kc, vc = caches[i % NBUF]
-            q.attn_decode_partial_push(qn, kc, vc, pos, T, SCALE, nq, nk, n_ctx, lo, hi - lo, peers, sh.z)
-            q.lse_merge_wait(own, sh.nz, T * nq, qg, o2)
+            q.attn_decode_exchange(qn, qg, kc, vc, o2, pos, T, SCALE, nq, nk, n_ctx, lo, hi - lo, peers, sh.z)
         step(0)
         step_p2p(0)
         torch.cuda.synchronize()
@@ -636,8 +635,8 @@ def strong_scaling(q, dist, rank, world, n, steps, warmup):
         out["us_per_step"] = ms2 * 1e3
         out["value"] = kv_bytes(NKVH, n) / (ms2 * 1e-3) / 1e9
         out["what"] = out["what"].replace("NCCL all-gather of partials + LSE merge",
-                                          "partials stored into the peers' exchange buffers over NVLink by the merge kernel "
-                                          "+ waiting LSE merge (nccl_us_per_step: the same with an NCCL all-gather)")
+                                          "the merge kernel stores its slice into the peers' exchange buffers over NVLink, waits for "
+                                          "theirs and writes the output (nccl_us_per_step: the same with an NCCL all-gather)")
         out["p2p_equals_nccl_bitwise"] = same
     return out
 

@@ -242,6 +242,14 @@ int q27b_attn_decode_partial_push(const float* qn, const void* kcache, const voi
                                   float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos, int n_local,
                                   void* const* peer_xbuf, int my_z, int nz, void* stream);
 int q27b_lse_merge_wait(void* xbuf, int nz, int64_t rows, const float* qg, float* o, void* stream);
+/* The two calls above as one: after the split-K kernel a single kernel merges this rank's slice, stores it
+ * into the peers' buffers and, having pushed, waits (bounded) for the peers' slices in its own buffer and
+ * writes the gated output - one launch less per step. Every rank of the group must run the same call in the
+ * same step (each pushes before it waits, so the waits cannot wait for one another). Falls back to the pair
+ * when the slice's shape does not take the many-partials form of the merge (more than two KV heads per GPU). */
+int q27b_attn_decode_exchange(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
+                              const int* pos0, int T, float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos,
+                              int n_local, void* const* peer_xbuf, int my_z, int nz, void* stream);
 
 /* How the path is shared out over the GPUs of one box, as host arithmetic (no GPU needed), for hosts that do
  * not go through the Python helpers (qwen27-engine_b200/shard.py gives the same answers). The reference splits

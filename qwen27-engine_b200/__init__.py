@@ -37,7 +37,7 @@ SYMBOLS = [
     "q27b_attn_workspace_destroy", "q27b_debug_mma_peak", "q27b_xbuf_reset", "q27b_plan_single_sequence", "q27b_kv_slice", "q27b_plan_prefill",
     "q27b_attn_prep_paged", "q27b_pager_create", "q27b_pager_destroy", "q27b_pager_open", "q27b_pager_extend",
     "q27b_pager_cut", "q27b_pager_close", "q27b_pager_fork", "q27b_pager_free_pages", "q27b_pager_len",
-    "q27b_pager_tables", "q27b_kv_page_copy", "q27b_pager_unshare",
+    "q27b_pager_tables", "q27b_kv_page_copy", "q27b_pager_unshare", "q27b_attn_decode_exchange",
 ]
 
 
@@ -253,6 +253,16 @@ def set_prefill_kernel(which):
 def debug_split_event(event):
     """event: a recorded-at-least-once torch.cuda.Event (timing enabled) or None."""
     _check(_lib.q27b_debug_split_event(ctypes.c_void_p(event.cuda_event if event is not None else 0)))
+
+
+def attn_decode_exchange(qn, qg, kcache, vcache, o, pos0, T, kq_scale, nqh, nkvh, n_ctx, base_pos, n_local, peer_ptrs, my_z,
+                         q8=True):
+    """attn_decode_partial_push + lse_merge_wait as one call (one kernel after the split-K kernel where the shape allows)."""
+    arr = (ctypes.c_void_p * len(peer_ptrs))(*[ctypes.c_void_p(int(x)) for x in peer_ptrs])
+    _check(_lib.q27b_attn_decode_exchange(_ptr(qn, torch.float32), _ptr(qg, torch.float32, True), _ptr(kcache), _ptr(vcache),
+                                          _ptr(o, torch.float32), _ptr(pos0, torch.int32), int(T), _f(kq_scale), int(nqh),
+                                          int(nkvh), int(n_ctx), int(bool(q8)), int(base_pos), int(n_local), arr, int(my_z),
+                                          len(peer_ptrs), _stream()))
 
 
 def attn_decode_ref(qn, qg, kcache, vcache, o, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8=True):

@@ -243,13 +243,56 @@ __global__ void __launch_bounds__(1024) merge_wide_kernel(const MergeParams p) {
     }
 
   if (p.push_n > 0) {  // merged, not normalised, into slot push_z of every rank's exchange buffer
-    for (int k = 0; lead && k < p.push_n; k++) {
+    if (!lead) return;
+    const bool fused = p.o != nullptr;  // ... and the final merge of all slices right here, without a second kernel
+    for (int k = 0; k < p.push_n; k++) {
+      if (fused && k == p.push_z) continue;  // this rank's own slice stays in registers
       uint64_t* po = xbuf_row(p.push_buf[k], epoch & 1, p.push_n, p.push_z, p.rows, row);
       ll_store(po + 2 + d, A, epoch + 1);
-      if (d == 0) {
+      if (dl == 0) {
         ll_store(po, M, epoch + 1);
         ll_store(po + 1, L, epoch + 1);
       }
+    }
+    if (!fused) return;
+    // Every rank has pushed before it waits, so the waits below cannot wait for one another. Same arithmetic,
+    // in slice order, as the waiting merge kernel.
+    bool ok = true;
+    float mz[8], lz[8], az[8];
+#pragma unroll
+    for (int z = 0; z < 8; z++)
+      if (z < p.push_n) {
+        if (z == p.push_z) {
+          mz[z] = M; lz[z] = L; az[z] = A;
+        } else {
+          const uint64_t* pz = xbuf_row(p.xbuf, epoch & 1, p.push_n, z, p.rows, row);
+          az[z] = ll_load(pz + 2 + d, epoch + 1, ok);
+          mz[z] = ll_load(pz, epoch + 1, ok);
+          lz[z] = ll_load(pz + 1, epoch + 1, ok);
+        }
+      }
+    if (!ok) {  // a slice never arrived: the status word says so, nothing is written
+      if (p.status) atomicOr(p.status, ST_WAIT_EXPIRED);
+      return;
+    }
+    float MM = M_INIT;
+#pragma unroll
+    for (int z = 0; z < 8; z++)
+      if (z < p.push_n) MM = fmaxf(MM, mz[z]);
+    float LL = 0.f, AA = 0.f;
+#pragma unroll
+    for (int z = 0; z < 8; z++)
+      if (z < p.push_n) {
+        const float f = expf(mz[z] - MM);
+        LL += lz[z] * f;
+        AA += az[z] * f;
+      }
+    float y = AA / LL;
+    if (rm.gate) y *= 1.0f / (1.0f + expf(-gate));
+    p.o[(size_t)row * AD + d] = y;
+    if (tid == 0 && atomicAdd(p.xbuf + 2, 1) == (int)p.rows * WIDE_SLICES - 1) {  // the last CTA advances the step
+      p.xbuf[2] = 0;
+      *(volatile int*)p.xbuf = epoch + 1;
     }
     return;
   }
@@ -348,6 +391,7 @@ int launch_merge(const MergeParams& p, bool decode_layout, cudaStream_t s) {
   // as many slices as keep the CTAs (1024 threads) within one wave of a B200's 148 SMs (with the 96 rows of a
   // 4-head call two slices were measured 3 us slower than one CTA per row, four 6 us)
   const int slices = !(wide && sliced) ? 1 : (p.rows * 4 <= 160 ? 4 : (p.rows * 2 <= 160 ? 2 : 1));
+  if (p.push_n > 0 && p.o && slices <= 1) return fail(Q27B_UNSUPPORTED, "fused exchange needs the sliced merge");
   if (slices > 1) {
     const dim3 wgrid((unsigned)p.rows, slices);
     if (decode_layout && slices == 4) Q27B_CK(launch_pdl(merge_wide_kernel<true, 4>, wgrid, dim3(1024), 0, s, p));

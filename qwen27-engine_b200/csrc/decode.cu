@@ -796,6 +796,43 @@ int q27b_attn_decode_partial_push(const float* qn, const void* kcache, const voi
   return launch_merge(mp, true, (cudaStream_t)stream);
 }
 
+int q27b_attn_decode_exchange(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
+                              const int* pos0, int T, float kq_scale, int nqh, int nkvh, int n_ctx, int q8, int base_pos,
+                              int n_local, void* const* peer_xbuf, int my_z, int nz, void* stream) {
+  if (!o) return fail(Q27B_BAD_SHAPE, "attn_decode_exchange: null pointer");
+  if (T < 1 || T > Q27B_MAX_T || nkvh < 1 || nqh != nkvh * GQA || n_ctx < 1 || base_pos < 0 || n_local < 0 ||
+      n_local > n_ctx || nz < 1 || nz > 8 || my_z < 0 || my_z >= nz)
+    return fail(Q27B_BAD_SHAPE, "attn_decode_exchange: bad shape");
+  if (!qn || !kcache || !vcache || !pos0 || !peer_xbuf) return fail(Q27B_BAD_SHAPE, "attn_decode_exchange: null pointer");
+  for (int k = 0; k < nz; k++)
+    if (!peer_xbuf[k]) return fail(Q27B_BAD_SHAPE, "attn_decode_exchange: null pointer");
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  // One kernel after the split-K kernel pushes and merges when a row has many partials and few rows (the shape
+  // of a KV-length slice: one or two KV heads on a whole GPU); otherwise the pair of calls does the same.
+  const int64_t rows = (int64_t)T * nqh;
+  const int nch = std::max(1, ctx->n_sm / nkvh);
+  const char* e = getenv("Q27B_MERGE_SLICED");
+  const bool fused = nch > 64 && rows * 2 <= 160 && !(e && e[0] == '0');
+  if (!fused) {
+    if (int rc = q27b_attn_decode_partial_push(qn, kcache, vcache, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8, base_pos, n_local,
+                                               peer_xbuf, my_z, nz, stream))
+      return rc;
+    return q27b_lse_merge_wait(peer_xbuf[my_z], nz, rows, qg, o, stream);
+  }
+  for (int k = 0; k < nz; k++)
+    if (int rc = check_peer_buffer(peer_xbuf[k], "attn_decode_exchange")) return rc;
+  int nch_out;
+  if (int rc = decode_split(ctx, qn, kcache, vcache, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8, base_pos, n_local, &nch_out,
+                            (cudaStream_t)stream))
+    return rc;
+  MergeParams mp = {};
+  mp.part = ctx->dec.p; mp.nparts = nch_out; mp.rows = rows; mp.T = T; mp.nqh = nqh; mp.qg = qg; mp.o = o;
+  for (int k = 0; k < nz; k++) mp.push_buf[k] = peer_xbuf[k];
+  mp.push_n = nz; mp.push_z = my_z; mp.xbuf = (int*)peer_xbuf[my_z]; mp.status = ctx->status;
+  return launch_merge(mp, true, (cudaStream_t)stream);
+}
+
 int q27b_attn_decode_noalloc(const float* qn, const float* qg, const void* kcache, const void* vcache, float* o,
                              int8_t* xq, float* xd, const int* pos0, int T, float kq_scale, int nqh, int nkvh, int n_ctx,
                              int q8, void* stream) {

@@ -223,6 +223,55 @@ def test_kv_length_slices_exchanged_over_peer_memory(q27, orc, n, cuts):
     assert q27.device_status() == 0
 
 
+@pytest.mark.parametrize("n,cuts", [(5000, [0, 2560, 5000]), (3000, [0, 1024, 2048, 3000])])
+def test_fused_exchange_equals_the_pair_of_calls(q27, orc, n, cuts):
+    """q27b_attn_decode_exchange (one kernel pushes this rank's slice, waits for the others and writes the
+    output) against the gathered merge. On one GPU the other ranks' slices are pushed first, with the push-only
+    call, so that the rank under test finds them and never waits for a later launch; fresh buffers per rank
+    under test (the other ranks' step counters do not advance here)."""
+    from qwen27_engine_b200 import synth
+    T, nkvh = 4, 1
+    nqh = nkvh * GQA
+    nz = len(cuts) - 1
+    rows = T * nqh
+    qn, qg, kf, vf = synth.decode_inputs(T, nqh, nkvh, n)
+    slices, parts = [], []
+    for z in range(nz):
+        lo, hi = cuts[z], cuts[z + 1]
+        n_ctx = hi - lo + 3
+        kc_ref, vc_ref = orc.fill_cache(kf[:, lo:hi], vf[:, lo:hi], n_ctx)
+        kc, vc = poisoned_cache(q27, kc_ref, nkvh, n_ctx, hi - lo), poisoned_cache(q27, vc_ref, nkvh, n_ctx, hi - lo)
+        slices.append((kc, vc, n_ctx, lo, hi))
+        part = torch.empty((T, nqh, 258), device="cuda")
+        q27.attn_decode_partial(dev(qn), kc, vc, part, pos_tensor(n - T), T, SCALE, nqh, nkvh, n_ctx, lo, hi - lo)
+        parts.append(part)
+    gathered = torch.empty((T, nqh, AD), device="cuda")
+    q27.lse_merge(torch.stack(parts).contiguous(), nz, rows * 258, rows, dev(qg), gathered)
+    for me in range(nz):
+        bufs = [torch.zeros(q27.xbuf_bytes(nz, rows), dtype=torch.uint8, device="cuda") for _ in range(nz)]
+        ptrs = [b.data_ptr() for b in bufs]
+        for z, (kc, vc, n_ctx, lo, hi) in enumerate(slices):
+            if z != me:
+                q27.attn_decode_partial_push(dev(qn), kc, vc, pos_tensor(n - T), T, SCALE, nqh, nkvh, n_ctx, lo, hi - lo, ptrs, z)
+        torch.cuda.synchronize()
+        kc, vc, n_ctx, lo, hi = slices[me]
+        o = torch.full((T, nqh, AD), float("nan"), device="cuda")
+        q27.attn_decode_exchange(dev(qn), dev(qg), kc, vc, o, pos_tensor(n - T), T, SCALE, nqh, nkvh, n_ctx, lo, hi - lo, ptrs, me)
+        torch.cuda.synchronize()
+        assert q27.device_status() == 0
+        assert torch.equal(o, gathered), "rank %d" % me
+        assert int(bufs[me][:4].view(torch.int32).item()) == 1  # its step counter advanced
+        # and what it pushed is what the push-only call pushes
+        other = (me + 1) % nz
+        ref = [torch.zeros(q27.xbuf_bytes(nz, rows), dtype=torch.uint8, device="cuda") for _ in range(nz)]
+        q27.attn_decode_partial_push(dev(qn), kc, vc, pos_tensor(n - T), T, SCALE, nqh, nkvh, n_ctx, lo, hi - lo,
+                                     [b.data_ptr() for b in ref], me)
+        torch.cuda.synchronize()
+        per = rows * 258 * 8
+        a0 = 256 + me * per
+        assert torch.equal(bufs[other][a0:a0 + per], ref[other][a0:a0 + per])
+
+
 def _tagged(parts, tag):
     """float rows -> the exchange buffer's words: {value, step tag} as int32 pairs."""
     w = torch.empty(parts.shape + (2,), dtype=torch.int32, device=parts.device)
