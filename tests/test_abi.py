@@ -104,7 +104,7 @@ def test_sum_norm_entry_points_check_their_arguments(q27):
     lib = ctypes.CDLL(q27.LIB_PATH)
     lib.q27b_last_error.restype = ctypes.c_char_p
     lib.q27b_sum_xbuf_bytes.restype = ctypes.c_uint64
-    assert lib.q27b_sum_xbuf_bytes(8, 4, 5120) == 256 + 2 * 8 * 4 * 5120 * 4
+    assert lib.q27b_sum_xbuf_bytes(8, 4, 5120) == 256 + 2 * 8 * 4 * 5120 * 8  # 8-byte words {value, step tag}
     assert lib.q27b_sum_xbuf_bytes(0, 4, 5120) == 0
     null, one = ctypes.c_void_p(0), ctypes.c_void_p(16)
     f = ctypes.c_float(1e-6)
