@@ -672,8 +672,7 @@ def sum_norm_scaling(q, dist, rank, world, steps, warmup):
     xq2, xd2 = torch.zeros_like(xq), torch.zeros_like(xd)
 
     def step_p2p(i):
-        q.sum_push(partial, n, rows, rank, peers)
-        q.sum_norm_q8_wait(x, own, world, n, rows, w, eps, None, xq2, xd2)
+        q.sum_exchange_norm_q8(x, partial, n, rows, rank, peers, w, eps, None, xq2, xd2)  # push + waiting norm, one kernel
 
     x.copy_(x0)
     step_p2p(0)

@@ -289,6 +289,11 @@ int q27b_sum_norm_q8(float* x, const float* partial, int n, int rows, const floa
 int q27b_sum_push(const float* partial, int n, int rows, int rank, int world, void* const* xbufs, void* stream);
 int q27b_sum_norm_q8_wait(float* x, void* xbuf, int world, int n, int rows, const float* w, float eps, float* h, int8_t* xq,
                           float* xd, void* stream);
+/* q27b_sum_push + q27b_sum_norm_q8_wait as one kernel: every CTA stores its row of this rank's partial into the
+ * peers' buffers, then waits for theirs and normalises (every rank of the group runs the same call in the same
+ * step; each pushes before it waits). */
+int q27b_sum_exchange_norm_q8(float* x, const float* partial, int n, int rows, int rank, int world, void* const* xbufs,
+                              const float* w, float eps, float* h, int8_t* xq, float* xd, void* stream);
 
 /* Which split-K kernel q27b_attn_decode* uses for q8_0 caches: 0 = default (the warp-specialised
  * kernel), 1 = the single-role warp-MMA kernel (every warp runs both contractions), 2 = the tcgen05

@@ -37,7 +37,7 @@ SYMBOLS = [
     "q27b_attn_workspace_destroy", "q27b_debug_mma_peak", "q27b_xbuf_reset", "q27b_plan_single_sequence", "q27b_kv_slice", "q27b_plan_prefill",
     "q27b_attn_prep_paged", "q27b_pager_create", "q27b_pager_destroy", "q27b_pager_open", "q27b_pager_extend",
     "q27b_pager_cut", "q27b_pager_close", "q27b_pager_fork", "q27b_pager_free_pages", "q27b_pager_len",
-    "q27b_pager_tables", "q27b_kv_page_copy", "q27b_pager_unshare", "q27b_attn_decode_exchange",
+    "q27b_pager_tables", "q27b_kv_page_copy", "q27b_pager_unshare", "q27b_attn_decode_exchange", "q27b_sum_exchange_norm_q8",
 ]
 
 
@@ -229,6 +229,16 @@ def sum_norm_q8_wait(x, xbuf, world, n, rows, w, eps, h=None, xq=None, xd=None):
                                       _f(eps), _ptr(h, torch.float32) if h is not None else None,
                                       _ptr(xq, torch.int8) if xq is not None else None,
                                       _ptr(xd, torch.float32) if xd is not None else None, _stream()))
+
+
+def sum_exchange_norm_q8(x, partial, n, rows, rank, xbufs, w, eps, h=None, xq=None, xd=None):
+    """sum_push + sum_norm_q8_wait as one kernel (xbufs: the exchange buffers of all ranks as mapped here)."""
+    arr = (ctypes.c_void_p * len(xbufs))(*[ctypes.c_void_p(int(b) if isinstance(b, int) else b.data_ptr()) for b in xbufs])
+    _check(_lib.q27b_sum_exchange_norm_q8(_ptr(x, torch.float32), _ptr(partial, torch.float32), int(n), int(rows), int(rank),
+                                          len(xbufs), arr, _ptr(w, torch.float32), _f(eps),
+                                          _ptr(h, torch.float32) if h is not None else None,
+                                          _ptr(xq, torch.int8) if xq is not None else None,
+                                          _ptr(xd, torch.float32) if xd is not None else None, _stream()))
 
 
 def set_decode_kernel(which):

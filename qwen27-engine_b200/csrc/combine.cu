@@ -361,7 +361,6 @@ __global__ void __launch_bounds__(AD) merge_wait_kernel(const MergeParams p) {
   if (p.qg) y *= 1.0f / (1.0f + expf(-gate));
   p.o[(size_t)row * AD + d] = y;
   if (d == 0) {  // the last CTA of the step advances the epoch (nobody reads it again before the next launch)
-    __threadfence();
     if (atomicAdd(p.xbuf + 2, 1) == (int)p.rows - 1) {
       p.xbuf[2] = 0;
       *(volatile int*)p.xbuf = epoch + 1;

@@ -35,6 +35,10 @@ struct SumNormParams {
   int* status;
   float eps;
   int rows, n, world;
+  // wait mode, fused with the push: this rank's partial rows and the buffers of all ranks as mapped here
+  const float* push_src;  // [rows][n] or null
+  void* peer[8];
+  int rank;
 };
 
 __device__ __forceinline__ float block_sum_1024(float t, float* sred) {
@@ -68,12 +72,29 @@ __global__ void __launch_bounds__(SN_THREADS) sum_norm_kernel(const SumNormParam
   float add[SN_MAX_NPT];
   if (WAIT) {
     bool ok = true;
+    float own[SN_MAX_NPT];
+    if (p.push_src) {  // fused: this rank's row goes to the peers first (every rank pushes before it waits)
+#pragma unroll
+      for (int k = 0; k < SN_MAX_NPT; k++)
+        if (k < npt) {
+          const int i = tid + k * SN_THREADS;
+          own[k] = p.push_src[(size_t)row * n + i];
+          for (int dst = 0; dst < p.world; dst++)
+            if (dst != p.rank)
+              ll_store((uint64_t*)((uint8_t*)p.peer[dst] + XBUF_HEADER_BYTES) +
+                           (((size_t)(epoch & 1) * p.world + p.rank) * p.rows + row) * n + i,
+                       own[k], epoch + 1);
+        }
+    }
 #pragma unroll
     for (int k = 0; k < SN_MAX_NPT; k++)
       if (k < npt) {
         const int i = tid + k * SN_THREADS;
-        float sum = ll_load(data + (size_t)row * n + i, epoch + 1, ok);
-        for (int z = 1; z < p.world; z++) sum += ll_load(data + ((size_t)z * p.rows + row) * n + i, epoch + 1, ok);  // rank order on every rank
+        float sum = 0.f;
+        for (int z = 0; z < p.world; z++) {  // rank order on every rank
+          const float t = (p.push_src && z == p.rank) ? own[k] : ll_load(data + ((size_t)z * p.rows + row) * n + i, epoch + 1, ok);
+          sum = z == 0 ? t : sum + t;
+        }
         add[k] = sum;
       }
     if (__syncthreads_or(!ok)) {  // a rank's rows never arrived: the status word says so, nothing is written
@@ -94,7 +115,6 @@ __global__ void __launch_bounds__(SN_THREADS) sum_norm_kernel(const SumNormParam
   }
   if (WAIT && tid == 0) {
     // the last CTA of the step advances the epoch (nobody reads it again before the next launch)
-    __threadfence();
     if (atomicAdd(p.xbuf + 2, 1) == p.rows - 1) {
       p.xbuf[2] = 0;
       *(volatile int*)p.xbuf = epoch + 1;
@@ -213,6 +233,26 @@ int q27b_sum_norm_q8_wait(float* x, void* xbuf, int world, int n, int rows, cons
   SumNormParams p = {};
   p.x = x; p.w = w; p.h = h; p.xq = xq; p.xd = xd; p.eps = eps; p.rows = rows; p.n = n; p.world = world;
   p.xbuf = (int*)xbuf; p.status = ctx->status;
+  Q27B_CK(launch_pdl(sum_norm_kernel<true>, dim3(rows), dim3(SN_THREADS), 0, (cudaStream_t)stream, p));
+  return Q27B_OK;
+}
+
+int q27b_sum_exchange_norm_q8(float* x, const float* partial, int n, int rows, int rank, int world, void* const* xbufs,
+                              const float* w, float eps, float* h, int8_t* xq, float* xd, void* stream) {
+  if (!x || !partial || !xbufs || !w || (xq && !xd)) return fail(Q27B_BAD_SHAPE, "sum_exchange_norm_q8: null pointer");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(Q27B_BAD_SHAPE, "sum_exchange_norm_q8: bad rank/world");
+  if (int rc = check_shape(rows, n, "sum_exchange_norm_q8: rows >= 1, n a multiple of 32 up to 16384")) return rc;
+  DeviceCtx* ctx;
+  if (int rc = device_ctx(&ctx)) return rc;
+  SumNormParams p = {};
+  p.x = x; p.w = w; p.h = h; p.xq = xq; p.xd = xd; p.eps = eps; p.rows = rows; p.n = n; p.world = world;
+  p.push_src = partial; p.rank = rank; p.status = ctx->status;
+  for (int k = 0; k < world; k++) {
+    if (!xbufs[k]) return fail(Q27B_BAD_SHAPE, "sum_exchange_norm_q8: null exchange buffer");
+    if (int rc = check_peer_buffer(xbufs[k], "sum_exchange_norm_q8")) return rc;
+    p.peer[k] = xbufs[k];
+  }
+  p.xbuf = (int*)xbufs[rank];
   Q27B_CK(launch_pdl(sum_norm_kernel<true>, dim3(rows), dim3(SN_THREADS), 0, (cudaStream_t)stream, p));
   return Q27B_OK;
 }

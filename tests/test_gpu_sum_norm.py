@@ -75,6 +75,41 @@ def test_sum_norm_q8_exchanged_over_peer_memory(q27, orc, world):
             q27.xbuf_free(b)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_exchange_equals_push_and_wait(q27, orc, world):
+    """q27b_sum_exchange_norm_q8 (one kernel pushes this rank's rows, waits for the others and normalises) against
+    the pair of calls. On one GPU the other ranks push first (push-only call), so that the rank under test never
+    waits for a later launch; fresh buffers per rank under test."""
+    rows, n = 4, 5120
+    x, w, parts = inputs(rows, n, world, 1)
+
+    def run(me, fused):
+        bufs = [q27.xbuf_alloc_bytes(q27.sum_xbuf_bytes(world, rows, n)) for _ in range(world)]
+        try:
+            for r in range(world):
+                if r != me or not fused:
+                    q27.sum_push(dev(parts[r]), n, rows, r, bufs)
+            dx = dev(x)
+            h = torch.full((rows, n), float("nan"), device="cuda")
+            xq = torch.zeros((rows, n), dtype=torch.int8, device="cuda")
+            xd = torch.zeros((rows * n // 32,), dtype=torch.float32, device="cuda")
+            if fused:
+                q27.sum_exchange_norm_q8(dx, dev(parts[me]), n, rows, me, bufs, dev(w), EPS, h, xq, xd)
+            else:
+                q27.sum_norm_q8_wait(dx, bufs[me], world, n, rows, dev(w), EPS, h, xq, xd)
+            torch.cuda.synchronize()
+            assert q27.device_status() == 0
+            return dx, h, xq, xd
+        finally:
+            for b in bufs:
+                q27.xbuf_free(b)
+
+    for me in range(world):
+        a, b = run(me, True), run(me, False)
+        for u, v in zip(a, b):
+            assert torch.equal(u, v), "rank %d" % me
+
+
 def test_sum_norm_wait_reports_a_missing_rank(q27):
     """Rank 1 never pushes: rank 0's wait runs out (about a second), the status word says so, the
     context stays usable."""
