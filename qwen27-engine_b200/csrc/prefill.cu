@@ -306,7 +306,12 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
 #pragma unroll
       for (int b = 0; b < 8; b++) {
         const int slot = b & 3;
+#ifdef Q27B_PF_COMMIT_EACH
         mbar_wait(&bar[B_SFULL + slot], (b >> 2) & 1, abort_flag, p.status);
+#else
+        // (blocks are committed in pairs: the barrier of the pair's second slot covers both)
+        mbar_wait(&bar[B_SFULL + (slot | 1)], (b >> 2) & 1, abort_flag, p.status);
+#endif
         tc_fence_after();
         // The accumulators come in two halves of 16 columns: 16 registers fewer are live at a time
         // than with one 32-column load, and this kernel runs at its register limit.
@@ -598,7 +603,14 @@ prefill_i8_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_consta
           tc_fence_after();
           tc_mma_i8(tmem + TM_S + slot * PT, desc_kblock(sbase + OFF_Q, QT, b),
                     desc_kblock(sbase + OFF_K + pb * KST_PAD, PT, b), IDESC_QK, 0u);
+#ifdef Q27B_PF_COMMIT_EACH
           tc_commit(&bar[B_SFULL + slot]);
+#else
+          // One commit per two blocks: an MMA followed by its own commit costs the issuing thread the better
+          // part of a thousand cycles (measured on the decode kernel with P V on tcgen05), eight of them per
+          // tile were most of a tile's time here.
+          if (b & 1) tc_commit(&bar[B_SFULL + slot]);
+#endif
         }
         tc_commit(&bar[B_KEMPTY + pb]);
         if (j >= 1) issue_pv(j - 1);
