@@ -73,18 +73,24 @@ __global__ void __launch_bounds__(SN_THREADS) sum_norm_kernel(const SumNormParam
   if (WAIT) {
     bool ok = true;
     float own[SN_MAX_NPT];
-    if (p.push_src) {  // fused: this rank's row goes to the peers first (every rank pushes before it waits)
+    if (p.push_src) {
+      // Fused with the push: the grid is (rows, world). CTA (row, dst) with dst != rank stores the row into rank
+      // dst's buffer and is done; CTA (row, rank) keeps the row in registers and goes on to wait for the others
+      // (every rank's pushes are CTAs of their own, and they come first in the grid: the waiting CTAs have the
+      // highest blockIdx.y; the host only takes this form when the whole grid is resident at once, so no
+      // wait can hold up a push).
+      const int dst = (blockIdx.y + p.rank + 1) % p.world;
 #pragma unroll
       for (int k = 0; k < SN_MAX_NPT; k++)
         if (k < npt) {
           const int i = tid + k * SN_THREADS;
           own[k] = p.push_src[(size_t)row * n + i];
-          for (int dst = 0; dst < p.world; dst++)
-            if (dst != p.rank)
-              ll_store((uint64_t*)((uint8_t*)p.peer[dst] + XBUF_HEADER_BYTES) +
-                           (((size_t)(epoch & 1) * p.world + p.rank) * p.rows + row) * n + i,
-                       own[k], epoch + 1);
+          if (dst != p.rank)
+            ll_store((uint64_t*)((uint8_t*)p.peer[dst] + XBUF_HEADER_BYTES) +
+                         (((size_t)(epoch & 1) * p.world + p.rank) * p.rows + row) * n + i,
+                     own[k], epoch + 1);
         }
+      if (dst != p.rank) return;
     }
 #pragma unroll
     for (int k = 0; k < SN_MAX_NPT; k++)
@@ -253,7 +259,11 @@ int q27b_sum_exchange_norm_q8(float* x, const float* partial, int n, int rows, i
     p.peer[k] = xbufs[k];
   }
   p.xbuf = (int*)xbufs[rank];
-  Q27B_CK(launch_pdl(sum_norm_kernel<true>, dim3(rows), dim3(SN_THREADS), 0, (cudaStream_t)stream, p));
+  if ((int64_t)rows * world > ctx->n_sm) {  // more CTAs than are resident at once: push, then wait, as two launches
+    if (int rc = q27b_sum_push(partial, n, rows, rank, world, xbufs, stream)) return rc;
+    return q27b_sum_norm_q8_wait(x, xbufs[rank], world, n, rows, w, eps, h, xq, xd, stream);
+  }
+  Q27B_CK(launch_pdl(sum_norm_kernel<true>, dim3(rows, world), dim3(SN_THREADS), 0, (cudaStream_t)stream, p));
   return Q27B_OK;
 }
 
