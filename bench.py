@@ -606,8 +606,8 @@ def strong_scaling(q, dist, rank, world, n, steps, warmup):
         ms_e = time_steps(step, steps, warmup, dist)
         out["eager_us_per_step"] = ms_e * 1e3
     if sh.nz > 1 and os.environ.get("Q27B_P2P_MERGE", "1") != "0":
-        # the same exchange over peer memory: the merge kernel of each slice stores its rows into every
-        # rank's exchange buffer and raises a flag; the final merge waits for the flags of its own buffer
+        # the same exchange over peer memory: the merge kernel of each slice stores its rows (tagged words) into
+        # the other ranks' exchange buffers, waits for theirs in its own buffer and writes the output
         ok = torch.ones(1, device="cuda")
         try:  # raises on every rank of the head group or on none
             own, peers = shard.make_exchange(q, sh, group, T * nq)
@@ -644,7 +644,7 @@ def strong_scaling(q, dist, rank, world, n, steps, warmup):
 def sum_norm_scaling(q, dist, rank, world, steps, warmup):
     """The step after the attention output projection: x [4][5120] += the sum of the ranks' partial rows,
     RMSNorm, q8_1 (the reference's sum_norm_q8 with its two-card exchange). Peer-memory form (each rank
-    stores its rows into every rank's exchange buffer, the norm kernel waits for the flags) against an
+    stores its rows as tagged words into every rank's exchange buffer and waits for the others') against an
     NCCL all-reduce followed by the single-GPU kernel."""
     from qwen27_engine_b200 import shard
     rows, n, eps = T, 5120, 1e-6

@@ -53,8 +53,8 @@ __device__ __forceinline__ float block_sum_1024(float t, float* sred) {
   return s;
 }
 
-// One CTA per row. WAIT: the partials of all ranks are taken from the exchange buffer once their
-// flags of this step have arrived.
+// One CTA per row. WAIT: the partials of all ranks are taken from the exchange buffer, word by word, once
+// they carry the tag of this step (with push_src: after this rank's own rows have gone out, see below).
 template <bool WAIT>
 __global__ void __launch_bounds__(SN_THREADS) sum_norm_kernel(const SumNormParams p) {
   pdl_wait();
