@@ -211,6 +211,11 @@ def time_graph_steps(fn, steps, warmup, dist=None, calls=20):
         dist.barrier()
         torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # One untimed replay goes first and is not waited for: while the GPU runs it the host queues the first event
+    # and the timed replays, so the events bracket exactly K steps of device time and not the host's launch
+    # latency of the first timed replay (with K = 20 that is the only one: 0.6 us per step on one GPU, 3 to 4 us
+    # with several ranks launching from one host).
+    g.replay()
     e0.record()
     for _ in range(steps // calls):
         g.replay()
@@ -373,7 +378,8 @@ def main():
                    "per_gpu": "one sequence per GPU (batched decode sharded by sequence, no exchange)",
                    "bytes_per_step_per_gpu": kv_bytes(NKVH, n),
                    "l2": "%.0f MB of KV per step, %d caches in rotation: inputs larger than L2" % (kv_bytes(NKVH, n) / 1e6, NBUF),
-                   "timing": "steps captured in CUDA graphs of 20 calls and replayed (tools/bench_attn.cu:131-147); "
+                   "timing": "steps captured in CUDA graphs of 20 calls and replayed (tools/bench_attn.cu:131-147), after 0.4 s of "
+                             "idle and one untimed replay that is still running when the first event is queued; "
                              "eager_* = the same calls issued one by one"},
     }
 
