@@ -119,6 +119,38 @@ def test_sum_norm_entry_points_check_their_arguments(q27):
     assert lib.q27b_xbuf_alloc_bytes(ctypes.c_uint64(8), ctypes.byref(ctypes.c_void_p(0))) == q27.BAD_SHAPE
 
 
+def test_paged_and_exchange_entry_points_check_their_arguments(q27):
+    """The entry points added around the paged cache and the peer-memory exchanges refuse bad arguments
+    before any CUDA call."""
+    lib = ctypes.CDLL(q27.LIB_PATH)
+    lib.q27b_last_error.restype = ctypes.c_char_p
+    null, one = ctypes.c_void_p(0), ctypes.c_void_p(16)
+    f = ctypes.c_float(1.0)
+    # q27b_attn_prep_paged: null pool; norm weights without the rest; bad shape
+    args = lambda **kw: [kw.get("qg", null), one, one, kw.get("q_norm", null), null, null, kw.get("kpool", one), one, one, one,
+                         kw.get("B", 2), 4, f, f, 24, 4, 16, 8, null, null, null]
+    assert lib.q27b_attn_prep_paged(*args(kpool=null)) == q27.BAD_SHAPE
+    assert lib.q27b_attn_prep_paged(*args(q_norm=one)) == q27.BAD_SHAPE
+    assert lib.q27b_attn_prep_paged(*args(B=0)) == q27.BAD_SHAPE
+    assert b"attn_prep_paged" in lib.q27b_last_error()
+    # q27b_attn_decode_exchange: no output, bad slice index, null buffer list
+    ex = lambda o=one, z=0, nz=2, bufs=one: [one, one, one, one, o, one, 4, f, 6, 1, 1000, 1, 0, 500, bufs, z, nz, null]
+    assert lib.q27b_attn_decode_exchange(*ex(o=null)) == q27.BAD_SHAPE
+    assert lib.q27b_attn_decode_exchange(*ex(z=2)) == q27.BAD_SHAPE
+    assert lib.q27b_attn_decode_exchange(*ex(nz=9)) == q27.BAD_SHAPE
+    assert lib.q27b_attn_decode_exchange(*ex(bufs=null)) == q27.BAD_SHAPE
+    # q27b_sum_exchange_norm_q8
+    assert lib.q27b_sum_exchange_norm_q8(one, null, 5120, 4, 0, 2, one, one, f, null, null, null, null) == q27.BAD_SHAPE
+    assert lib.q27b_sum_exchange_norm_q8(one, one, 5120, 4, 2, 2, one, one, f, null, null, null, null) == q27.BAD_SHAPE
+    assert lib.q27b_sum_exchange_norm_q8(one, one, 5100, 4, 0, 2, one, one, f, null, null, null, null) == q27.BAD_SHAPE
+    # q27b_xbuf_reset: less than the header; q27b_kv_page_copy: a page onto itself
+    assert lib.q27b_xbuf_reset(one, ctypes.c_uint64(8), null) == q27.BAD_SHAPE
+    assert lib.q27b_kv_page_copy(one, 1, 1, 10, 4, 8, null) == q27.BAD_SHAPE
+    assert lib.q27b_kv_page_copy(one, 0, 9, 10, 4, 8, null) == q27.BAD_SHAPE
+    lib.q27b_xbuf_bytes.restype = ctypes.c_uint64
+    assert lib.q27b_xbuf_bytes(2, ctypes.c_int64(24)) == 256 + 2 * 2 * 24 * 258 * 8
+
+
 def test_python_mirror_raises(q27):
     with pytest.raises(RuntimeError):
         q27.kv_append(None, None, None, None, None, 1, 4, 16)
