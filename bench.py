@@ -288,6 +288,7 @@ def measure_mma_peak(q, kind, iters=4000, reps=3):
     torch.cuda.synchronize()
     best = 0.0
     for _ in range(reps):
+        cool_down(0.5)  # a peak is a burst figure: not taken in the power-capped state that earlier timings leave
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         ops = q.debug_mma_peak(kind, iters)
