@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(AD * NGRP) merge_kernel(const MergeParams p) {
 constexpr int WIDE_PRE = 10;
 
 template <bool DECODE_LAYOUT, int WIDE_SLICES>
-__global__ void __launch_bounds__(1024) merge_wide_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(1024, 1) merge_wide_kernel(const MergeParams p) {
   constexpr int WIDE_COLS = AD / WIDE_SLICES, WIDE_GROUPS = 1024 / WIDE_COLS;
   pdl_wait();
   pdl_trigger();
@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(1024) merge_wide_kernel(const MergeParams p) {
 // The final merge of the peer-memory exchange: one CTA per output row merges the wait_n slices that the ranks
 // of the group pushed into this rank's own buffer, waiting (bounded) for each word of the current step; same
 // arithmetic, in the same order, as merge_kernel on the gathered partials. The last CTA advances the step.
-__global__ void __launch_bounds__(AD) merge_wait_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(AD, 1) merge_wait_kernel(const MergeParams p) {
   pdl_wait();
   pdl_trigger();
   const int64_t row = blockIdx.x;

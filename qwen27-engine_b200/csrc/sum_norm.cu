@@ -56,7 +56,7 @@ __device__ __forceinline__ float block_sum_1024(float t, float* sred) {
 // One CTA per row. WAIT: the partials of all ranks are taken from the exchange buffer, word by word, once
 // they carry the tag of this step (with push_src: after this rank's own rows have gone out, see below).
 template <bool WAIT>
-__global__ void __launch_bounds__(SN_THREADS) sum_norm_kernel(const SumNormParams p) {
+__global__ void __launch_bounds__(SN_THREADS, 1) sum_norm_kernel(const SumNormParams p) {
   pdl_wait();
   pdl_trigger();
   __shared__ float sred[32];
