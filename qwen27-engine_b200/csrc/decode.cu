@@ -813,7 +813,10 @@ int q27b_attn_decode_exchange(const float* qn, const float* qg, const void* kcac
   const int64_t rows = (int64_t)T * nqh;
   const int nch = std::max(1, ctx->n_sm / nkvh);
   const char* e = getenv("Q27B_MERGE_SLICED");
-  const bool fused = nch > 64 && rows * 2 <= 160 && !(e && e[0] == '0');
+  // (the CTAs of the fused kernel wait for their peers' CTAs of the same index, so all of them must be resident at
+  // once: no more CTAs than SMs)
+  const int64_t slices = rows * 4 <= 160 ? 4 : 2;
+  const bool fused = nch > 64 && rows * 2 <= 160 && rows * slices <= ctx->n_sm && !(e && e[0] == '0');
   if (!fused) {
     if (int rc = q27b_attn_decode_partial_push(qn, kcache, vcache, pos0, T, kq_scale, nqh, nkvh, n_ctx, q8, base_pos, n_local,
                                                peer_xbuf, my_z, nz, stream))

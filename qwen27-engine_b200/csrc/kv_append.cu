@@ -208,7 +208,7 @@ int q27b_attn_prep_paged(const float* qg, const float* k, const float* v, const 
   const bool norm = q_norm != nullptr;
   if (!k || !v || !kpool || !vpool || !page_table || !seq_len || (norm && (!qg || !k_norm || !qn)))
     return fail(Q27B_BAD_SHAPE, "attn_prep_paged: null pointer");
-  if (B < 1 || T < 1 || nkvh < 1 || n_pages < 1 || max_pages < 1 || (norm && nqh < 1) ||
+  if (B < 1 || T < 1 || nkvh < 1 || n_pages < 1 || max_pages < 1 || max_pages > (1 << 22) || (norm && nqh < 1) ||
       (int64_t)B * T * (nqh + 2 * nkvh) > (int64_t)1 << 30)
     return fail(Q27B_BAD_SHAPE, "attn_prep_paged: bad shape");
   DeviceCtx* ctx;

@@ -13,6 +13,7 @@
 #include "common.cuh"
 #include "host.h"
 
+#include <exception>
 #include <mutex>
 #include <vector>
 
@@ -57,14 +58,21 @@ extern "C" {
 
 int q27b_pager_create(int n_pages, int max_seqs, int max_pages_per_seq, q27b_pager** out) {
   if (!out || n_pages < 1 || max_seqs < 1 || max_pages_per_seq < 1) return fail(Q27B_BAD_SHAPE, "pager_create: bad shape");
-  q27b_pager* pg = new q27b_pager;
-  pg->n_pages = n_pages;
-  pg->max_seqs = max_seqs;
-  pg->max_pages = max_pages_per_seq;
-  pg->refs.assign(n_pages, 0);
-  pg->free_list.resize(n_pages);
-  for (int i = 0; i < n_pages; i++) pg->free_list[i] = n_pages - 1 - i;  // page 0 is handed out first
-  pg->seqs.resize(max_seqs);
+  q27b_pager* pg = nullptr;
+  try {  // (no exception crosses the C boundary)
+    pg = new q27b_pager;
+    pg->n_pages = n_pages;
+    pg->max_seqs = max_seqs;
+    pg->max_pages = max_pages_per_seq;
+    pg->refs.assign(n_pages, 0);
+    pg->free_list.resize(n_pages);
+    for (int i = 0; i < n_pages; i++) pg->free_list[i] = n_pages - 1 - i;  // page 0 is handed out first
+    pg->seqs.resize(max_seqs);
+    for (auto& q : pg->seqs) q.pages.reserve(max_pages_per_seq);  // extend and fork then never allocate
+  } catch (const std::exception&) {
+    delete pg;
+    return fail(Q27B_UNSUPPORTED, "pager_create: out of host memory");
+  }
   *out = pg;
   return Q27B_OK;
 }

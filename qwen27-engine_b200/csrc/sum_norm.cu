@@ -90,7 +90,15 @@ __global__ void __launch_bounds__(SN_THREADS, 1) sum_norm_kernel(const SumNormPa
                          (((size_t)(epoch & 1) * p.world + p.rank) * p.rows + row) * n + i,
                      own[k], epoch + 1);
         }
-      if (dst != p.rank) return;
+      if (dst != p.rank) {
+        // counted like the waiting CTAs, so that the step only advances once every CTA of the grid has read it
+        __syncthreads();
+        if (tid == 0 && atomicAdd(p.xbuf + 2, 1) == p.rows * p.world - 1) {
+          p.xbuf[2] = 0;
+          *(volatile int*)p.xbuf = epoch + 1;
+        }
+        return;
+      }
     }
 #pragma unroll
     for (int k = 0; k < SN_MAX_NPT; k++)
@@ -121,7 +129,7 @@ __global__ void __launch_bounds__(SN_THREADS, 1) sum_norm_kernel(const SumNormPa
   }
   if (WAIT && tid == 0) {
     // the last CTA of the step advances the epoch (nobody reads it again before the next launch)
-    if (atomicAdd(p.xbuf + 2, 1) == p.rows - 1) {
+    if (atomicAdd(p.xbuf + 2, 1) == (p.push_src ? p.rows * p.world : p.rows) - 1) {
       p.xbuf[2] = 0;
       *(volatile int*)p.xbuf = epoch + 1;
     }
