@@ -610,8 +610,8 @@ int launch_decode_t(const CUtensorMap* kv, const CUtensorMap* ks, const CUtensor
 }
 
 // Which split-K kernel serves a q8_0 cache: the warp-specialised kernel of decode_ws.cu unless
-// Q27B_DECODE_KERNEL=mma|tc or q27b_set_decode_kernel(1|2) asks for the single-role warp-MMA kernel of
-// this file or the tcgen05 kernel (decode_tc.cu). Measured on B200 (same call, 20 calls in a CUDA
+// Q27B_DECODE_KERNEL=mma|tc|wt or q27b_set_decode_kernel(1|2|4) asks for the single-role warp-MMA kernel of
+// this file, the tcgen05 kernel (decode_tc.cu) or the warp-specialised kernel with P V on tcgen05 (decode_wt.cu). Measured on B200 (same call, 20 calls in a CUDA
 // graph, 150k positions, T = 4): warp-specialised 69.7 us per call, single-role 75.7 us, tcgen05
 // 73.7-80.8 us depending on the build (eight differently specialised warp roles with a serial hand-off
 // chain: sensitive to code layout). f16 caches always use the kernel of this file.
@@ -622,7 +622,7 @@ std::atomic<bool> g_pool_schedule{[] {
   const char* e = getenv("Q27B_DECODE_POOL");
   return !(e && e[0] == '0');
 }()};
-std::atomic<int> g_kernel_choice{-1};  // -1: not read yet; 0 default (= 3), 1 single-role warp-MMA, 2 tcgen05, 3 warp-specialised
+std::atomic<int> g_kernel_choice{-1};  // -1: not read yet; 0 default (= 3), 1 single-role warp-MMA, 2 tcgen05, 3 warp-specialised, 4 the same with P V on tcgen05
 int kernel_choice() {
   int k = g_kernel_choice.load(std::memory_order_relaxed);
   if (k < 0) {
